@@ -1,0 +1,124 @@
+/* C ABI of libtriattn_sm100a.so — the B200 (sm_100a) kernels behind TriAttention's quantised
+ * attention path.  Plain pointers and sizes only; every pointer is a device pointer unless it says
+ * "host".  All functions return 0 on success or a negative status and leave a message for
+ * tri_last_error().  Work is enqueued on `stream` (a cudaStream_t); nothing synchronises the host.
+ * The caller allocates every buffer, like the reference's callers do
+ * (triattention/kernels/prefill.py:42-85, triattention/kernels/decode.py:62-75).
+ *
+ * "Replaces" lines name the reference interface each entry point stands in for (paths inside the
+ * reference project).  The reference is batch 1 everywhere; these take a batch count, and
+ * unit = sequence * heads + head indexes the leading dimension of every per-head buffer.
+ *
+ * Tile blob layouts (K8, K4X, K4, V8, V4, V16) are documented in triattention_b200/csrc/common.cuh.
+ */
+#ifndef TRIATTENTION_B200_H
+#define TRIATTENTION_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { TRI_OK = 0, TRI_ERR_ARGUMENT = -1, TRI_ERR_CUDA = -2, TRI_ERR_DEVICE = -3 };
+
+/* Message of the last failing call made by this host thread. */
+const char* tri_last_error(void);
+int tri_abi_version(void);
+
+/* Rotate + quantise Q (per token) and K (centred by the channel mean over the prompt, per 16-key
+ * group) into tensor-core operands.
+ * Replaces prepare_qk(q,k,q8,qa,kp,ka,partial,kstat,q4,qa4,k4p,ka4),
+ *   triattention/kernels/cuda/common_host.cuh:1-25.
+ * q  bf16 [B,Hq,T,128], k bf16 [B,Hkv,T,128]: element strides given, feature stride 1, rows 16-byte aligned.
+ * q8 int8 [B*Hq,T,128]; qa f32 [B*Hq,T]; k8 K8 blobs [B*Hkv,tiles,8192 B]; ka f32 [B*Hkv,tiles,4];
+ * partial f32 [B*Hkv,64,3,128] scratch; kstat f32 [B*Hkv,3,128] (mean, -, -).
+ * INT4 outputs, all or none: q4x int8 [B*Hq,T,128] (4-bit codes as int8), qa4, k4x K4X blobs
+ * [B*Hkv,tiles,8192 B], ka4; k4 (optional with the others) packed K4 blobs [B*Hkv,tiles,4096 B]. */
+int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int heads_kv, int tokens,
+                   int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                   int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                   void* q8, float* qa, void* k8, float* ka, float* partial, float* kstat,
+                   void* q4x, float* qa4, void* k4x, void* k4, float* ka4, void* stream);
+
+/* Per-channel affine normalisation of V and packing into FP16 / INT8 / INT4 tile blobs.
+ * Replaces pack_v(v,partial,vstat,v16p,v8p,v4p), triattention/kernels/cuda/common_host.cuh:27-45.
+ * vstat f32 [B*Hkv,3,128] = (mean, scale, 1/scale); (0,1,1) when neither v8 nor v4 is requested.
+ * v16 [B*Hkv,tiles,16384 B], v8 [..,8192 B], v4 [..,4096 B]; each may be NULL. */
+int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
+               int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+               float* partial, float* vstat, void* v16, void* v8, void* v4, void* stream);
+
+/* Banded causal prefill attention (tcgen05).
+ * Replaces attention(order,bands,groups,entries,v16p,v8p,v4p,vstat,q8,k8p,qa8,ka8,q4,k4p,qa4,ka4,out,scale),
+ *   triattention/kernels/cuda/prefill_sm80.cu:510-543, in band mode.  The CTA order is internal
+ *   (heaviest query blocks first); task-table mode (groups/entries) has no Python caller in the
+ *   reference and is not provided.
+ * bands int32 [Hq,2] = (w8,w4) in tile distances; a head with w8 < 1 is skipped (un-quantised BF16
+ * extension heads are computed by the caller).  out is bf16 (or fp16 when out_is_half) [B,Hq,T,128]
+ * with element strides.  device_error: int32 word, set non-zero if a bounded wait ran out. */
+int tri_attention(const int32_t* bands, const void* v16, const void* v8, const float* vstat,
+                  const void* q8, const void* k8, const float* qa8, const float* ka8,
+                  const void* q4x, const void* k4x, const float* qa4, const float* ka4,
+                  void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
+                  int batch, int heads_q, int heads_kv, int tokens, double scale,
+                  int* device_error, void* stream);
+
+/* Gather the kept tiles of the prefill operands into per-(sequence, KV head) cache streams.
+ * Replaces the index_select gathers of DecodeCache.store, triattention/kernels/decode.py:46-61.
+ * Stream of a quantised unit: per kept tile, ascending, one chunk = K blob (K8 8192 B or K4 4096 B),
+ * V blob (V8 8192 B or V4 4096 B), 4 f32 K scales.  unit_base int64 [U] byte offsets into pool;
+ * unit_tab int32 [U] first row of the unit's table in tmeta; unit_count int32 [U]; unit_flags int32
+ * [U] (bit 0: BF16 unit, skipped here); tmeta int32 [N,2] = (chunk offset in 16-byte units from the
+ * unit base, info) with info = tile | rowmask<<12 | K4<<20 | V4<<21 | BF16<<22. */
+int tri_cache_store(void* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_count,
+                    const int32_t* unit_flags, const int32_t* tmeta, int units, int max_count,
+                    const void* k8, const void* k4, const float* ka, const float* ka4,
+                    const void* v8, const void* v4, int tiles, void* stream);
+
+/* Same for un-quantised BF16 units (an extension; the reference has no BF16 heads in its kernels):
+ * K and V rows are copied into 32-key chunks of 16384 B in MMA fragment order.  units int32 [n]. */
+int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* units, int num_units,
+                         const void* k, const void* v, int tokens, int heads_kv,
+                         int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                         int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t, void* stream);
+
+/* One decode step of one layer for the whole batch: split-KV pass over the cache streams, then the
+ * merge with the BF16 tail of generated tokens (the current K/V row is appended to the tail).
+ * Replaces decode(q,k8c,k4c,ka,ka4,entry,kinfo,count,fmt,slot,v8,v4,vstat,kstat,ktail,vtail,kcur,vcur,
+ *   step,out,pm,pl,po,prompt,per,scale), triattention/kernels/cuda/common_host.cuh:47-87.
+ * work int32 [W,4] = (unit, first kept tile, tile count, partial slot), heaviest first;
+ * unit_slots int32 [U,2] = (first partial slot, number of splits); pm, pl f32 [P,8]; po f32 [P,8,128];
+ * tail_k/tail_v bf16 [U,max_tail,128] with element strides; kcur/vcur bf16 [B,Hkv,1,128];
+ * step int64 [1] on the device; out bf16 [B,Hq,1,128]. */
+int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
+               const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* work, int num_work,
+               const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
+               int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
+               int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out,
+               int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po,
+               int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale,
+               int* device_error, void* stream);
+
+/* Resident decode CTAs per SM.  Replaces decode_occupancy(), triattention/kernels/cuda/common_host.cuh:89-94. */
+int tri_decode_occupancy(void);
+
+/* Integer QK^T accumulators of chosen tiles through the prefill kernel's operand path (TMA + tcgen05),
+ * for parity checks.  requests int32 [n,4] = (Q unit, query-block pair, key tile, 0 = INT8 / 1 = INT4 codes);
+ * acc int32 [n,128,64].  No counterpart in the reference (its accumulators never leave registers). */
+int tri_qk_accumulators(const int32_t* requests, int num_requests, const void* q8, const void* q4x, const void* k8,
+                        const void* k4x, int32_t* acc, int batch, int heads_q, int heads_kv, int tokens,
+                        int* device_error, void* stream);
+
+/* Single-tile tensor-core probe used by the tests to pin the operand-layout conventions:
+ * D[128 x ncols] = A . B^T from caller-built shared-memory images and descriptor fields.
+ * No counterpart in the reference. */
+int tri_umma_probe(const void* a_img, int a_bytes, const void* b_img, int b_bytes,
+                   uint32_t a_lbo, uint32_t a_sbo, uint32_t a_layout, uint32_t a_step,
+                   uint32_t b_lbo, uint32_t b_sbo, uint32_t b_layout, uint32_t b_step,
+                   uint32_t idesc, int f16_kind, int ksteps, int ncols, uint32_t* out,
+                   int* device_error, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,210 @@
+"""CPU checks of the host side: blob layouts, map loading, band tables, cache planning, and that the
+C-ABI library loads and exports every symbol the header declares (no compute calls)."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import triattention_oracle as orc
+from triattention_b200 import maps
+from triattention_b200.kernels import decode as dec
+from triattention_b200.kernels import layouts
+from triattention_b200.kernels.extension import SIGNATURES, load_library
+from triattention_b200.kernels.prefill import F16, I8, Q4, BandTable
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+# ---- blob layouts: the numpy packers follow the index formulas of csrc/kv_write.cu -----------------------
+def test_k8_blob_formula():
+    codes = np.random.default_rng(0).integers(-127, 128, (64, 128), dtype=np.int8)
+    blob = layouts.pack_k8(codes).view(np.int8)
+    for r, c in ((0, 0), (5, 17), (63, 127), (40, 96), (9, 15)):
+        assert blob[(r // 8) * 1024 + (c // 16) * 128 + (r % 8) * 16 + c % 16] == codes[r, c]
+    assert (layouts.unpack_k8(layouts.pack_k8(codes)) == codes).all()
+
+
+def test_k4_blob_formula():
+    rng = np.random.default_rng(1)
+    blob = rng.integers(0, 256, 4096, dtype=np.uint8)
+    codes = layouts.unpack_k4(blob)
+    for r, c in ((0, 0), (5, 17), (63, 127), (40, 96), (9, 47)):
+        byte = int(blob[(r // 8) * 512 + (c // 32) * 128 + (r % 8) * 16 + c % 16])
+        nib = (byte >> 4) if (c % 32) >= 16 else (byte & 0xF)
+        assert codes[r, c] == (nib - 16 if nib > 7 else nib)
+
+
+def test_v_blob_formulas():
+    rng = np.random.default_rng(2)
+    v = rng.integers(-127, 128, (64, 128), dtype=np.int8)        # [key][channel]
+    blob = layouts.pack_v8(v).view(np.int8)
+    for key, ch in ((0, 0), (13, 5), (63, 127), (34, 77)):
+        blk, k16 = key // 16, key % 16
+        pos = int(np.nonzero(layouts.KPERM == k16)[0][0])
+        assert blob[(ch // 8) * 512 + blk * 128 + (ch % 8) * 16 + pos] == v[key, ch]
+    assert (layouts.unpack_v8(layouts.pack_v8(v)) == v).all()
+    b4 = rng.integers(0, 256, 4096, dtype=np.uint8)
+    v4 = layouts.unpack_v4(b4)
+    for key, ch in ((0, 0), (13, 5), (63, 127), (34, 77), (50, 3)):
+        kc, k32 = key // 32, key % 32
+        pos = int(np.nonzero(layouts.KPERM == k32 % 16)[0][0])
+        byte = int(b4[(ch // 8) * 256 + kc * 128 + (ch % 8) * 16 + pos])
+        nib = (byte >> 4) if k32 >= 16 else (byte & 0xF)
+        assert v4[key, ch] == (nib - 16 if nib > 7 else nib)
+    h = rng.standard_normal((64, 128)).astype(np.float16)
+    assert (layouts.unpack_v16(layouts.pack_v16(h)) == h).all()
+    b16 = layouts.pack_v16(h).view(np.float16)
+    assert b16[(77 // 8) * 512 + (34 // 8) * 64 + (77 % 8) * 8 + 34 % 8] == h[34, 77]
+    assert sorted(layouts.KPERM.tolist()) == list(range(16))
+
+
+def test_swizzle128_is_an_involution_per_row_group():
+    rows = np.arange(16 * 128, dtype=np.uint8).reshape(16, 128)
+    img = layouts.swizzle128(rows)
+    assert (layouts.swizzle128(img) == rows).all()
+    assert (img[0] == rows[0]).all() and (img[1, :16] == rows[1, 16:32]).all()
+
+
+# ---- maps --------------------------------------------------------------------------------------------
+class _Cfg:
+    def __init__(self, layers, heads, model_type="llama"):
+        self.num_hidden_layers, self.num_attention_heads, self.model_type = layers, heads, model_type
+
+
+class _Model:
+    def __init__(self, layers, heads, model_type="llama"):
+        self.config = _Cfg(layers, heads, model_type)
+
+
+def test_load_map_v1(tmp_path):
+    doc = dict(format="triattention-map-v1", model_type="llama", length=65536, c4=0.905, point=0.8, cost=0.79,
+               bands={"0": [[maps.INF, maps.INF], [2, 16]], "1": [[1, 4], [8, maps.INF]]})
+    path = tmp_path / "m.json"
+    path.write_text(json.dumps(doc))
+    fn = maps.load_map(path, _Model(2, 2))
+    assert fn(1, 2).tolist() == [[1, 4], [8, maps.INF]] and fn(0, 2).dtype == torch.int32
+    assert not hasattr(fn, "bf16_kv_heads")
+    with pytest.raises(ValueError):
+        maps.load_map(path, _Model(3, 2))
+    with pytest.raises(ValueError):
+        maps.load_map(path, _Model(2, 4))
+    doc["bf16_kv_heads"] = {"1": [0]}
+    path.write_text(json.dumps(doc))
+    fn = maps.load_map(path, _Model(2, 2))
+    assert fn.bf16_kv_heads(1) == (0,) and fn.bf16_kv_heads(0) == ()
+
+
+def test_uniform_and_presets():
+    fn = maps.uniform(4, 8)
+    assert fn.layer_independent and fn(3, 5).tolist() == [[4, 8]] * 5
+    with pytest.raises(ValueError):
+        maps.preset(_Model(1, 1, "gpt2"))
+    fn = maps.per_kv_head(["int8", "int4", "bf16"], 2)
+    assert fn(0, 6).tolist() == [[maps.INF, maps.INF]] * 2 + [[1, maps.INF]] * 2 + [[maps.INF, maps.INF]] * 2
+    assert fn.bf16_kv_heads(0) == (2,)
+
+
+# ---- band table ----------------------------------------------------------------------------------------
+def test_band_table_matches_oracle():
+    bands = [[maps.INF, maps.INF], [2, 3], [1, maps.INF], [1, 1]]
+    for rows in (1, 2, 5, 40):
+        table = BandTable.build(bands, rows, 2, "cpu")
+        assert set(table.formats) == orc.band_formats(np.asarray(bands), rows)
+        assert (table.order.numpy() == orc.cta_order(4, 2, rows)).all()
+        assert table.bands.tolist() == bands
+    assert BandTable.build([[1, 1]] * 2, 9, 1, "cpu").formats == frozenset({F16})
+    assert BandTable.build([[2, 2]] * 2, 9, 1, "cpu").formats == frozenset({F16, I8})
+    assert Q4 in BandTable.build([[1, 2]] * 2, 9, 1, "cpu").formats
+    with pytest.raises(ValueError):
+        BandTable.build([[0, 4]] * 2, 9, 1, "cpu")
+    t = BandTable.build(bands, 5, 2, "cpu", bf16_kv=(1,))
+    assert t.bands.tolist() == bands[:2] + [[0, 0], [0, 0]] and t.host.tolist() == bands
+
+
+# ---- cache planning ---------------------------------------------------------------------------------------
+def test_plan_matches_reference_tile_rules():
+    bands = np.array([[2, 5], [1, 3], [maps.INF, maps.INF], [1, 1]])
+    prompt = 64 * 40 - 7
+    plan = dec.plan_streams(bands, 2, prompt, batch=3, ctas=16)
+    tabs = orc.decode_tables(bands, 2, prompt)
+    for kh in range(2):
+        rows = plan["tmeta"][plan["tab_begin"][kh]:plan["tab_begin"][kh] + plan["count"][kh]]
+        info = rows[:, 1].astype(np.int64)
+        assert (info & 0xFFF).tolist() == tabs[kh]["tiles"].tolist()
+        assert ((info >> 12) & 0xFF).tolist() == tabs[kh]["rowmask"].tolist()
+        assert (((info >> 20) & 1) == (tabs[kh]["state"] == 4)).all()
+        assert (((info >> 21) & 1) == (tabs[kh]["vfmt"] == orc.I4)).all()
+        size = np.where(tabs[kh]["state"] == 4, 4096, 8192) + np.where(tabs[kh]["vfmt"] == orc.I4, 4096, 8192) + 16
+        assert (rows[:, 0].astype(np.int64) * 16 == np.concatenate([[0], np.cumsum(size)[:-1]])).all()
+
+
+def test_plan_work_list_covers_every_tile_once():
+    bands = np.array([[maps.INF, maps.INF]] * 4 + [[1, maps.INF]] * 2 + [[4, 9]] * 2)
+    for bf16 in ((), (1,), (0, 3)):
+        plan = dec.plan_streams(bands, 4, 8192, batch=5, bf16_kv=bf16, ctas=64)
+        units = 20
+        seen = [np.zeros(plan["unit_count"][u], int) for u in range(units)]
+        slots = set()
+        for u, first, cnt, slot in plan["work"]:
+            seen[u][first:first + cnt] += 1
+            assert cnt > 0 and slot not in slots
+            slots.add(slot)
+            lo, n = plan["unit_slots"][u]
+            assert lo <= slot < lo + n
+        assert all((s == 1).all() for s in seen) and len(slots) == plan["slots"]
+        # streams do not overlap and stay inside the pool
+        ends = plan["unit_base"] + plan["head_bytes"][np.arange(units) % 4]
+        order = np.argsort(plan["unit_base"])
+        assert (plan["unit_base"][order][1:] >= ends[order][:-1]).all() and ends.max() <= plan["pool_bytes"]
+        assert (plan["unit_flags"] == np.isin(np.arange(units) % 4, list(bf16))).all()
+        w = plan["work"]
+        assert len(w) >= min(64, units)
+
+
+def test_plan_c2_byte_model():
+    """BASELINE config 2: 8 KV heads (4 INT8, 2 INT4, 2 BF16), cache of 8192 tokens, batch 32."""
+    bands = np.array([[maps.INF, maps.INF]] * 12 + [[1, maps.INF]] * 6 + [[maps.INF, maps.INF]] * 6)
+    plan = dec.plan_streams(bands, 8, 8192, batch=32, bf16_kv=(6, 7), ctas=444)
+    assert plan["head_bytes"].tolist() == [1644544] * 4 + [1128448] * 2 + [4194304] * 2
+    assert plan["payload_bytes"] == 551157760
+
+
+def test_needs_k4():
+    assert dec.DecodeCache.needs_k4(np.array([[1, maps.INF]] * 2), 1, 5)
+    assert not dec.DecodeCache.needs_k4(np.array([[maps.INF, maps.INF]] * 2), 1, 5)
+    assert not dec.DecodeCache.needs_k4(np.array([[1, maps.INF]] * 2), 1, 1)
+
+
+# ---- C ABI ------------------------------------------------------------------------------------------------
+def header_functions():
+    text = (ROOT / "include" / "triattention_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    found = {}
+    for m in re.finditer(r"\b(?:int|const char\*)\s+(tri_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        args = m.group(2).strip()
+        found[m.group(1)] = 0 if args in ("", "void") else len(args.split(","))
+    return found
+
+
+def test_library_exports_every_declared_symbol():
+    lib = load_library()
+    declared = header_functions()
+    assert set(SIGNATURES) | {"tri_last_error"} == set(declared), set(SIGNATURES) ^ set(declared)
+    for name, nargs in declared.items():
+        assert hasattr(lib, name), name
+        if name in SIGNATURES:
+            assert len(SIGNATURES[name]) == nargs, (name, len(SIGNATURES[name]), nargs)
+    assert lib.tri_abi_version() == 1
+    assert isinstance(lib.tri_last_error(), bytes)
+
+
+def test_argument_errors_without_gpu():
+    """Validation happens before any CUDA call, so it can be exercised on CPU."""
+    lib = load_library()
+    assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 12)) == -1
+    assert b"null" in lib.tri_last_error()
+    assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 6)) == -1

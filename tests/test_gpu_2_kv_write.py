@@ -1,0 +1,118 @@
+"""KV-cache write path (rotate + quantise + pack) against the CPU oracle and the reference extension."""
+import numpy as np
+import pytest
+import torch
+
+import triattention_oracle as orc
+from ref_harness import RefRunner, ref_logical
+from triattention_b200.kernels import layouts
+from triattention_b200.kernels.prefill import F16, I4, I8, Q4, Prefill
+from triattention_b200.maps import INF
+from util import bf16_cuda, code_mismatch, make_inputs, ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+# Allowance of the IEEE oracle against fast-math kernels: approximate division moves a scale by a few
+# ulp, which flips a code only where x*inv sits on a rounding boundary.
+SCALE_ULP, CODE_RATE = 4, 2e-3
+
+
+def run_write(module, q, k, v, want4=True):
+    """Product write path on [B,H,T,128] float32 inputs; returns logical numpy arrays per batch."""
+    b, hq, t, _ = q.shape
+    hk, tiles = k.shape[1], (t + 63) // 64
+    pre = Prefill(module, None)
+    formats = frozenset({F16, I8, I4})
+    ops = pre.operands(b, hq, hk, t, want4, want4, formats, "cuda")
+    qd, kd, vd = bf16_cuda(q), bf16_cuda(k), bf16_cuda(v)
+    module.prepare_qk(qd, kd, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
+                      ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
+    module.pack_v(vd, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"])
+    torch.cuda.synchronize()
+    cpu = lambda x: x.detach().cpu().numpy()
+    blob = lambda x, n: cpu(x).reshape(b, hk, tiles, n)
+    res = dict(q8=cpu(ops["q8"]).reshape(b, hq, t, 128), qa=cpu(ops["qa"]).reshape(b, hq, t),
+               k8=layouts.unpack_k8(blob(ops["k8"], 8192)), ka=cpu(ops["ka"]).reshape(b, hk, tiles, 4),
+               kstat=cpu(ops["kstat"]).reshape(b, hk, 3, 128), vstat=cpu(ops["vstat"]).reshape(b, hk, 3, 128),
+               v16=layouts.unpack_v16(blob(ops["v16"], 16384)), v8=layouts.unpack_v8(blob(ops["v8"], 8192)),
+               v4=layouts.unpack_v4(blob(ops["v4"], 4096)))
+    if want4:
+        res.update(q4=cpu(ops["q4x"]).reshape(b, hq, t, 128), qa4=cpu(ops["qa4"]).reshape(b, hq, t),
+                   k4x=layouts.unpack_k8(blob(ops["k4x"], 8192)), k4=layouts.unpack_k4(blob(ops["k4"], 4096)),
+                   ka4=cpu(ops["ka4"]).reshape(b, hk, tiles, 4))
+    return res
+
+
+def oracle_write(q, k, v):
+    q8, qa, q4, qa4 = orc.quantize_q(q)
+    kstat = orc.channel_stats(k)
+    k8, ka, k4, ka4 = orc.quantize_k(k, kstat[:, 0])
+    vstat = orc.channel_stats(v)
+    v16, v8, v4 = orc.pack_v(v, vstat)
+    return dict(q8=q8, qa=qa, q4=q4, qa4=qa4, kstat=kstat, k8=k8, ka=ka, k4=k4, ka4=ka4, vstat=vstat, v16=v16, v8=v8, v4=v4)
+
+
+@pytest.mark.parametrize("hq,hk,t,batch", [(4, 2, 200, 2), (8, 2, 512, 1), (2, 1, 1, 1), (2, 1, 63, 1), (2, 2, 64, 1),
+                                           (2, 1, 65, 1), (3, 1, 129, 1), (24, 8, 1024, 1)])
+def test_write_vs_oracle(module, hq, hk, t, batch):
+    q, k, v = make_inputs(hq, hk, t, seed=11, batch=batch)
+    got = run_write(module, q, k, v)
+    worst = {}
+    for b in range(batch):
+        want = oracle_write(q[b], k[b], v[b])
+        assert ulp_diff(got["kstat"][b][:, 0], want["kstat"][:, 0]).max() <= SCALE_ULP
+        for name in ("qa", "qa4", "ka", "ka4"):
+            assert ulp_diff(got[name][b], want[name]).max() <= SCALE_ULP, name
+        assert ulp_diff(got["vstat"][b], want["vstat"]).max() <= SCALE_ULP
+        for name in ("q8", "q4", "k8", "k4", "v8", "v4"):
+            rate, big = code_mismatch(got[name][b], want[name])
+            worst[name] = max(worst.get(name, 0.0), rate)
+            assert big <= 1 and rate <= CODE_RATE, (name, rate, big)
+        assert (got["k4x"][b] == got["k4"][b]).all()          # the packed and widened INT4 K codes are the same codes
+        d16 = np.abs(got["v16"][b].astype(np.float32) - want["v16"].astype(np.float32))
+        assert (d16 <= np.abs(want["v16"].astype(np.float32)) * 2.0 ** -10 + 1e-6).all()
+    print("code mismatch rates vs IEEE oracle", worst)
+
+
+@pytest.mark.parametrize("hq,hk,t", [(4, 2, 200), (8, 2, 512), (2, 1, 65), (24, 8, 1024)])
+def test_write_bit_exact_vs_reference(module, ref_ext, hq, hk, t):
+    """Codes and scale bit patterns equal the reference kernels' on the same GPU."""
+    q, k, v = make_inputs(hq, hk, t, seed=23, batch=2)
+    got = run_write(module, q, k, v)
+    run = RefRunner(ref_ext)
+    bands = np.array([[2, 3]] * hq, np.int64) if t > 128 else np.array([[1, INF]] * hq, np.int64)
+    for b in range(2):
+        o = run.prefill(bf16_cuda(q[b])[None], bf16_cuda(k[b])[None], bf16_cuda(v[b])[None], bands, 0.088, with_decode=True)
+        torch.cuda.synchronize()
+        ref = ref_logical(o)
+        for name in ("qa", "ka", "qa4", "ka4"):
+            if name in ref:
+                assert (got[name][b].view(np.uint32) == ref[name].view(np.uint32)).all(), name
+        assert (got["kstat"][b][:, 0].view(np.uint32) == ref["kstat"][:, 0].view(np.uint32)).all()
+        assert (got["vstat"][b].view(np.uint32) == ref["vstat"].view(np.uint32)).all()
+        for name in ("q8", "q4", "k8", "k4", "v8", "v4"):
+            if name in ref:
+                assert (got[name][b] == ref[name]).all(), (name, code_mismatch(got[name][b], ref[name]))
+        assert (got["v16"][b].view(np.uint16) == ref["v16"].view(np.uint16)).all()
+
+
+def test_write_strided_inputs(module):
+    """The HF hook hands over [B,T,H,128] storage viewed as [B,H,T,128]."""
+    q, k, v = make_inputs(4, 2, 130, seed=5, batch=2)
+    base = run_write(module, q, k, v)
+    pre = Prefill(module, None)
+    ops = pre.operands(2, 4, 2, 130, True, True, frozenset({F16, I8, I4}), "cuda")
+    tr = lambda x: bf16_cuda(x).transpose(1, 2).contiguous().transpose(1, 2)
+    module.prepare_qk(tr(q), tr(k), ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
+                      ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
+    module.pack_v(tr(v), ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"])
+    torch.cuda.synchronize()
+    assert (ops["q8"].cpu().numpy().reshape(2, 4, 130, 128) == base["q8"]).all()
+    assert (layouts.unpack_k8(ops["k8"].cpu().numpy().reshape(2, 2, 3, 8192)) == base["k8"]).all()
+    assert (layouts.unpack_v8(ops["v8"].cpu().numpy().reshape(2, 2, 3, 8192)) == base["v8"]).all()
+
+
+def test_argument_errors(module):
+    q = torch.zeros((1, 2, 8, 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        module.prepare_qk(q, q, q, q, q, q, q, q)

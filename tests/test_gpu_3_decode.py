@@ -1,0 +1,140 @@
+"""Split-KV decode + merge against the CPU oracle and the reference extension."""
+import numpy as np
+import pytest
+import torch
+
+import triattention_oracle as orc
+from ref_harness import RefRunner
+from triattention_b200.kernels.decode import DecodeCache
+from triattention_b200.kernels.prefill import Prefill
+from triattention_b200.maps import INF, from_bands
+from util import assert_fp_close, bf16_cuda, make_inputs
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / np.sqrt(128.0)
+
+
+def bands_fn_of(bands, bf16=()):
+    fn = from_bands({"0": np.asarray(bands).tolist()}, None, {"0": list(bf16)} if bf16 else None)
+    return fn
+
+
+def product_decode(module, q, k, v, bands, qd, kd, vd, steps, max_tail=8, bf16=()):
+    """Write the cache with the product path, then run `steps` decode steps.  Arrays are [B,H,*,128]."""
+    cache = DecodeCache(module, max_tail=max_tail)
+    pre = Prefill(module, bands_fn_of(bands, bf16), cache)
+    kc, vc = bf16_cuda(k), bf16_cuda(v)
+    table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+    cache.store(0, q.shape[2], ops, table.host, kc, vc, table.bf16_kv)
+    outs = []
+    for s in range(steps):
+        out = cache(0, bf16_cuda(qd[:, :, s:s + 1]), bf16_cuda(kd[:, :, s:s + 1]), bf16_cuda(vd[:, :, s:s + 1]), SCALE)
+        cache.advance()
+        outs.append(out.float().cpu().numpy()[:, :, 0])
+    module.check_device_error()
+    return np.stack(outs, 1), cache      # [B, steps, Hq, 128]
+
+
+def oracle_ops(q, k, v):
+    kstat = orc.channel_stats(k)
+    k8, ka, k4, ka4 = orc.quantize_k(k, kstat[:, 0])
+    vstat = orc.channel_stats(v)
+    v16, v8, v4 = orc.pack_v(v, vstat)
+    return dict(kstat=kstat, k8=k8, ka=ka, k4=k4, ka4=ka4, vstat=vstat, v16=v16, v8=v8, v4=v4)
+
+
+def oracle_steps(k, v, bands, qd, kd, vd, steps, max_tail=8, per=None):
+    """One sequence: [H,T,128] arrays -> [steps, Hq, 128] float32."""
+    ops = oracle_ops(None, k, v)
+    hk = k.shape[0]
+    tk, tv = np.zeros((hk, max_tail, 128), np.float32), np.zeros((hk, max_tail, 128), np.float32)
+    outs = []
+    for s in range(steps):
+        outs.append(orc.decode_step(qd[:, s], ops, bands, k.shape[1], SCALE, tk, tv, kd[:, s], vd[:, s], s, max_tail, per))
+    return np.stack(outs)
+
+
+CASES = [
+    # hq, hk, t, bands
+    (4, 2, 200, [[INF, INF], [INF, INF], [2, 3], [2, 3]]),
+    (8, 2, 512, [[INF, INF]] * 4 + [[1, INF]] * 4),
+    (6, 2, 1500, [[INF, INF]] * 3 + [[4, 12]] * 2 + [[1, 2]]),     # INT4 V tiles, dropped tiles, mixed row masks
+    (3, 1, 65, [[INF, INF]] * 3),
+    (8, 1, 130, [[1, INF]] * 8),
+]
+
+
+@pytest.mark.parametrize("hq,hk,t,bands", CASES)
+def test_decode_vs_oracle(module, hq, hk, t, bands):
+    bands = np.asarray(bands, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=31, batch=2)
+    qd, kd, vd = make_inputs(hq, hk, 3, seed=77, batch=2)
+    got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3)
+    for b in range(2):
+        want = oracle_steps(k[b], v[b], bands, qd[b], kd[b], vd[b], 3)
+        assert_fp_close(got[b], orc.to_bf16(want), f"decode b={b}")
+
+
+@pytest.mark.parametrize("hq,hk,t,bands", CASES)
+def test_decode_vs_reference(module, ref_ext, hq, hk, t, bands):
+    bands = np.asarray(bands, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=41, batch=1)
+    qd, kd, vd = make_inputs(hq, hk, 3, seed=88, batch=1)
+    got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3)
+    run = RefRunner(ref_ext)
+    o = run.prefill(bf16_cuda(q[0])[None], bf16_cuda(k[0])[None], bf16_cuda(v[0])[None], bands, SCALE)
+    st = run.decode_setup(o, bands, max_tail=8, per=3)
+    for s in range(3):
+        ref = run.decode(st, bf16_cuda(qd[:, :, s:s + 1]), bf16_cuda(kd[:, :, s:s + 1]), bf16_cuda(vd[:, :, s:s + 1]), SCALE)
+        st["step"].add_(1)
+        assert_fp_close(got[0, s], ref.float().cpu().numpy()[0, :, 0], f"decode step {s}")
+
+
+def test_decode_bf16_heads(module):
+    """Un-quantised extension heads against exact attention over prompt + tail."""
+    hq, hk, t = 6, 3, 300
+    bands = np.asarray([[INF, INF]] * 6, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=51, batch=2)
+    qd, kd, vd = make_inputs(hq, hk, 2, seed=99, batch=2)
+    got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=2, bf16=(1,))
+    for b in range(2):
+        for s in range(2):
+            for h in (2, 3):
+                kk = np.concatenate([k[b, 1], kd[b, 1, :s + 1]])
+                vv = np.concatenate([v[b, 1], vd[b, 1, :s + 1]])
+                want = orc.exact_decode(qd[b, h, s], kk, vv, SCALE)
+                assert_fp_close(got[b, s, h], orc.to_bf16(want), f"bf16 head {h} step {s}")
+        # quantised heads in the same launch still match the oracle
+        want = oracle_steps(k[b], v[b], bands, qd[b], kd[b], vd[b], 2)
+        assert_fp_close(got[b][:, [0, 1, 4, 5]], orc.to_bf16(want[:, [0, 1, 4, 5]]), "mixed launch")
+
+
+def test_decode_split_invariance(module):
+    """The work-list cut must not change the result beyond float summation order."""
+    from triattention_b200.kernels import decode as dm
+    hq, hk, t = 4, 2, 2000
+    bands = np.asarray([[INF, INF]] * 4, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=61)
+    qd, kd, vd = make_inputs(hq, hk, 1, seed=62)
+    results = []
+    for ctas in (1, 16, 444):
+        cache = DecodeCache(module, max_tail=4)
+        cache._wave = ctas
+        pre = Prefill(module, bands_fn_of(bands), cache)
+        kc, vc = bf16_cuda(k), bf16_cuda(v)
+        table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+        cache.store(0, t, ops, table.host, kc, vc)
+        results.append(cache(0, bf16_cuda(qd), bf16_cuda(kd), bf16_cuda(vd), SCALE).float().cpu().numpy())
+    module.check_device_error()
+    assert np.abs(results[0] - results[1]).max() <= 2e-3 and np.abs(results[0] - results[2]).max() <= 2e-3
+
+
+def test_tail_saturates(module):
+    """Steps beyond max_tail-1 keep overwriting the last tail slot (common_device.cuh:384)."""
+    hq, hk, t = 2, 1, 64
+    bands = np.asarray([[INF, INF]] * 2, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=71)
+    qd, kd, vd = make_inputs(hq, hk, 4, seed=72)
+    got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=4, max_tail=2)
+    want = oracle_steps(k[0], v[0], bands, qd[0], kd[0], vd[0], 4, max_tail=2)
+    assert_fp_close(got[0], orc.to_bf16(want), "saturated tail")

@@ -1,0 +1,33 @@
+// Error plumbing shared by the C-ABI entry points.  Every entry point returns 0 on success or a
+// negative code; the message is kept per host thread and read with tri_last_error().
+// The reference raises RuntimeError from TORCH_CHECK / C10_CUDA_KERNEL_LAUNCH_CHECK
+// (triattention/kernels/cuda/common_host.cuh:4-13,24); the Python shim turns these codes into the
+// same exception type.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+enum TriStatus : int { TRI_OK = 0, TRI_ERR_ARGUMENT = -1, TRI_ERR_CUDA = -2, TRI_ERR_DEVICE = -3 };
+
+void tri_set_error(const char* what);
+int tri_launch_status(const char* where);
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define TRI_CHECK(cond, msg)             \
+  do {                                   \
+    if (!(cond)) {                       \
+      tri_set_error(msg);                \
+      return TRI_ERR_ARGUMENT;           \
+    }                                    \
+  } while (0)
+
+#define TRI_CUDA(call, where)                 \
+  do {                                        \
+    cudaError_t e_ = (call);                  \
+    if (e_ != cudaSuccess) {                  \
+      tri_set_error(cudaGetErrorString(e_));  \
+      (void)where;                            \
+      return TRI_ERR_CUDA;                    \
+    }                                         \
+  } while (0)

@@ -1,0 +1,334 @@
+// KV-cache write path for sm_100a: channel statistics, then fused rotate + quantise + pack.
+//
+// Replaces (paths inside the reference project)
+//   triattention/kernels/cuda/common_device.cuh:1-28     quantize_q_kernel
+//   triattention/kernels/cuda/common_device.cuh:32-56    partial_kernel, finalize_kernel
+//   triattention/kernels/cuda/common_device.cuh:58-131   quantize_k_kernel
+//   triattention/kernels/cuda/common_device.cuh:132-172  pack_v_kernel
+//   triattention/kernels/cuda/common_host.cuh:1-45       prepare_qk, pack_v host launchers
+// with a batch dimension added (the reference is batch 1).  Float operation order is kept where the
+// result bits depend on it: the 64-way strided partial sums, their in-order total, the butterflies of
+// the rotation, and the scale expressions.
+//
+// Design: everything here is HBM-bound byte work.  The Walsh-Hadamard transform runs in registers
+// with 16 features per lane (8 lanes per row): 4 in-register radix-2 stages and 3 shuffle stages,
+// so every lane ends up owning one 16-byte run of codes and stores it with one 128-bit store.
+// K needs the whole-prompt channel mean and V the whole-prompt mean and range before any code can be
+// produced, so the write is two phases: statistics (K and V together), then codes (K, V).
+#include "common.cuh"
+#include "abi_internal.h"
+
+namespace tri {
+
+// ------------------------------------------------------------------------------------------------
+// statistics: partial[tensor][unit][block][3][128], stat[unit][3][128]
+// ------------------------------------------------------------------------------------------------
+// grid (StatBlocks, units, 2 tensors), 128 threads = one per channel.  Block b owns tokens b, b+64, ...
+// and adds them in token order (common_device.cuh:36-39): the order is part of the mean's bit pattern.
+__global__ void __launch_bounds__(D) stats_partial_kernel(const __nv_bfloat16* k, const __nv_bfloat16* v,
+    float* partial_k, float* partial_v, int tokens, int heads, int64_t ksb, int64_t ksh, int64_t kst,
+    int64_t vsb, int64_t vsh, int64_t vst) {
+  const int c = threadIdx.x, unit = blockIdx.y, which = blockIdx.z;
+  const int b = unit / heads, h = unit % heads;
+  const __nv_bfloat16* base;
+  int64_t st;
+  float* partial;
+  if (which == 0) {
+    if (k == nullptr) return;
+    base = k + b * ksb + h * ksh + c; st = kst; partial = partial_k;
+  } else {
+    if (v == nullptr) return;
+    base = v + b * vsb + h * vsh + c; st = vst; partial = partial_v;
+  }
+  float sum = 0.f, hi = -FLT_MAX, lo = FLT_MAX;
+  int t = blockIdx.x;
+  // loads are issued eight at a time; the adds stay sequential in token order
+  for (; t + 7 * StatBlocks < tokens; t += 8 * StatBlocks) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = __bfloat162float(base[(int64_t)(t + u * StatBlocks) * st]);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { sum += x[u]; hi = fmaxf(hi, x[u]); lo = fminf(lo, x[u]); }
+  }
+  for (; t < tokens; t += StatBlocks) {
+    const float x = __bfloat162float(base[(int64_t)t * st]);
+    sum += x; hi = fmaxf(hi, x); lo = fminf(lo, x);
+  }
+  float* o = partial + (((int64_t)unit * StatBlocks + blockIdx.x) * 3) * D + c;
+  o[0] = sum; o[D] = hi; o[2 * D] = lo;
+}
+
+// grid (units, 2), 128 threads.  common_device.cuh:44-56.
+__global__ void __launch_bounds__(D) stats_finalize_kernel(const float* partial_k, const float* partial_v,
+    float* kstat, float* vstat, int tokens, int v_identity) {
+  const int64_t unit = blockIdx.x;
+  const int c = threadIdx.x, which = blockIdx.y;
+  const float* partial = which == 0 ? partial_k : partial_v;
+  float* stat = which == 0 ? kstat : vstat;
+  if (stat == nullptr) return;
+  float mean = 0.f, scale = 1.f;
+  if (!(which == 1 && v_identity)) {
+    const float* in = partial + unit * StatBlocks * 3 * D + c;
+    float sum = 0.f, hi = -FLT_MAX, lo = FLT_MAX;
+    for (int b = 0; b < StatBlocks; ++b) {
+      sum += in[b * 3 * D]; hi = fmaxf(hi, in[b * 3 * D + D]); lo = fminf(lo, in[b * 3 * D + 2 * D]);
+    }
+    mean = sum / tokens;
+    const float range = fmaxf(hi - mean, mean - lo);
+    scale = range > 0.f ? range / 127.f : 1.f;
+  }
+  stat[unit * 3 * D + c] = mean; stat[unit * 3 * D + D + c] = scale; stat[unit * 3 * D + 2 * D + c] = 1.f / scale;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Q: rotate, per-token absmax, INT8 codes + INT4 codes (as int8 values), scales
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* src, float (&x)[16]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 8);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 codes16(const float (&x)[16], float inv) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) word |= (uint32_t)(__float2int_rn(x[4 * j + b] * inv) & 0xff) << (8 * b);
+    w[j] = word;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// grid (ceil(T/16), B*Hq), 128 threads: 4 rows per warp, 8 lanes per row.  q8/q4x are plain
+// [B*Hq][T][128] int8 (the reference's q8 layout, common_device.cuh:18); q4x holds the 4-bit codes
+// sign-extended to int8 so that the prefill kernel can feed them to the INT8 tensor-core path.
+__global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q, int8_t* q8, float* qa, int8_t* q4x,
+    float* qa4, int tokens, int heads, int64_t qsb, int64_t qsh, int64_t qst) {
+  const int lane = threadIdx.x % 32, l8 = lane % 8;
+  const int row = blockIdx.x * 16 + (threadIdx.x / 32) * 4 + lane / 8;
+  const int unit = blockIdx.y;
+  const bool live = row < tokens;
+  float x[16];
+  if (live) load16_bf16(q + (unit / heads) * qsb + (unit % heads) * qsh + (int64_t)row * qst + l8 * 16, x);
+  else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = 0.f;
+  }
+  rotate128_x16(x, l8);
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(x[i]));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (!live) return;
+  const int64_t r = (int64_t)unit * tokens + row;
+  const float inv = m > 0.f ? 127.f / m : 0.f;
+  *reinterpret_cast<uint4*>(q8 + r * D + l8 * 16) = codes16(x, inv);
+  if (l8 == 0) qa[r] = m / 127.f;
+  if (q4x != nullptr) {
+    const float inv4 = m > 0.f ? 7.f / m : 0.f;
+    *reinterpret_cast<uint4*>(q4x + r * D + l8 * 16) = codes16(x, inv4);
+    if (l8 == 0) qa4[r] = m / 7.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// K: centre, rotate, per-16-key absmax, INT8 / INT4 codes into tile blobs
+// ------------------------------------------------------------------------------------------------
+// grid (tiles, B*Hkv), 128 threads.  One warp owns one 16-key scale group end to end, so no block
+// barrier is needed: 4 passes of 4 rows, 64 rotated values kept in registers until the group
+// maximum is known.
+__global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k, const float* kstat, uint8_t* k8,
+    float* ka, uint8_t* k4x, uint8_t* k4, float* ka4, int tokens, int heads, int64_t ksb, int64_t ksh, int64_t kst) {
+  const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x;
+  const int col = threadIdx.x / 32, lane = threadIdx.x % 32, l8 = lane % 8, sub_row = lane / 8;
+  const __nv_bfloat16* src = k + (unit / heads) * ksb + (unit % heads) * ksh + l8 * 16;
+  float mean[16];
+  {
+    const float4* mp = reinterpret_cast<const float4*>(kstat + (int64_t)unit * StatFloats + l8 * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = mp[i];
+      mean[4 * i] = v.x; mean[4 * i + 1] = v.y; mean[4 * i + 2] = v.z; mean[4 * i + 3] = v.w;
+    }
+  }
+  float y[4][16];
+  float cm = 0.f;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int t = tile * BN + col * 16 + p * 4 + sub_row;
+    if (t < tokens) {
+      load16_bf16(src + (int64_t)t * kst, y[p]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) y[p][i] -= mean[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) y[p][i] = 0.f;
+    }
+    rotate128_x16(y[p], l8);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) cm = fmaxf(cm, fabsf(y[p][i]));
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+  const float inv = cm > 0.f ? 127.f / cm : 0.f, inv4 = cm > 0.f ? 7.f / cm : 0.f;
+  const int64_t ht = (int64_t)unit * tiles + tile;
+  if (lane == 0) {
+    ka[ht * 4 + col] = cm > 0.f ? cm / 127.f : 1.f;
+    if (ka4 != nullptr) ka4[ht * 4 + col] = cm > 0.f ? cm / 7.f : 1.f;
+  }
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int r = col * 16 + p * 4 + sub_row;            // key row inside the tile
+    const int core = (r / 8) * 1024 + l8 * 128 + (r % 8) * 16;
+    *reinterpret_cast<uint4*>(k8 + ht * K8Bytes + core) = codes16(y[p], inv);
+    if (k4x == nullptr && k4 == nullptr) continue;
+    const uint4 c4 = codes16(y[p], inv4);
+    if (k4x != nullptr) *reinterpret_cast<uint4*>(k4x + ht * K8Bytes + core) = c4;
+    if (k4 != nullptr) {
+      // lane pair (even, odd) covers features 32s..32s+31; byte i = feature 32s+i | feature 32s+16+i << 4
+      const bool odd = l8 & 1;
+      const uint32_t n0 = c4.x & 0x0f0f0f0fu, n1 = c4.y & 0x0f0f0f0fu, n2 = c4.z & 0x0f0f0f0fu, n3 = c4.w & 0x0f0f0f0fu;
+      const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? n0 : n2, 1);
+      const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? n1 : n3, 1);
+      const uint2 out = odd ? make_uint2(r0 | (n2 << 4), r1 | (n3 << 4)) : make_uint2(n0 | (r0 << 4), n1 | (r1 << 4));
+      *reinterpret_cast<uint2*>(k4 + ht * K4Bytes + (r / 8) * 512 + (l8 >> 1) * 128 + (r % 8) * 16 + (odd ? 8 : 0)) = out;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// V: per-channel affine normalise, FP16 / INT8 / INT4 tile blobs (channel-major, keys contiguous)
+// ------------------------------------------------------------------------------------------------
+// grid (tiles, B*Hkv), 256 threads.  The tile is transposed through shared memory once; each thread
+// then emits whole 16-byte runs.
+__global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, const float* vstat, uint8_t* v16,
+    uint8_t* v8, uint8_t* v4, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
+  __shared__ float vn[BN][D + 1];
+  const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x, tid = threadIdx.x;
+  const __nv_bfloat16* base = v + (unit / heads) * vsb + (unit % heads) * vsh;
+  const float* stat = vstat + (int64_t)unit * StatFloats;
+  for (int i = tid; i < BN * D / 8; i += 256) {
+    const int r = i / (D / 8), c0 = (i % (D / 8)) * 8, t = tile * BN + r;
+    if (t < tokens) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(base + (int64_t)t * vst + c0);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // vnorm, common_device.cuh:132-134: (v - mean) * (1/scale)
+        vn[r][c0 + 2 * j] = (__uint_as_float(w[j] << 16) - stat[c0 + 2 * j]) * stat[2 * D + c0 + 2 * j];
+        vn[r][c0 + 2 * j + 1] = (__uint_as_float(w[j] & 0xffff0000u) - stat[c0 + 2 * j + 1]) * stat[2 * D + c0 + 2 * j + 1];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vn[r][c0 + j] = 0.f;
+    }
+  }
+  __syncthreads();
+  const int64_t ht = (int64_t)unit * tiles + tile;
+  if (v16 != nullptr) {
+    for (int i = tid; i < 1024; i += 256) {   // run = (ch/8, key/8, ch%8): 8 keys of one channel
+      const int ch = (i / 64) * 8 + i % 8, k8b = (i / 8) % 8;
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        w[j] = (uint32_t)__half_as_ushort(__float2half_rn(vn[k8b * 8 + 2 * j][ch])) |
+               ((uint32_t)__half_as_ushort(__float2half_rn(vn[k8b * 8 + 2 * j + 1][ch])) << 16);
+      *reinterpret_cast<uint4*>(v16 + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (v8 != nullptr) {
+    for (int i = tid; i < 512; i += 256) {    // run = (ch/8, key/16, ch%8): 16 keys in kperm order
+      const int ch = (i / 32) * 8 + i % 8, blk = (i / 8) % 4;
+      uint32_t w[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int qv = max(-127, min(127, __float2int_rn(vn[blk * 16 + kperm(s, b)][ch])));
+          word |= (uint32_t)(qv & 0xff) << (8 * b);
+        }
+        w[s] = word;
+      }
+      *reinterpret_cast<uint4*>(v8 + ht * V8Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (v4 != nullptr) {
+    const int i = tid;                         // run = (ch/8, key/32, ch%8): 32 keys, two per byte
+    const int ch = (i / 16) * 8 + i % 8, kc = (i / 8) % 2;
+    uint32_t w[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int lo = max(-7, min(7, __float2int_rn(vn[kc * 32 + kperm(s, b)][ch] * (7.f / 127.f))));
+        const int hi = max(-7, min(7, __float2int_rn(vn[kc * 32 + 16 + kperm(s, b)][ch] * (7.f / 127.f))));
+        word |= (uint32_t)((lo & 0xf) | ((hi & 0xf) << 4)) << (8 * b);
+      }
+      w[s] = word;
+    }
+    *reinterpret_cast<uint4*>(v4 + ht * V4Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace tri
+
+using namespace tri;
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int heads_kv, int tokens,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t, int64_t k_stride_b, int64_t k_stride_h,
+    int64_t k_stride_t, void* q8, float* qa, void* k8, float* ka, float* partial, float* kstat, void* q4x,
+    float* qa4, void* k4x, void* k4, float* ka4, void* stream) {
+  TRI_CHECK(q && k && q8 && qa && k8 && ka && partial && kstat, "prepare_qk: null Q/K buffers");
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && tokens > 0 && heads_q % heads_kv == 0, "prepare_qk: bad geometry");
+  TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
+  const bool int4 = q4x != nullptr;
+  TRI_CHECK(int4 == (qa4 != nullptr) && int4 == (k4x != nullptr) && int4 == (ka4 != nullptr) && (int4 || k4 == nullptr),
+            "INT4 Q/K buffers (all or none)");
+  TRI_CHECK(aligned16(q) && aligned16(k) && q_stride_b % 8 == 0 && q_stride_h % 8 == 0 && q_stride_t % 8 == 0 &&
+            k_stride_b % 8 == 0 && k_stride_h % 8 == 0 && k_stride_t % 8 == 0,
+            "BF16 Q/K [B,H,T,128] with contiguous features, 16-byte aligned rows");
+  TRI_CHECK(aligned16(q8) && aligned16(k8) && aligned16(q4x) && aligned16(k4x) && aligned16(k4) && aligned16(kstat),
+            "prepare_qk: output buffers must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tiles = (tokens + BN - 1) / BN, uq = batch * heads_q, uk = batch * heads_kv;
+  const auto* qp = static_cast<const __nv_bfloat16*>(q);
+  const auto* kp = static_cast<const __nv_bfloat16*>(k);
+  quantize_q_kernel<<<dim3((tokens + 15) / 16, uq), 128, 0, s>>>(qp, static_cast<int8_t*>(q8), qa,
+      static_cast<int8_t*>(q4x), qa4, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
+  stats_partial_kernel<<<dim3(StatBlocks, uk, 1), D, 0, s>>>(kp, nullptr, partial, nullptr, tokens, heads_kv,
+      k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
+  stats_finalize_kernel<<<dim3(uk, 1), D, 0, s>>>(partial, nullptr, kstat, nullptr, tokens, 0);
+  quantize_k_kernel<<<dim3(tiles, uk), 128, 0, s>>>(kp, kstat, static_cast<uint8_t*>(k8), ka,
+      static_cast<uint8_t*>(k4x), static_cast<uint8_t*>(k4), ka4, tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
+  return tri_launch_status("prepare_qk");
+}
+
+extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, int64_t v_stride_b, int64_t v_stride_h,
+    int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* stream) {
+  TRI_CHECK(v && partial && vstat, "pack_v: null V buffers");
+  TRI_CHECK(batch > 0 && heads_kv > 0 && tokens > 0, "pack_v: bad geometry");
+  TRI_CHECK(aligned16(v) && v_stride_b % 8 == 0 && v_stride_h % 8 == 0 && v_stride_t % 8 == 0, "BF16 V [B,Hkv,T,128]");
+  TRI_CHECK(aligned16(v16) && aligned16(v8) && aligned16(v4) && aligned16(vstat), "packed V alignment");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tiles = (tokens + BN - 1) / BN, uk = batch * heads_kv;
+  const auto* vp = static_cast<const __nv_bfloat16*>(v);
+  const int identity = (v8 == nullptr && v4 == nullptr) ? 1 : 0;  // common_host.cuh:39
+  if (!identity)
+    stats_partial_kernel<<<dim3(StatBlocks, uk, 2), D, 0, s>>>(nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
+        v_stride_b, v_stride_h, v_stride_t);
+  stats_finalize_kernel<<<dim3(uk, 2), D, 0, s>>>(nullptr, partial, nullptr, vstat, tokens, identity);
+  pack_v_kernel<<<dim3(tiles, uk), 256, 0, s>>>(vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
+      static_cast<uint8_t*>(v4), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
+  return tri_launch_status("pack_v");
+}

@@ -1,0 +1,606 @@
+// Banded causal prefill attention on tcgen05 (sm_100a): INT8 QK^T and INT8 / FP16 PV as dense
+// tensor-core contractions with TMEM accumulators.
+//
+// Replaces (paths inside the reference project)
+//   triattention/kernels/cuda/prefill_sm80.cu:158-257  qk8 / qk4 fragments, masks, scaled row max, margin
+//   triattention/kernels/cuda/prefill_sm80.cu:259-488  run_task: tile lists, passes, online softmax, epilogue
+//   triattention/kernels/cuda/prefill_sm80.cu:490-543  unified_kernel, attention() host launcher
+// in band mode (the only mode the reference's Python ever uses, kernels/prefill.py:103), with a batch
+// dimension added.
+//
+// Shape of the computation.  One CTA of 128 threads owns 128 query rows of one Q head: two adjacent
+// query blocks ("halves", 64 rows each; warps 0-1 and 2-3).  Thread t owns row t: it reads its row of
+// the score / PV accumulators from TMEM lane t (tcgen05.ld 32x32b), so the online softmax needs no
+// cross-thread reduction.  Per key tile:
+//   QK   S[128x64]  = Q8[128x128] . K8[64x128]^T   4 x tcgen05.mma kind::i8 (M128 N64 K32), s8 x s8 -> s32
+//   PV   D[128x128] = P8[128x64]  . V8[128x64]^T   2 x tcgen05.mma kind::i8 (M128 N128 K32), u8 x s8 -> s32
+//   or   D[128x128] = P16[128x64] . V16[128x64]^T  4 x tcgen05.mma kind::f16 (M128 N128 K16), fp32 accumulate
+// The two halves follow the reference's visiting order (sink tile, own diagonal tile, INT8 band
+// ascending, INT4 band ascending); a tile that only one half visits runs with the other half idle.
+// INT4 QK uses the 4-bit codes widened to int8 by the write kernel (K4X blobs, Q4X rows), so the
+// integer accumulators equal the reference's s4 x s4 MMAs exactly.
+// Q arrives by TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle), K/V tiles by TMA bulk
+// copies of pre-tiled blobs (cp.async.bulk), double buffered.  Every wait is bounded.
+#include "common.cuh"
+#include "abi_internal.h"
+#include <cuda.h>
+
+namespace tri {
+
+// ---- tcgen05 / TMA tensor wrappers --------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets in 16-byte
+// units, descriptor version 1, layout type (0 = no swizzle, 2 = 128-byte swizzle).
+__host__ __device__ constexpr uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | ((uint64_t)1 << 46) | ((uint64_t)layout << 61);
+}
+// Instruction descriptor: accumulator format (1 = f32, 2 = s32), A/B formats (i8: 0 = u8, 1 = s8;
+// f16: 0 = f16, 1 = bf16), both operands K-major, N/8 and M/16.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t cfmt, uint32_t afmt, uint32_t bfmt, uint32_t m, uint32_t n) {
+  return (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+constexpr uint32_t LayoutNone = 0, Layout128B = 2;
+constexpr uint32_t IdescQK = instr_desc(2, 1, 1, 128, 64);    // s8 x s8 -> s32
+constexpr uint32_t IdescPV8 = instr_desc(2, 0, 1, 128, 128);  // u8 x s8 -> s32
+constexpr uint32_t IdescPV16 = instr_desc(1, 0, 0, 128, 128); // f16 x f16 -> f32
+
+// ---- shared-memory plan of the prefill CTA ----------------------------------------------------
+constexpr int PrefillThreads = 128;
+constexpr int SmQ8 = 0, SmQ4 = 16384, SmP = 32768, SmK = 49152, SmV = SmK + 2 * K8Bytes, SmEnd = SmV + 2 * V16Bytes;
+constexpr int PrefillShared = SmEnd + 1024;   // + slack to align the base to 1024 bytes
+constexpr uint32_t TmemCols = 256, TmemS = 0, TmemD = 64;
+enum Mode : int { ModeF16 = 0, ModeI8 = 1, ModeQ4 = 2 };
+
+struct StepPlan {   // tile visiting order of one CTA, all warp-uniform integers
+  int b0, b1, has1, nF, lo8, n8, lo4, n4, w8, w4;
+  int f_tile[3], f_mask[3];
+  __device__ void build(int pair, int rows, int w8_, int w4_) {
+    w8 = w8_; w4 = w4_;
+    b0 = 2 * pair; b1 = b0 + 1; has1 = b1 < rows;
+    nF = 0;
+    f_tile[nF] = 0; f_mask[nF] = has1 ? 3 : 1; ++nF;
+    if (b0 > 0) { f_tile[nF] = b0; f_mask[nF] = 1; ++nF; }
+    if (has1) { f_tile[nF] = b1; f_mask[nF] = 2; ++nF; }
+    // prefill_sm80.cu:281-283 per half, then the union of the two contiguous ranges
+    int lo = 1 << 30, hi = 0, lq = 1 << 30, hq = 0;
+    for (int h = 0; h <= has1; ++h) {
+      const int qb = b0 + h, l8 = max(1, qb - w8 + 1), c8 = max(0, qb - l8);
+      const int l4 = max(1, qb - w4 + 1), c4 = max(0, qb - w8 - l4 + 1);
+      if (c8 > 0) { lo = min(lo, l8); hi = max(hi, l8 + c8); }
+      if (c4 > 0) { lq = min(lq, l4); hq = max(hq, l4 + c4); }
+    }
+    lo8 = lo; n8 = max(0, hi - lo); lo4 = lq; n4 = max(0, hq - lq);
+  }
+  __device__ int steps() const { return nF + n8 + n4; }
+  __device__ void get(int i, int& tile, int& mode, int& mask) const {
+    if (i < nF) { tile = f_tile[i]; mode = ModeF16; mask = f_mask[i]; return; }
+    mask = 0;
+    if (i < nF + n8) {
+      tile = lo8 + (i - nF); mode = ModeI8;
+      for (int h = 0; h <= has1; ++h) {
+        const int qb = b0 + h;
+        if (tile >= max(1, qb - w8 + 1) && tile <= qb - 1) mask |= 1 << h;
+      }
+    } else {
+      tile = lo4 + (i - nF - n8); mode = ModeQ4;
+      for (int h = 0; h <= has1; ++h) {
+        const int qb = b0 + h;
+        if (tile >= max(1, qb - w4 + 1) && tile <= qb - w8) mask |= 1 << h;
+      }
+    }
+  }
+};
+
+template <typename Out> __device__ __forceinline__ Out to_out(float x);
+template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float x) { return __float2bfloat16(x); }
+template <> __device__ __forceinline__ __half to_out<__half>(float x) { return __float2half(x); }
+
+// grid = pairs * batch * heads_q CTAs, heaviest query-block pairs first; 128 threads; 2 CTAs per SM.
+template <typename Out>
+__global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
+    const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
+    const float* ka4, const uint8_t* v16, const uint8_t* v8, const float* qa8, const float* qa4, const float* vstat, Out* out,
+    int64_t osb, int64_t osh, int64_t ost, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
+  extern __shared__ uint8_t raw_smem[];
+  __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_d;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
+  const int tid = threadIdx.x, warp = tid / 32, half = tid / 64;
+  const int rows = (tokens + BM - 1) / BM, pairs = (rows + 1) / 2, tiles = rows;
+  const int pair = pairs - 1 - blockIdx.x / units_q, qunit = blockIdx.x % units_q;
+  const int b = qunit / heads_q, h = qunit % heads_q, g = heads_q / heads_kv;
+  const int64_t kvunit = (int64_t)b * heads_kv + h / g;
+  const int w8 = bands[h * 2], w4 = bands[h * 2 + 1];
+  if (w8 < 1) return;   // head handled elsewhere (un-quantised BF16 extension); uniform for the CTA
+  StepPlan plan;
+  plan.build(pair, rows, w8, w4);
+  const int nsteps = plan.steps();
+  const bool need_q4 = plan.n4 > 0;
+
+  if (tid == 0) {
+    mbar_init(&bar_q, 1); mbar_init(&bar_kv[0], 1); mbar_init(&bar_kv[1], 1); mbar_init(&bar_s, 1); mbar_init(&bar_d, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(&tmem_slot, TmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+
+  auto issue_loads = [&](int i) {   // thread 0 only
+    int tile, mode, mask;
+    plan.get(i, tile, mode, mask);
+    const int s = i & 1;
+    const int64_t ht = kvunit * tiles + tile;
+    const uint32_t vbytes = mode == ModeF16 ? V16Bytes : V8Bytes;
+    mbar_expect_tx(&bar_kv[s], K8Bytes + vbytes);
+    bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bar_kv[s]);
+    bulk_g2s(smem + SmV + s * V16Bytes, mode == ModeF16 ? v16 + ht * V16Bytes : v8 + ht * V8Bytes, vbytes, &bar_kv[s]);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&bar_q, need_q4 ? 32768u : 16384u);
+    tma_load_3d(smem + SmQ8, &map_q8, 0, plan.b0 * BM, qunit, &bar_q);
+    if (need_q4) tma_load_3d(smem + SmQ4, &map_q4, 0, plan.b0 * BM, qunit, &bar_q);
+    issue_loads(0);
+  }
+
+  // per-row state (thread = row)
+  const int bh = plan.b0 + half, qi = bh * BM + (tid & 63);
+  const bool row_valid = (half == 0 || plan.has1) && qi < tokens;
+  const int64_t qrow = (int64_t)qunit * tokens + qi;
+  const float qs8 = row_valid ? qa8[qrow] * sm_log2 : FLT_MIN;
+  const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
+  float o[D];
+#pragma unroll
+  for (int j = 0; j < D; ++j) o[j] = 0.f;
+  float m = -FLT_MAX, denom = 0.f, corr = 0.f;
+  int n8seen = 0;
+  uint32_t ph_s = 0, ph_d = 0, ph_kv[2] = {0, 0};
+  bool ok = true;
+  const uint32_t q8_addr = smem_u32(smem + SmQ8), q4_addr = smem_u32(smem + SmQ4), p_addr = smem_u32(smem + SmP);
+  uint8_t* prow8 = smem + SmP + (tid / 8) * 512 + (tid % 8) * 16;     // u8 P row: core matrices [row/8][key/16]
+  uint8_t* prow16 = smem + SmP + (tid / 8) * 1024 + (tid % 8) * 16;   // fp16 P row: core matrices [row/8][key/8]
+
+  for (int i = 0; i < nsteps && ok; ++i) {
+    int tile, mode, mask;
+    plan.get(i, tile, mode, mask);
+    const int s = i & 1;
+    if (tid == 0) {
+      if (i + 1 < nsteps) issue_loads(i + 1);
+      if (i == 0) ok = mbar_wait(&bar_q, 0);
+      ok = ok && mbar_wait(&bar_kv[s], ph_kv[s]);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t qa_ = mode == ModeQ4 ? q4_addr : q8_addr, ka_ = smem_u32(smem + SmK + s * K8Bytes);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_i8(tmem + TmemS, smem_desc(qa_ + kk * 32, 0, 1024, Layout128B), smem_desc(ka_ + kk * 256, 128, 1024, LayoutNone),
+                  IdescQK, kk > 0);
+        tc_commit(&bar_s);
+      }
+    }
+    ph_kv[s] ^= 1;
+    __syncwarp();
+    ok = mbar_wait(&bar_s, ph_s);
+    ph_s ^= 1;
+    // thread 0 may have failed before the commit; make the decision uniform
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after();
+
+    const bool active = (mask >> half) & 1;
+    const bool diag = tile == bh;
+    const float qs = mode == ModeQ4 ? qs4 : qs8;
+    const float* kscale = (mode == ModeQ4 ? ka4 : ka8) + (kvunit * tiles + tile) * 4;
+    float ks[4] = {__ldg(kscale), __ldg(kscale + 1), __ldg(kscale + 2), __ldg(kscale + 3)};
+    float bq = 0.f;
+    if (active) {
+      // pass 1 over the score row: scaled tile maximum (prefill_sm80.cu:244-253)
+      float tmax = -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t a[16];
+        tmem_ld16(lane_base + TmemS + c * 16, a);
+        tmem_ld_wait();
+        int mx = INT_MIN;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int key = tile * BN + c * 16 + j;
+          const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
+          if (!dead) mx = max(mx, (int)a[j]);
+        }
+        if (mx != INT_MIN) tmax = fmaxf(tmax, qs * ks[c] * (float)mx);
+      }
+      const float n = fmaxf(m, tmax), alpha = exp2f(m - n);
+      m = n;
+      bool flush = false;
+      if (mode != ModeF16) { flush = (n8seen % 16) == 15; ++n8seen; }
+      if (flush || alpha != 1.f) {   // prefill_sm80.cu:350-357
+        const float shift = -corr * alpha;
+#pragma unroll
+        for (int j = 0; j < D; ++j) o[j] = fmaf(o[j], alpha, shift);
+        corr = 0.f;
+      }
+      if (mode == ModeF16) {
+        denom *= alpha;
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t a[16];
+          tmem_ld16(lane_base + TmemS + c * 16, a);
+          tmem_ld_wait();
+          const float slope = qs * ks[c], off = fmaf(-slope, 12582912.f, -m);
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            float e[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int key = tile * BN + c * 16 + j + u;
+              const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
+              e[u] = dead ? 0.f : exp2f(fmaf(slope, __int_as_float((int)a[j + u] + Magic), off));
+            }
+            const __half2 hp = __floats2half2_rn(e[0], e[1]);
+            sum += __low2float(hp) + __high2float(hp);
+            w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+          *reinterpret_cast<uint4*>(prow16 + (2 * c) * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(prow16 + (2 * c + 1) * 128) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        denom += sum;
+      } else {
+        // prefill_sm80.cu:386-414
+        const float ks_max = fmaxf(fmaxf(ks[0], ks[1]), fmaxf(ks[2], ks[3]));
+        float base = tmax > -CUDART_INF_F ? tmax : m;
+        base += tile_base_margin(qs * ks_max, base);
+        bq = exp2f(base - m) / 255.f;
+        int rs = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t a[16];
+          tmem_ld16(lane_base + TmemS + c * 16, a);
+          tmem_ld_wait();
+          const float slope = qs * ks[c];
+          const float off = mode == ModeQ4 ? -base : fmaf(-slope, 12582912.f, -base);
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int key = tile * BN + c * 16 + j;
+            const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
+            const float x = mode == ModeQ4 ? (float)(int)a[j] : __int_as_float((int)a[j] + Magic);
+            const float e = dead ? 0.f : exp2f(fmaf(slope, x, off));
+            w[j] = __float_as_uint(fmaf(e, 255.f, PMagicHalf));
+          }
+          uint32_t pw[4];
+#pragma unroll
+          for (int sidx = 0; sidx < 4; ++sidx) {   // byte 4s+b of the run holds key kperm(s,b), like the V8 blob
+            pw[sidx] = pack_bytes(w[2 * sidx], w[2 * sidx + 1], w[2 * sidx + 8], w[2 * sidx + 9]);
+            rs = (int)__dp4a(pw[sidx], 0x01010101u, (uint32_t)rs);
+          }
+          *reinterpret_cast<uint4*>(prow8 + c * 128) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        }
+        denom = fmaf((float)rs, bq, denom * alpha);
+        corr = fmaf(12582912.f, bq, corr);
+      }
+    }
+    // rows of an idle half keep stale P bytes: each output row depends only on its own P row, and idle
+    // rows never read their accumulators
+    fence_proxy_async_smem();   // P (generic-proxy stores) must be visible to the tensor core's async proxy
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t va = smem_u32(smem + SmV + s * V16Bytes);
+      if (mode == ModeF16) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16(tmem + TmemD, smem_desc(p_addr + kk * 256, 128, 1024, LayoutNone), smem_desc(va + kk * 256, 128, 1024, LayoutNone),
+                   IdescPV16, kk > 0);
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)
+          umma_i8(tmem + TmemD, smem_desc(p_addr + kk * 256, 128, 512, LayoutNone), smem_desc(va + kk * 256, 128, 512, LayoutNone),
+                  IdescPV8, kk > 0);
+      }
+      tc_commit(&bar_d);
+    }
+    __syncwarp();
+    ok = mbar_wait(&bar_d, ph_d);
+    ph_d ^= 1;
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tc_fence_after();
+    if (active) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t a[16];
+        tmem_ld16(lane_base + TmemD + c * 16, a);
+        tmem_ld_wait();
+        if (mode == ModeF16) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[c * 16 + j] += __uint_as_float(a[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[c * 16 + j] = fmaf(__int_as_float((int)a[j] + Magic), bq, o[c * 16 + j]);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();   // S, D, P and this K/V stage are free again
+  }
+
+  if (!ok && tid == 0) atomicExch(err, ErrBarrierTimeout);
+  if (ok && row_valid) {
+    // prefill_sm80.cu:466-487
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    const float* mean = vstat + kvunit * StatFloats;
+    const float* scale = mean + D;
+    Out* dst = out + b * osb + h * osh + (int64_t)qi * ost;
+#pragma unroll
+    for (int c = 0; c < D; c += 8) {
+      Out vals[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[j] = to_out<Out>(fmaf((o[c + j] - corr) * inv, __ldg(scale + c + j), __ldg(mean + c + j)));
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(vals);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TmemCols);
+}
+
+// ---- integer QK^T accumulators of chosen (Q unit, pair, tile) through the production operand path ---
+// grid = requests, 128 threads.  req = {qunit, pair, tile, four_bit}; writes int32 [req][128][64].
+__global__ void __launch_bounds__(PrefillThreads) qk_accum_kernel(const __grid_constant__ CUtensorMap map_q8,
+    const __grid_constant__ CUtensorMap map_q4, const int4* req, const uint8_t* k8, const uint8_t* k4x, int32_t* acc, int heads_q,
+    int heads_kv, int tokens, int* err) {
+  extern __shared__ uint8_t raw_smem[];
+  __shared__ __align__(8) uint64_t bar_ld, bar_s;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
+  const int tid = threadIdx.x, warp = tid / 32;
+  const int4 r = req[blockIdx.x];
+  const int tiles = (tokens + BN - 1) / BN, g = heads_q / heads_kv;
+  const int64_t kvunit = (int64_t)(r.x / heads_q) * heads_kv + (r.x % heads_q) / g;
+  if (tid == 0) { mbar_init(&bar_ld, 1); mbar_init(&bar_s, 1); mbar_fence_init(); }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(&bar_ld, 16384u + K8Bytes);
+    tma_load_3d(smem, r.w ? &map_q4 : &map_q8, 0, r.y * 2 * BM, r.x, &bar_ld);
+    bulk_g2s(smem + 16384, (r.w ? k4x : k8) + (kvunit * tiles + r.z) * K8Bytes, K8Bytes, &bar_ld);
+    ok = mbar_wait(&bar_ld, 0);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t qa_ = smem_u32(smem), ka_ = smem_u32(smem + 16384);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_i8(tmem, smem_desc(qa_ + kk * 32, 0, 1024, Layout128B), smem_desc(ka_ + kk * 256, 128, 1024, LayoutNone), IdescQK, kk > 0);
+      tc_commit(&bar_s);
+    }
+  }
+  __syncwarp();
+  ok = mbar_wait(&bar_s, 0);
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    tc_fence_after();
+    int32_t* dst = acc + ((int64_t)blockIdx.x * 128 + tid) * 64;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t a[16];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c * 16, a);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) dst[c * 16 + j] = (int)a[j];
+    }
+  } else if (tid == 0) {
+    atomicExch(err, ErrBarrierTimeout);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 64);
+}
+
+// ---- generic single-tile tensor-core probe: D[128 x n] = A . B^T from caller-built operand images ---
+// One CTA.  The images are copied verbatim to 1024-byte aligned shared memory; descriptor fields come
+// from the caller so that the tests can pin the layout conventions used above.
+__global__ void __launch_bounds__(PrefillThreads) umma_probe_kernel(const uint8_t* a_img, int a_bytes, const uint8_t* b_img,
+    int b_bytes, uint32_t a_lbo, uint32_t a_sbo, uint32_t a_layout, uint32_t a_step, uint32_t b_lbo, uint32_t b_sbo,
+    uint32_t b_layout, uint32_t b_step, uint32_t idesc, int f16_kind, int ksteps, int ncols, uint32_t* out, int* err) {
+  extern __shared__ uint8_t raw_smem[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
+  const int tid = threadIdx.x, warp = tid / 32;
+  for (int i = tid; i < a_bytes / 16; i += PrefillThreads) reinterpret_cast<uint4*>(smem)[i] = reinterpret_cast<const uint4*>(a_img)[i];
+  for (int i = tid; i < b_bytes / 16; i += PrefillThreads)
+    reinterpret_cast<uint4*>(smem + 32768)[i] = reinterpret_cast<const uint4*>(b_img)[i];
+  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  if (tid == 0) {
+    const uint32_t aa = smem_u32(smem), ba = smem_u32(smem + 32768);
+    for (int kk = 0; kk < ksteps; ++kk) {
+      const uint64_t ad = smem_desc(aa + kk * a_step, a_lbo, a_sbo, a_layout), bd = smem_desc(ba + kk * b_step, b_lbo, b_sbo, b_layout);
+      if (f16_kind) umma_f16(tmem, ad, bd, idesc, kk > 0);
+      else umma_i8(tmem, ad, bd, idesc, kk > 0);
+    }
+    tc_commit(&bar);
+  }
+  __syncwarp();
+  bool ok = mbar_wait(&bar, 0);
+  ok = __syncthreads_and(ok);
+  if (ok) {
+    tc_fence_after();
+    for (int c = 0; c < ncols / 16; ++c) {
+      uint32_t a[16];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c * 16, a);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) out[(int64_t)tid * ncols + c * 16 + j] = a[j];
+    }
+  } else if (tid == 0) {
+    atomicExch(err, ErrBarrierTimeout);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+
+// int8 rows [units][tokens][128]: box = 128 rows x 128 bytes of one unit, 128-byte swizzle, rows past
+// `tokens` are filled with zeros by the copy engine.
+static int make_q_map(CUtensorMap* map, const void* base, int tokens, int units) {
+  EncodeTiled enc = encode_fn();
+  TRI_CHECK(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)tokens, (cuuint64_t)units};
+  const cuuint64_t strides[2] = {(cuuint64_t)D, (cuuint64_t)tokens * D};
+  const cuuint32_t box[3] = {(cuuint32_t)D, 128u, 1u}, estr[3] = {1u, 1u, 1u};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TRI_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for the Q operand");
+  return TRI_OK;
+}
+
+template <typename K> static int allow_smem(K kernel, int bytes) {
+  TRI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attribute");
+  return TRI_OK;
+}
+
+}  // namespace tri
+
+using namespace tri;
+
+extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8, const float* vstat, const void* q8,
+    const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4, const float* ka4,
+    void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
+    int heads_kv, int tokens, double scale, int* device_error, void* stream) {
+  TRI_CHECK(bands && v16 && vstat && q8 && k8 && qa8 && ka8 && out && device_error, "attention: null buffers");
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && tokens > 0, "attention: bad geometry");
+  TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
+  const bool int4 = q4x != nullptr;
+  TRI_CHECK(int4 == (k4x != nullptr) && int4 == (qa4 != nullptr) && int4 == (ka4 != nullptr), "INT4 Q/K operands (all or none)");
+  TRI_CHECK(aligned16(out) && out_stride_t % 8 == 0 && out_stride_h % 8 == 0 && out_stride_b % 8 == 0,
+            "output [B,Hq,T,128] aligned");
+  TRI_CHECK(aligned16(q8) && aligned16(q4x) && aligned16(k8) && aligned16(k4x) && aligned16(v16) && aligned16(v8),
+            "attention: operands must be 16-byte aligned");
+  static int configured = 0;
+  if (!configured) {
+    if (allow_smem(prefill_kernel<__nv_bfloat16>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    if (allow_smem(prefill_kernel<__half>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    configured = 1;
+  }
+  const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, pairs = (rows + 1) / 2;
+  CUtensorMap map8, map4;
+  if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
+  if (make_q_map(&map4, int4 ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const float sm_log2 = (float)(scale * 1.4426950408889634);
+  const dim3 grid((unsigned)((int64_t)pairs * units));
+#define TRI_LAUNCH(T)                                                                                                      \
+  prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, bands, static_cast<const uint8_t*>(k8),       \
+      static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8), qa8, \
+      qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, heads_q, heads_kv, tokens, units,       \
+      sm_log2, device_error)
+  if (out_is_half) TRI_LAUNCH(__half); else TRI_LAUNCH(__nv_bfloat16);
+#undef TRI_LAUNCH
+  return tri_launch_status("attention");
+}
+
+extern "C" int tri_qk_accumulators(const int32_t* requests, int num_requests, const void* q8, const void* q4x, const void* k8,
+    const void* k4x, int32_t* acc, int batch, int heads_q, int heads_kv, int tokens, int* device_error, void* stream) {
+  TRI_CHECK(requests && q8 && k8 && acc && device_error && num_requests > 0, "qk_accumulators: null buffers");
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && tokens > 0, "qk_accumulators: bad geometry");
+  static int configured = 0;
+  if (!configured) {
+    if (allow_smem(qk_accum_kernel, 16384 + K8Bytes + 1024) != TRI_OK) return TRI_ERR_CUDA;
+    configured = 1;
+  }
+  const int units = batch * heads_q;
+  CUtensorMap map8, map4;
+  if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
+  if (make_q_map(&map4, q4x ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
+  qk_accum_kernel<<<num_requests, PrefillThreads, 16384 + K8Bytes + 1024, static_cast<cudaStream_t>(stream)>>>(map8, map4,
+      reinterpret_cast<const int4*>(requests), static_cast<const uint8_t*>(k8), static_cast<const uint8_t*>(k4x ? k4x : k8), acc,
+      heads_q, heads_kv, tokens, device_error);
+  return tri_launch_status("qk_accumulators");
+}
+
+extern "C" int tri_umma_probe(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint32_t a_lbo, uint32_t a_sbo,
+    uint32_t a_layout, uint32_t a_step, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_layout, uint32_t b_step, uint32_t idesc,
+    int f16_kind, int ksteps, int ncols, uint32_t* out, int* device_error, void* stream) {
+  TRI_CHECK(a_img && b_img && out && device_error, "umma_probe: null buffers");
+  TRI_CHECK(a_bytes > 0 && a_bytes <= 32768 && b_bytes > 0 && b_bytes <= 32768 && a_bytes % 16 == 0 && b_bytes % 16 == 0 &&
+            ksteps > 0 && ksteps <= 8 && ncols >= 16 && ncols <= 256 && ncols % 16 == 0, "umma_probe: sizes");
+  static int configured = 0;
+  if (!configured) {
+    if (allow_smem(umma_probe_kernel, 65536 + 1024) != TRI_OK) return TRI_ERR_CUDA;
+    configured = 1;
+  }
+  umma_probe_kernel<<<1, PrefillThreads, 65536 + 1024, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(a_img),
+      a_bytes, static_cast<const uint8_t*>(b_img), b_bytes, a_lbo, a_sbo, a_layout, a_step, b_lbo, b_sbo, b_layout, b_step, idesc,
+      f16_kind, ksteps, ncols, out, device_error);
+  return tri_launch_status("umma_probe");
+}

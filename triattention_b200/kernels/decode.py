@@ -1,0 +1,182 @@
+"""Decode cache: per-(sequence, KV head) byte streams of kept tiles, a byte-balanced work list, the
+BF16 tail of generated tokens, and the decode step.
+
+Mirrors ``triattention/kernels/decode.py`` (``DecodeCache(module, max_tail)``, ``codes``, ``store``,
+``__call__``, ``advance``, ``stored``).  The tile-state rules are the reference's
+(``decode.py:28-36``): tile 0 and tiles closer than ``w8`` to the end keep INT8 K, tiles closer than
+``w4`` keep INT4 K, the rest are dropped; a KV head keeps the widest state of its Q heads and a row
+mask says which Q heads attend; V is INT8 for tile 0 and the last 16 tiles, INT4 elsewhere
+(``decode.py:17-22``).  What differs is the data structure: the reference compacts tiles into four
+dense arrays with host-side argsort/cumsum and splits by a fixed tile count; here each unit is one
+contiguous byte stream (K blob, V blob, K scales per tile) filled by one gather kernel, and splits
+are cut by bytes so that INT8 / INT4 / BF16 units cost the same per work item.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from triattention_b200.kernels.prefill import I4, I8
+
+NEAR_V8 = 16
+K8_BYTES, K4_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 8192, 4096
+BF16_CHUNK_KEYS, BF16_CHUNK_BYTES = 32, 16384
+INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16 = 12, 1 << 20, 1 << 21, 1 << 22
+MAX_GROUP = 8
+
+
+def tile_states(bands, heads_kv, tiles):
+    """decode.py:28-36 -> (kv state [Hkv,tiles] in {0,4,8}, rowmask [Hkv,tiles])."""
+    b = np.asarray(bands, np.int64)
+    j = np.arange(tiles)
+    w8, w4, d = b[:, :1], b[:, 1:], (tiles - 1) - j[None, :]
+    state = np.where((j[None, :] == 0) | (d < w8), 8, np.where(d < w4, 4, 0)).reshape(heads_kv, -1, tiles)
+    rowmask = ((state > 0).astype(np.int64) << np.arange(state.shape[1])[None, :, None]).sum(1)
+    return state.max(1), rowmask
+
+
+def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=444, waves=3.0, min_tiles=4):
+    """Host-side layout of one layer's cache and its work list (numpy, a few microseconds per head).
+
+    Returns a dict of numpy arrays: tmeta [N,2], tab_begin/count/head_bytes [Hkv], unit_base [U] (int64),
+    unit_tab/unit_count/unit_flags [U], work [W,4], unit_slots [U,2], plus totals.
+    """
+    tiles = (prompt + 63) // 64
+    kv, rowmask = tile_states(bands, heads_kv, tiles)
+    j = np.arange(tiles)
+    v4 = ~((tiles - 1 - j < NEAR_V8) | (j == 0))
+    metas, sizes, tab_begin, count, head_bytes = [], [], [], [], []
+    for kh in range(heads_kv):
+        if kh in bf16_kv:
+            n = (prompt + BF16_CHUNK_KEYS - 1) // BF16_CHUNK_KEYS
+            info = np.arange(n, dtype=np.int64) | (0xFF << INFO_ROW_SHIFT) | INFO_BF16
+            size = np.full(n, BF16_CHUNK_BYTES, np.int64)
+        else:
+            kept = np.nonzero(kv[kh] > 0)[0]
+            k4 = kv[kh][kept] == 4
+            info = kept | ((rowmask[kh][kept] & 0xFF) << INFO_ROW_SHIFT) | np.where(k4, INFO_K4, 0) | np.where(v4[kept], INFO_V4, 0)
+            size = np.where(k4, K4_BYTES, K8_BYTES) + np.where(v4[kept], V4_BYTES, V8_BYTES) + 16
+        off = np.concatenate([[0], np.cumsum(size)])
+        tab_begin.append(sum(len(m) for m in metas))
+        metas.append(np.stack([off[:-1] // 16, info], 1))
+        sizes.append(size)
+        count.append(len(size))
+        head_bytes.append(int(-(-off[-1] // 128) * 128))
+    tmeta = np.concatenate(metas).astype(np.int32)
+    head_off = np.concatenate([[0], np.cumsum(head_bytes)])
+    seq_bytes = int(head_off[-1])
+    units = batch * heads_kv
+    kh_of = np.arange(units) % heads_kv
+    unit_base = (np.arange(units) // heads_kv).astype(np.int64) * seq_bytes + head_off[kh_of]
+    unit_flags = np.isin(kh_of, list(bf16_kv)).astype(np.int32)
+    # work list: cut every unit into pieces of about `target` bytes
+    total = batch * seq_bytes
+    target = max(total / max(1.0, ctas * waves), 1.0)
+    pieces = []       # per kv head: list of (first, count, bytes)
+    for kh in range(heads_kv):
+        n = count[kh]
+        csum = np.concatenate([[0], np.cumsum(sizes[kh])])
+        nsplit = int(np.clip(round(csum[-1] / target), 1, max(1, n // min_tiles)))
+        cuts = np.searchsorted(csum, np.arange(1, nsplit) * (csum[-1] / nsplit)) if nsplit > 1 else np.zeros(0, np.int64)
+        edges = np.unique(np.concatenate([[0], cuts, [n]]))
+        pieces.append([(int(a), int(e - a), int(csum[e] - csum[a])) for a, e in zip(edges[:-1], edges[1:]) if e > a])
+    nsplit = np.array([len(p) for p in pieces])
+    slot_begin = np.concatenate([[0], np.cumsum(nsplit[kh_of])])
+    rows, weights = [], []
+    for u in range(units):
+        for s, (first, cnt, nbytes) in enumerate(pieces[kh_of[u]]):
+            rows.append((u, first, cnt, slot_begin[u] + s))
+            weights.append(nbytes)
+    order = np.argsort(-np.asarray(weights), kind="stable")
+    work = np.asarray(rows, np.int32).reshape(-1, 4)[order]
+    return dict(tmeta=tmeta, tab_begin=np.asarray(tab_begin, np.int32), count=np.asarray(count, np.int32),
+                head_bytes=np.asarray(head_bytes, np.int64), unit_base=unit_base,
+                unit_tab=np.asarray(tab_begin, np.int32)[kh_of], unit_count=np.asarray(count, np.int32)[kh_of],
+                unit_flags=unit_flags, work=np.ascontiguousarray(work),
+                unit_slots=np.stack([slot_begin[:-1], nsplit[kh_of]], 1).astype(np.int32), slots=int(slot_begin[-1]),
+                pool_bytes=int(total), seq_bytes=seq_bytes, tiles=tiles,
+                payload_bytes=int(batch * sum(int(s.sum()) for s in sizes)))
+
+
+class DecodeCache:
+    def __init__(self, module, max_tail=256):
+        if not 1 <= max_tail <= 1024:
+            raise ValueError("max_tail must be in 1..1024")
+        self.module, self.max_tail = module, max_tail
+        self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
+        self._wave = None
+
+    def codes(self, rows):
+        """decode.py:17-22: V format per prompt tile in decode, and the set of formats used."""
+        if rows not in self.formats:
+            j = torch.arange(rows)
+            codes = torch.where((rows - 1 - j < NEAR_V8) | (j == 0), I8, I4)
+            self.formats[rows] = codes, frozenset(codes.unique().tolist())
+        return self.formats[rows]
+
+    @staticmethod
+    def needs_k4(bands, heads_kv, rows, bf16_kv=()):
+        kv, _ = tile_states(np.asarray(bands), heads_kv, rows)
+        quant = [kh for kh in range(heads_kv) if kh not in bf16_kv]
+        return bool((kv[quant] == 4).any()) if quant else False
+
+    def wave(self, device):
+        if self._wave is None:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            self._wave = sms * max(1, self.module.decode_occupancy())
+        return self._wave
+
+    def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device):
+        key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device))
+        if key not in self.plans:
+            host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device))
+            dev = {name: torch.from_numpy(host[name]).to(device) for name in
+                   ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "work", "unit_slots")}
+            if bf16_kv:
+                units = np.nonzero(host["unit_flags"])[0].astype(np.int32)
+                dev["bf16_units"] = torch.from_numpy(units).to(device)
+            self.plans[key] = host, dev
+        return self.plans[key]
+
+    def store(self, layer, prompt, ops, bands, k, v, bf16_kv=()):
+        """Build the layer's cache streams from the prefill operands (one gather launch, plus one for BF16 units)."""
+        batch, heads_kv, device = k.shape[0], k.shape[1], k.device
+        host, dev = self.plan(bands, heads_kv, prompt, batch, bf16_kv, device)
+        entry = self.layers.get(layer)
+        if entry is None or entry["pool"].numel() != host["pool_bytes"] or entry["plan"] is not host:
+            units = batch * heads_kv
+            entry = self.layers[layer] = dict(
+                plan=host, dev=dev, prompt=prompt, pool=torch.empty(host["pool_bytes"], dtype=torch.uint8, device=device),
+                tail_k=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
+                tail_v=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
+                pm=torch.empty((host["slots"], MAX_GROUP), dtype=torch.float32, device=device),
+                pl=torch.empty((host["slots"], MAX_GROUP), dtype=torch.float32, device=device),
+                po=torch.empty((host["slots"], MAX_GROUP, 128), dtype=torch.float32, device=device))
+        entry["kstat"], entry["vstat"] = ops["kstat"].clone(), ops["vstat"].clone()
+        if self.step is None:
+            self.step = torch.zeros(1, dtype=torch.int64, device=device)
+        self.step.zero_()
+        max_count = int(host["count"].max())
+        self.module.cache_store(entry["pool"], dev["unit_base"], dev["unit_tab"], dev["unit_count"], dev["unit_flags"],
+                                dev["tmeta"], batch * heads_kv, max_count, ops["k8"], ops["k4"], ops["ka"], ops["ka4"],
+                                ops["v8"], ops["v4"], host["tiles"])
+        if bf16_kv:
+            self.module.cache_store_bf16(entry["pool"], dev["unit_base"], dev["bf16_units"], k, v)
+            ident = torch.tensor([0.0, 1.0, 1.0], device=device)[None, :, None]
+            entry["kstat"][dev["bf16_units"].long()] = ident
+            entry["vstat"][dev["bf16_units"].long()] = ident
+
+    def __call__(self, layer, q, k, v, scale):
+        e = self.layers[layer]
+        d = e["dev"]
+        out = torch.empty_like(q)
+        self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["work"],
+                           d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out,
+                           e["pm"], e["pl"], e["po"], e["prompt"], scale)
+        return out
+
+    def advance(self):
+        self.step.add_(1)
+
+    def stored(self, layer):
+        return layer in self.layers

@@ -1,0 +1,205 @@
+"""Loader and thin Python shim over the sm_100a C-ABI library.
+
+Mirrors ``triattention/kernels/extension.py:28-54`` (``load_extension()`` returns an object with
+``prepare_qk``, ``pack_v``, ``attention``, ``decode`` and ``decode_occupancy``), but the library is built
+ahead of time for sm_100a only (``python -m triattention_b200.build``) and bound with ctypes: no JIT, no
+architecture dispatch, no CPU fallback.  A missing library or a missing GPU is an error, raised as
+``RuntimeError`` like the reference does (``extension.py:15-19``).
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+from pathlib import Path
+
+import torch
+
+LIBRARY = Path(__file__).resolve().parent.parent / "libtriattn_sm100a.so"
+
+_P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_double, ctypes.c_uint32
+
+# name -> argtypes, in the order of include/triattention_b200.h
+SIGNATURES = {
+    "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P],
+    "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
+    "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _P],
+    "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
+                   _P, _P, _P, _I, _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_occupancy": [],
+    "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "tri_umma_probe": [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, _P, _P],
+    "tri_abi_version": [],
+}
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen the library and declare every entry point (no GPU needed for this)."""
+    if not LIBRARY.is_file():
+        raise RuntimeError(f"{LIBRARY.name} is missing: build it with `python -m triattention_b200.build` "
+                           "(there is no CPU or PyTorch fallback)")
+    lib = ctypes.CDLL(str(LIBRARY))
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = argtypes, ctypes.c_int
+    lib.tri_last_error.argtypes, lib.tri_last_error.restype = [], ctypes.c_char_p
+    return lib
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Module:
+    """The five reference method names (batched), plus the cache-store and parity helpers."""
+
+    def __init__(self, lib):
+        self.lib = lib
+        self._errors = {}
+
+    # -- plumbing ------------------------------------------------------------------------------
+    def _check(self, status):
+        if status < 0:
+            raise RuntimeError(self.lib.tri_last_error().decode())
+        return status
+
+    def error_word(self, device):
+        key = torch.device(device).index or 0
+        if key not in self._errors:
+            self._errors[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._errors[key]
+
+    def check_device_error(self, device="cuda"):
+        """Synchronise and raise if a kernel reported a bounded wait that ran out."""
+        word = int(self.error_word(device).item())
+        if word:
+            self.error_word(device).zero_()
+            raise RuntimeError(f"TriAttention kernel reported device error {word} (1 = barrier wait ran out)")
+
+    @staticmethod
+    def _bhtd(x, name):
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.shape[3] == 128 and x.stride(3) == 1):
+            raise RuntimeError(f"BF16 {name} [B,H,T,128] with contiguous features")
+        return x
+
+    # -- reference surface ---------------------------------------------------------------------
+    def prepare_qk(self, q, k, q8, qa, k8, ka, partial, kstat, q4x=None, qa4=None, k4x=None, ka4=None, k4=None):
+        self._bhtd(q, "Q"), self._bhtd(k, "K")
+        b, hq, t, _ = q.shape
+        hk, tiles = k.shape[1], (t + 63) // 64
+        if k.shape[0] != b or k.shape[2] != t or hq % hk:
+            raise RuntimeError("BF16 Q/K [B,H,T,128] with contiguous features")
+        if not (q8.numel() == b * hq * t * 128 and qa.numel() == b * hq * t and k8.numel() == b * hk * tiles * 8192 and
+                ka.numel() == b * hk * tiles * 4 and partial.numel() >= b * hk * 64 * 3 * 128 and
+                kstat.numel() == b * hk * 3 * 128):
+            raise RuntimeError("Q/K buffers")
+        int4 = q4x is not None
+        if not (int4 == (qa4 is not None) == (k4x is not None) == (ka4 is not None)) or (k4 is not None and not int4):
+            raise RuntimeError("INT4 Q/K buffers (all or none)")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_prepare_qk(q.data_ptr(), k.data_ptr(), b, hq, hk, t, q.stride(0), q.stride(1),
+                                                q.stride(2), k.stride(0), k.stride(1), k.stride(2), q8.data_ptr(),
+                                                qa.data_ptr(), k8.data_ptr(), ka.data_ptr(), partial.data_ptr(),
+                                                kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4), _ptr(ka4),
+                                                _stream()))
+
+    def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None):
+        self._bhtd(v, "V")
+        b, hk, t, _ = v.shape
+        tiles = (t + 63) // 64
+        for buf, size in ((v16, 16384), (v8, 8192), (v4, 4096)):
+            if buf is not None and buf.numel() * buf.element_size() != b * hk * tiles * size:
+                raise RuntimeError("packed V size")
+        if partial.numel() < b * hk * 64 * 3 * 128 or vstat.numel() != b * hk * 3 * 128:
+            raise RuntimeError("V statistics buffers")
+        with torch.cuda.device(v.device):
+            self._check(self.lib.tri_pack_v(v.data_ptr(), b, hk, t, v.stride(0), v.stride(1), v.stride(2),
+                                            partial.data_ptr(), vstat.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4), _stream()))
+
+    def attention(self, bands, v16, v8, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
+        if not (out.dim() == 4 and out.stride(3) == 1 and out.dtype in (torch.bfloat16, torch.float16)):
+            raise RuntimeError("output [B,Hq,T,128] aligned")
+        b, hq, t, _ = out.shape
+        if bands.dtype != torch.int32 or bands.numel() != hq * 2 or not bands.is_contiguous():
+            raise RuntimeError("bands [Hq,2] or task tables")
+        with torch.cuda.device(out.device):
+            self._check(self.lib.tri_attention(bands.data_ptr(), _ptr(v16), _ptr(v8), vstat.data_ptr(), q8.data_ptr(),
+                                               k8.data_ptr(), qa8.data_ptr(), ka8.data_ptr(), _ptr(q4x), _ptr(k4x),
+                                               _ptr(qa4), _ptr(ka4), out.data_ptr(), int(out.dtype == torch.float16),
+                                               out.stride(0), out.stride(1), out.stride(2), b, hq, heads_kv, t,
+                                               float(scale), self.error_word(out.device).data_ptr(), _stream()))
+        return out
+
+    def cache_store(self, pool, unit_base, unit_tab, unit_count, unit_flags, tmeta, units, max_count, k8, k4, ka, ka4,
+                    v8, v4, tiles):
+        with torch.cuda.device(pool.device):
+            self._check(self.lib.tri_cache_store(pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
+                                                 unit_count.data_ptr(), unit_flags.data_ptr(), tmeta.data_ptr(), units,
+                                                 max_count, k8.data_ptr(), _ptr(k4), ka.data_ptr(), _ptr(ka4),
+                                                 v8.data_ptr(), _ptr(v4), tiles, _stream()))
+
+    def cache_store_bf16(self, pool, unit_base, units, k, v):
+        self._bhtd(k, "K"), self._bhtd(v, "V")
+        with torch.cuda.device(pool.device):
+            self._check(self.lib.tri_cache_store_bf16(pool.data_ptr(), unit_base.data_ptr(), units.data_ptr(),
+                                                      units.numel(), k.data_ptr(), v.data_ptr(), k.shape[2], k.shape[1],
+                                                      k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
+                                                      v.stride(2), _stream()))
+
+    def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, work, unit_slots, kstat, vstat, tail_k, tail_v,
+               kcur, vcur, step, out, pm, pl, po, prompt, scale):
+        if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1):
+            raise RuntimeError("q [B,Hq,1,128]")
+        b, hq = q.shape[0], q.shape[1]
+        hk, max_tail = kcur.shape[1], tail_k.shape[1]
+        if not (hq % hk == 0 and hq // hk <= 8 and max_tail <= 1024 and step.dtype == torch.int64 and step.is_cuda and
+                kcur.stride(3) == 1 and vcur.stride(1) == kcur.stride(1) and vcur.stride(0) == kcur.stride(0) and
+                work.dtype == torch.int32 and tmeta.dtype == torch.int32 and unit_base.dtype == torch.int64 and
+                tail_v.stride() == tail_k.stride() and out.stride(3) == 1):
+            raise RuntimeError("decode geometry/buffers")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_decode(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(),
+                                            unit_tab.data_ptr(), unit_flags.data_ptr(), tmeta.data_ptr(), work.data_ptr(),
+                                            work.shape[0], unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(),
+                                            tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), tail_k.stride(1),
+                                            kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
+                                            step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(),
+                                            pl.data_ptr(), po.data_ptr(), b, hq, hk, int(prompt), max_tail, float(scale),
+                                            self.error_word(q.device).data_ptr(), _stream()))
+        return out
+
+    def decode_occupancy(self):
+        return self._check(self.lib.tri_decode_occupancy())
+
+    # -- parity helpers --------------------------------------------------------------------------
+    def qk_accumulators(self, requests, q8, q4x, k8, k4x, batch, heads_q, heads_kv, tokens):
+        acc = torch.empty((requests.shape[0], 128, 64), dtype=torch.int32, device=q8.device)
+        with torch.cuda.device(q8.device):
+            self._check(self.lib.tri_qk_accumulators(requests.data_ptr(), requests.shape[0], q8.data_ptr(), _ptr(q4x),
+                                                     k8.data_ptr(), _ptr(k4x), acc.data_ptr(), batch, heads_q, heads_kv,
+                                                     tokens, self.error_word(q8.device).data_ptr(), _stream()))
+        return acc
+
+    def umma_probe(self, a_img, b_img, a_desc, b_desc, idesc, f16_kind, ksteps, ncols):
+        """a_desc/b_desc = (lbo bytes, sbo bytes, layout type, byte advance per K step)."""
+        out = torch.zeros((128, ncols), dtype=torch.int32, device=a_img.device)
+        with torch.cuda.device(a_img.device):
+            self._check(self.lib.tri_umma_probe(a_img.data_ptr(), a_img.numel(), b_img.data_ptr(), b_img.numel(), *a_desc,
+                                                *b_desc, idesc, int(f16_kind), ksteps, ncols, out.data_ptr(),
+                                                self.error_word(a_img.device).data_ptr(), _stream()))
+        return out
+
+
+@functools.cache
+def load_extension() -> Module:
+    if not torch.cuda.is_available():
+        raise RuntimeError("TriAttention requires a CUDA GPU.")
+    major, minor = torch.cuda.get_device_capability()
+    if major != 10:
+        raise RuntimeError(f"this build targets sm_100a (B200) only; found compute capability {major}.{minor}")
+    return Module(load_library())
