@@ -1,0 +1,278 @@
+"""Benchmark of the quantised-attention decode path (BASELINE config 2) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of one attention layer for the whole batch: Llama-3.2-3B-shaped layer
+(24 Q heads, 8 KV heads, head_dim 128), batch 32, one new token per sequence over a quantised KV cache of
+8192 tokens; map = seeded per-KV-head assignment, 4 INT8 / 2 INT4 / 2 BF16.  The cache is written by the
+product's own KV-write kernels from synthetic K/V (N(0,1) in bf16 with 1 % of the channels scaled x20).
+Under torchrun every rank runs the same per-GPU workload on its own sequences (weak scaling; units are
+independent, so there is no data-path collective).
+
+Printed JSON (one line, rank 0): value = tokens/s with all inputs resident in HBM; e2e = the same through
+the public DecodeCache call with host buffers (pinned H2D of q/k/v and D2H of the output inside the
+timed region); roofline = algorithmic cache bytes per launch / CUDA-event time of the split-KV kernel
+against the measured HBM copy peak; cpu_baseline = the CPU oracle port on a bounded sample.
+`--impl reference` times that CPU port alone (the reference has no CPU or sm_100 implementation of its
+own to run; its CUDA extension is used only as the parity oracle in the tests).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+INF = 1 << 20
+CONFIG = dict(workload="decode C2: 24 Q / 8 KV heads, head_dim 128, batch 32, cache 8192 tokens, one layer-step",
+              heads_q=24, heads_kv=8, batch=32, cache_tokens=8192, map="seed 1: 4 INT8 / 2 INT4 / 2 BF16 KV heads",
+              l2="inputs larger than L2 (551 MB of cache per step per GPU)")
+FALLBACK_HBM_GBS = 6650.0
+
+
+def kv_kinds(seed=1):
+    kinds = np.array(["int8"] * 4 + ["int4"] * 2 + ["bf16"] * 2)
+    return list(np.random.default_rng(seed).permutation(kinds))
+
+
+def synth(shape, seed, fraction=0.01, factor=20.0):
+    """N(0,1) [H,T,128] with round(fraction*H*128) channels scaled by `factor` for all tokens; bf16."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    h = shape[0]
+    pick = torch.randperm(h * 128, generator=g)[: int(round(fraction * h * 128))]
+    x.view(h, -1, 128)[pick // 128, :, pick % 128] *= factor
+    return x.to(torch.bfloat16)
+
+
+def peak_hbm():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()   # the exact child started above
+            self.proc.wait()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        rows = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
+        if not rows:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return dict(sm_mhz=float(np.median([int(r[0]) for r in rows])), sm_max_mhz=float(rows[0][1]), reasons=reasons,
+                    samples=len(rows))
+
+
+def build_cache(batch, seed0):
+    """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan)."""
+    from triattention_b200.kernels.decode import DecodeCache
+    from triattention_b200.kernels.extension import load_extension
+    from triattention_b200.kernels.prefill import Prefill
+    from triattention_b200.maps import per_kv_head
+    hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
+    module = load_extension()
+    cache = DecodeCache(module, max_tail=256)
+    pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
+    k = torch.empty((batch, hk, t, 128), dtype=torch.bfloat16, device="cuda")
+    v = torch.empty_like(k)
+    for b in range(batch):
+        k[b] = synth((hk, t, 128), 2 * (seed0 + b)).cuda()
+        v[b] = synth((hk, t, 128), 2 * (seed0 + b) + 1).cuda()
+    q = torch.zeros((1, 1, 1, 128), dtype=torch.bfloat16, device="cuda").expand(batch, hq, t, 128)   # Q does not enter the cache
+    table, ops = pre.write(0, q, k, v)
+    cache.store(0, t, ops, table.host, k, v, table.bf16_kv)
+    torch.cuda.synchronize()
+    pre.buffers.clear(), pre.views.clear()
+    del k, v, ops
+    torch.cuda.empty_cache()
+    return module, cache, cache.layers[0]["plan"]
+
+
+def timed(fn, steps, dist):
+    """`steps` calls of fn between barriers + synchronize; CUDA events; max over ranks.  Returns ms."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    stop.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = torch.tensor([start.elapsed_time(stop)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+class CpuPort:
+    """The CPU oracle port on one sequence of the workload: one decode step of 24 heads over 8192 cached tokens."""
+    SAMPLE = ("1 of the 32 sequences per step, one layer-step (24 heads over 8192 cached tokens); numpy/IEEE "
+              "restatement of the reference's CUDA arithmetic")
+
+    def __init__(self, threads):
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import triattention_oracle as orc
+        self.orc, self.threads = orc, threads
+        torch.set_num_threads(threads)
+        hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
+        self.kinds, self.g = kv_kinds(), hq // hk
+        self.k, self.v = synth((hk, t, 128), 0).float().numpy(), synth((hk, t, 128), 1).float().numpy()
+        self.bands = np.array([[1, INF] if kind == "int4" else [INF, INF] for kind in self.kinds for _ in range(self.g)], np.int64)
+        kstat = orc.channel_stats(self.k)
+        k8, ka, k4, ka4 = orc.quantize_k(self.k, kstat[:, 0])
+        vstat = orc.channel_stats(self.v)
+        v16, v8, v4 = orc.pack_v(self.v, vstat)
+        self.ops = dict(kstat=kstat, k8=k8, ka=ka, k4=k4, ka4=ka4, vstat=vstat, v16=v16, v8=v8, v4=v4)
+        self.qd = synth((hq, 1, 128), 7).float().numpy()[:, 0]
+        self.kc, self.vc = synth((hk, 1, 128), 8).float().numpy()[:, 0], synth((hk, 1, 128), 9).float().numpy()[:, 0]
+
+    def step(self):
+        orc, hk, t = self.orc, CONFIG["heads_kv"], CONFIG["cache_tokens"]
+        tk, tv = np.zeros((hk, 4, 128), np.float32), np.zeros((hk, 4, 128), np.float32)
+        out = orc.decode_step(self.qd, self.ops, self.bands, t, 128 ** -0.5, tk, tv, self.kc, self.vc, 0, 4, None)
+        for kh, kind in enumerate(self.kinds):     # BF16 heads: exact attention over the raw prompt
+            if kind == "bf16":
+                kk, vv = np.concatenate([self.k[kh], self.kc[kh][None]]), np.concatenate([self.v[kh], self.vc[kh][None]])
+                for h in range(kh * self.g, (kh + 1) * self.g):
+                    out[h] = orc.exact_decode(self.qd[h], kk, vv, 128 ** -0.5)
+        return out
+
+    def run(self, steps, warmup):
+        for _ in range(warmup):
+            self.step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            out = self.step()
+        seconds = time.perf_counter() - t0
+        assert np.isfinite(out).all()
+        return dict(value=steps / seconds, unit="tokens/s", cores=self.threads, kind="port", sample=self.SAMPLE), seconds
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    base, seconds = CpuPort(os.cpu_count() or 1).run(args.steps, args.warmup)
+    line = dict(metric="decode_tokens_per_s", value=base["value"], unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=seconds * 1e3 / args.steps, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG, impl="reference", cpu_baseline=base,
+                e2e=dict(value=base["value"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                note="the reference has no CPU path and no sm_100 kernel; this arm times the CPU oracle port of its arithmetic")
+    print(json.dumps(line))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--cpu-steps", type=int, default=10, help="timed steps of the CPU baseline leg (0 = skip)")
+    parser.add_argument("--batch", type=int, default=CONFIG["batch"],
+                        help="sequences per GPU; anything but 32 is a reduced case for profiler captures, flagged in the output")
+    args = parser.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
+    warmup = max(3, args.warmup)
+    module, cache, plan = build_cache(batch, seed0=rank * batch)
+    scale = 128 ** -0.5
+    # decode-step inputs: device-resident copies for `value`, pinned host copies for `e2e`
+    host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (rank * batch + b)) for b in range(batch)]).pin_memory()
+            for i, h in enumerate((hq, hk, hk))]
+    qd, kd, vd = (x.cuda() for x in host)
+    out = torch.empty_like(qd)
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    for i in range(warmup):
+        cache(0, qd, kd, vd, scale, out=out)
+    module.check_device_error()
+    with ClockSampler(local) as clocks:
+        ms_total = timed(lambda i: cache(0, qd, kd, vd, scale, out=out), args.steps, dist)
+        ms_kernel = timed(lambda i: cache(0, qd, kd, vd, scale, phases=1, out=out), args.steps, dist)
+
+        def e2e_step(i):
+            qd.copy_(host[0], non_blocking=True), kd.copy_(host[1], non_blocking=True), vd.copy_(host[2], non_blocking=True)
+            cache(0, qd, kd, vd, scale, out=out)
+            out_host.copy_(out, non_blocking=True)
+        for i in range(3):
+            e2e_step(i)
+        ms_e2e = timed(e2e_step, args.steps, dist)
+    module.check_device_error()
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+    tokens = batch * world
+    peak, peak_kind = peak_hbm()
+    bytes_per_launch = plan["payload_bytes"]
+    kernel_s = ms_kernel / args.steps / 1e3
+    achieved = bytes_per_launch / kernel_s / 1e9
+    line = dict(metric="decode_tokens_per_s", value=tokens * args.steps / (ms_total / 1e3), unit="tokens/s", n_gpus=world,
+                steps=args.steps, warmup=warmup, ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG,
+                e2e=dict(value=tokens * args.steps / (ms_e2e / 1e3), unit="tokens/s",
+                         h2d_bytes_per_step=sum(x.numel() * 2 for x in host), d2h_bytes_per_step=out.numel() * 2),
+                gpu_launches=2 * args.steps,
+                roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
+                              kernel="decode_kernel", us_per_launch=kernel_s * 1e6, bytes_per_launch=bytes_per_launch,
+                              peak_source=f"{peak_kind} copy bandwidth", frac_of_8tbs=achieved / 8000.0,
+                              work_items=int(plan["work"].shape[0])),
+                hbm_gbs_whole_step=bytes_per_launch / (ms_total / args.steps / 1e3) / 1e9,
+                clocks=clocks.summary())
+    if batch != CONFIG["batch"]:
+        line["reduced_case"] = f"batch {batch} instead of {CONFIG['batch']}: not a benchmark value"
+    if args.cpu_steps > 0:
+        line["cpu_baseline"] = CpuPort(os.cpu_count() or 1).run(args.cpu_steps, 1)[0]
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

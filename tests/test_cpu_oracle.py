@@ -113,8 +113,9 @@ def test_decode_tables_rules():
 
 # ---- golden vectors from the reference's CUDA extension ------------------------------------------------
 # Allowance of this IEEE restatement against the fast-math kernels, frozen from the recorded vectors:
-# scales within 4 ulp, codes differ by at most one level on at most 0.2 % of the elements.
-SCALE_ULP, CODE_RATE = 4, 2e-3
+# measured: scales within 2 ulp, no differing code in the recorded cases.  Bound: 4 ulp, and codes may
+# differ by one level on at most 0.05 % of the elements (a scale that moved by an ulp flips a rounding tie).
+SCALE_ULP, CODE_RATE = 4, 5e-4
 
 
 @pytest.mark.parametrize("name", ["small", "c1"])
@@ -138,10 +139,10 @@ def test_oracle_matches_reference_golden(name):
             rate, big = code_mismatch(mine, g[key])
             assert big <= 1 and rate <= CODE_RATE, (key, rate, big)
     r = fp_report(orc.to_bf16(out)[:, ::keep], from_bits(g["out_bits"]))
-    assert r["worst_excess"] <= 0 and r["cos"] >= 0.9999, r
+    assert r["worst_excess"] <= 0 and r["cos"] >= 0.9999 and r["mean_abs"] <= ABS_TOL / 4, r
     for per in (2, 1000):
         tk, tv = np.zeros((hk, 8, 128), np.float32), np.zeros((hk, 8, 128), np.float32)
         for step in range(3):
             od = orc.decode_step(qd[:, step], ops, bands, t, scale, tk, tv, kd[:, step], vd[:, step], step, 8, per)
             r = fp_report(orc.to_bf16(od), from_bits(g[f"decode_bits_per{per}"][step]))
-            assert r["worst_excess"] <= 0 and r["cos"] >= 0.9999, (per, step, r)
+            assert r["worst_excess"] <= 0 and r["cos"] >= 0.9999 and r["mean_abs"] <= ABS_TOL / 4, (per, step, r)

@@ -460,7 +460,7 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
     const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v, int64_t tail_stride_u,
     int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b, int64_t cur_stride_h,
     const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po, int batch,
-    int heads_q, int heads_kv, int prompt, int max_tail, double scale, int* device_error, void* stream) {
+    int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases, int* device_error, void* stream) {
   TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && work && unit_slots && kstat && vstat && tail_k &&
             tail_v && kcur && vcur && step && out && pm && pl && po && device_error, "decode: null buffers");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
@@ -471,11 +471,12 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
-  if (num_work > 0)
+  if (num_work > 0 && (phases & 1))
     decode_kernel<<<num_work, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
         unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(work), pm, pl, po,
         heads_q, heads_kv, prompt, sm_log2, device_error);
-  decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
+  if (phases & 2)
+    decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
       kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
       tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),
       cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, heads_q, heads_kv,

@@ -166,13 +166,13 @@ class DecodeCache:
             entry["kstat"][dev["bf16_units"].long()] = ident
             entry["vstat"][dev["bf16_units"].long()] = ident
 
-    def __call__(self, layer, q, k, v, scale):
+    def __call__(self, layer, q, k, v, scale, phases=3, out=None):
         e = self.layers[layer]
         d = e["dev"]
-        out = torch.empty_like(q)
+        out = torch.empty_like(q) if out is None else out
         self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["work"],
                            d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out,
-                           e["pm"], e["pl"], e["po"], e["prompt"], scale)
+                           e["pm"], e["pl"], e["po"], e["prompt"], scale, phases)
         return out
 
     def advance(self):

@@ -26,7 +26,7 @@ SIGNATURES = {
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _P],
     "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
-                   _P, _P, _P, _I, _I, _I, _I, _I, _D, _P, _P],
+                   _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_umma_probe": [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, _P, _P],
@@ -152,7 +152,7 @@ class Module:
                                                       v.stride(2), _stream()))
 
     def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, work, unit_slots, kstat, vstat, tail_k, tail_v,
-               kcur, vcur, step, out, pm, pl, po, prompt, scale):
+               kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3):
         if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1):
             raise RuntimeError("q [B,Hq,1,128]")
         b, hq = q.shape[0], q.shape[1]
@@ -169,7 +169,7 @@ class Module:
                                             tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), tail_k.stride(1),
                                             kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
                                             step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(),
-                                            pl.data_ptr(), po.data_ptr(), b, hq, hk, int(prompt), max_tail, float(scale),
+                                            pl.data_ptr(), po.data_ptr(), b, hq, hk, int(prompt), max_tail, float(scale), int(phases),
                                             self.error_word(q.device).data_ptr(), _stream()))
         return out
 
