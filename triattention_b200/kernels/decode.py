@@ -99,10 +99,10 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=444, waves=3.0
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256):
+    def __init__(self, module, max_tail=256, waves=3.0):
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
-        self.module, self.max_tail = module, max_tail
+        self.module, self.max_tail, self.waves = module, max_tail, waves
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
         self._wave = None
 
@@ -129,7 +129,7 @@ class DecodeCache:
     def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device):
         key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device))
         if key not in self.plans:
-            host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device))
+            host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device), waves=self.waves)
             dev = {name: torch.from_numpy(host[name]).to(device) for name in
                    ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "work", "unit_slots")}
             if bf16_kv:
