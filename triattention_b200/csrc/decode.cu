@@ -26,6 +26,7 @@ constexpr int DecodeStages = 4;
 constexpr int StageBytes = 16512;                      // >= 8192 + 8192 + 16, multiple of 128
 constexpr int DecodeShared = DecodeStages * StageBytes;
 constexpr int Bf16ChunkKeys = 32, Bf16ChunkBytes = 16384;
+constexpr int MaxItemTiles = 256;                      // tiles (chunks) per work item; the planner cuts finer than this
 
 // tile_info bits
 constexpr uint32_t InfoTileMask = 0xfffu, InfoRowShift = 12, InfoK4 = 1u << 20, InfoV4 = 1u << 21, InfoBf16 = 1u << 22;
@@ -42,9 +43,9 @@ struct RowState {
 
 // One quantised tile.  Lane (group = lane/4, sub = lane%4) of warp w owns row `group` and keys
 // 16w + {2sub, 2sub+1, 8+2sub, 9+2sub} for QK, channels 32w + 8i + 2sub + {0,1} for PV.
-template <bool K4, bool V4>
+template <bool K4, bool V4, typename AfterSync>
 __device__ __forceinline__ void quantised_tile(const uint8_t* stage, const uint32_t (&qf)[4][2], float qs, uint32_t* pbuf,
-    float* rowmax, RowState& st, int key_begin, int prompt, bool row_on) {
+    float* rowmax, RowState& st, int key_begin, int prompt, bool row_on, AfterSync after_sync) {
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, group = lane / 4, sub = lane % 4;
   constexpr int KB = K4 ? K4Bytes : K8Bytes, VB = V4 ? V4Bytes : V8Bytes;
   const uint8_t* vb = stage + KB;
@@ -85,6 +86,7 @@ __device__ __forceinline__ void quantised_tile(const uint8_t* stage, const uint3
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
   if (sub == 0) rowmax[warp * 8 + group] = mx > -CUDART_INF_F ? slope[0] * __fsub_rn(mx, 12582912.f) : -CUDART_INF_F;
   __syncthreads();
+  after_sync();
   const float tile = fmaxf(fmaxf(rowmax[group], rowmax[8 + group]), fmaxf(rowmax[16 + group], rowmax[24 + group]));
   const float bias = -slope[0] * 12582912.f;
   const float n = fmaxf(st.m, tile), alpha = exp2f(st.m - n);
@@ -143,8 +145,9 @@ __device__ __forceinline__ void quantised_tile(const uint8_t* stage, const uint3
 // One 32-key chunk of an un-quantised BF16 head.  Warp w owns keys 8w..8w+7 for QK and channels
 // 32w..32w+31 for PV.  Chunk layout: K words [w][feature/16][half][lane], V words
 // [channel/8][key/16][half][lane], both in mma.sync B-fragment order.
+template <typename AfterSync>
 __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t (&qa)[8][2], float sm_log2, uint32_t* pbuf,
-    float* rowmax, RowState& st, int key_begin, int prompt, bool row_on) {
+    float* rowmax, RowState& st, int key_begin, int prompt, bool row_on, AfterSync after_sync) {
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, group = lane / 4, sub = lane % 4;
   const uint32_t* kw = reinterpret_cast<const uint32_t*>(stage);
   const uint32_t* vw = reinterpret_cast<const uint32_t*>(stage + 8192);
@@ -163,6 +166,7 @@ __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t 
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
   if (sub == 0) rowmax[warp * 8 + group] = mx;
   __syncthreads();
+  after_sync();
   const float tile = fmaxf(fmaxf(rowmax[group], rowmax[8 + group]), fmaxf(rowmax[16 + group], rowmax[24 + group]));
   const float n = fmaxf(st.m, tile), alpha = exp2f(st.m - n);
   st.m = n;
@@ -194,7 +198,8 @@ __global__ void __launch_bounds__(DecodeThreads) decode_kernel(const __nv_bfloat
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full[DecodeStages];
   __shared__ __align__(16) uint8_t qt[MaxGroup * D], qt4[MaxGroup * D];
-  __shared__ uint32_t pbuf[4 * 32];
+  __shared__ uint32_t pbuf[2][4 * 32];
+  __shared__ int2 smeta[MaxItemTiles];
   __shared__ float rowmax[32], qscale[MaxGroup], qscale4[MaxGroup], dsum[4][8];
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, group = lane / 4, sub = lane % 4;
   const int4 wk = work[blockIdx.x];
@@ -208,9 +213,10 @@ __global__ void __launch_bounds__(DecodeThreads) decode_kernel(const __nv_bfloat
     for (int s = 0; s < DecodeStages; ++s) mbar_init(&full[s], 1);
     mbar_fence_init();
   }
+  for (int i = tid; i < count; i += DecodeThreads) smeta[i] = meta[i];   // the item's tile table, read per tile below
   __syncthreads();
   auto issue = [&](int i) {
-    const int2 mt = meta[i];
+    const int2 mt = smeta[i];
     const uint32_t bytes = chunk_bytes((uint32_t)mt.y);
     uint64_t* bar = &full[i % DecodeStages];
     mbar_expect_tx(bar, bytes);
@@ -273,24 +279,27 @@ __global__ void __launch_bounds__(DecodeThreads) decode_kernel(const __nv_bfloat
 
   bool ok = true;
   for (int i = 0; i < count; ++i) {
-    if (tid == 0 && i + DecodeStages - 1 < count) issue(i + DecodeStages - 1);
+    // Tile i+3 reuses the stage of tile i-1.  Every thread has finished tile i-1 once it reaches the
+    // first barrier of tile i, so the refill is issued right after that barrier; the tile's second
+    // barrier orders the rest (pbuf alternates by tile parity), and no third barrier is needed.
+    auto refill = [&]() { if (tid == 0 && i + DecodeStages - 1 < count) issue(i + DecodeStages - 1); };
+    uint32_t* pb = pbuf[i & 1];
     const int s = i % DecodeStages;
     if (!mbar_wait(&full[s], (i / DecodeStages) & 1)) { ok = false; break; }
     const uint8_t* stage = ring + s * StageBytes;
-    const uint32_t info = (uint32_t)meta[i].y;
+    const uint32_t info = (uint32_t)smeta[i].y;
     const int tile = info & InfoTileMask;
     const unsigned rowmask = (info >> InfoRowShift) & 0xffu;
     const bool row_on = group < g && ((rowmask >> group) & 1u);
     if (info & InfoBf16) {
-      bf16_chunk(stage, qb16, sm_log2, pbuf, rowmax, st, tile * Bf16ChunkKeys, prompt, row_on);
+      bf16_chunk(stage, qb16, sm_log2, pb, rowmax, st, tile * Bf16ChunkKeys, prompt, row_on, refill);
     } else if (info & InfoK4) {
-      if (info & InfoV4) quantised_tile<true, true>(stage, qf4, qs4, pbuf, rowmax, st, tile * BN, prompt, row_on);
-      else quantised_tile<true, false>(stage, qf4, qs4, pbuf, rowmax, st, tile * BN, prompt, row_on);
+      if (info & InfoV4) quantised_tile<true, true>(stage, qf4, qs4, pb, rowmax, st, tile * BN, prompt, row_on, refill);
+      else quantised_tile<true, false>(stage, qf4, qs4, pb, rowmax, st, tile * BN, prompt, row_on, refill);
     } else {
-      if (info & InfoV4) quantised_tile<false, true>(stage, qf, qs8, pbuf, rowmax, st, tile * BN, prompt, row_on);
-      else quantised_tile<false, false>(stage, qf, qs8, pbuf, rowmax, st, tile * BN, prompt, row_on);
+      if (info & InfoV4) quantised_tile<false, true>(stage, qf, qs8, pb, rowmax, st, tile * BN, prompt, row_on, refill);
+      else quantised_tile<false, false>(stage, qf, qs8, pb, rowmax, st, tile * BN, prompt, row_on, refill);
     }
-    __syncthreads();   // the stage, pbuf and rowmax are free again
   }
   if (!ok) {
     // A bulk copy never completed.  Record it and leave without touching the outputs; the waits of
@@ -465,6 +474,7 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
             tail_v && kcur && vcur && step && out && pm && pl && po && device_error, "decode: null buffers");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
             max_tail >= 1 && max_tail <= 1024 && prompt > 0 && num_work >= 0, "decode geometry/buffers");
+  // every work item must hold at most MaxItemTiles tiles; the host planner guarantees it (checked there)
   TRI_CHECK(aligned16(pool) && aligned16(po) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 &&
             q_stride_h % 4 == 0, "decode: alignment");
   if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;

@@ -23,6 +23,7 @@ K8_BYTES, K4_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 8192, 4096
 BF16_CHUNK_KEYS, BF16_CHUNK_BYTES = 32, 16384
 INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16 = 12, 1 << 20, 1 << 21, 1 << 22
 MAX_GROUP = 8
+MAX_ITEM_TILES = 256   # csrc/decode.cu MaxItemTiles
 
 
 def tile_states(bands, heads_kv, tiles):
@@ -77,8 +78,10 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=444, waves=3.0
         n = count[kh]
         csum = np.concatenate([[0], np.cumsum(sizes[kh])])
         nsplit = int(np.clip(round(csum[-1] / target), 1, max(1, n // min_tiles)))
+        nsplit = max(nsplit, -(-n // (MAX_ITEM_TILES // 2)))     # the kernel keeps an item's tile table in shared memory
         cuts = np.searchsorted(csum, np.arange(1, nsplit) * (csum[-1] / nsplit)) if nsplit > 1 else np.zeros(0, np.int64)
         edges = np.unique(np.concatenate([[0], cuts, [n]]))
+        assert np.diff(edges).max(initial=0) <= MAX_ITEM_TILES
         pieces.append([(int(a), int(e - a), int(csum[e] - csum[a])) for a, e in zip(edges[:-1], edges[1:]) if e > a])
     nsplit = np.array([len(p) for p in pieces])
     slot_begin = np.concatenate([[0], np.cumsum(nsplit[kh_of])])
