@@ -86,14 +86,16 @@ int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* un
  * merge with the BF16 tail of generated tokens (the current K/V row is appended to the tail).
  * Replaces decode(q,k8c,k4c,ka,ka4,entry,kinfo,count,fmt,slot,v8,v4,vstat,kstat,ktail,vtail,kcur,vcur,
  *   step,out,pm,pl,po,prompt,per,scale), triattention/kernels/cuda/common_host.cuh:47-87.
- * work int32 [W,4] = (unit, first kept tile, tile count, partial slot), heaviest first;
+ * The split pass runs num_ctas persistent CTAs (one per SM); CTA c streams segments
+ * cta_segments[c] .. cta_segments[c+1]-1 (int32 [num_ctas+1]) of segments int32 [S,4] =
+ * (unit, first kept tile, tile count, partial slot): a cost-balanced contiguous cut of the tile sequence.
  * unit_slots int32 [U,2] = (first partial slot, number of splits); pm, pl f32 [P,8]; po f32 [P,8,128];
  * tail_k/tail_v bf16 [U,max_tail,128] with element strides; kcur/vcur bf16 [B,Hkv,1,128];
  * step int64 [1] on the device; out bf16 [B,Hq,1,128].  phases: 1 = split pass only, 2 = merge only,
  * 3 = both (normal use; the single phases exist so that each kernel can be timed alone). */
 int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
-               const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* work, int num_work,
-               const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
+               const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
+               const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
                int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
                int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out,
                int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po,

@@ -33,8 +33,8 @@ def test_k4_blob_formula():
     blob = rng.integers(0, 256, 4096, dtype=np.uint8)
     codes = layouts.unpack_k4(blob)
     for r, c in ((0, 0), (5, 17), (63, 127), (40, 96), (9, 47)):
-        byte = int(blob[(r // 8) * 512 + (c // 32) * 128 + (r % 8) * 16 + c % 16])
-        nib = (byte >> 4) if (c % 32) >= 16 else (byte & 0xF)
+        byte = int(blob[(r // 8) * 512 + (r % 8) * 64 + (c // 32) * 16 + ((c % 32) // 8) * 4 + c % 4])
+        nib = (byte >> 4) if (c % 8) >= 4 else (byte & 0xF)
         assert codes[r, c] == (nib - 16 if nib > 7 else nib)
 
 
@@ -149,20 +149,30 @@ def test_plan_work_list_covers_every_tile_once():
         units = 20
         seen = [np.zeros(plan["unit_count"][u], int) for u in range(units)]
         slots = set()
-        for u, first, cnt, slot in plan["work"]:
+        for u, first, cnt, slot in plan["segments"]:
             seen[u][first:first + cnt] += 1
             assert cnt > 0 and slot not in slots
             slots.add(slot)
             lo, n = plan["unit_slots"][u]
             assert lo <= slot < lo + n
         assert all((s == 1).all() for s in seen) and len(slots) == plan["slots"]
+        # every CTA owns a contiguous run of segments, and the runs are balanced by cost
+        cs = plan["cta_segments"]
+        assert cs[0] == 0 and cs[-1] == len(plan["segments"]) and (np.diff(cs) >= 0).all() and len(cs) == 65
+        sizes = {u: None for u in range(units)}
+        cost = np.zeros(64)
+        for c in range(64):
+            for u, first, cnt, slot in plan["segments"][cs[c]:cs[c + 1]]:
+                rows = plan["tmeta"][plan["unit_tab"][u] + first:plan["unit_tab"][u] + first + cnt]
+                info = rows[:, 1].astype(np.int64)
+                nbytes = np.where(info >> 22 & 1, 16384, np.where(info >> 20 & 1, 4096, 8192) + np.where(info >> 21 & 1, 4096, 8192) + 16)
+                cost[c] += nbytes.sum() + dec.TILE_COST * cnt
+        assert cost.max() - cost.min() <= 2 * (16384 + dec.TILE_COST)
         # streams do not overlap and stay inside the pool
         ends = plan["unit_base"] + plan["head_bytes"][np.arange(units) % 4]
         order = np.argsort(plan["unit_base"])
         assert (plan["unit_base"][order][1:] >= ends[order][:-1]).all() and ends.max() <= plan["pool_bytes"]
         assert (plan["unit_flags"] == np.isin(np.arange(units) % 4, list(bf16))).all()
-        w = plan["work"]
-        assert len(w) >= min(64, units)
 
 
 def test_plan_c2_byte_model():

@@ -118,16 +118,15 @@ def test_decode_split_invariance(module):
     qd, kd, vd = make_inputs(hq, hk, 1, seed=62)
     results = []
     for ctas in (1, 16, 444):
-        cache = DecodeCache(module, max_tail=4)
-        cache._wave = ctas
+        cache = DecodeCache(module, max_tail=4, ctas=ctas)
         pre = Prefill(module, bands_fn_of(bands), cache)
         kc, vc = bf16_cuda(k), bf16_cuda(v)
         table, ops = pre.write(0, bf16_cuda(q), kc, vc)
         cache.store(0, t, ops, table.host, kc, vc)
         results.append(cache(0, bf16_cuda(qd), bf16_cuda(kd), bf16_cuda(vd), SCALE).float().cpu().numpy())
     module.check_device_error()
-    assert_fp_close(results[1], results[0], "16 work items per wave vs 1")
-    assert_fp_close(results[2], results[0], "444 work items per wave vs 1")
+    assert_fp_close(results[1], results[0], "16 CTAs vs 1")
+    assert_fp_close(results[2], results[0], "444 CTAs vs 1")
 
 
 def test_tail_saturates(module):

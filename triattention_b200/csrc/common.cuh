@@ -13,8 +13,8 @@
 // reads (a warp reads one whole core matrix per 32-bit load).
 //   K8  8192 B  [key/8][feature/16][key%8][feature%16]            int8
 //   K4X 8192 B  same as K8, holding the 4-bit codes as int8        (prefill operand only)
-//   K4  4096 B  [key/8][s=feature/32][key%8][16 B]; byte i: low nibble = feature 32s+i,
-//               high nibble = feature 32s+16+i                     (decode cache)
+//   K4  4096 B  [key/8][key%8][sub=feature/32][16 B]; word s, byte j: low nibble = feature
+//               32*sub+8s+j, high nibble = feature 32*sub+8s+4+j   (decode cache layout, see decode_kernel.cuh)
 //   V8  8192 B  [ch/8][key/16][ch%8][16 B]; byte 4s+b = key 16*blk + kperm(s,b)
 //   V4  4096 B  [ch/8][kc=key/32][ch%8][16 B]; byte 4s+b: low nibble = key 32kc+kperm(s,b),
 //               high nibble = key 32kc+16+kperm(s,b)

@@ -1,0 +1,387 @@
+// Split-KV decode kernel, sm_100a: persistent warp-specialised CTAs streaming an equal share of the
+// cache bytes each.  Included by decode.cu.
+//
+// Replaces triattention/kernels/cuda/common_device.cuh:178-371 (decode_tile, decode_kernel) of the
+// reference.  The arithmetic per tile is the reference's (same float expressions, same 8-bit / 4-bit
+// P codes with the accumulator's low byte as dither); the organisation is not:
+//   * one CTA per SM; warp 4 is the producer: it walks the CTA's tile list and keeps a 12-stage
+//     shared-memory ring full with TMA bulk copies (one per tile chunk, mbarrier transaction counts);
+//   * warps 0-3 are consumers.  Each owns whole tiles (tile t of the CTA goes to warp t % 4), so the
+//     probabilities never leave registers: the accumulator fragment of QK^T is repacked in place as
+//     the A fragment of P.V.  No block barrier and no shared-memory exchange per tile;
+//   * a CTA's tile list is a contiguous slice of the global tile sequence cut by cost, so all CTAs
+//     finish together; where the slice crosses a (sequence, KV head) boundary the four consumers
+//     fold their states through shared memory and emit one partial (m, l, o) per segment.
+// Tile chunk layouts in the cache pool (written by cache_store_kernel; a lane reads 16 contiguous
+// bytes and a warp 512 contiguous bytes per load):
+//   K8 [key/8][half][key%8][sub][16 B]   16 B = features 32*sub + 16*half + 0..15 of the key
+//   K4 [key/8][key%8][sub][16 B]         word s, byte j: low nibble = feature 32*sub+8s+j, high = +4
+//   V8 [ch/8][ch%8][sub][16 B]           word w, byte j: key 16w + kperm(sub, j)
+//   V4 [ch/8][ch%8][sub][8 B]            word kc, byte j: low = key 32kc+kperm(sub,j), high = +16
+//   BF16 K [key/8][u][key%8][sub][16 B]  16 B = features 32*sub + 8u + 0..7;  32 keys per chunk
+//   BF16 V [ch/8][ch%8][sub][16 B]       word 2ks+h = keys 16ks + 8h + 2sub + {0,1} of the channel
+// In every integer contraction the k index is only a position; Q fragments are gathered with the
+// same feature permutation, P fragments come out of the accumulators in the V blobs' key order.
+#pragma once
+#include "common.cuh"
+
+namespace tri {
+
+constexpr int ConsumerWarps = 4;
+constexpr int DecodeThreads = (ConsumerWarps + 1) * 32;
+constexpr int DecodeStages = 12;
+constexpr int StageBytes = 16512;                      // >= 8192 + 8192 + 16, multiple of 128
+constexpr int Bf16ChunkKeys = 32, Bf16ChunkBytes = 16384;
+constexpr int CombFloats = MaxGroup * D + 2 * MaxGroup;
+constexpr int SmRing = 0, SmQ = DecodeStages * StageBytes, SmComb = SmQ + ConsumerWarps * 2048;
+constexpr int DecodeShared = SmComb + ConsumerWarps * CombFloats * 4;
+
+// tile_info bits
+constexpr uint32_t InfoTileMask = 0xfffu, InfoRowShift = 12, InfoK4 = 1u << 20, InfoV4 = 1u << 21, InfoBf16 = 1u << 22;
+
+__device__ __forceinline__ uint32_t chunk_bytes(uint32_t info) {
+  if (info & InfoBf16) return Bf16ChunkBytes;
+  return ((info & InfoK4) ? K4Bytes : K8Bytes) + ((info & InfoV4) ? V4Bytes : V8Bytes) + 16;
+}
+
+// Bounded, abortable wait: gives up when the CTA's abort flag is set or after ~2 s.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
+  }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() {   // the four consumer warps only
+  asm volatile("bar.sync 1, %0;" ::"n"(ConsumerWarps * 32) : "memory");
+}
+
+struct WarpState {        // online-softmax state of one consumer warp; lane = (row = lane/4, sub = lane%4)
+  float m, denom, corr;   // denom is the lane's share; the quad is summed when the segment ends
+  float out[16][2];       // channels 8*cb + 2*sub + {0,1}
+};
+
+// One quantised 64-key tile, whole warp.  common_device.cuh:178-273 of the reference, per row.
+template <bool K4, bool V4>
+__device__ __forceinline__ void quantised_tile(const uint8_t* stage, const uint32_t (&qf)[4][2], float qs, WarpState& st,
+    int key_begin, int prompt, bool row_on) {
+  const int lane = threadIdx.x % 32, group = lane / 4, sub = lane % 4;
+  constexpr int KB = K4 ? K4Bytes : K8Bytes, VB = V4 ? V4Bytes : V8Bytes;
+  const uint8_t* vb = stage + KB;
+  const float4 kt4 = *reinterpret_cast<const float4*>(stage + KB + VB);
+  const float kt[4] = {kt4.x, kt4.y, kt4.z, kt4.w};
+  int c[8][4];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb) {
+    c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0;
+    if constexpr (!K4) {
+      const uint4 u0 = *reinterpret_cast<const uint4*>(stage + nb * 1024 + group * 64 + sub * 16);
+      const uint4 u1 = *reinterpret_cast<const uint4*>(stage + nb * 1024 + 512 + group * 64 + sub * 16);
+      mma_s8(c[nb], qf[0][0], qf[0][1], u0.x, u0.y);
+      mma_s8(c[nb], qf[1][0], qf[1][1], u0.z, u0.w);
+      mma_s8(c[nb], qf[2][0], qf[2][1], u1.x, u1.y);
+      mma_s8(c[nb], qf[3][0], qf[3][1], u1.z, u1.w);
+    } else {
+      const uint4 u = *reinterpret_cast<const uint4*>(stage + nb * 512 + group * 64 + sub * 16);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int s = 0; s < 4; ++s) mma_s8(c[nb], qf[s][0], qf[s][1], (w[s] << 4) & 0xf0f0f0f0u, w[s] & 0xf0f0f0f0u);
+    }
+  }
+  int acc[16];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb) {
+    acc[2 * nb] = K4 ? c[nb][0] >> 8 : c[nb][0];   // INT4: both operands were widened by 16
+    acc[2 * nb + 1] = K4 ? c[nb][1] >> 8 : c[nb][1];
+  }
+  const bool ragged = key_begin + BN > prompt;       // only the last prompt tile has keys past the prompt
+  unsigned live = row_on ? 0xffffu : 0u;
+  if (ragged) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (key_begin + (i / 2) * 8 + sub * 2 + (i % 2) >= prompt) live &= ~(1u << i);
+  }
+  // scaled tile maximum: max over the 16-key groups of slope_c * max(acc) (slope_c > 0, so the order is free)
+  float tmax = -CUDART_INF_F;
+#pragma unroll
+  for (int col = 0; col < 4; ++col) {
+    int mi = INT_MIN;
+#pragma unroll
+    for (int i = 4 * col; i < 4 * col + 4; ++i)
+      if ((live >> i) & 1u) mi = max(mi, acc[i]);
+    if (mi != INT_MIN) tmax = fmaxf(tmax, qs * kt[col] * (float)mi);
+  }
+  tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+  tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+  const float tile = tmax;
+  const float n = fmaxf(st.m, tile), alpha = exp2f(st.m - n);
+  st.m = n;
+  if (alpha != 1.f) {
+#pragma unroll
+    for (int cb = 0; cb < 16; ++cb) { st.out[cb][0] *= alpha; st.out[cb][1] *= alpha; }
+    st.corr *= alpha;
+  }
+  constexpr float levels = V4 ? 15.f : 255.f;
+  const bool any = tile > -CUDART_INF_F;
+  const float slope1 = qs * fmaxf(fmaxf(kt[0], kt[1]), fmaxf(kt[2], kt[3]));
+  float base = any ? tile : n;
+  base += tile_base_margin(slope1, base);
+  const float bq = any ? exp2f(base - n) / levels : 0.f, restore = V4 ? bq * (127.f / 7.f) : bq;
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float slope0 = qs * kt[i / 4];
+    const int xbits = acc[i] + Magic;
+    const float x = __int_as_float(xbits);
+    const float bias = -slope0 * 12582912.f;
+    const float arg = K4 ? fmaf(slope0, __fsub_rn(x, 12582912.f), -base) : fmaf(slope0, x, bias - base);
+    const bool on = (live >> i) & 1u;
+    w[i] = __float_as_uint(fmaf(on ? exp2f(arg) : 0.f, levels, on ? pmagic_dither(xbits) : 49152.f));
+  }
+  uint32_t pa[4];   // A fragments of P: a0/a2 of k-step 0, a0/a2 of k-step 1
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pa[j] = pack_bytes(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  const int psum = (int)__dp4a(pa[0], 0x01010101u, __dp4a(pa[1], 0x01010101u, __dp4a(pa[2], 0x01010101u, __dp4a(pa[3], 0x01010101u, 0u))));
+  st.denom = fmaf(st.denom, alpha, (float)psum * bq);
+  if constexpr (!V4) st.corr = fmaf(12582912.f, restore, st.corr);
+#pragma unroll
+  for (int cb = 0; cb < 16; ++cb) {
+    int d[4] = {0, 0, 0, 0};
+    if constexpr (!V4) {
+      const uint4 u = *reinterpret_cast<const uint4*>(vb + cb * 512 + group * 64 + sub * 16);
+      mma_u8s8(d, pa[0], pa[1], u.x, u.y);
+      mma_u8s8(d, pa[2], pa[3], u.z, u.w);
+      st.out[cb][0] = fmaf(__int_as_float(d[0] + Magic), restore, st.out[cb][0]);
+      st.out[cb][1] = fmaf(__int_as_float(d[1] + Magic), restore, st.out[cb][1]);
+    } else {
+      const uint2 u = *reinterpret_cast<const uint2*>(vb + cb * 256 + group * 32 + sub * 8);
+      mma_u8s8(d, pa[0], pa[1], (u.x << 4) & 0xf0f0f0f0u, u.x & 0xf0f0f0f0u);
+      mma_u8s8(d, pa[2], pa[3], (u.y << 4) & 0xf0f0f0f0u, u.y & 0xf0f0f0f0u);
+      st.out[cb][0] = fmaf((float)(d[0] >> 4), restore, st.out[cb][0]);
+      st.out[cb][1] = fmaf((float)(d[1] >> 4), restore, st.out[cb][1]);
+    }
+  }
+}
+
+// One 32-key chunk of an un-quantised BF16 head, whole warp (no counterpart in the reference).
+__device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t (&qb)[8][2], float sm_log2, WarpState& st,
+    int key_begin, int prompt, bool row_on) {
+  const int lane = threadIdx.x % 32, group = lane / 4, sub = lane % 4;
+  const uint8_t* vb = stage + 8192;
+  float c[4][4];
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb) {
+    c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint4 x = *reinterpret_cast<const uint4*>(stage + (nb * 4 + u) * 512 + group * 64 + sub * 16);
+      mma_bf16(c[nb], qb[2 * u][0], qb[2 * u][1], x.x, x.y);
+      mma_bf16(c[nb], qb[2 * u + 1][0], qb[2 * u + 1][1], x.z, x.w);
+    }
+  }
+  float s[8], tmax = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int key = key_begin + (i / 2) * 8 + sub * 2 + (i % 2);
+    s[i] = (row_on && key < prompt) ? c[i / 2][i % 2] * sm_log2 : -CUDART_INF_F;
+    tmax = fmaxf(tmax, s[i]);
+  }
+  tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+  tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+  const float n = fmaxf(st.m, tmax), alpha = exp2f(st.m - n);
+  st.m = n;
+  float p[8], part = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { p[i] = s[i] > -CUDART_INF_F ? exp2f(s[i] - n) : 0.f; part += p[i]; }
+  st.denom = fmaf(st.denom, alpha, part);
+  uint32_t pa[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(p[2 * j], p[2 * j + 1]);
+    pa[j] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+#pragma unroll
+  for (int cb = 0; cb < 16; ++cb) {
+    float o[4] = {st.out[cb][0] * alpha, st.out[cb][1] * alpha, 0.f, 0.f};
+    const uint4 x = *reinterpret_cast<const uint4*>(vb + cb * 512 + group * 64 + sub * 16);
+    mma_bf16(o, pa[0], pa[1], x.x, x.y);
+    mma_bf16(o, pa[2], pa[3], x.z, x.w);
+    st.out[cb][0] = o[0]; st.out[cb][1] = o[1];
+  }
+}
+
+// grid = persistent CTAs (one per SM), 160 threads.  cta_seg[c]..cta_seg[c+1] indexes the CTA's
+// segments; segs[j] = {unit, first kept tile, tile count, partial slot}; unit = sequence*heads_kv + kv head.
+__global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
+    const uint8_t* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int2* tmeta,
+    const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt,
+    float sm_log2, int* err) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t full[DecodeStages], empty[DecodeStages];
+  __shared__ uint32_t stage_info[DecodeStages];
+
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, group = lane / 4, sub = lane % 4;
+  const int seg0 = cta_seg[blockIdx.x], nseg = cta_seg[blockIdx.x + 1] - seg0;
+  const int g = heads_q / heads_kv;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < DecodeStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+
+  __syncthreads();
+  volatile int* abortp = &abort_flag;
+
+  if (warp == ConsumerWarps) {
+    // ---- producer: one lane keeps the ring full -------------------------------------------------
+    if (lane == 0) {
+      int t = 0;
+      for (int j = 0; j < nseg && !*abortp; ++j) {
+        const int4 sg = segs[seg0 + j];
+        const int2* meta = tmeta + unit_tab[sg.x] + sg.y;
+        const uint8_t* base = pool + unit_base[sg.x];
+        int2 mt = sg.z > 0 ? meta[0] : make_int2(0, 0);
+        for (int i = 0; i < sg.z; ++i, ++t) {
+          const int2 next = i + 1 < sg.z ? meta[i + 1] : make_int2(0, 0);   // table read ahead of its use
+          const int s = t % DecodeStages;
+          if (!mbar_wait_abortable(&empty[s], ((t / DecodeStages) & 1) ^ 1, abortp)) break;
+          const uint32_t bytes = chunk_bytes((uint32_t)mt.y);
+          stage_info[s] = (uint32_t)mt.y;
+          mbar_expect_tx(&full[s], bytes);
+          bulk_g2s(smem + SmRing + s * StageBytes, base + (int64_t)mt.x * 16, bytes, &full[s]);
+          mt = next;
+        }
+      }
+    }
+  } else {
+    // ---- consumers: warp w owns tiles t = w, w+4, ... of the CTA's list ------------------------------
+    uint8_t* q8buf = smem + SmQ + warp * 2048;
+    uint8_t* q4buf = q8buf + 1024;
+    float* comb = reinterpret_cast<float*>(smem + SmComb);
+    int t0 = 0;
+    for (int j = 0; j < nseg; ++j) {
+      const int4 sg = segs[seg0 + j];
+      const int unit = sg.x, count = sg.z, slot = sg.w;
+      const int b = unit / heads_kv, kh = unit % heads_kv;
+      const bool bf16 = unit_flags[unit] & 1;
+      const __nv_bfloat16* qrow = q + b * qsb + (int64_t)(kh * g) * qsh;
+      uint32_t qf[4][2], qf4[4][2], qb[8][2];
+      float qs8 = FLT_MIN, qs4 = FLT_MIN;
+      if (!bf16) {
+        // Q of the group: rotate + quantise, one row at a time with the reference's lane mapping
+        // (common_device.cuh:291-315), then gather this lane's fragments through shared memory.
+        __syncwarp();
+        for (int r = 0; r < MaxGroup; ++r) {
+          uint32_t word = 0, word4 = 0;
+          if (r < g) {
+            float xv[4], mxq = 0.f;
+            const __nv_bfloat16* src = qrow + r * qsh + lane * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(src[i]);
+            rotate128_x4(xv, lane);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mxq = fmaxf(mxq, fabsf(xv[i]));
+#pragma unroll
+            for (int o = 16; o; o >>= 1) mxq = fmaxf(mxq, __shfl_xor_sync(0xffffffffu, mxq, o));
+            const float inv = mxq > 0.f ? 127.f / mxq : 0.f, inv4 = mxq > 0.f ? 7.f / mxq : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              word |= (uint32_t)(__float2int_rn(xv[i] * inv) & 0xff) << (8 * i);
+              word4 |= (uint32_t)((__float2int_rn(xv[i] * inv4) & 0xf) << 4) << (8 * i);   // code * 16 as int8
+            }
+            if (group == r) {
+              qs8 = mxq > 0.f ? mxq / 127.f * sm_log2 : FLT_MIN;
+              qs4 = mxq > 0.f ? mxq / 7.f * sm_log2 : FLT_MIN;
+            }
+          }
+          reinterpret_cast<uint32_t*>(q8buf + r * D)[lane] = word;
+          reinterpret_cast<uint32_t*>(q4buf + r * D)[lane] = word4;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {   // k-step s, positions 4sub+j -> feature 32sub+8s+j, 16+4sub+j -> +4
+          qf[s][0] = *reinterpret_cast<const uint32_t*>(q8buf + group * D + sub * 32 + s * 8);
+          qf[s][1] = *reinterpret_cast<const uint32_t*>(q8buf + group * D + sub * 32 + s * 8 + 4);
+          qf4[s][0] = *reinterpret_cast<const uint32_t*>(q4buf + group * D + sub * 32 + s * 8);
+          qf4[s][1] = *reinterpret_cast<const uint32_t*>(q4buf + group * D + sub * 32 + s * 8 + 4);
+        }
+      } else {
+#pragma unroll
+        for (int fs = 0; fs < 8; ++fs) {   // k-step fs: features 32sub + 4fs + {0,1} and + {2,3}
+          qb[fs][0] = group < g ? *reinterpret_cast<const uint32_t*>(qrow + group * qsh + sub * 32 + fs * 4) : 0u;
+          qb[fs][1] = group < g ? *reinterpret_cast<const uint32_t*>(qrow + group * qsh + sub * 32 + fs * 4 + 2) : 0u;
+        }
+      }
+      WarpState st;
+      st.m = -FLT_MAX; st.denom = 0.f; st.corr = 0.f;
+#pragma unroll
+      for (int cb = 0; cb < 16; ++cb) st.out[cb][0] = st.out[cb][1] = 0.f;
+
+      int first_t = t0 + ((warp - t0 % ConsumerWarps) + ConsumerWarps) % ConsumerWarps;
+      for (int t = first_t; t < t0 + count; t += ConsumerWarps) {
+        const int s = t % DecodeStages;
+        if (!mbar_wait_abortable(&full[s], (t / DecodeStages) & 1, abortp)) break;
+        const uint8_t* stage = smem + SmRing + s * StageBytes;
+        const uint32_t info = stage_info[s];
+        const int tile = info & InfoTileMask;
+        const unsigned rowmask = (info >> InfoRowShift) & 0xffu;
+        const bool row_on = group < g && ((rowmask >> group) & 1u);
+        if (info & InfoBf16) {
+          bf16_chunk(stage, qb, sm_log2, st, tile * Bf16ChunkKeys, prompt, row_on);
+        } else if (info & InfoK4) {
+          if (info & InfoV4) quantised_tile<true, true>(stage, qf4, qs4, st, tile * BN, prompt, row_on);
+          else quantised_tile<true, false>(stage, qf4, qs4, st, tile * BN, prompt, row_on);
+        } else {
+          if (info & InfoV4) quantised_tile<false, true>(stage, qf, qs8, st, tile * BN, prompt, row_on);
+          else quantised_tile<false, false>(stage, qf, qs8, st, tile * BN, prompt, row_on);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);   // the stage may be refilled
+      }
+      t0 += count;
+
+      // ---- fold the four warps' states of this segment into one partial (m, l, o) per Q head ------
+      float den = st.denom;
+      den += __shfl_xor_sync(0xffffffffu, den, 1);
+      den += __shfl_xor_sync(0xffffffffu, den, 2);
+      float* mine = comb + warp * CombFloats;
+#pragma unroll
+      for (int cb = 0; cb < 16; ++cb)
+        *reinterpret_cast<float2*>(mine + group * D + cb * 8 + sub * 2) = make_float2(st.out[cb][0] - st.corr, st.out[cb][1] - st.corr);
+      if (sub == 0) { mine[MaxGroup * D + group] = st.m; mine[MaxGroup * D + MaxGroup + group] = den; }
+      consumer_sync();
+      {
+        const int ch = tid;   // 128 consumer threads = 128 channels
+        for (int r = 0; r < g; ++r) {
+          float mw[ConsumerWarps], big = -FLT_MAX;
+#pragma unroll
+          for (int w = 0; w < ConsumerWarps; ++w) { mw[w] = comb[w * CombFloats + MaxGroup * D + r]; big = fmaxf(big, mw[w]); }
+          float o = 0.f, l = 0.f;
+#pragma unroll
+          for (int w = 0; w < ConsumerWarps; ++w) {
+            const float sc = exp2f(mw[w] - big);
+            o = fmaf(comb[w * CombFloats + r * D + ch], sc, o);
+            l = fmaf(comb[w * CombFloats + MaxGroup * D + MaxGroup + r], sc, l);
+          }
+          const int64_t idx = (int64_t)slot * MaxGroup + r;
+          po[idx * D + ch] = o;
+          if (ch == 0) { pm[idx] = big; pl[idx] = l; }
+        }
+      }
+      consumer_sync();   // the fold buffer is free for the next segment
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && abort_flag) atomicExch(err, ErrBarrierTimeout);
+}
+
+}  // namespace tri

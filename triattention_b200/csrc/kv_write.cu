@@ -191,13 +191,11 @@ __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k,
     const uint4 c4 = codes16(y[p], inv4);
     if (k4x != nullptr) *reinterpret_cast<uint4*>(k4x + ht * K8Bytes + core) = c4;
     if (k4 != nullptr) {
-      // lane pair (even, odd) covers features 32s..32s+31; byte i = feature 32s+i | feature 32s+16+i << 4
-      const bool odd = l8 & 1;
-      const uint32_t n0 = c4.x & 0x0f0f0f0fu, n1 = c4.y & 0x0f0f0f0fu, n2 = c4.z & 0x0f0f0f0fu, n3 = c4.w & 0x0f0f0f0fu;
-      const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? n0 : n2, 1);
-      const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? n1 : n3, 1);
-      const uint2 out = odd ? make_uint2(r0 | (n2 << 4), r1 | (n3 << 4)) : make_uint2(n0 | (r0 << 4), n1 | (r1 << 4));
-      *reinterpret_cast<uint2*>(k4 + ht * K4Bytes + (r / 8) * 512 + (l8 >> 1) * 128 + (r % 8) * 16 + (odd ? 8 : 0)) = out;
+      // decode layout [key/8][key%8][sub][16 B]: this lane owns features 32*sub + 16*h + 0..15 and writes
+      // words s = 2h, 2h+1 of the run; byte j of word s: low nibble = feature 32*sub+8s+j, high = +4
+      const uint32_t lo = (c4.x & 0x0f0f0f0fu) | ((c4.y & 0x0f0f0f0fu) << 4);
+      const uint32_t hi = (c4.z & 0x0f0f0f0fu) | ((c4.w & 0x0f0f0f0fu) << 4);
+      *reinterpret_cast<uint2*>(k4 + ht * K4Bytes + (r / 8) * 512 + (r % 8) * 64 + (l8 >> 1) * 16 + (l8 & 1) * 8) = make_uint2(lo, hi);
     }
   }
 }

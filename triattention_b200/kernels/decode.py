@@ -1,5 +1,5 @@
-"""Decode cache: per-(sequence, KV head) byte streams of kept tiles, a byte-balanced work list, the
-BF16 tail of generated tokens, and the decode step.
+"""Decode cache: per-(sequence, KV head) byte streams of kept tiles, a cost-balanced static partition
+of the tile sequence over persistent CTAs, the BF16 tail of generated tokens, and the decode step.
 
 Mirrors ``triattention/kernels/decode.py`` (``DecodeCache(module, max_tail)``, ``codes``, ``store``,
 ``__call__``, ``advance``, ``stored``).  The tile-state rules are the reference's
@@ -8,8 +8,9 @@ Mirrors ``triattention/kernels/decode.py`` (``DecodeCache(module, max_tail)``, `
 mask says which Q heads attend; V is INT8 for tile 0 and the last 16 tiles, INT4 elsewhere
 (``decode.py:17-22``).  What differs is the data structure: the reference compacts tiles into four
 dense arrays with host-side argsort/cumsum and splits by a fixed tile count; here each unit is one
-contiguous byte stream (K blob, V blob, K scales per tile) filled by one gather kernel, and splits
-are cut by bytes so that INT8 / INT4 / BF16 units cost the same per work item.
+contiguous byte stream (K blob, V blob, K scales per tile) filled by one gather kernel, and the
+sequence of all tiles is cut into one contiguous slice of equal cost per CTA (one CTA per SM), so
+INT8 / INT4 / BF16 units are balanced by bytes and every CTA finishes at the same time.
 """
 from __future__ import annotations
 
@@ -23,7 +24,7 @@ K8_BYTES, K4_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 8192, 4096
 BF16_CHUNK_KEYS, BF16_CHUNK_BYTES = 32, 16384
 INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16 = 12, 1 << 20, 1 << 21, 1 << 22
 MAX_GROUP = 8
-MAX_ITEM_TILES = 256   # csrc/decode.cu MaxItemTiles
+TILE_COST = 4096   # bytes-equivalent of the fixed per-tile work in the partition's cost model
 
 
 def tile_states(bands, heads_kv, tiles):
@@ -36,11 +37,12 @@ def tile_states(bands, heads_kv, tiles):
     return state.max(1), rowmask
 
 
-def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=444, waves=3.0, min_tiles=4):
-    """Host-side layout of one layer's cache and its work list (numpy, a few microseconds per head).
+def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost=TILE_COST):
+    """Host-side layout of one layer's cache and its partition over `ctas` persistent CTAs (numpy).
 
     Returns a dict of numpy arrays: tmeta [N,2], tab_begin/count/head_bytes [Hkv], unit_base [U] (int64),
-    unit_tab/unit_count/unit_flags [U], work [W,4], unit_slots [U,2], plus totals.
+    unit_tab/unit_count/unit_flags [U], segments [S,4] = (unit, first kept tile, tile count, partial slot),
+    cta_segments [ctas+1], unit_slots [U,2], plus totals.
     """
     tiles = (prompt + 63) // 64
     kv, rowmask = tile_states(bands, heads_kv, tiles)
@@ -70,44 +72,41 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=444, waves=3.0
     kh_of = np.arange(units) % heads_kv
     unit_base = (np.arange(units) // heads_kv).astype(np.int64) * seq_bytes + head_off[kh_of]
     unit_flags = np.isin(kh_of, list(bf16_kv)).astype(np.int32)
-    # work list: cut every unit into pieces of about `target` bytes
-    total = batch * seq_bytes
-    target = max(total / max(1.0, ctas * waves), 1.0)
-    pieces = []       # per kv head: list of (first, count, bytes)
-    for kh in range(heads_kv):
-        n = count[kh]
-        csum = np.concatenate([[0], np.cumsum(sizes[kh])])
-        nsplit = int(np.clip(round(csum[-1] / target), 1, max(1, n // min_tiles)))
-        nsplit = max(nsplit, -(-n // (MAX_ITEM_TILES // 2)))     # the kernel keeps an item's tile table in shared memory
-        cuts = np.searchsorted(csum, np.arange(1, nsplit) * (csum[-1] / nsplit)) if nsplit > 1 else np.zeros(0, np.int64)
-        edges = np.unique(np.concatenate([[0], cuts, [n]]))
-        assert np.diff(edges).max(initial=0) <= MAX_ITEM_TILES
-        pieces.append([(int(a), int(e - a), int(csum[e] - csum[a])) for a, e in zip(edges[:-1], edges[1:]) if e > a])
-    nsplit = np.array([len(p) for p in pieces])
-    slot_begin = np.concatenate([[0], np.cumsum(nsplit[kh_of])])
-    rows, weights = [], []
+    # static partition: the tiles of all units in unit order form one sequence; CTA c takes the tiles whose
+    # cumulative cost (bytes + a fixed per-tile term) starts inside [c, c+1) * total / ctas
+    ccum = [np.concatenate([[0], np.cumsum(s + tile_cost)]) for s in sizes]
+    unit_cost = np.array([ccum[kh][-1] for kh in kh_of], np.float64)
+    unit_start = np.concatenate([[0.0], np.cumsum(unit_cost)])
+    share = max(unit_start[-1] / ctas, 1.0)
+    segments, seg_cta, unit_slots = [], [], []
     for u in range(units):
-        for s, (first, cnt, nbytes) in enumerate(pieces[kh_of[u]]):
-            rows.append((u, first, cnt, slot_begin[u] + s))
-            weights.append(nbytes)
-    order = np.argsort(-np.asarray(weights), kind="stable")
-    work = np.asarray(rows, np.int32).reshape(-1, 4)[order]
+        kh, n, lo = kh_of[u], count[kh_of[u]], unit_start[u]
+        c0, c1 = int(lo // share), int(min(ctas - 1, (unit_start[u + 1] - 1e-6) // share))
+        cuts = np.searchsorted(ccum[kh], (np.arange(c0 + 1, c1 + 1) * share) - lo, side="left") if c1 > c0 else np.zeros(0, np.int64)
+        edges = np.concatenate([[0], np.clip(cuts, 0, n), [n]]).astype(np.int64)
+        first_slot = len(segments)
+        for i, (a, e) in enumerate(zip(edges[:-1], edges[1:])):
+            if e > a:
+                segments.append((u, int(a), int(e - a), len(segments)))
+                seg_cta.append(min(ctas - 1, c0 + i))
+        unit_slots.append((first_slot, len(segments) - first_slot))
+    seg_cta = np.asarray(seg_cta, np.int64)
+    cta_segments = np.searchsorted(seg_cta, np.arange(ctas + 1), side="left").astype(np.int32)
     return dict(tmeta=tmeta, tab_begin=np.asarray(tab_begin, np.int32), count=np.asarray(count, np.int32),
                 head_bytes=np.asarray(head_bytes, np.int64), unit_base=unit_base,
                 unit_tab=np.asarray(tab_begin, np.int32)[kh_of], unit_count=np.asarray(count, np.int32)[kh_of],
-                unit_flags=unit_flags, work=np.ascontiguousarray(work),
-                unit_slots=np.stack([slot_begin[:-1], nsplit[kh_of]], 1).astype(np.int32), slots=int(slot_begin[-1]),
-                pool_bytes=int(total), seq_bytes=seq_bytes, tiles=tiles,
+                unit_flags=unit_flags, segments=np.asarray(segments, np.int32).reshape(-1, 4), cta_segments=cta_segments,
+                unit_slots=np.asarray(unit_slots, np.int32).reshape(-1, 2), slots=len(segments),
+                pool_bytes=int(batch * seq_bytes), seq_bytes=seq_bytes, tiles=tiles,
                 payload_bytes=int(batch * sum(int(s.sum()) for s in sizes)))
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256, waves=3.0):
+    def __init__(self, module, max_tail=256, ctas=None, tile_cost=TILE_COST):
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
-        self.module, self.max_tail, self.waves = module, max_tail, waves
+        self.module, self.max_tail, self.ctas, self.tile_cost = module, max_tail, ctas, tile_cost
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
-        self._wave = None
 
     def codes(self, rows):
         """decode.py:17-22: V format per prompt tile in decode, and the set of formats used."""
@@ -124,17 +123,19 @@ class DecodeCache:
         return bool((kv[quant] == 4).any()) if quant else False
 
     def wave(self, device):
-        if self._wave is None:
+        """Persistent CTAs of the split pass: SMs x resident CTAs per SM (decode.py:54 of the reference)."""
+        if self.ctas is None:
             sms = torch.cuda.get_device_properties(device).multi_processor_count
-            self._wave = sms * max(1, self.module.decode_occupancy())
-        return self._wave
+            self.ctas = sms * max(1, self.module.decode_occupancy())
+        return self.ctas
 
     def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device):
         key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device))
         if key not in self.plans:
-            host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device), waves=self.waves)
+            host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
+                                tile_cost=self.tile_cost)
             dev = {name: torch.from_numpy(host[name]).to(device) for name in
-                   ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "work", "unit_slots")}
+                   ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
             if bf16_kv:
                 units = np.nonzero(host["unit_flags"])[0].astype(np.int32)
                 dev["bf16_units"] = torch.from_numpy(units).to(device)
@@ -173,9 +174,9 @@ class DecodeCache:
         e = self.layers[layer]
         d = e["dev"]
         out = torch.empty_like(q) if out is None else out
-        self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["work"],
-                           d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out,
-                           e["pm"], e["pl"], e["po"], e["prompt"], scale, phases)
+        self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
+                           d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v,
+                           self.step, out, e["pm"], e["pl"], e["po"], e["prompt"], scale, phases)
         return out
 
     def advance(self):

@@ -25,7 +25,7 @@ SIGNATURES = {
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _P],
-    "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
+    "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
                    _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
@@ -151,21 +151,22 @@ class Module:
                                                       k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
                                                       v.stride(2), _stream()))
 
-    def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, work, unit_slots, kstat, vstat, tail_k, tail_v,
-               kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3):
+    def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, kstat, vstat,
+               tail_k, tail_v, kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3):
         if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1):
             raise RuntimeError("q [B,Hq,1,128]")
         b, hq = q.shape[0], q.shape[1]
         hk, max_tail = kcur.shape[1], tail_k.shape[1]
         if not (hq % hk == 0 and hq // hk <= 8 and max_tail <= 1024 and step.dtype == torch.int64 and step.is_cuda and
                 kcur.stride(3) == 1 and vcur.stride(1) == kcur.stride(1) and vcur.stride(0) == kcur.stride(0) and
-                work.dtype == torch.int32 and tmeta.dtype == torch.int32 and unit_base.dtype == torch.int64 and
+                segments.dtype == torch.int32 and cta_segments.dtype == torch.int32 and tmeta.dtype == torch.int32 and
+                unit_base.dtype == torch.int64 and
                 tail_v.stride() == tail_k.stride() and out.stride(3) == 1):
             raise RuntimeError("decode geometry/buffers")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_decode(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(),
-                                            unit_tab.data_ptr(), unit_flags.data_ptr(), tmeta.data_ptr(), work.data_ptr(),
-                                            work.shape[0], unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(),
+                                            unit_tab.data_ptr(), unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(),
+                                            cta_segments.data_ptr(), cta_segments.numel() - 1, unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(),
                                             tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), tail_k.stride(1),
                                             kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
                                             step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(),

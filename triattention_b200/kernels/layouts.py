@@ -27,8 +27,8 @@ def _k8_index():
 
 def _k4_index():
     p = np.arange(4096)
-    key, s, i = (p // 512) * 8 + (p // 16) % 8, (p // 128) % 4, p % 16
-    return key, 32 * s + i, 32 * s + 16 + i                                          # key, low feature, high feature
+    key, sub, s, j = (p // 512) * 8 + (p // 64) % 8, (p // 16) % 4, (p // 4) % 4, p % 4
+    return key, 32 * sub + 8 * s + j, 32 * sub + 8 * s + 4 + j                       # key, low feature, high feature
 
 
 def _v8_index():
