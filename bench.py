@@ -100,7 +100,7 @@ class ClockSampler:
                     samples=len(rows))
 
 
-def build_cache(batch, seed0, tile_cost=4096):
+def build_cache(batch, seed0, tile_costs=None):
     """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan)."""
     from triattention_b200.kernels.decode import DecodeCache
     from triattention_b200.kernels.extension import load_extension
@@ -108,7 +108,7 @@ def build_cache(batch, seed0, tile_cost=4096):
     from triattention_b200.maps import per_kv_head
     hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
     module = load_extension()
-    cache = DecodeCache(module, max_tail=256, tile_cost=tile_cost)
+    cache = DecodeCache(module, max_tail=256, **({"tile_costs": tile_costs} if tile_costs else {}))
     pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
     k = torch.empty((batch, hk, t, 128), dtype=torch.bfloat16, device="cuda")
     v = torch.empty_like(k)
@@ -207,7 +207,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--cpu-steps", type=int, default=10, help="timed steps of the CPU baseline leg (0 = skip)")
-    parser.add_argument("--tile-cost", type=int, default=4096, help="per-tile term (bytes) of the decode partition's cost model")
+    parser.add_argument("--tile-costs", default="", help="override the decode partition's cost model: bf16,k8v8,other (relative)")
     parser.add_argument("--batch", type=int, default=CONFIG["batch"],
                         help="sequences per GPU; anything but 32 is a reduced case for profiler captures, flagged in the output")
     args = parser.parse_args()
@@ -223,7 +223,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
     warmup = max(3, args.warmup)
-    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_cost=args.tile_cost)
+    costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
+    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs)
     scale = 128 ** -0.5
     # decode-step inputs: device-resident copies for `value`, pinned host copies for `e2e`
     host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (rank * batch + b)) for b in range(batch)]).pin_memory()
@@ -237,6 +238,7 @@ def main():
     with ClockSampler(local) as clocks:
         ms_total = timed(lambda i: cache(0, qd, kd, vd, scale, out=out), args.steps, dist)
         ms_kernel = timed(lambda i: cache(0, qd, kd, vd, scale, phases=1, out=out), args.steps, dist)
+        ms_stream = timed(lambda i: cache(0, qd, kd, vd, scale, phases=5, out=out), args.steps, dist)
 
         def e2e_step(i):
             qd.copy_(host[0], non_blocking=True), kd.copy_(host[1], non_blocking=True), vd.copy_(host[2], non_blocking=True)
@@ -263,6 +265,7 @@ def main():
                 roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
                               kernel="decode_kernel", us_per_launch=kernel_s * 1e6, bytes_per_launch=bytes_per_launch,
                               peak_source=f"{peak_kind} copy bandwidth", frac_of_8tbs=achieved / 8000.0,
+                              copy_pipeline_only_gbs=bytes_per_launch / (ms_stream / args.steps / 1e3) / 1e9,
                               ctas=int(plan["cta_segments"].shape[0] - 1), segments=int(plan["segments"].shape[0])),
                 hbm_gbs_whole_step=bytes_per_launch / (ms_total / args.steps / 1e3) / 1e9,
                 clocks=clocks.summary())

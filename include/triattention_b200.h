@@ -92,7 +92,8 @@ int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* un
  * unit_slots int32 [U,2] = (first partial slot, number of splits); pm, pl f32 [P,8]; po f32 [P,8,128];
  * tail_k/tail_v bf16 [U,max_tail,128] with element strides; kcur/vcur bf16 [B,Hkv,1,128];
  * step int64 [1] on the device; out bf16 [B,Hq,1,128].  phases: 1 = split pass only, 2 = merge only,
- * 3 = both (normal use; the single phases exist so that each kernel can be timed alone). */
+ * 3 = both (normal use; the single phases exist so that each kernel can be timed alone); 5 = split pass
+ * that only streams the cache through shared memory without arithmetic (diagnostic of the copy pipeline). */
 int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
                const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
                const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,

@@ -165,9 +165,9 @@ def test_plan_work_list_covers_every_tile_once():
             for u, first, cnt, slot in plan["segments"][cs[c]:cs[c + 1]]:
                 rows = plan["tmeta"][plan["unit_tab"][u] + first:plan["unit_tab"][u] + first + cnt]
                 info = rows[:, 1].astype(np.int64)
-                nbytes = np.where(info >> 22 & 1, 16384, np.where(info >> 20 & 1, 4096, 8192) + np.where(info >> 21 & 1, 4096, 8192) + 16)
-                cost[c] += nbytes.sum() + dec.TILE_COST * cnt
-        assert cost.max() - cost.min() <= 2 * (16384 + dec.TILE_COST)
+                bf, k4, v4 = info >> 22 & 1, info >> 20 & 1, info >> 21 & 1
+                cost[c] += np.where(bf == 1, dec.TILE_COSTS[0], np.where((k4 == 0) & (v4 == 0), dec.TILE_COSTS[1], dec.TILE_COSTS[2])).sum()
+        assert cost.max() - cost.min() <= 2 * max(dec.TILE_COSTS)
         # streams do not overlap and stay inside the pool
         ends = plan["unit_base"] + plan["head_bytes"][np.arange(units) % 4]
         order = np.argsort(plan["unit_base"])

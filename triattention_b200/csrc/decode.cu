@@ -200,7 +200,7 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
   if (num_ctas > 0 && (phases & 1))
     decode_kernel<<<num_ctas, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
         unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),
-        cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, device_error);
+        cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, (phases & 4) ? 1 : 0, device_error);
   if (phases & 2)
     decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
         kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),

@@ -4,14 +4,16 @@
 // Replaces triattention/kernels/cuda/common_device.cuh:178-371 (decode_tile, decode_kernel) of the
 // reference.  The arithmetic per tile is the reference's (same float expressions, same 8-bit / 4-bit
 // P codes with the accumulator's low byte as dither); the organisation is not:
-//   * one CTA per SM; warp 4 is the producer: it walks the CTA's tile list and keeps a 12-stage
-//     shared-memory ring full with TMA bulk copies (one per tile chunk, mbarrier transaction counts);
-//   * warps 0-3 are consumers.  Each owns whole tiles (tile t of the CTA goes to warp t % 4), so the
-//     probabilities never leave registers: the accumulator fragment of QK^T is repacked in place as
-//     the A fragment of P.V.  No block barrier and no shared-memory exchange per tile;
+//   * one CTA per SM; the last warp is the producer: it walks the CTA's tile list and keeps a
+//     12-stage shared-memory ring full with TMA bulk copies (one per tile chunk, mbarrier transaction
+//     counts);
+//   * the other ConsumerWarps warps are consumers.  Each owns whole tiles (tile t of the CTA goes to
+//     warp t % ConsumerWarps), so the probabilities never leave registers: the accumulator fragment
+//     of QK^T is repacked in place as the A fragment of P.V.  No block barrier and no shared-memory
+//     exchange per tile;
 //   * a CTA's tile list is a contiguous slice of the global tile sequence cut by cost, so all CTAs
-//     finish together; where the slice crosses a (sequence, KV head) boundary the four consumers
-//     fold their states through shared memory and emit one partial (m, l, o) per segment.
+//     finish together; where the slice crosses a (sequence, KV head) boundary the consumers fold
+//     their states through shared memory and emit one partial (m, l, o) per segment.
 // Tile chunk layouts in the cache pool (written by cache_store_kernel; a lane reads 16 contiguous
 // bytes and a warp 512 contiguous bytes per load):
 //   K8 [key/8][half][key%8][sub][16 B]   16 B = features 32*sub + 16*half + 0..15 of the key
@@ -27,14 +29,19 @@
 
 namespace tri {
 
-constexpr int ConsumerWarps = 4;
+constexpr int ConsumerWarps = 6;
 constexpr int DecodeThreads = (ConsumerWarps + 1) * 32;
 constexpr int DecodeStages = 12;
+// A stage must always be consumed by the same warp: a consumer that could run a whole ring round ahead
+// of another would see the stage's barrier parity of two phases ago and read stale bytes.
+static_assert(DecodeStages % ConsumerWarps == 0, "stage ownership");
 constexpr int StageBytes = 16512;                      // >= 8192 + 8192 + 16, multiple of 128
 constexpr int Bf16ChunkKeys = 32, Bf16ChunkBytes = 16384;
 constexpr int CombFloats = MaxGroup * D + 2 * MaxGroup;
-constexpr int SmRing = 0, SmQ = DecodeStages * StageBytes, SmComb = SmQ + ConsumerWarps * 2048;
+// per-warp fold slot (CombFloats floats); its first 2 KB double as the warp's Q scratch between folds
+constexpr int SmRing = 0, SmComb = DecodeStages * StageBytes;
 constexpr int DecodeShared = SmComb + ConsumerWarps * CombFloats * 4;
+static_assert(DecodeShared <= 227 * 1024 && CombFloats * 4 >= 2048, "decode shared-memory plan");
 
 // tile_info bits
 constexpr uint32_t InfoTileMask = 0xfffu, InfoRowShift = 12, InfoK4 = 1u << 20, InfoV4 = 1u << 21, InfoBf16 = 1u << 22;
@@ -59,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() {   // the four consumer warps only
+__device__ __forceinline__ void consumer_sync() {   // the consumer warps only
   asm volatile("bar.sync 1, %0;" ::"n"(ConsumerWarps * 32) : "memory");
 }
 
@@ -222,7 +229,7 @@ __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t 
 __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
     const uint8_t* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int2* tmeta,
     const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt,
-    float sm_log2, int* err) {
+    float sm_log2, int stream_only, int* err) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[DecodeStages], empty[DecodeStages];
   __shared__ uint32_t stage_info[DecodeStages];
@@ -242,29 +249,37 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
   volatile int* abortp = &abort_flag;
 
   if (warp == ConsumerWarps) {
-    // ---- producer: one lane keeps the ring full -------------------------------------------------
-    if (lane == 0) {
-      int t = 0;
-      for (int j = 0; j < nseg && !*abortp; ++j) {
-        const int4 sg = segs[seg0 + j];
-        const int2* meta = tmeta + unit_tab[sg.x] + sg.y;
-        const uint8_t* base = pool + unit_base[sg.x];
-        int2 mt = sg.z > 0 ? meta[0] : make_int2(0, 0);
-        for (int i = 0; i < sg.z; ++i, ++t) {
-          const int2 next = i + 1 < sg.z ? meta[i + 1] : make_int2(0, 0);   // table read ahead of its use
-          const int s = t % DecodeStages;
-          if (!mbar_wait_abortable(&empty[s], ((t / DecodeStages) & 1) ^ 1, abortp)) break;
-          const uint32_t bytes = chunk_bytes((uint32_t)mt.y);
-          stage_info[s] = (uint32_t)mt.y;
-          mbar_expect_tx(&full[s], bytes);
-          bulk_g2s(smem + SmRing + s * StageBytes, base + (int64_t)mt.x * 16, bytes, &full[s]);
-          mt = next;
+    // ---- producer warp: keeps the ring full ----------------------------------------------------------
+    // The tile table is read 32 entries at a time (one coalesced load per lane, the next batch in
+    // flight while the current one is issued), so no global-memory latency sits between two copies;
+    // lane 0 waits for a free stage and issues the bulk copy.
+    int t = 0;
+    for (int j = 0; j < nseg && !*abortp; ++j) {
+      const int4 sg = segs[seg0 + j];
+      const int2* meta = tmeta + unit_tab[sg.x] + sg.y;
+      const uint8_t* base = pool + unit_base[sg.x];
+      int2 batch = lane < sg.z ? meta[lane] : make_int2(0, 0);
+      for (int i0 = 0; i0 < sg.z && !*abortp; i0 += 32) {
+        const int2 next = i0 + 32 + lane < sg.z ? meta[i0 + 32 + lane] : make_int2(0, 0);
+        const int nb = min(32, sg.z - i0);
+        for (int k = 0; k < nb; ++k, ++t) {
+          const int off16 = __shfl_sync(0xffffffffu, batch.x, k), info = __shfl_sync(0xffffffffu, batch.y, k);
+          if (lane == 0) {
+            const int s = t % DecodeStages;
+            if (mbar_wait_abortable(&empty[s], ((t / DecodeStages) & 1) ^ 1, abortp)) {
+              const uint32_t bytes = chunk_bytes((uint32_t)info);
+              stage_info[s] = (uint32_t)info;
+              mbar_expect_tx(&full[s], bytes);
+              bulk_g2s(smem + SmRing + s * StageBytes, base + (int64_t)off16 * 16, bytes, &full[s]);
+            }
+          }
         }
+        batch = next;
       }
     }
   } else {
     // ---- consumers: warp w owns tiles t = w, w+4, ... of the CTA's list ------------------------------
-    uint8_t* q8buf = smem + SmQ + warp * 2048;
+    uint8_t* q8buf = smem + SmComb + warp * CombFloats * 4;
     uint8_t* q4buf = q8buf + 1024;
     float* comb = reinterpret_cast<float*>(smem + SmComb);
     int t0 = 0;
@@ -335,7 +350,9 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
         const int tile = info & InfoTileMask;
         const unsigned rowmask = (info >> InfoRowShift) & 0xffu;
         const bool row_on = group < g && ((rowmask >> group) & 1u);
-        if (info & InfoBf16) {
+        if (stream_only) {
+          // diagnostic: consume the ring without arithmetic (measures the copy pipeline alone)
+        } else if (info & InfoBf16) {
           bf16_chunk(stage, qb, sm_log2, st, tile * Bf16ChunkKeys, prompt, row_on);
         } else if (info & InfoK4) {
           if (info & InfoV4) quantised_tile<true, true>(stage, qf4, qs4, st, tile * BN, prompt, row_on);
@@ -349,7 +366,7 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
       }
       t0 += count;
 
-      // ---- fold the four warps' states of this segment into one partial (m, l, o) per Q head ------
+      // ---- fold the consumer warps' states of this segment into one partial (m, l, o) per Q head ---
       float den = st.denom;
       den += __shfl_xor_sync(0xffffffffu, den, 1);
       den += __shfl_xor_sync(0xffffffffu, den, 2);
@@ -360,8 +377,8 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
       if (sub == 0) { mine[MaxGroup * D + group] = st.m; mine[MaxGroup * D + MaxGroup + group] = den; }
       consumer_sync();
       {
-        const int ch = tid;   // 128 consumer threads = 128 channels
-        for (int r = 0; r < g; ++r) {
+        for (int e = tid; e < g * D; e += ConsumerWarps * 32) {   // one (Q head, channel) per consumer thread
+          const int r = e / D, ch = e % D;
           float mw[ConsumerWarps], big = -FLT_MAX;
 #pragma unroll
           for (int w = 0; w < ConsumerWarps; ++w) { mw[w] = comb[w * CombFloats + MaxGroup * D + r]; big = fmaxf(big, mw[w]); }
@@ -379,6 +396,12 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
       }
       consumer_sync();   // the fold buffer is free for the next segment
     }
+  }
+  if (*abortp) {
+    // a wait ran out: give copies that may still be in flight a bounded time to land before the CTA
+    // (and its shared memory) goes away
+    const uint64_t t_abort = globaltimer_ns();
+    while (globaltimer_ns() - t_abort < 2000000ull) {}
   }
   __syncthreads();
   if (tid == 0 && abort_flag) atomicExch(err, ErrBarrierTimeout);

@@ -24,7 +24,10 @@ K8_BYTES, K4_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 8192, 4096
 BF16_CHUNK_KEYS, BF16_CHUNK_BYTES = 32, 16384
 INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16 = 12, 1 << 20, 1 << 21, 1 << 22
 MAX_GROUP = 8
-TILE_COST = 4096   # bytes-equivalent of the fixed per-tile work in the partition's cost model
+# Relative time of one tile on one SM, by kind, for the partition's cost model: (BF16 32-key chunk,
+# INT8-K/INT8-V tile, any other quantised tile).  Quantised tiles are bound by their arithmetic (the same
+# for 8 and 12 KB of codes); 16 KB tiles are bound by the SM's share of the HBM bandwidth.
+TILE_COSTS = (0.85, 1.05, 1.0)
 
 
 def tile_states(bands, heads_kv, tiles):
@@ -37,7 +40,7 @@ def tile_states(bands, heads_kv, tiles):
     return state.max(1), rowmask
 
 
-def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost=TILE_COST):
+def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_costs=TILE_COSTS):
     """Host-side layout of one layer's cache and its partition over `ctas` persistent CTAs (numpy).
 
     Returns a dict of numpy arrays: tmeta [N,2], tab_begin/count/head_bytes [Hkv], unit_base [U] (int64),
@@ -48,17 +51,19 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
     kv, rowmask = tile_states(bands, heads_kv, tiles)
     j = np.arange(tiles)
     v4 = ~((tiles - 1 - j < NEAR_V8) | (j == 0))
-    metas, sizes, tab_begin, count, head_bytes = [], [], [], [], []
+    metas, sizes, costs, tab_begin, count, head_bytes = [], [], [], [], [], []
     for kh in range(heads_kv):
         if kh in bf16_kv:
             n = (prompt + BF16_CHUNK_KEYS - 1) // BF16_CHUNK_KEYS
             info = np.arange(n, dtype=np.int64) | (0xFF << INFO_ROW_SHIFT) | INFO_BF16
             size = np.full(n, BF16_CHUNK_BYTES, np.int64)
+            costs.append(np.full(n, tile_costs[0], np.float64))
         else:
             kept = np.nonzero(kv[kh] > 0)[0]
             k4 = kv[kh][kept] == 4
             info = kept | ((rowmask[kh][kept] & 0xFF) << INFO_ROW_SHIFT) | np.where(k4, INFO_K4, 0) | np.where(v4[kept], INFO_V4, 0)
             size = np.where(k4, K4_BYTES, K8_BYTES) + np.where(v4[kept], V4_BYTES, V8_BYTES) + 16
+            costs.append(np.where(~k4 & ~v4[kept], tile_costs[1], tile_costs[2]).astype(np.float64))
         off = np.concatenate([[0], np.cumsum(size)])
         tab_begin.append(sum(len(m) for m in metas))
         metas.append(np.stack([off[:-1] // 16, info], 1))
@@ -73,8 +78,8 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
     unit_base = (np.arange(units) // heads_kv).astype(np.int64) * seq_bytes + head_off[kh_of]
     unit_flags = np.isin(kh_of, list(bf16_kv)).astype(np.int32)
     # static partition: the tiles of all units in unit order form one sequence; CTA c takes the tiles whose
-    # cumulative cost (bytes + a fixed per-tile term) starts inside [c, c+1) * total / ctas
-    ccum = [np.concatenate([[0], np.cumsum(s + tile_cost)]) for s in sizes]
+    # cumulative cost (TILE_COSTS by kind) starts inside [c, c+1) * total / ctas
+    ccum = [np.concatenate([[0], np.cumsum(c)]) for c in costs]
     unit_cost = np.array([ccum[kh][-1] for kh in kh_of], np.float64)
     unit_start = np.concatenate([[0.0], np.cumsum(unit_cost)])
     share = max(unit_start[-1] / ctas, 1.0)
@@ -102,10 +107,10 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256, ctas=None, tile_cost=TILE_COST):
+    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS):
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
-        self.module, self.max_tail, self.ctas, self.tile_cost = module, max_tail, ctas, tile_cost
+        self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
 
     def codes(self, rows):
@@ -133,7 +138,7 @@ class DecodeCache:
         key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device))
         if key not in self.plans:
             host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
-                                tile_cost=self.tile_cost)
+                                tile_costs=self.tile_costs)
             dev = {name: torch.from_numpy(host[name]).to(device) for name in
                    ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
             if bf16_kv:
