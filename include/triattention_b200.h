@@ -103,6 +103,26 @@ int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void
                int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases,
                int* device_error, void* stream);
 
+/* tri_decode for callers that cannot allocate device memory (a runtime that gave all of HBM to its KV
+ * pool up front, a binding that can only pass buffers it was handed).  Same arguments as tri_decode
+ * without pm / pl / po and without phases: the split-KV partials live in a fixed 4,259,840-byte array
+ * inside the library, held by every GPU that loads it until the process exits.  num_slots = number of
+ * rows of `segments`; more than 1024 is refused with TRI_ERR_ARGUMENT (use tri_decode then).  The call
+ * makes no allocation of any kind.  The first call on each device looks up the array's device address
+ * (with that device current), so make that first call outside any stream capture.  All calls on a device
+ * share the array: calls that can overlap on the GPU (different streams) race on it, so keep them on
+ * one stream or order them yourself.  Nothing needs clearing between calls.
+ * No counterpart in the reference, whose Python caller allocates the partials (kernels/decode.py:72-75). */
+int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
+                      const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
+                      const int32_t* cta_segments, int num_ctas, int num_slots, const int32_t* unit_slots,
+                      const float* kstat, const float* vstat, void* tail_k, void* tail_v,
+                      int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
+                      int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out,
+                      int64_t out_stride_b, int64_t out_stride_h,
+                      int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale,
+                      int* device_error, void* stream);
+
 /* Resident decode CTAs per SM.  Replaces decode_occupancy(), triattention/kernels/cuda/common_host.cuh:89-94. */
 int tri_decode_occupancy(void);
 

@@ -234,3 +234,67 @@ extern "C" int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const 
       k_stride_b, k_stride_h, k_stride_t, v_stride_b, v_stride_h, v_stride_t);
   return tri_launch_status("cache_store_bf16");
 }
+
+// ---- decode step for callers that cannot allocate device memory -----------------------------------
+// Some callers of this library own no allocator on the GPU: a serving runtime that has handed every
+// byte of HBM to its paged KV pool before the first request arrives, or a host language binding that
+// can pass tensors it was given but has no way to ask the driver for more.  tri_decode needs scratch
+// for the split-KV partials (pm, pl, po); this variant keeps that scratch inside the library image, in
+// a fixed array that every GPU loading the library holds until the process exits.
+constexpr int StaticSlots = 1024;                                     // partial slots (segments) per call, at most
+constexpr size_t StaticFloats = (size_t)StaticSlots * MaxGroup * (D + 2);
+static __device__ __align__(256) float g_static_partials[StaticFloats];   // 4,259,840 bytes per GPU
+
+// Device address of the array, looked up once per device.  In host code the array's name is only a
+// handle for the runtime, never an address a kernel may use.
+static float* static_partials_for_current_device(void) {
+  constexpr int MaxDevices = 64;
+  static float* known[MaxDevices] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MaxDevices) return nullptr;
+  if (known[device] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_partials) != cudaSuccess) return nullptr;
+    known[device] = static_cast<float*>(p);
+  }
+  return known[device];
+}
+
+extern "C" int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool,
+    const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
+    const int32_t* cta_segments, int num_ctas, int num_slots, const int32_t* unit_slots, const float* kstat, const float* vstat,
+    void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
+    int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,
+    int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int* device_error, void* stream) {
+  TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && kstat &&
+            vstat && tail_k && tail_v && kcur && vcur && step && out && device_error, "decode_static: null buffers");
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
+            max_tail >= 1 && max_tail <= 1024 && prompt > 0 && num_ctas > 0 && num_slots > 0, "decode geometry/buffers");
+  TRI_CHECK(num_slots <= StaticSlots,
+            "decode_static: more than 1024 partial slots (segments); use tri_decode with caller-allocated partials");
+  TRI_CHECK(aligned16(pool) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 && q_stride_h % 4 == 0,
+            "decode: alignment");
+  if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
+  float* scratch = static_partials_for_current_device();
+  if (scratch == nullptr) {
+    tri_set_error("decode_static: cudaGetSymbolAddress failed for the partials array on the current device");
+    return TRI_ERR_CUDA;
+  }
+  // Nothing in the array has to start at zero: the split pass writes every (slot, Q head) entry that the
+  // merge reads, so the previous call's contents are simply overwritten.
+  float* pm = scratch;
+  float* pl = scratch + (size_t)StaticSlots * MaxGroup;
+  float* po = scratch + (size_t)StaticSlots * MaxGroup * 2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const float sm_log2 = (float)(scale * 1.4426950408889634);
+  const auto* qp = static_cast<const __nv_bfloat16*>(q);
+  decode_kernel<<<num_ctas, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
+      unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),
+      cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, 0, device_error);
+  decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
+      kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
+      tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),
+      cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, heads_q, heads_kv,
+      max_tail, sm_log2);
+  return tri_launch_status("decode_static");
+}

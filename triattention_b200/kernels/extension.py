@@ -27,6 +27,8 @@ SIGNATURES = {
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _P],
     "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
                    _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
+    "tri_decode_static": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P,
+                          _L, _L, _I, _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_umma_probe": [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, _P, _P],
@@ -172,6 +174,22 @@ class Module:
                                             step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(),
                                             pl.data_ptr(), po.data_ptr(), b, hq, hk, int(prompt), max_tail, float(scale), int(phases),
                                             self.error_word(q.device).data_ptr(), _stream()))
+        return out
+
+    def decode_static(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, kstat,
+                      vstat, tail_k, tail_v, kcur, vcur, step, out, prompt, scale):
+        """Decode step whose split-KV partials live in the library's own fixed device array, for callers that
+        cannot allocate GPU memory.  Refuses plans with more than 1024 segments; calls that may overlap on the
+        GPU must not share a device."""
+        b, hq, hk = q.shape[0], q.shape[1], kcur.shape[1]
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_decode_static(
+                q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
+                unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(), cta_segments.data_ptr(),
+                cta_segments.numel() - 1, segments.shape[0], unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(),
+                tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), tail_k.stride(1), kcur.data_ptr(), vcur.data_ptr(),
+                kcur.stride(0), kcur.stride(1), step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), b, hq, hk,
+                int(prompt), tail_k.shape[1], float(scale), self.error_word(q.device).data_ptr(), _stream()))
         return out
 
     def decode_occupancy(self):
