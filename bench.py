@@ -262,7 +262,10 @@ def main():
                 e2e=dict(value=tokens * args.steps / (ms_e2e / 1e3), unit="tokens/s",
                          h2d_bytes_per_step=sum(x.numel() * 2 for x in host), d2h_bytes_per_step=out.numel() * 2),
                 gpu_launches=2 * args.steps,
-                roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
+                roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
+                              # ncu capture of a batch-8 case (profiles/decode_kernel_c2.md): reads = 1.0014 x algorithmic
+                              # bytes, writes = 23.4 KB per segment; scaled by the tiles / segments of this launch
+                              traffic=int(bytes_per_launch * 1.0014 + plan["segments"].shape[0] * 23400),
                               kernel="decode_kernel", us_per_launch=kernel_s * 1e6, bytes_per_launch=bytes_per_launch,
                               peak_source=f"{peak_kind} copy bandwidth", frac_of_8tbs=achieved / 8000.0,
                               copy_pipeline_only_gbs=bytes_per_launch / (ms_stream / args.steps / 1e3) / 1e9,
