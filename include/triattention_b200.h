@@ -76,11 +76,14 @@ int tri_cache_store(void* pool, const int64_t* unit_base, const int32_t* unit_ta
                     const void* v8, const void* v4, int tiles, void* stream);
 
 /* Same for un-quantised BF16 units (an extension; the reference has no BF16 heads in its kernels):
- * K and V rows are copied into 32-key chunks of 16384 B in MMA fragment order.  units int32 [n]. */
+ * K and V rows are copied into 32-key chunks of 16384 B in MMA fragment order.  units int32 [n].
+ * Chunks chunk_begin .. chunk_begin+chunk_count-1 of each unit are written, starting at the unit's base
+ * (the whole prompt, or this GPU's part of it when the sequence is split across GPUs). */
 int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* units, int num_units,
                          const void* k, const void* v, int tokens, int heads_kv,
                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
-                         int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t, void* stream);
+                         int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+                         int chunk_begin, int chunk_count, void* stream);
 
 /* One decode step of one layer for the whole batch: split-KV pass over the cache streams, then the
  * merge with the BF16 tail of generated tokens (the current K/V row is appended to the tail).
@@ -102,6 +105,13 @@ int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void
                int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po,
                int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases,
                int* device_error, void* stream);
+
+/* Fold a unit's segment partials into one (m, l, o) per Q head: fm, fl f32 [U,8], fo f32 [U,8,128].
+ * Used when the tile range of a unit is split across GPUs: each rank folds, the triples are all-gathered
+ * and tri_decode(phases = 2) merges them with one slot per rank.  Extends the split merge of
+ * triattention/kernels/cuda/common_device.cuh:418-438 across devices; the reference is single-GPU. */
+int tri_decode_fold(const float* pm, const float* pl, const float* po, const int32_t* unit_slots,
+                    float* fm, float* fl, float* fo, int units, int group, void* stream);
 
 /* tri_decode for callers that cannot allocate device memory (a runtime that gave all of HBM to its KV
  * pool up front, a binding that can only pass buffers it was handed).  Same arguments as tri_decode

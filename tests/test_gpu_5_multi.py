@@ -1,0 +1,85 @@
+"""Two-GPU paths: unit sharding with output gather, and the sequence split with the NCCL (m, l, o) exchange.
+Skipped on a single-GPU box; the host logic of both is covered on CPU by tests/test_cpu_sharding.py."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+SCALE = 128 ** -0.5
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(hq, hk, t, batch, steps):
+    from util import make_inputs
+    return make_inputs(hq, hk, t, seed=3, batch=batch) + make_inputs(hq, hk, steps, seed=4, batch=batch)
+
+
+def _decode_steps(module, bands_fn, q, k, v, qd, kd, vd, steps, group=None):
+    from triattention_b200.kernels.decode import DecodeCache
+    from triattention_b200.kernels.prefill import Prefill
+    cache = DecodeCache(module, max_tail=8, split_group=group)
+    pre = Prefill(module, bands_fn, cache)
+    table, ops = pre.write(0, q, k, v)
+    cache.store(0, q.shape[2], ops, table.host, k, v, table.bf16_kv)
+    outs = []
+    for s in range(steps):
+        outs.append(cache(0, qd[:, :, s:s + 1], kd[:, :, s:s + 1], vd[:, :, s:s + 1], SCALE).float())
+        cache.advance()
+    module.check_device_error()
+    return torch.stack(outs, 1)
+
+
+def _worker(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from triattention_b200 import sharding
+        from triattention_b200.kernels.extension import load_extension
+        from triattention_b200.maps import per_kv_head
+        from util import bf16_cuda, fp_report
+        module = load_extension()
+        hq, hk, t, batch, steps = 8, 4, 3000, 2, 2
+        fn = per_kv_head(["int8", "int4", "bf16", "int8"], 2)
+        q, k, v, qd, kd, vd = (bf16_cuda(x) for x in _inputs(hq, hk, t, batch, steps))
+        whole = _decode_steps(module, fn, q, k, v, qd, kd, vd, steps)
+        # 1. sequence split: every unit's tile range cut in two, folded triples all-gathered over NCCL
+        split = _decode_steps(module, fn, q, k, v, qd, kd, vd, steps, group=dist.group.WORLD)
+        r1 = fp_report(split.cpu().numpy(), whole.cpu().numpy())
+        # 2. unit sharding: this rank's (batch slice, KV-head group), outputs gathered
+        costs = sharding.head_costs(fn(0, hq).numpy(), hk, t, fn.bf16_kv_heads(0))
+        shards = sharding.shard_grid(batch, costs, world)
+        s = shards[rank]
+        take = lambda x, heads: sharding.take_shard(x, s, heads).contiguous()
+        kvh, qh = list(s.kv_heads), list(s.q_heads(2))
+        local = _decode_steps(module, sharding.slice_map(fn, s, 2, hq), take(q, qh), take(k, kvh), take(v, kvh),
+                              take(qd, qh), take(kd, kvh), take(vd, kvh), steps)
+        full = sharding.gather_outputs(local.transpose(1, 2).contiguous(), shards, 2, batch, hq).transpose(1, 2)
+        r2 = fp_report(full.cpu().numpy(), whole.cpu().numpy())
+        result[rank] = (r1, r2, [list(x.kv_heads) for x in shards])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_split_and_sharding():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    with mp.Manager() as manager:
+        result = manager.dict()
+        mp.spawn(_worker, args=(world, port, result), nprocs=world, join=True)
+        for rank in range(world):
+            r1, r2, groups = result[rank]
+            assert r1["worst_excess"] <= 0 and r1["cos"] >= 0.9999, ("sequence split", r1)
+            # a shard is a smaller problem with its own CTA partition, so only the float summation order differs
+            assert r2["worst_excess"] <= 0 and r2["cos"] >= 0.9999, ("unit sharding", r2, groups)

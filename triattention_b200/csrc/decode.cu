@@ -139,12 +139,12 @@ __global__ void __launch_bounds__(256) cache_store_kernel(uint8_t* pool, const i
 // grid (32-key chunks, listed BF16 units), 256 threads: K/V bf16 [B,Hkv,T,128] -> decode-layout chunks.
 __global__ void __launch_bounds__(256) cache_store_bf16_kernel(uint8_t* pool, const int64_t* unit_base, const int32_t* units,
     const __nv_bfloat16* k, const __nv_bfloat16* v, int tokens, int heads, int64_t ksb, int64_t ksh, int64_t kst, int64_t vsb,
-    int64_t vsh, int64_t vst) {
-  const int chunk = blockIdx.x, unit = units[blockIdx.y];
+    int64_t vsh, int64_t vst, int chunk_begin) {
+  const int unit = units[blockIdx.y];
   const __nv_bfloat16* kb = k + (unit / heads) * ksb + (unit % heads) * ksh;
   const __nv_bfloat16* vb = v + (unit / heads) * vsb + (unit % heads) * vsh;
-  uint8_t* dst = pool + unit_base[unit] + (int64_t)chunk * Bf16ChunkBytes;
-  const int key0 = chunk * Bf16ChunkKeys;
+  uint8_t* dst = pool + unit_base[unit] + (int64_t)blockIdx.x * Bf16ChunkBytes;   // the stream holds chunks begin, begin+1, ...
+  const int key0 = (chunk_begin + blockIdx.x) * Bf16ChunkKeys;
   for (int d = threadIdx.x; d < 512; d += 256) {      // K: 16-byte runs [key/8][u][key%8][sub] = features 32sub+8u..+7
     const int nb = d / 128, u = (d % 128) / 32, key = key0 + nb * 8 + (d % 32) / 4, sub = d % 4;
     reinterpret_cast<uint4*>(dst)[d] = key < tokens ? *reinterpret_cast<const uint4*>(kb + (int64_t)key * kst + sub * 32 + u * 8)
@@ -224,15 +224,51 @@ extern "C" int tri_cache_store(void* pool, const int64_t* unit_base, const int32
 
 extern "C" int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* units, int num_units, const void* k,
     const void* v, int tokens, int heads_kv, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t, int64_t v_stride_b,
-    int64_t v_stride_h, int64_t v_stride_t, void* stream) {
+    int64_t v_stride_h, int64_t v_stride_t, int chunk_begin, int chunk_count, void* stream) {
   TRI_CHECK(pool && unit_base && units && k && v && num_units > 0 && tokens > 0 && heads_kv > 0, "cache_store_bf16: arguments");
   TRI_CHECK(k_stride_t % 8 == 0 && k_stride_h % 8 == 0 && k_stride_b % 8 == 0 && aligned16(k) && aligned16(pool),
             "cache_store_bf16: K rows must be 16-byte aligned");
   const int chunks = (tokens + Bf16ChunkKeys - 1) / Bf16ChunkKeys;
-  cache_store_bf16_kernel<<<dim3(chunks, num_units), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint8_t*>(pool),
+  TRI_CHECK(chunk_begin >= 0 && chunk_count > 0 && chunk_begin + chunk_count <= chunks, "cache_store_bf16: chunk range");
+  cache_store_bf16_kernel<<<dim3(chunk_count, num_units), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint8_t*>(pool),
       unit_base, units, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), tokens, heads_kv,
-      k_stride_b, k_stride_h, k_stride_t, v_stride_b, v_stride_h, v_stride_t);
+      k_stride_b, k_stride_h, k_stride_t, v_stride_b, v_stride_h, v_stride_t, chunk_begin);
   return tri_launch_status("cache_store_bf16");
+}
+
+// ---- fold: one (m, l, o) per unit and Q head from the unit's segment partials ---------------------
+// Used when a unit's tile range is split across GPUs: every rank folds its local segments, the
+// folded triples (1,040 B per Q head) are all-gathered, and the merge kernel then sees one "segment" per
+// rank.  Same arithmetic as the first half of decode_merge_kernel; no V de-normalisation, no tail.
+namespace tri {
+__global__ void __launch_bounds__(D) decode_fold_kernel(const float* pm, const float* pl, const float* po,
+    const int2* unit_slots, float* fm, float* fl, float* fo, int group) {
+  const int unit = blockIdx.x, ch = threadIdx.x;
+  const int2 sl = unit_slots[unit];
+  for (int r = 0; r < group; ++r) {
+    float big = -FLT_MAX;
+    for (int s = 0; s < sl.y; ++s) big = fmaxf(big, pm[(int64_t)(sl.x + s) * MaxGroup + r]);
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < sl.y; ++s) {
+      const int64_t idx = (int64_t)(sl.x + s) * MaxGroup + r;
+      const float w = exp2f(pm[idx] - big);
+      o = fmaf(po[idx * D + ch], w, o);
+      l = fmaf(pl[idx], w, l);
+    }
+    const int64_t dst = (int64_t)unit * MaxGroup + r;
+    fo[dst * D + ch] = o;
+    if (ch == 0) { fm[dst] = big; fl[dst] = l; }
+  }
+}
+}  // namespace tri
+
+extern "C" int tri_decode_fold(const float* pm, const float* pl, const float* po, const int32_t* unit_slots, float* fm,
+    float* fl, float* fo, int units, int group, void* stream) {
+  TRI_CHECK(pm && pl && po && unit_slots && fm && fl && fo, "decode_fold: null buffers");
+  TRI_CHECK(units > 0 && group >= 1 && group <= MaxGroup, "decode_fold: geometry");
+  decode_fold_kernel<<<units, D, 0, static_cast<cudaStream_t>(stream)>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots),
+      fm, fl, fo, group);
+  return tri_launch_status("decode_fold");
 }
 
 // ---- decode step for callers that cannot allocate device memory -----------------------------------

@@ -40,8 +40,9 @@ def tile_states(bands, heads_kv, tiles):
     return state.max(1), rowmask
 
 
-def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_costs=TILE_COSTS):
+def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_costs=TILE_COSTS, split=None):
     """Host-side layout of one layer's cache and its partition over `ctas` persistent CTAs (numpy).
+    split = (rank, world) keeps only this rank's part of every unit's kept-tile list (sequence split).
 
     Returns a dict of numpy arrays: tmeta [N,2], tab_begin/count/head_bytes [Hkv], unit_base [U] (int64),
     unit_tab/unit_count/unit_flags [U], segments [S,4] = (unit, first kept tile, tile count, partial slot),
@@ -52,6 +53,7 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
     j = np.arange(tiles)
     v4 = ~((tiles - 1 - j < NEAR_V8) | (j == 0))
     metas, sizes, costs, tab_begin, count, head_bytes = [], [], [], [], [], []
+    bf16_range = (0, (prompt + BF16_CHUNK_KEYS - 1) // BF16_CHUNK_KEYS)
     for kh in range(heads_kv):
         if kh in bf16_kv:
             n = (prompt + BF16_CHUNK_KEYS - 1) // BF16_CHUNK_KEYS
@@ -64,6 +66,14 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
             info = kept | ((rowmask[kh][kept] & 0xFF) << INFO_ROW_SHIFT) | np.where(k4, INFO_K4, 0) | np.where(v4[kept], INFO_V4, 0)
             size = np.where(k4, K4_BYTES, K8_BYTES) + np.where(v4[kept], V4_BYTES, V8_BYTES) + 16
             costs.append(np.where(~k4 & ~v4[kept], tile_costs[1], tile_costs[2]).astype(np.float64))
+        if split is not None:   # sequence split across GPUs: this rank keeps one contiguous, cost-balanced part
+            rank, world = split
+            cc = np.concatenate([[0], np.cumsum(costs[-1])])
+            lo = int(np.searchsorted(cc, rank * cc[-1] / world, side="left"))
+            hi = len(info) if rank == world - 1 else int(np.searchsorted(cc, (rank + 1) * cc[-1] / world, side="left"))
+            info, size, costs[-1] = info[lo:hi], size[lo:hi], costs[-1][lo:hi]
+            if kh in bf16_kv:
+                bf16_range = (lo, hi - lo)
         off = np.concatenate([[0], np.cumsum(size)])
         tab_begin.append(sum(len(m) for m in metas))
         metas.append(np.stack([off[:-1] // 16, info], 1))
@@ -102,16 +112,23 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
                 unit_tab=np.asarray(tab_begin, np.int32)[kh_of], unit_count=np.asarray(count, np.int32)[kh_of],
                 unit_flags=unit_flags, segments=np.asarray(segments, np.int32).reshape(-1, 4), cta_segments=cta_segments,
                 unit_slots=np.asarray(unit_slots, np.int32).reshape(-1, 2), slots=len(segments),
-                pool_bytes=int(batch * seq_bytes), seq_bytes=seq_bytes, tiles=tiles,
+                pool_bytes=int(batch * seq_bytes), seq_bytes=seq_bytes, tiles=tiles, bf16_range=bf16_range,
                 payload_bytes=int(batch * sum(int(s.sum()) for s in sizes)))
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS):
+    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None):
+        """split_group: a torch.distributed process group over which every unit's tile range is split
+        (long-context decode): each rank streams its part, the folded (m, l, o) triples are all-gathered over
+        NCCL and every rank runs the final merge.  None = this process holds whole units."""
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
+        self.split_group, self.split = split_group, None
+        if split_group is not None:
+            import torch.distributed as dist
+            self.split = (dist.get_rank(split_group), dist.get_world_size(split_group))
 
     def codes(self, rows):
         """decode.py:17-22: V format per prompt tile in decode, and the set of formats used."""
@@ -135,10 +152,10 @@ class DecodeCache:
         return self.ctas
 
     def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device):
-        key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device))
+        key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device), self.split)
         if key not in self.plans:
             host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
-                                tile_costs=self.tile_costs)
+                                tile_costs=self.tile_costs, split=self.split)
             dev = {name: torch.from_numpy(host[name]).to(device) for name in
                    ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
             if bf16_kv:
@@ -153,24 +170,33 @@ class DecodeCache:
         host, dev = self.plan(bands, heads_kv, prompt, batch, bf16_kv, device)
         entry = self.layers.get(layer)
         if entry is None or entry["pool"].numel() != host["pool_bytes"] or entry["plan"] is not host:
-            units = batch * heads_kv
+            units, slots = batch * heads_kv, max(1, host["slots"])
+            f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=device)
             entry = self.layers[layer] = dict(
-                plan=host, dev=dev, prompt=prompt, pool=torch.empty(host["pool_bytes"], dtype=torch.uint8, device=device),
+                plan=host, dev=dev, prompt=prompt,
+                pool=torch.empty(max(16, host["pool_bytes"]), dtype=torch.uint8, device=device),
                 tail_k=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
                 tail_v=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
-                pm=torch.empty((host["slots"], MAX_GROUP), dtype=torch.float32, device=device),
-                pl=torch.empty((host["slots"], MAX_GROUP), dtype=torch.float32, device=device),
-                po=torch.empty((host["slots"], MAX_GROUP, 128), dtype=torch.float32, device=device))
+                pm=f32(slots, MAX_GROUP), pl=f32(slots, MAX_GROUP), po=f32(slots, MAX_GROUP, 128))
+            if self.split is not None:   # folded triples of this rank, and of all ranks after the all-gather
+                world = self.split[1]
+                entry.update(fm=f32(units, MAX_GROUP), fl=f32(units, MAX_GROUP), fo=f32(units, MAX_GROUP, 128),
+                             gm=f32(world, units, MAX_GROUP), gl=f32(world, units, MAX_GROUP),
+                             go=f32(world, units, MAX_GROUP, 128),
+                             rank_slots=torch.stack([torch.arange(units, dtype=torch.int32) * world,
+                                                     torch.full((units,), world, dtype=torch.int32)], 1).to(device))
         entry["kstat"], entry["vstat"] = ops["kstat"].clone(), ops["vstat"].clone()
         if self.step is None:
             self.step = torch.zeros(1, dtype=torch.int64, device=device)
         self.step.zero_()
         max_count = int(host["count"].max())
-        self.module.cache_store(entry["pool"], dev["unit_base"], dev["unit_tab"], dev["unit_count"], dev["unit_flags"],
-                                dev["tmeta"], batch * heads_kv, max_count, ops["k8"], ops["k4"], ops["ka"], ops["ka4"],
-                                ops["v8"], ops["v4"], host["tiles"])
+        if max_count > 0:
+            self.module.cache_store(entry["pool"], dev["unit_base"], dev["unit_tab"], dev["unit_count"], dev["unit_flags"],
+                                    dev["tmeta"], batch * heads_kv, max_count, ops["k8"], ops["k4"], ops["ka"], ops["ka4"],
+                                    ops["v8"], ops["v4"], host["tiles"])
         if bf16_kv:
-            self.module.cache_store_bf16(entry["pool"], dev["unit_base"], dev["bf16_units"], k, v)
+            if host["bf16_range"][1] > 0:
+                self.module.cache_store_bf16(entry["pool"], dev["unit_base"], dev["bf16_units"], k, v, *host["bf16_range"])
             ident = torch.tensor([0.0, 1.0, 1.0], device=device)[None, :, None]
             entry["kstat"][dev["bf16_units"].long()] = ident
             entry["vstat"][dev["bf16_units"].long()] = ident
@@ -179,9 +205,21 @@ class DecodeCache:
         e = self.layers[layer]
         d = e["dev"]
         out = torch.empty_like(q) if out is None else out
-        self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
-                           d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v,
-                           self.step, out, e["pm"], e["pl"], e["po"], e["prompt"], scale, phases)
+        run = lambda pm, pl, po, slots, ph: self.module.decode(
+            q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"], d["cta_segments"],
+            slots, e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, pm, pl, po, e["prompt"], scale, ph)
+        if self.split is None:
+            run(e["pm"], e["pl"], e["po"], d["unit_slots"], phases)
+            return out
+        # sequence split: local split pass, fold to one triple per (unit, Q head), all-gather over the group,
+        # then the usual merge with one slot per rank
+        import torch.distributed as dist
+        run(e["pm"], e["pl"], e["po"], d["unit_slots"], 1)
+        self.module.decode_fold(e["pm"], e["pl"], e["po"], d["unit_slots"], e["fm"], e["fl"], e["fo"], q.shape[1] // k.shape[1])
+        for mine, gathered in ((e["fm"], e["gm"]), (e["fl"], e["gl"]), (e["fo"], e["go"])):
+            dist.all_gather_into_tensor(gathered, mine[None], group=self.split_group)
+        merged = [g.transpose(0, 1).contiguous() for g in (e["gm"], e["gl"], e["go"])]   # [unit][rank][...]
+        run(merged[0], merged[1], merged[2], e["rank_slots"], 2)
         return out
 
     def advance(self):

@@ -24,11 +24,12 @@ SIGNATURES = {
     "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
-    "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _P],
+    "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
     "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
                    _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
     "tri_decode_static": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P,
                           _L, _L, _I, _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_fold": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_umma_probe": [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, _P, _P],
@@ -145,13 +146,15 @@ class Module:
                                                  max_count, k8.data_ptr(), _ptr(k4), ka.data_ptr(), _ptr(ka4),
                                                  v8.data_ptr(), _ptr(v4), tiles, _stream()))
 
-    def cache_store_bf16(self, pool, unit_base, units, k, v):
+    def cache_store_bf16(self, pool, unit_base, units, k, v, chunk_begin=0, chunk_count=None):
         self._bhtd(k, "K"), self._bhtd(v, "V")
+        if chunk_count is None:
+            chunk_count = (k.shape[2] + 31) // 32 - chunk_begin
         with torch.cuda.device(pool.device):
             self._check(self.lib.tri_cache_store_bf16(pool.data_ptr(), unit_base.data_ptr(), units.data_ptr(),
                                                       units.numel(), k.data_ptr(), v.data_ptr(), k.shape[2], k.shape[1],
                                                       k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
-                                                      v.stride(2), _stream()))
+                                                      v.stride(2), int(chunk_begin), int(chunk_count), _stream()))
 
     def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, kstat, vstat,
                tail_k, tail_v, kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3):
@@ -191,6 +194,12 @@ class Module:
                 kcur.stride(0), kcur.stride(1), step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), b, hq, hk,
                 int(prompt), tail_k.shape[1], float(scale), self.error_word(q.device).data_ptr(), _stream()))
         return out
+
+    def decode_fold(self, pm, pl, po, unit_slots, fm, fl, fo, group):
+        with torch.cuda.device(pm.device):
+            self._check(self.lib.tri_decode_fold(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), unit_slots.data_ptr(),
+                                                 fm.data_ptr(), fl.data_ptr(), fo.data_ptr(), unit_slots.shape[0], group,
+                                                 _stream()))
 
     def decode_occupancy(self):
         return self._check(self.lib.tri_decode_occupancy())

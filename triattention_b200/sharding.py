@@ -1,0 +1,117 @@
+"""Multi-GPU partitioning of the attention path (one process per GPU, torch.distributed).
+
+The reference is single-GPU.  The path shards naturally: every (sequence, KV head) unit is independent in
+the KV write, in prefill and in decode (`triattention/kernels/cuda/common_device.cuh:33,62,138,288` index
+everything by head, and the reference has no batch at all).  Two levels:
+
+* units: a rectangular grid of (batch slice) x (KV-head group) per rank, the head groups balanced by the
+  per-head byte cost of the cache under the mixed INT8 / INT4 / BF16 map (`shard_grid`).  No collective
+  on the data path; outputs are gathered only if the caller wants the full tensor (`gather_outputs`).
+* sequence split for long contexts with few units: `DecodeCache(split_group=...)` splits every unit's
+  kept-tile list across the ranks of a group and all-gathers folded (m, l, o) triples (NCCL over NVLink)
+  before the final merge.  `merge_triples` is the same merge written in torch, used by the CPU tests.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from triattention_b200.kernels.decode import plan_streams
+
+
+def lpt_partition(costs, parts):
+    """Longest-processing-time bin packing.  Returns (list of index lists, loads)."""
+    costs = np.asarray(costs, np.float64)
+    bins, loads = [[] for _ in range(parts)], np.zeros(parts)
+    for i in np.argsort(-costs, kind="stable"):
+        j = int(np.argmin(loads))
+        bins[j].append(int(i))
+        loads[j] += costs[i]
+    return [sorted(b) for b in bins], loads
+
+
+def head_costs(bands, heads_kv, prompt, bf16_kv=()):
+    """Decode cache bytes of one sequence per KV head under this map (what one decode step must stream)."""
+    return plan_streams(np.asarray(bands), heads_kv, prompt, 1, tuple(bf16_kv), ctas=1)["head_bytes"].astype(np.float64)
+
+
+@dataclass(frozen=True)
+class Shard:
+    rank: int
+    batch: slice          # sequences of this rank
+    kv_heads: tuple       # KV heads of this rank (indices into the full head list)
+
+    def q_heads(self, group):
+        return tuple(h * group + r for h in self.kv_heads for r in range(group))
+
+
+def shard_grid(batch, costs, world):
+    """Split `world` ranks into (batch parts) x (head groups) minimising the heaviest rank.
+    costs = per-KV-head byte cost of one sequence.  Returns a list of Shard, one per rank."""
+    costs = np.asarray(costs, np.float64)
+    best = None
+    for wh in range(1, world + 1):
+        if world % wh or wh > len(costs):
+            continue
+        wb = world // wh
+        if wb > batch:
+            continue
+        groups, loads = lpt_partition(costs, wh)
+        heaviest = loads.max() * -(-batch // wb)
+        if best is None or heaviest < best[0] - 1e-9:
+            best = (heaviest, wb, groups)
+    if best is None:
+        raise ValueError(f"cannot place {world} ranks on {batch} sequences x {len(costs)} KV heads; use a sequence split")
+    _, wb, groups = best
+    edges = np.linspace(0, batch, wb + 1).round().astype(int)
+    return [Shard(bi * len(groups) + gi, slice(int(edges[bi]), int(edges[bi + 1])), tuple(groups[gi]))
+            for bi in range(wb) for gi in range(len(groups))]
+
+
+def slice_map(bands_fn, shard, group, heads_q):
+    """bands_fn of the full model (heads_q Q heads) -> bands_fn of this rank's heads (BF16 head list re-indexed)."""
+    q_heads = list(shard.q_heads(group))
+    full_bf16 = getattr(bands_fn, "bf16_kv_heads", None)
+
+    def local(layer, heads):
+        if heads != len(q_heads):
+            raise ValueError("the map does not match the model's layers and heads")
+        return bands_fn(layer, heads_q)[q_heads]
+
+    if getattr(bands_fn, "layer_independent", False):
+        local.layer_independent = True
+    if full_bf16 is not None:
+        local.bf16_kv_heads = lambda layer: tuple(i for i, h in enumerate(shard.kv_heads) if h in set(full_bf16(layer)))
+    return local
+
+
+def take_shard(x, shard, heads):
+    """[B,H,T,128] -> this rank's [b,h,T,128] (heads = the KV or Q head indices to keep)."""
+    return x[shard.batch].index_select(1, torch.as_tensor(heads, device=x.device))
+
+
+def gather_outputs(local, shards, group_size, batch, heads_q, group=None):
+    """All-gather per-rank outputs [b,h_local,T,128] into the full [B,Hq,T,128] on every rank."""
+    import torch.distributed as dist
+    world = len(shards)
+    bmax = max(s.batch.stop - s.batch.start for s in shards)
+    hmax = max(len(s.kv_heads) for s in shards) * group_size
+    pad = local.new_zeros((bmax, hmax) + tuple(local.shape[2:]))
+    pad[:local.shape[0], :local.shape[1]] = local
+    parts = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(parts, pad, group=group)
+    out = local.new_empty((batch, heads_q) + tuple(local.shape[2:]))
+    for s, part in zip(shards, parts):
+        qh = torch.as_tensor(s.q_heads(group_size), device=local.device)
+        out[s.batch] = out[s.batch].index_copy(1, qh, part[:s.batch.stop - s.batch.start, :len(qh)])
+    return out
+
+
+def merge_triples(m, l, o):
+    """Merge split partials along dim 0: m, l [S,...], o [S,...,128] -> (m, l, o) of the union.
+    common_device.cuh:418-438 of the reference (base-2 running maximum), in torch for any device."""
+    big = m.max(0).values
+    w = torch.exp2(m - big)
+    return big, (l * w).sum(0), (o * w.unsqueeze(-1)).sum(0)
