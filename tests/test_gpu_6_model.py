@@ -1,0 +1,57 @@
+"""End to end through the Hugging Face hook: a small random-init Llama, batched prompts, greedy decode.
+The reference's surface (TriAttention(model, map, n).generate) with its attention replaced by the sm_100a
+kernels; logits are compared with the same model under exact attention."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_llama():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, vocab_size=1024, max_position_embeddings=1024,
+                      rope_theta=500000.0)
+    return LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+
+
+@torch.inference_mode()
+def test_generate_matches_exact_attention_logits():
+    from triattention_b200.maps import INF, uniform
+    from triattention_b200.models import TriAttention
+    model = tiny_llama()
+    ids = torch.randint(0, 1024, (3, 200), generator=torch.Generator().manual_seed(1)).cuda()
+    model.set_attn_implementation("sdpa")
+    ref = model(input_ids=ids, use_cache=True)
+    ref_logits = ref.logits[:, -1].float()
+    nxt = ref_logits.argmax(-1)
+    ref2 = model(input_ids=nxt[:, None], past_key_values=ref.past_key_values, use_cache=True).logits[:, -1].float()
+
+    engine = TriAttention(model, uniform(INF, INF), max_new_tokens=8)
+    out = model(input_ids=ids, use_cache=False, logits_to_keep=1)
+    got = out.logits[:, -1].float()
+    assert all(engine.decode_cache.stored(layer) for layer in range(3))
+    position = torch.full((3, 1), 200, device="cuda")
+    got2 = model(input_ids=nxt[:, None], position_ids=position, use_cache=False).logits[:, -1].float()
+    engine.module.check_device_error()
+    for name, a, b in (("prefill", got, ref_logits), ("decode", got2, ref2)):
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=-1).min().item()
+        rel = ((a - b).abs().max() / b.abs().max()).item()
+        assert cos > 0.995 and rel < 0.1, (name, cos, rel)
+
+
+@torch.inference_mode()
+def test_generate_batched_and_single():
+    from triattention_b200.maps import INF, per_kv_head
+    from triattention_b200.models import TriAttention
+    model = tiny_llama()
+    engine = TriAttention(model, per_kv_head(["int8", "int4"], 2), max_new_tokens=6)
+    ids = torch.randint(0, 1024, (2, 130), generator=torch.Generator().manual_seed(2)).cuda()
+    rows = engine.generate(ids, 6, eos=())
+    assert len(rows) == 2 and all(len(r) == 6 for r in rows)
+    single = engine.generate(ids[:1], 6, eos=())
+    assert isinstance(single, list) and len(single) == 6 and all(isinstance(t, int) for t in single)
+    stop = engine.generate(ids[:1], 6, eos={single[2]})
+    assert stop == single[:single.index(single[2])]
