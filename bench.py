@@ -200,8 +200,49 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def run_prefill(args):
+    """Secondary metric: INT8 TOP/s of the banded prefill (BASELINE config 3: 28 Q / 4 KV heads, batch 2,
+    16384 tokens, 3 INT8 + 1 INT4 KV heads) including the fused KV-cache write.  One GPU, one JSON line."""
+    from triattention_b200.kernels.extension import load_extension
+    from triattention_b200.kernels.prefill import Prefill
+    from triattention_b200.maps import per_kv_head
+    torch.cuda.set_device(0)
+    module = load_extension()
+    b, hq, hk, t = (args.batch if args.batch != CONFIG["batch"] else 2), 28, 4, args.tokens
+    kinds = list(np.random.default_rng(1).permutation(np.array(["int8", "int8", "int8", "int4"])))
+    q = torch.stack([synth((hq, t, 128), 10 + i) for i in range(b)]).cuda()
+    k = torch.stack([synth((hk, t, 128), 20 + i) for i in range(b)]).cuda()
+    v = torch.stack([synth((hk, t, 128), 30 + i) for i in range(b)]).cuda()
+    pre = Prefill(module, per_kv_head(kinds, hq // hk))
+    scale = 128 ** -0.5
+    for _ in range(max(3, args.warmup)):
+        pre(0, q, k, v, scale)
+    module.check_device_error()
+    steps = max(1, min(args.steps, 20))
+    with ClockSampler(0) as clocks:
+        ms_all = timed(lambda i: pre(0, q, k, v, scale), steps, None) / steps
+        ms_write = timed(lambda i: pre.write(0, q, k, v), steps, None) / steps
+    module.check_device_error()
+    rows = (t + 63) // 64
+    ops = b * hq * (rows * (rows + 1) // 2) * 2 * 64 * 64 * 128 * 2
+    tops = ops / ((ms_all - ms_write) / 1e3) / 1e12
+    nominal = 4500.0
+    print(json.dumps(dict(metric="prefill_int8_tops", value=ops / (ms_all / 1e3) / 1e12, unit="TOP/s", n_gpus=1, steps=steps,
+                          warmup=max(3, args.warmup), ms_per_step=ms_all, higher_is_better=True, dtype="int8", data="synthetic",
+                          config=dict(workload=f"prefill C3: 28 Q / 4 KV heads, batch {b}, {t} tokens, map {kinds}, incl. KV write",
+                                      l2="operands larger than L2"),
+                          roofline=dict(bound="tensor", achieved=tops, peak=nominal, unit="TOP/s", frac=tops / nominal,
+                                        kernel="prefill_kernel", ms_per_launch=ms_all - ms_write, ops_per_launch=ops,
+                                        peak_source="nominal dense INT8 (2 x bf16 nominal); no measured INT8 peak in MEASURED_PEAKS.json",
+                                        traffic=None),
+                          kv_write_ms=ms_write, clocks=clocks.summary())))
+
+
 def main():
     parser = argparse.ArgumentParser()
+    parser.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                        help="decode = the benchmark contract (BASELINE config 2); prefill = config 3, secondary metric")
+    parser.add_argument("--tokens", type=int, default=16384, help="prompt length of the prefill workload")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
@@ -215,6 +256,10 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "prefill":
+        if rank == 0:
+            run_prefill(args)
         return
     torch.cuda.set_device(local)
     dist = None

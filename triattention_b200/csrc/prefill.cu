@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "abi_internal.h"
 #include <cuda.h>
+#include <type_traits>
 
 namespace tri {
 
@@ -231,7 +232,16 @@ __global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid
     const float* kscale = (mode == ModeQ4 ? ka4 : ka8) + (kvunit * tiles + tile) * 4;
     float ks[4] = {__ldg(kscale), __ldg(kscale + 1), __ldg(kscale + 2), __ldg(kscale + 3)};
     float bq = 0.f;
-    if (active) {
+    // The softmax body is instantiated per (diagonal?, mode): only the diagonal tile of a query block is
+    // masked (it is always an FP16-PV tile), so the band tiles carry no per-element mask arithmetic.
+    auto softmax = [&](auto diag_tag, auto mode_tag) {
+      constexpr bool Diag = decltype(diag_tag)::value;
+      constexpr int M = decltype(mode_tag)::value;
+      const int key0 = tile * BN;
+      auto dead = [&](int key) { return Diag && (key >= tokens || key > qi || qi >= tokens); };
+      float slope[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) slope[c] = qs * ks[c];
       // pass 1 over the score row: scaled tile maximum (prefill_sm80.cu:244-253)
       float tmax = -CUDART_INF_F;
 #pragma unroll
@@ -241,24 +251,21 @@ __global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid
         tmem_ld_wait();
         int mx = INT_MIN;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int key = tile * BN + c * 16 + j;
-          const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
-          if (!dead) mx = max(mx, (int)a[j]);
-        }
-        if (mx != INT_MIN) tmax = fmaxf(tmax, qs * ks[c] * (float)mx);
+        for (int j = 0; j < 16; ++j)
+          if (!dead(key0 + c * 16 + j)) mx = max(mx, (int)a[j]);
+        if (!Diag || mx != INT_MIN) tmax = fmaxf(tmax, slope[c] * (float)mx);
       }
       const float n = fmaxf(m, tmax), alpha = exp2f(m - n);
       m = n;
       bool flush = false;
-      if (mode != ModeF16) { flush = (n8seen % 16) == 15; ++n8seen; }
+      if (M != ModeF16) { flush = (n8seen % 16) == 15; ++n8seen; }
       if (flush || alpha != 1.f) {   // prefill_sm80.cu:350-357
         const float shift = -corr * alpha;
 #pragma unroll
         for (int j = 0; j < D; ++j) o[j] = fmaf(o[j], alpha, shift);
         corr = 0.f;
       }
-      if (mode == ModeF16) {
+      if constexpr (M == ModeF16) {
         denom *= alpha;
         float sum = 0.f;
 #pragma unroll
@@ -266,17 +273,14 @@ __global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid
           uint32_t a[16];
           tmem_ld16(lane_base + TmemS + c * 16, a);
           tmem_ld_wait();
-          const float slope = qs * ks[c], off = fmaf(-slope, 12582912.f, -m);
+          const float off = fmaf(-slope[c], 12582912.f, -m);
           uint32_t w[8];
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             float e[2];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int key = tile * BN + c * 16 + j + u;
-              const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
-              e[u] = dead ? 0.f : exp2f(fmaf(slope, __int_as_float((int)a[j + u] + Magic), off));
-            }
+            for (int u = 0; u < 2; ++u)
+              e[u] = dead(key0 + c * 16 + j + u) ? 0.f : exp2f(fmaf(slope[c], __int_as_float((int)a[j + u] + Magic), off));
             const __half2 hp = __floats2half2_rn(e[0], e[1]);
             sum += __low2float(hp) + __high2float(hp);
             w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
@@ -297,16 +301,12 @@ __global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid
           uint32_t a[16];
           tmem_ld16(lane_base + TmemS + c * 16, a);
           tmem_ld_wait();
-          const float slope = qs * ks[c];
-          const float off = mode == ModeQ4 ? -base : fmaf(-slope, 12582912.f, -base);
+          const float off = M == ModeQ4 ? -base : fmaf(-slope[c], 12582912.f, -base);
           uint32_t w[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int key = tile * BN + c * 16 + j;
-            const bool dead = diag && (key >= tokens || key > qi || qi >= tokens);
-            const float x = mode == ModeQ4 ? (float)(int)a[j] : __int_as_float((int)a[j] + Magic);
-            const float e = dead ? 0.f : exp2f(fmaf(slope, x, off));
-            w[j] = __float_as_uint(fmaf(e, 255.f, PMagicHalf));
+            const float x = M == ModeQ4 ? (float)(int)a[j] : __int_as_float((int)a[j] + Magic);
+            w[j] = __float_as_uint(fmaf(exp2f(fmaf(slope[c], x, off)), 255.f, PMagicHalf));
           }
           uint32_t pw[4];
 #pragma unroll
@@ -318,6 +318,17 @@ __global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid
         }
         denom = fmaf((float)rs, bq, denom * alpha);
         corr = fmaf(12582912.f, bq, corr);
+      }
+    };
+    if (active) {
+      using std::integral_constant;
+      if (mode == ModeF16) {
+        if (diag) softmax(integral_constant<bool, true>{}, integral_constant<int, ModeF16>{});
+        else softmax(integral_constant<bool, false>{}, integral_constant<int, ModeF16>{});
+      } else if (mode == ModeI8) {
+        softmax(integral_constant<bool, false>{}, integral_constant<int, ModeI8>{});
+      } else {
+        softmax(integral_constant<bool, false>{}, integral_constant<int, ModeQ4>{});
       }
     }
     // rows of an idle half keep stale P bytes: each output row depends only on its own P row, and idle
