@@ -154,6 +154,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
     if (globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
+// Bounded, abortable wait for kernels whose warps wait on different barriers: gives up when the CTA's
+// abort flag (shared memory) is set by anyone, or sets it itself after ~2 s.  After an abort every warp
+// keeps following its control flow without computing, so no thread is left behind at a barrier.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
+  }
+}
 // 1-D bulk copy global -> shared; dst, src and bytes are multiples of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -51,18 +51,6 @@ __device__ __forceinline__ uint32_t chunk_bytes(uint32_t info) {
   return ((info & InfoK4) ? K4Bytes : K8Bytes) + ((info & InfoV4) ? V4Bytes : V8Bytes) + 16;
 }
 
-// Bounded, abortable wait: gives up when the CTA's abort flag is set or after ~2 s.
-__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
-  }
-}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }

@@ -82,9 +82,11 @@ constexpr uint32_t IdescPV8 = instr_desc(2, 0, 1, 128, 128);  // u8 x s8 -> s32
 constexpr uint32_t IdescPV16 = instr_desc(1, 0, 0, 128, 128); // f16 x f16 -> f32
 
 // ---- shared-memory plan of the prefill CTA ----------------------------------------------------
-constexpr int PrefillThreads = 128;
+constexpr int PrefillThreads = 256;   // two threads per query row
+constexpr int ProbeThreads = 128;
 constexpr int SmQ8 = 0, SmQ4 = 16384, SmP = 32768, SmK = 49152, SmV = SmK + 2 * K8Bytes, SmEnd = SmV + 2 * V16Bytes;
-constexpr int PrefillShared = SmEnd + 1024;   // + slack to align the base to 1024 bytes
+constexpr int SmSteps = SmEnd, StepBytes = (2 * MaxTiles + 8) * 2;   // visiting-order table, 2 bytes per step
+constexpr int PrefillShared = SmSteps + StepBytes + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t TmemCols = 256, TmemS = 0, TmemD = 64;
 enum Mode : int { ModeF16 = 0, ModeI8 = 1, ModeQ4 = 2 };
 
@@ -132,274 +134,11 @@ template <typename Out> __device__ __forceinline__ Out to_out(float x);
 template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float x) { return __float2bfloat16(x); }
 template <> __device__ __forceinline__ __half to_out<__half>(float x) { return __float2half(x); }
 
-// grid = pairs * batch * heads_q CTAs, heaviest query-block pairs first; 128 threads; 2 CTAs per SM.
-template <typename Out>
-__global__ void __launch_bounds__(PrefillThreads, 2) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
-    const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
-    const float* ka4, const uint8_t* v16, const uint8_t* v8, const float* qa8, const float* qa4, const float* vstat, Out* out,
-    int64_t osb, int64_t osh, int64_t ost, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
-  extern __shared__ uint8_t raw_smem[];
-  __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_d;
-  __shared__ uint32_t tmem_slot;
-  uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
-  const int tid = threadIdx.x, warp = tid / 32, half = tid / 64;
-  const int rows = (tokens + BM - 1) / BM, pairs = (rows + 1) / 2, tiles = rows;
-  const int pair = pairs - 1 - blockIdx.x / units_q, qunit = blockIdx.x % units_q;
-  const int b = qunit / heads_q, h = qunit % heads_q, g = heads_q / heads_kv;
-  const int64_t kvunit = (int64_t)b * heads_kv + h / g;
-  const int w8 = bands[h * 2], w4 = bands[h * 2 + 1];
-  if (w8 < 1) return;   // head handled elsewhere (un-quantised BF16 extension); uniform for the CTA
-  StepPlan plan;
-  plan.build(pair, rows, w8, w4);
-  const int nsteps = plan.steps();
-  const bool need_q4 = plan.n4 > 0;
-
-  if (tid == 0) {
-    mbar_init(&bar_q, 1); mbar_init(&bar_kv[0], 1); mbar_init(&bar_kv[1], 1); mbar_init(&bar_s, 1); mbar_init(&bar_d, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) { tmem_alloc(&tmem_slot, TmemCols); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-
-  auto issue_loads = [&](int i) {   // thread 0 only
-    int tile, mode, mask;
-    plan.get(i, tile, mode, mask);
-    const int s = i & 1;
-    const int64_t ht = kvunit * tiles + tile;
-    const uint32_t vbytes = mode == ModeF16 ? V16Bytes : V8Bytes;
-    mbar_expect_tx(&bar_kv[s], K8Bytes + vbytes);
-    bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bar_kv[s]);
-    bulk_g2s(smem + SmV + s * V16Bytes, mode == ModeF16 ? v16 + ht * V16Bytes : v8 + ht * V8Bytes, vbytes, &bar_kv[s]);
-  };
-  if (tid == 0) {
-    mbar_expect_tx(&bar_q, need_q4 ? 32768u : 16384u);
-    tma_load_3d(smem + SmQ8, &map_q8, 0, plan.b0 * BM, qunit, &bar_q);
-    if (need_q4) tma_load_3d(smem + SmQ4, &map_q4, 0, plan.b0 * BM, qunit, &bar_q);
-    issue_loads(0);
-  }
-
-  // per-row state (thread = row)
-  const int bh = plan.b0 + half, qi = bh * BM + (tid & 63);
-  const bool row_valid = (half == 0 || plan.has1) && qi < tokens;
-  const int64_t qrow = (int64_t)qunit * tokens + qi;
-  const float qs8 = row_valid ? qa8[qrow] * sm_log2 : FLT_MIN;
-  const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
-  float o[D];
-#pragma unroll
-  for (int j = 0; j < D; ++j) o[j] = 0.f;
-  float m = -FLT_MAX, denom = 0.f, corr = 0.f;
-  int n8seen = 0;
-  uint32_t ph_s = 0, ph_d = 0, ph_kv[2] = {0, 0};
-  bool ok = true;
-  const uint32_t q8_addr = smem_u32(smem + SmQ8), q4_addr = smem_u32(smem + SmQ4), p_addr = smem_u32(smem + SmP);
-  uint8_t* prow8 = smem + SmP + (tid / 8) * 512 + (tid % 8) * 16;     // u8 P row: core matrices [row/8][key/16]
-  uint8_t* prow16 = smem + SmP + (tid / 8) * 1024 + (tid % 8) * 16;   // fp16 P row: core matrices [row/8][key/8]
-
-  for (int i = 0; i < nsteps && ok; ++i) {
-    int tile, mode, mask;
-    plan.get(i, tile, mode, mask);
-    const int s = i & 1;
-    if (tid == 0) {
-      if (i + 1 < nsteps) issue_loads(i + 1);
-      if (i == 0) ok = mbar_wait(&bar_q, 0);
-      ok = ok && mbar_wait(&bar_kv[s], ph_kv[s]);
-      if (ok) {
-        tc_fence_after();
-        const uint32_t qa_ = mode == ModeQ4 ? q4_addr : q8_addr, ka_ = smem_u32(smem + SmK + s * K8Bytes);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_i8(tmem + TmemS, smem_desc(qa_ + kk * 32, 0, 1024, Layout128B), smem_desc(ka_ + kk * 256, 128, 1024, LayoutNone),
-                  IdescQK, kk > 0);
-        tc_commit(&bar_s);
-      }
-    }
-    ph_kv[s] ^= 1;
-    __syncwarp();
-    ok = mbar_wait(&bar_s, ph_s);
-    ph_s ^= 1;
-    // thread 0 may have failed before the commit; make the decision uniform
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    tc_fence_after();
-
-    const bool active = (mask >> half) & 1;
-    const bool diag = tile == bh;
-    const float qs = mode == ModeQ4 ? qs4 : qs8;
-    const float* kscale = (mode == ModeQ4 ? ka4 : ka8) + (kvunit * tiles + tile) * 4;
-    float ks[4] = {__ldg(kscale), __ldg(kscale + 1), __ldg(kscale + 2), __ldg(kscale + 3)};
-    float bq = 0.f;
-    // The softmax body is instantiated per (diagonal?, mode): only the diagonal tile of a query block is
-    // masked (it is always an FP16-PV tile), so the band tiles carry no per-element mask arithmetic.
-    auto softmax = [&](auto diag_tag, auto mode_tag) {
-      constexpr bool Diag = decltype(diag_tag)::value;
-      constexpr int M = decltype(mode_tag)::value;
-      const int key0 = tile * BN;
-      auto dead = [&](int key) { return Diag && (key >= tokens || key > qi || qi >= tokens); };
-      float slope[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) slope[c] = qs * ks[c];
-      // pass 1 over the score row: scaled tile maximum (prefill_sm80.cu:244-253)
-      float tmax = -CUDART_INF_F;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t a[16];
-        tmem_ld16(lane_base + TmemS + c * 16, a);
-        tmem_ld_wait();
-        int mx = INT_MIN;
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (!dead(key0 + c * 16 + j)) mx = max(mx, (int)a[j]);
-        if (!Diag || mx != INT_MIN) tmax = fmaxf(tmax, slope[c] * (float)mx);
-      }
-      const float n = fmaxf(m, tmax), alpha = exp2f(m - n);
-      m = n;
-      bool flush = false;
-      if (M != ModeF16) { flush = (n8seen % 16) == 15; ++n8seen; }
-      if (flush || alpha != 1.f) {   // prefill_sm80.cu:350-357
-        const float shift = -corr * alpha;
-#pragma unroll
-        for (int j = 0; j < D; ++j) o[j] = fmaf(o[j], alpha, shift);
-        corr = 0.f;
-      }
-      if constexpr (M == ModeF16) {
-        denom *= alpha;
-        float sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t a[16];
-          tmem_ld16(lane_base + TmemS + c * 16, a);
-          tmem_ld_wait();
-          const float off = fmaf(-slope[c], 12582912.f, -m);
-          uint32_t w[8];
-#pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float e[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u)
-              e[u] = dead(key0 + c * 16 + j + u) ? 0.f : exp2f(fmaf(slope[c], __int_as_float((int)a[j + u] + Magic), off));
-            const __half2 hp = __floats2half2_rn(e[0], e[1]);
-            sum += __low2float(hp) + __high2float(hp);
-            w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
-          }
-          *reinterpret_cast<uint4*>(prow16 + (2 * c) * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(prow16 + (2 * c + 1) * 128) = make_uint4(w[4], w[5], w[6], w[7]);
-        }
-        denom += sum;
-      } else {
-        // prefill_sm80.cu:386-414
-        const float ks_max = fmaxf(fmaxf(ks[0], ks[1]), fmaxf(ks[2], ks[3]));
-        float base = tmax > -CUDART_INF_F ? tmax : m;
-        base += tile_base_margin(qs * ks_max, base);
-        bq = exp2f(base - m) / 255.f;
-        int rs = 0;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t a[16];
-          tmem_ld16(lane_base + TmemS + c * 16, a);
-          tmem_ld_wait();
-          const float off = M == ModeQ4 ? -base : fmaf(-slope[c], 12582912.f, -base);
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float x = M == ModeQ4 ? (float)(int)a[j] : __int_as_float((int)a[j] + Magic);
-            w[j] = __float_as_uint(fmaf(exp2f(fmaf(slope[c], x, off)), 255.f, PMagicHalf));
-          }
-          uint32_t pw[4];
-#pragma unroll
-          for (int sidx = 0; sidx < 4; ++sidx) {   // byte 4s+b of the run holds key kperm(s,b), like the V8 blob
-            pw[sidx] = pack_bytes(w[2 * sidx], w[2 * sidx + 1], w[2 * sidx + 8], w[2 * sidx + 9]);
-            rs = (int)__dp4a(pw[sidx], 0x01010101u, (uint32_t)rs);
-          }
-          *reinterpret_cast<uint4*>(prow8 + c * 128) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        }
-        denom = fmaf((float)rs, bq, denom * alpha);
-        corr = fmaf(12582912.f, bq, corr);
-      }
-    };
-    if (active) {
-      using std::integral_constant;
-      if (mode == ModeF16) {
-        if (diag) softmax(integral_constant<bool, true>{}, integral_constant<int, ModeF16>{});
-        else softmax(integral_constant<bool, false>{}, integral_constant<int, ModeF16>{});
-      } else if (mode == ModeI8) {
-        softmax(integral_constant<bool, false>{}, integral_constant<int, ModeI8>{});
-      } else {
-        softmax(integral_constant<bool, false>{}, integral_constant<int, ModeQ4>{});
-      }
-    }
-    // rows of an idle half keep stale P bytes: each output row depends only on its own P row, and idle
-    // rows never read their accumulators
-    fence_proxy_async_smem();   // P (generic-proxy stores) must be visible to the tensor core's async proxy
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t va = smem_u32(smem + SmV + s * V16Bytes);
-      if (mode == ModeF16) {
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem + TmemD, smem_desc(p_addr + kk * 256, 128, 1024, LayoutNone), smem_desc(va + kk * 256, 128, 1024, LayoutNone),
-                   IdescPV16, kk > 0);
-      } else {
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk)
-          umma_i8(tmem + TmemD, smem_desc(p_addr + kk * 256, 128, 512, LayoutNone), smem_desc(va + kk * 256, 128, 512, LayoutNone),
-                  IdescPV8, kk > 0);
-      }
-      tc_commit(&bar_d);
-    }
-    __syncwarp();
-    ok = mbar_wait(&bar_d, ph_d);
-    ph_d ^= 1;
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    tc_fence_after();
-    if (active) {
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t a[16];
-        tmem_ld16(lane_base + TmemD + c * 16, a);
-        tmem_ld_wait();
-        if (mode == ModeF16) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) o[c * 16 + j] += __uint_as_float(a[j]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) o[c * 16 + j] = fmaf(__int_as_float((int)a[j] + Magic), bq, o[c * 16 + j]);
-        }
-      }
-    }
-    tc_fence_before();
-    __syncthreads();   // S, D, P and this K/V stage are free again
-  }
-
-  if (!ok && tid == 0) atomicExch(err, ErrBarrierTimeout);
-  if (ok && row_valid) {
-    // prefill_sm80.cu:466-487
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    const float* mean = vstat + kvunit * StatFloats;
-    const float* scale = mean + D;
-    Out* dst = out + b * osb + h * osh + (int64_t)qi * ost;
-#pragma unroll
-    for (int c = 0; c < D; c += 8) {
-      Out vals[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) vals[j] = to_out<Out>(fmaf((o[c + j] - corr) * inv, __ldg(scale + c + j), __ldg(mean + c + j)));
-      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(vals);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, TmemCols);
-}
+#include "prefill_kernel.cuh"
 
 // ---- integer QK^T accumulators of chosen (Q unit, pair, tile) through the production operand path ---
 // grid = requests, 128 threads.  req = {qunit, pair, tile, four_bit}; writes int32 [req][128][64].
-__global__ void __launch_bounds__(PrefillThreads) qk_accum_kernel(const __grid_constant__ CUtensorMap map_q8,
+__global__ void __launch_bounds__(ProbeThreads) qk_accum_kernel(const __grid_constant__ CUtensorMap map_q8,
     const __grid_constant__ CUtensorMap map_q4, const int4* req, const uint8_t* k8, const uint8_t* k4x, int32_t* acc, int heads_q,
     int heads_kv, int tokens, int* err) {
   extern __shared__ uint8_t raw_smem[];
@@ -456,7 +195,7 @@ __global__ void __launch_bounds__(PrefillThreads) qk_accum_kernel(const __grid_c
 // ---- generic single-tile tensor-core probe: D[128 x n] = A . B^T from caller-built operand images ---
 // One CTA.  The images are copied verbatim to 1024-byte aligned shared memory; descriptor fields come
 // from the caller so that the tests can pin the layout conventions used above.
-__global__ void __launch_bounds__(PrefillThreads) umma_probe_kernel(const uint8_t* a_img, int a_bytes, const uint8_t* b_img,
+__global__ void __launch_bounds__(ProbeThreads) umma_probe_kernel(const uint8_t* a_img, int a_bytes, const uint8_t* b_img,
     int b_bytes, uint32_t a_lbo, uint32_t a_sbo, uint32_t a_layout, uint32_t a_step, uint32_t b_lbo, uint32_t b_sbo,
     uint32_t b_layout, uint32_t b_step, uint32_t idesc, int f16_kind, int ksteps, int ncols, uint32_t* out, int* err) {
   extern __shared__ uint8_t raw_smem[];
@@ -464,8 +203,8 @@ __global__ void __launch_bounds__(PrefillThreads) umma_probe_kernel(const uint8_
   __shared__ uint32_t tmem_slot;
   uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid / 32;
-  for (int i = tid; i < a_bytes / 16; i += PrefillThreads) reinterpret_cast<uint4*>(smem)[i] = reinterpret_cast<const uint4*>(a_img)[i];
-  for (int i = tid; i < b_bytes / 16; i += PrefillThreads)
+  for (int i = tid; i < a_bytes / 16; i += ProbeThreads) reinterpret_cast<uint4*>(smem)[i] = reinterpret_cast<const uint4*>(a_img)[i];
+  for (int i = tid; i < b_bytes / 16; i += ProbeThreads)
     reinterpret_cast<uint4*>(smem + 32768)[i] = reinterpret_cast<const uint4*>(b_img)[i];
   if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
@@ -593,7 +332,7 @@ extern "C" int tri_qk_accumulators(const int32_t* requests, int num_requests, co
   CUtensorMap map8, map4;
   if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
   if (make_q_map(&map4, q4x ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
-  qk_accum_kernel<<<num_requests, PrefillThreads, 16384 + K8Bytes + 1024, static_cast<cudaStream_t>(stream)>>>(map8, map4,
+  qk_accum_kernel<<<num_requests, ProbeThreads, 16384 + K8Bytes + 1024, static_cast<cudaStream_t>(stream)>>>(map8, map4,
       reinterpret_cast<const int4*>(requests), static_cast<const uint8_t*>(k8), static_cast<const uint8_t*>(k4x ? k4x : k8), acc,
       heads_q, heads_kv, tokens, device_error);
   return tri_launch_status("qk_accumulators");
@@ -610,7 +349,7 @@ extern "C" int tri_umma_probe(const void* a_img, int a_bytes, const void* b_img,
     if (allow_smem(umma_probe_kernel, 65536 + 1024) != TRI_OK) return TRI_ERR_CUDA;
     configured = 1;
   }
-  umma_probe_kernel<<<1, PrefillThreads, 65536 + 1024, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(a_img),
+  umma_probe_kernel<<<1, ProbeThreads, 65536 + 1024, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(a_img),
       a_bytes, static_cast<const uint8_t*>(b_img), b_bytes, a_lbo, a_sbo, a_layout, a_step, b_lbo, b_sbo, b_layout, b_step, idesc,
       f16_kind, ksteps, ncols, out, device_error);
   return tri_launch_status("umma_probe");
