@@ -100,7 +100,7 @@ class ClockSampler:
                     samples=len(rows))
 
 
-def build_cache(batch, seed0, tile_costs=None):
+def build_cache(batch, seed0, tile_costs=None, fused_merge=False):
     """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan)."""
     from triattention_b200.kernels.decode import DecodeCache
     from triattention_b200.kernels.extension import load_extension
@@ -108,7 +108,7 @@ def build_cache(batch, seed0, tile_costs=None):
     from triattention_b200.maps import per_kv_head
     hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
     module = load_extension()
-    cache = DecodeCache(module, max_tail=256, **({"tile_costs": tile_costs} if tile_costs else {}))
+    cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, **({"tile_costs": tile_costs} if tile_costs else {}))
     pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
     k = torch.empty((batch, hk, t, 128), dtype=torch.bfloat16, device="cuda")
     v = torch.empty_like(k)
@@ -249,6 +249,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--cpu-steps", type=int, default=10, help="timed steps of the CPU baseline leg (0 = skip)")
     parser.add_argument("--tile-costs", default="", help="override the decode partition's cost model: bf16,k8v8,other (relative)")
+    parser.add_argument("--fused-merge", action="store_true",
+                        help="one launch per step: the CTA that finishes a unit's last segment merges it")
     parser.add_argument("--batch", type=int, default=CONFIG["batch"],
                         help="sequences per GPU; anything but 32 is a reduced case for profiler captures, flagged in the output")
     args = parser.parse_args()
@@ -269,7 +271,7 @@ def main():
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
     warmup = max(3, args.warmup)
     costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
-    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs)
+    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs, fused_merge=args.fused_merge)
     scale = 128 ** -0.5
     # decode-step inputs: device-resident copies for `value`, pinned host copies for `e2e`
     host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (rank * batch + b)) for b in range(batch)]).pin_memory()
@@ -306,7 +308,7 @@ def main():
                 vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG,
                 e2e=dict(value=tokens * args.steps / (ms_e2e / 1e3), unit="tokens/s",
                          h2d_bytes_per_step=sum(x.numel() * 2 for x in host), d2h_bytes_per_step=out.numel() * 2),
-                gpu_launches=2 * args.steps,
+                gpu_launches=(1 if cache.layers[0]["unit_done"] is not None else 2) * args.steps,
                 roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
                               # ncu capture of a batch-8 case (profiles/decode_kernel_c2.md): reads = 1.0014 x algorithmic
                               # bytes, writes = 23.4 KB per segment; scaled by the tiles / segments of this launch

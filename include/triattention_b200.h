@@ -96,13 +96,16 @@ int tri_cache_store_bf16(void* pool, const int64_t* unit_base, const int32_t* un
  * tail_k/tail_v bf16 [U,max_tail,128] with element strides; kcur/vcur bf16 [B,Hkv,1,128];
  * step int64 [1] on the device; out bf16 [B,Hq,1,128].  phases: 1 = split pass only, 2 = merge only,
  * 3 = both (normal use; the single phases exist so that each kernel can be timed alone); 5 = split pass
- * that only streams the cache through shared memory without arithmetic (diagnostic of the copy pipeline). */
+ * that only streams the cache through shared memory without arithmetic (diagnostic of the copy pipeline).
+ * unit_done int32 [U], zero before the first call, or NULL.  With it and phases = 3 the step is ONE launch:
+ * the CTA that finishes a unit's last segment merges that unit (every unit needs >= 1 segment); the
+ * counters are left at zero again.  With NULL the split pass and the merge are two launches. */
 int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
                const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
                const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
                int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
                int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out,
-               int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po,
+               int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl, float* po, int32_t* unit_done,
                int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases,
                int* device_error, void* stream);
 

@@ -19,9 +19,9 @@ def bands_fn_of(bands, bf16=()):
     return fn
 
 
-def product_decode(module, q, k, v, bands, qd, kd, vd, steps, max_tail=8, bf16=()):
+def product_decode(module, q, k, v, bands, qd, kd, vd, steps, max_tail=8, bf16=(), fused=False, ctas=None):
     """Write the cache with the product path, then run `steps` decode steps.  Arrays are [B,H,*,128]."""
-    cache = DecodeCache(module, max_tail=max_tail)
+    cache = DecodeCache(module, max_tail=max_tail, fused_merge=fused, ctas=ctas)
     pre = Prefill(module, bands_fn_of(bands, bf16), cache)
     kc, vc = bf16_cuda(k), bf16_cuda(v)
     table, ops = pre.write(0, bf16_cuda(q), kc, vc)
@@ -64,12 +64,16 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["one-launch", "two-launches"])
 @pytest.mark.parametrize("hq,hk,t,bands", CASES)
-def test_decode_vs_oracle(module, hq, hk, t, bands):
+def test_decode_vs_oracle(module, hq, hk, t, bands, fused):
     bands = np.asarray(bands, np.int64)
     q, k, v = make_inputs(hq, hk, t, seed=31, batch=2)
     qd, kd, vd = make_inputs(hq, hk, 3, seed=77, batch=2)
-    got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3)
+    got, cache = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3, fused=fused)
+    assert (cache.layers[0]["unit_done"] is not None) == fused
+    if fused:   # the completion counters are back at zero after every step
+        assert int(cache.layers[0]["unit_done"].abs().sum()) == 0
     for b in range(2):
         want = oracle_steps(k[b], v[b], bands, qd[b], kd[b], vd[b], 3)
         assert_fp_close(got[b], orc.to_bf16(want), f"decode b={b}")
@@ -127,6 +131,19 @@ def test_decode_split_invariance(module):
     module.check_device_error()
     assert_fp_close(results[1], results[0], "16 CTAs vs 1")
     assert_fp_close(results[2], results[0], "444 CTAs vs 1")
+
+
+@pytest.mark.parametrize("ctas", [3, 148, 444])
+def test_fused_merge_matches_two_launches(module, ctas):
+    """The merge done by the last CTA of a unit against the separate merge launch, with units cut into many
+    segments and CTAs that own several units, over enough steps to reuse the completion counters."""
+    hq, hk, t = 8, 2, 3000
+    bands = np.asarray([[INF, INF]] * 4 + [[2, 6]] * 4, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=63, batch=3)
+    qd, kd, vd = make_inputs(hq, hk, 6, seed=64, batch=3)
+    one, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=6, max_tail=4, fused=True, ctas=ctas)
+    two, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=6, max_tail=4, fused=False, ctas=ctas)
+    assert_fp_close(one, two, f"one launch vs two, {ctas} CTAs")
 
 
 def test_tail_saturates(module):

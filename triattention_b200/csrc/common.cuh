@@ -137,6 +137,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+// Programmatic dependent launch: a kernel launched with launch_chained() (host side) may become resident
+// while the kernel before it in the stream still runs.  grid_dependency_wait() returns once that kernel
+// has completed and its writes are visible (a no-op for a plain launch), so everything that reads the
+// predecessor's results or overwrites what it reads sits behind it; grid_launch_dependents() lets the
+// next kernel of the stream start its own prologue.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Bounded wait: gives up after `limit_ns` of wall time (read from %globaltimer every 64 polls) and
 // returns false.  The caller records ErrBarrierTimeout and leaves; nothing spins forever.
 __device__ __forceinline__ uint64_t globaltimer_ns() {

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   __shared__ __align__(16) float wo[W][D];
   const int hq = blockIdx.x, b = blockIdx.y, g = heads_q / heads_kv, kh = hq / g, r = hq % g;
   const int unit = b * heads_kv + kh, tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+  grid_launch_dependents();   // the next step's split pass may set up its barriers behind this kernel
+  grid_dependency_wait();     // the split pass has written all partials
   const int prior = min((int)*step, max_tail - 1), tail = prior + 1;
   const float* mean = vstat + (int64_t)unit * StatFloats;
   const float* scale = mean + D;
@@ -91,6 +93,21 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   out[b * osb + hq * osh + tid] = __float2bfloat16(acc / total);
 }
 
+
+// Launch with programmatic stream serialisation: the kernel may become resident while its predecessor in
+// the stream is still running and orders itself with grid_dependency_wait() (common.cuh).  Hides the
+// launch latency between the split pass and the merge, and between consecutive steps.
+template <typename... Params, typename... Args>
+static cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                                  Args... args) {
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = shared; cfg.stream = stream;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
 
 // ---- cache store: gather kept tiles of the prefill operands into the per-unit streams ------------
 // grid (max kept tiles, units), 256 threads.  K8 / V8 / V4 blobs are re-ordered from the prefill
@@ -185,8 +202,8 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
     int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
     int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b,
     int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl,
-    float* po, int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases, int* device_error,
-    void* stream) {
+    float* po, int32_t* unit_done, int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases,
+    int* device_error, void* stream) {
   TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && kstat &&
             vstat && tail_k && tail_v && kcur && vcur && step && out && pm && pl && po && device_error, "decode: null buffers");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
@@ -197,13 +214,23 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
+  // One launch when both phases are wanted and the caller provides the per-unit completion counters: the CTA
+  // that finishes a unit's last segment merges it.  Otherwise the split pass and the merge are two launches.
+  const bool fused = phases == 3 && unit_done != nullptr && num_ctas > 0;
+  MergeArgs margs{};
+  if (fused)
+    margs = MergeArgs{reinterpret_cast<const int2*>(unit_slots), unit_done, vstat, kstat, static_cast<__nv_bfloat16*>(tail_k),
+                      static_cast<__nv_bfloat16*>(tail_v), tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur),
+                      static_cast<const __nv_bfloat16*>(vcur), cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out),
+                      out_stride_b, out_stride_h, max_tail};
   if (num_ctas > 0 && (phases & 1))
-    decode_kernel<<<num_ctas, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
-        unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),
-        cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, (phases & 4) ? 1 : 0, device_error);
-  if (phases & 2)
-    decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
-        kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
+    launch_chained(decode_kernel, dim3(num_ctas), dim3(DecodeThreads), DecodeShared, s, qp, q_stride_b, q_stride_h,
+        static_cast<const uint8_t*>(pool), unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta),
+        reinterpret_cast<const int4*>(segments), cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2,
+        (phases & 4) ? 1 : 0, margs, device_error);
+  if ((phases & 2) && !fused)
+    launch_chained(decode_merge_kernel, dim3(heads_q, batch), dim3(MergeThreads), 0, s, pm, pl, po,
+        reinterpret_cast<const int2*>(unit_slots), vstat, kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
         tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),
         cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, heads_q, heads_kv,
         max_tail, sm_log2);
@@ -326,7 +353,7 @@ extern "C" int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_st
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
   decode_kernel<<<num_ctas, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
       unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),
-      cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, 0, device_error);
+      cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, 0, MergeArgs{}, device_error);
   decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
       kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
       tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),

@@ -212,17 +212,112 @@ __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t 
   }
 }
 
+// Arguments of the merge (tail, statistics, output), passed by value to the kernel when the merge is fused.
+struct MergeArgs {
+  const int2* unit_slots; int32_t* unit_done;      // unit_done == nullptr: no fused merge
+  const float* vstat; const float* kstat;
+  __nv_bfloat16* ktail; __nv_bfloat16* vtail; int64_t tsu, tst;
+  const __nv_bfloat16* kcur; const __nv_bfloat16* vcur; int64_t csb, csh;
+  const int64_t* step; __nv_bfloat16* out; int64_t osb, osh;
+  int max_tail;
+};
+
+// Merge of one unit by the consumer warps of the CTA that finished the unit's last segment:
+// decode_merge_kernel's arithmetic (common_device.cuh:373-469 of the reference) for the unit's g Q heads,
+// one after the other, with the fold buffer as scratch.  All ConsumerWarps*32 threads call it.
+// The partials come from other CTAs of the same launch, so they are read past L1 (ld.cg).
+__device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
+    const __nv_bfloat16* q, int64_t qsb, int64_t qsh, int unit, int heads_kv, int g, float sm_log2, float* scratch) {
+  constexpr int NT = ConsumerWarps * 32;
+  const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+  const int b = unit / heads_kv, kh = unit % heads_kv;
+  float* ts = scratch;                 // [1024] tail scores
+  float* ew = scratch + 1024;          // [1024] tail weights
+  float* wred = scratch + 2048;        // [ConsumerWarps] block reductions
+  float* wl = wred + ConsumerWarps;    // [ConsumerWarps]
+  float* wo = wl + ConsumerWarps + (16 - 2 * ConsumerWarps % 16) % 16;   // [ConsumerWarps][128], 16-float aligned
+  const int prior = min((int)*a.step, a.max_tail - 1), tail = prior + 1;
+  const int2 sl = a.unit_slots[unit];
+  const float* mean = a.vstat + (int64_t)unit * StatFloats;
+  const float* scale = mean + D;
+  const __nv_bfloat16* kc = a.kcur + b * a.csb + kh * a.csh;
+  const __nv_bfloat16* vc = a.vcur + b * a.csb + kh * a.csh;
+  __nv_bfloat16* kt = a.ktail + unit * a.tsu;
+  __nv_bfloat16* vt = a.vtail + unit * a.tsu;
+  if (tid < D) {   // append the current token to the tail (read back only by later steps)
+    kt[prior * a.tst + tid] = kc[tid];
+    vt[prior * a.tst + tid] = vc[tid];
+  }
+  float kmean[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) kmean[i] = a.kstat[(int64_t)unit * StatFloats + lane * 4 + i];
+  for (int r = 0; r < g; ++r) {
+    const int hq = kh * g + r;
+    const __nv_bfloat16* qrow = q + b * qsb + hq * qsh;
+    float qv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qv[i] = __bfloat162float(qrow[lane * 4 + i]);
+    for (int t = warp; t < tail; t += ConsumerWarps) {
+      const __nv_bfloat16* kv = t < prior ? kt + t * a.tst : kc;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) part = fmaf(qv[i], __bfloat162float(kv[lane * 4 + i]) - kmean[i], part);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (lane == 0) ts[t] = part * sm_log2;
+    }
+    consumer_sync();
+    float m = -FLT_MAX;
+    for (int s = tid; s < sl.y; s += NT) m = fmaxf(m, __ldcg(pm + (int64_t)(sl.x + s) * MaxGroup + r));
+    for (int t = tid; t < tail; t += NT) m = fmaxf(m, ts[t]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) wred[warp] = m;
+    consumer_sync();
+    m = wred[0];
+#pragma unroll
+    for (int w = 1; w < ConsumerWarps; ++w) m = fmaxf(m, wred[w]);
+    for (int t = tid; t < tail; t += NT) ew[t] = exp2f(ts[t] - m);
+    float l = 0.f, o4[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = warp; s < sl.y; s += ConsumerWarps) {
+      const int64_t idx = (int64_t)(sl.x + s) * MaxGroup + r;
+      const float w = exp2f(__ldcg(pm + idx) - m);
+      l = fmaf(__ldcg(pl + idx), w, l);
+      const float4 p = __ldcg(reinterpret_cast<const float4*>(po + idx * D + lane * 4));
+      o4[0] = fmaf(p.x, w, o4[0]); o4[1] = fmaf(p.y, w, o4[1]); o4[2] = fmaf(p.z, w, o4[2]); o4[3] = fmaf(p.w, w, o4[3]);
+    }
+    if (lane == 0) wl[warp] = l;
+    *reinterpret_cast<float4*>(&wo[warp * D + lane * 4]) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+    consumer_sync();
+    if (tid < D) {
+      float total = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < ConsumerWarps; ++w) { total += wl[w]; acc += wo[w * D + tid]; }
+      acc = acc * scale[tid] + total * mean[tid];
+      for (int t = 0; t < prior; ++t) {
+        const float e = ew[t];
+        total += e;
+        acc = fmaf(e, __bfloat162float(vt[(int64_t)t * a.tst + tid]), acc);
+      }
+      total += ew[prior];
+      acc = fmaf(ew[prior], __bfloat162float(vc[tid]), acc);
+      a.out[b * a.osb + hq * a.osh + tid] = __float2bfloat16(acc / total);
+    }
+    consumer_sync();   // scratch is reused by the next Q head
+  }
+}
+
 // grid = persistent CTAs (one per SM), 160 threads.  cta_seg[c]..cta_seg[c+1] indexes the CTA's
 // segments; segs[j] = {unit, first kept tile, tile count, partial slot}; unit = sequence*heads_kv + kv head.
 __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
     const uint8_t* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int2* tmeta,
     const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt,
-    float sm_log2, int stream_only, int* err) {
+    float sm_log2, int stream_only, MergeArgs margs, int* err) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[DecodeStages], empty[DecodeStages];
   __shared__ uint32_t stage_info[DecodeStages];
 
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, merge_flag;
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, group = lane / 4, sub = lane % 4;
   const int seg0 = cta_seg[blockIdx.x], nseg = cta_seg[blockIdx.x + 1] - seg0;
   const int g = heads_q / heads_kv;
@@ -234,6 +329,10 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
   }
 
   __syncthreads();
+  // Up to here the CTA touched only its own shared memory and the plan tables; the cache, Q and the
+  // partial buffers (which the previous step's merge may still be reading) come after the wait.
+  grid_dependency_wait();
+  grid_launch_dependents();
   volatile int* abortp = &abort_flag;
 
   if (warp == ConsumerWarps) {
@@ -382,7 +481,23 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
           if (ch == 0) { pm[idx] = big; pl[idx] = l; }
         }
       }
+      if (margs.unit_done != nullptr) __threadfence();   // this segment's partial is visible device-wide
       consumer_sync();   // the fold buffer is free for the next segment
+      if (margs.unit_done != nullptr) {
+        // Fused merge: whoever finishes a unit's last segment merges the unit (its partials, the BF16 tail
+        // and the output) right here, while the producer warp keeps prefetching the next segment.
+        if (tid == 0) {
+          const int done = atomicAdd(&margs.unit_done[unit], 1);
+          const int last = done == margs.unit_slots[unit].y - 1;
+          if (last) margs.unit_done[unit] = 0;   // ready for the next launch
+          merge_flag = last;
+        }
+        consumer_sync();
+        if (merge_flag) {
+          __threadfence();
+          merge_unit_by_consumers(margs, pm, pl, po, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+        }
+      }
     }
   }
   if (*abortp) {

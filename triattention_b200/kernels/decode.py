@@ -117,15 +117,19 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None):
-        """split_group: a torch.distributed process group over which every unit's tile range is split
+    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None, fused_merge=False):
+        """fused_merge: a whole step is one launch (the CTA that finishes a unit's last segment merges the unit).
+        It pays when a step is launch-bound (few sequences, short caches); at full batch the merge sits on the
+        critical path of the CTA that does it, so the default keeps the split pass and the merge as two launches
+        chained by programmatic dependent launch.
+        split_group: a torch.distributed process group over which every unit's tile range is split
         (long-context decode): each rank streams its part, the folded (m, l, o) triples are all-gathered over
         NCCL and every rank runs the final merge.  None = this process holds whole units."""
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
-        self.split_group, self.split = split_group, None
+        self.split_group, self.split, self.fused_merge = split_group, None, bool(fused_merge)
         if split_group is not None:
             import torch.distributed as dist
             self.split = (dist.get_rank(split_group), dist.get_world_size(split_group))
@@ -177,7 +181,9 @@ class DecodeCache:
                 pool=torch.empty(max(16, host["pool_bytes"]), dtype=torch.uint8, device=device),
                 tail_k=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
                 tail_v=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
-                pm=f32(slots, MAX_GROUP), pl=f32(slots, MAX_GROUP), po=f32(slots, MAX_GROUP, 128))
+                pm=f32(slots, MAX_GROUP), pl=f32(slots, MAX_GROUP), po=f32(slots, MAX_GROUP, 128), unit_done=None)
+            if self.split is None and self.fused_merge and int(host["unit_slots"][:, 1].min()) >= 1:
+                entry["unit_done"] = torch.zeros(units, dtype=torch.int32, device=device)   # segments finished per unit
             if self.split is not None:   # folded triples of this rank, and of all ranks after the all-gather
                 world = self.split[1]
                 entry.update(fm=f32(units, MAX_GROUP), fl=f32(units, MAX_GROUP), fo=f32(units, MAX_GROUP, 128),
@@ -207,7 +213,8 @@ class DecodeCache:
         out = torch.empty_like(q) if out is None else out
         run = lambda pm, pl, po, slots, ph: self.module.decode(
             q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"], d["cta_segments"],
-            slots, e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, pm, pl, po, e["prompt"], scale, ph)
+            slots, e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, pm, pl, po, e["prompt"], scale, ph,
+            unit_done=e["unit_done"] if ph == 3 else None)
         if self.split is None:
             run(e["pm"], e["pl"], e["po"], d["unit_slots"], phases)
             return out

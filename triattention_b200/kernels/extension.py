@@ -26,7 +26,7 @@ SIGNATURES = {
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
     "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
-                   _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
+                   _P, _P, _P, _P, _I, _I, _I, _I, _I, _D, _I, _P, _P],
     "tri_decode_static": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P,
                           _L, _L, _I, _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_fold": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
@@ -157,7 +157,7 @@ class Module:
                                                       v.stride(2), int(chunk_begin), int(chunk_count), _stream()))
 
     def decode(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, kstat, vstat,
-               tail_k, tail_v, kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3):
+               tail_k, tail_v, kcur, vcur, step, out, pm, pl, po, prompt, scale, phases=3, unit_done=None):
         if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1):
             raise RuntimeError("q [B,Hq,1,128]")
         b, hq = q.shape[0], q.shape[1]
@@ -168,6 +168,9 @@ class Module:
                 unit_base.dtype == torch.int64 and
                 tail_v.stride() == tail_k.stride() and out.stride(3) == 1):
             raise RuntimeError("decode geometry/buffers")
+        if unit_done is not None and not (unit_done.dtype == torch.int32 and unit_done.is_cuda and
+                                          unit_done.numel() >= b * hk):
+            raise RuntimeError("unit_done int32 [units] on the device")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_decode(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(),
                                             unit_tab.data_ptr(), unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(),
@@ -175,7 +178,8 @@ class Module:
                                             tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), tail_k.stride(1),
                                             kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
                                             step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(),
-                                            pl.data_ptr(), po.data_ptr(), b, hq, hk, int(prompt), max_tail, float(scale), int(phases),
+                                            pl.data_ptr(), po.data_ptr(), unit_done.data_ptr() if unit_done is not None else None,
+                                            b, hq, hk, int(prompt), max_tail, float(scale), int(phases),
                                             self.error_word(q.device).data_ptr(), _stream()))
         return out
 
