@@ -155,3 +155,31 @@ def test_tail_saturates(module):
     got, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=4, max_tail=2)
     want = oracle_steps(k[0], v[0], bands, qd[0], kd[0], vd[0], 4, max_tail=2)
     assert_fp_close(got[0], orc.to_bf16(want), "saturated tail")
+
+
+def test_host_stepper_matches_device_calls(module):
+    """Pinned host buffers through the rotating device buffers give the same bits as device-resident calls,
+    for more steps than there are buffer sets and with a different input every step."""
+    from triattention_b200.kernels.decode import HostStepper
+    hq, hk, t, steps = 4, 2, 700, 5
+    bands = np.asarray([[INF, INF], [INF, INF], [3, 5], [3, 5]], np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=81, batch=2)
+    qd, kd, vd = make_inputs(hq, hk, steps, seed=82, batch=2)
+    want, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=steps)
+    cache = DecodeCache(module, max_tail=8)
+    pre = Prefill(module, bands_fn_of(bands), cache)
+    kc, vc = bf16_cuda(k), bf16_cuda(v)
+    table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+    cache.store(0, t, ops, table.host, kc, vc)
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).pin_memory()
+    stepper = HostStepper(cache, 0, (2, hq, 1, 128), (2, hk, 1, 128), "cuda")
+    outs = [torch.empty((2, hq, 1, 128), dtype=torch.bfloat16).pin_memory() for _ in range(steps)]
+    for s in range(steps):
+        stepper.submit(pin(qd[:, :, s:s + 1]), pin(kd[:, :, s:s + 1]), pin(vd[:, :, s:s + 1]), outs[s], SCALE)
+        cache.advance()
+    stepper.wait()
+    module.check_device_error()
+    got = np.stack([o.float().numpy()[:, :, 0] for o in outs], 1)
+    np.testing.assert_array_equal(got, want)
+    with pytest.raises(RuntimeError):
+        stepper.submit(torch.empty(1), outs[0], outs[0], outs[0], SCALE)

@@ -234,3 +234,55 @@ class DecodeCache:
 
     def stored(self, layer):
         return layer in self.layers
+
+
+class HostStepper:
+    """Decode steps whose Q / K / V rows and output live in pinned HOST memory (a runtime that keeps its
+    activations on the host, or a binding that only passes host pointers).  Copies run on two side streams
+    and `depth` sets of device buffers rotate, so the host-to-device copy of step i+1 and the device-to-host
+    copy of step i-1 overlap the kernels of step i; every step still moves all of its inputs and its output.
+    submit() only enqueues; wait() blocks until everything submitted so far has reached its host buffer."""
+
+    def __init__(self, cache, layer, q_shape, kv_shape, device, depth=2):
+        self.cache, self.layer, self.depth, self.count = cache, layer, depth, 0
+        bf16 = lambda shape: torch.empty(shape, dtype=torch.bfloat16, device=device)
+        self.q = [bf16(q_shape) for _ in range(depth)]
+        self.k = [bf16(kv_shape) for _ in range(depth)]
+        self.v = [bf16(kv_shape) for _ in range(depth)]
+        self.out = [bf16(q_shape) for _ in range(depth)]
+        self.copy_in, self.copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        event = lambda: [torch.cuda.Event() for _ in range(depth)]
+        self.loaded, self.computed, self.stored = event(), event(), event()
+
+    def submit(self, q_host, k_host, v_host, out_host, scale):
+        for t in (q_host, k_host, v_host, out_host):
+            if t.is_cuda or not t.is_pinned():
+                raise RuntimeError("HostStepper wants pinned host tensors")
+        slot, compute = self.count % self.depth, torch.cuda.current_stream()
+        reuse = self.count >= self.depth
+        with torch.cuda.stream(self.copy_in):
+            if reuse:
+                self.copy_in.wait_event(self.computed[slot])    # the kernels that read this slot's inputs are done
+            self.q[slot].copy_(q_host, non_blocking=True)
+            self.k[slot].copy_(k_host, non_blocking=True)
+            self.v[slot].copy_(v_host, non_blocking=True)
+            self.loaded[slot].record(self.copy_in)
+        compute.wait_event(self.loaded[slot])
+        if reuse:
+            compute.wait_event(self.stored[slot])               # this slot's previous output has left the device
+        self.cache(self.layer, self.q[slot], self.k[slot], self.v[slot], scale, out=self.out[slot])
+        self.computed[slot].record(compute)
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(self.computed[slot])
+            out_host.copy_(self.out[slot], non_blocking=True)
+            self.stored[slot].record(self.copy_out)
+        self.count += 1
+
+    def join(self):
+        """Make the current stream wait (on the device) for the last submitted step's output copy."""
+        if self.count:
+            torch.cuda.current_stream().wait_event(self.stored[(self.count - 1) % self.depth])
+
+    def wait(self):
+        self.copy_out.synchronize()
+        torch.cuda.current_stream().synchronize()
