@@ -8,19 +8,14 @@
 // in band mode (the only mode the reference's Python ever uses, kernels/prefill.py:103), with a batch
 // dimension added.
 //
-// Shape of the computation.  One CTA of 128 threads owns 128 query rows of one Q head: two adjacent
-// query blocks ("halves", 64 rows each; warps 0-1 and 2-3).  Thread t owns row t: it reads its row of
-// the score / PV accumulators from TMEM lane t (tcgen05.ld 32x32b), so the online softmax needs no
-// cross-thread reduction.  Per key tile:
-//   QK   S[128x64]  = Q8[128x128] . K8[64x128]^T   4 x tcgen05.mma kind::i8 (M128 N64 K32), s8 x s8 -> s32
-//   PV   D[128x128] = P8[128x64]  . V8[128x64]^T   2 x tcgen05.mma kind::i8 (M128 N128 K32), u8 x s8 -> s32
-//   or   D[128x128] = P16[128x64] . V16[128x64]^T  4 x tcgen05.mma kind::f16 (M128 N128 K16), fp32 accumulate
-// The two halves follow the reference's visiting order (sink tile, own diagonal tile, INT8 band
-// ascending, INT4 band ascending); a tile that only one half visits runs with the other half idle.
+// Shape of the computation: see prefill_kernel.cuh (one CTA per 256 query rows of a Q head, warp
+// specialised: TMA producer, MMA issuer, V widening, softmax).  The two 128-row MMA tiles of a CTA are made
+// of four 64-row query blocks that follow the reference's tile lists (sink tile, own diagonal tile, INT8
+// band, INT4 band); a tile that only some blocks visit runs with the other blocks' weights at zero.
 // INT4 QK uses the 4-bit codes widened to int8 by the write kernel (K4X blobs, Q4X rows), so the
 // integer accumulators equal the reference's s4 x s4 MMAs exactly.
 // Q arrives by TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle), K/V tiles by TMA bulk
-// copies of pre-tiled blobs (cp.async.bulk), double buffered.  Every wait is bounded.
+// copies of pre-tiled blobs (cp.async.bulk).  Every wait is bounded.
 #include "common.cuh"
 #include "abi_internal.h"
 #include <cuda.h>
@@ -78,32 +73,43 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t cfmt, uint32_t afmt, 
 }
 constexpr uint32_t LayoutNone = 0, Layout128B = 2;
 constexpr uint32_t IdescQK = instr_desc(2, 1, 1, 128, 64);    // s8 x s8 -> s32
-constexpr uint32_t IdescPV8 = instr_desc(2, 0, 1, 128, 128);  // u8 x s8 -> s32
 constexpr uint32_t IdescPV16 = instr_desc(1, 0, 0, 128, 128); // f16 x f16 -> f32
 
-// ---- shared-memory plan of the prefill CTA ----------------------------------------------------
-constexpr int PrefillThreads = 256;   // two threads per query row
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
+constexpr int PrefillThreads = 640;   // producer, issuer, 2 widening warps, 16 softmax warps
 constexpr int ProbeThreads = 128;
-constexpr int SmQ8 = 0, SmQ4 = 16384, SmP = 32768, SmK = 49152, SmV = SmK + 2 * K8Bytes, SmEnd = SmV + 2 * V16Bytes;
-constexpr int SmSteps = SmEnd, StepBytes = (2 * MaxTiles + 8) * 2;   // visiting-order table, 2 bytes per step
-constexpr int PrefillShared = SmSteps + StepBytes + 1024;   // + slack to align the base to 1024 bytes
-constexpr uint32_t TmemCols = 256, TmemS = 0, TmemD = 64;
+constexpr int MaxSteps = 2 * MaxTiles + 8;
+constexpr int SmQ8 = 0, SmQ4 = 32768, SmP = 65536;              // 2 Q tiles each; P: [tile][buffer] x 16 KB fp16
+constexpr int SmK = SmP + 4 * 16384, SmV8 = SmK + 3 * K8Bytes;   // three stages of K and raw V
+constexpr int SmV16 = SmV8 + 3 * V8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
+constexpr int SmSteps = SmEnd, StepBytes = (3 * MaxSteps + 15) / 16 * 16;  // visiting order: uint16 tile|mode, uint8 mask
+constexpr int PrefillShared = SmSteps + StepBytes + 1024;       // + slack to align the base to 1024 bytes
+constexpr uint32_t TmemCols = 512, TmemO = 0, TmemS = 256;      // O: [tile] x 128 columns; S: [tile][buffer] x 64
+constexpr float RefSlack = 8.f;   // a row's reference exponent moves when a tile's maximum exceeds it by this (log2)
+constexpr float PShift = 5.f;     // weights are carried times 2^5: keeps small tiles out of the fp16 subnormals
 enum Mode : int { ModeF16 = 0, ModeI8 = 1, ModeQ4 = 2 };
 
-struct StepPlan {   // tile visiting order of one CTA, all warp-uniform integers
-  int b0, b1, has1, nF, lo8, n8, lo4, n4, w8, w4;
-  int f_tile[3], f_mask[3];
-  __device__ void build(int pair, int rows, int w8_, int w4_) {
+struct QuadPlan {   // tile visiting order of one CTA (four query blocks q0..q0+3), all warp-uniform integers
+  int q0, nb, nF, lo8, n8, lo4, n4, w8, w4;
+  int f_tile[5], f_mask[5];
+  __device__ void build(int quad, int rows, int w8_, int w4_) {
     w8 = w8_; w4 = w4_;
-    b0 = 2 * pair; b1 = b0 + 1; has1 = b1 < rows;
+    q0 = 4 * quad; nb = min(4, rows - q0);
     nF = 0;
-    f_tile[nF] = 0; f_mask[nF] = has1 ? 3 : 1; ++nF;
-    if (b0 > 0) { f_tile[nF] = b0; f_mask[nF] = 1; ++nF; }
-    if (has1) { f_tile[nF] = b1; f_mask[nF] = 2; ++nF; }
-    // prefill_sm80.cu:281-283 per half, then the union of the two contiguous ranges
+    f_tile[nF] = 0; f_mask[nF] = (1 << nb) - 1; ++nF;      // sink tile; it is also block 0's diagonal tile
+    for (int j = 0; j < nb; ++j)
+      if (q0 + j > 0) { f_tile[nF] = q0 + j; f_mask[nF] = 1 << j; ++nF; }
+    // prefill_sm80.cu:281-283 per block, then the union of the contiguous ranges
     int lo = 1 << 30, hi = 0, lq = 1 << 30, hq = 0;
-    for (int h = 0; h <= has1; ++h) {
-      const int qb = b0 + h, l8 = max(1, qb - w8 + 1), c8 = max(0, qb - l8);
+    for (int j = 0; j < nb; ++j) {
+      const int qb = q0 + j, l8 = max(1, qb - w8 + 1), c8 = max(0, qb - l8);
       const int l4 = max(1, qb - w4 + 1), c4 = max(0, qb - w8 - l4 + 1);
       if (c8 > 0) { lo = min(lo, l8); hi = max(hi, l8 + c8); }
       if (c4 > 0) { lq = min(lq, l4); hq = max(hq, l4 + c4); }
@@ -116,15 +122,15 @@ struct StepPlan {   // tile visiting order of one CTA, all warp-uniform integers
     mask = 0;
     if (i < nF + n8) {
       tile = lo8 + (i - nF); mode = ModeI8;
-      for (int h = 0; h <= has1; ++h) {
-        const int qb = b0 + h;
-        if (tile >= max(1, qb - w8 + 1) && tile <= qb - 1) mask |= 1 << h;
+      for (int j = 0; j < nb; ++j) {
+        const int qb = q0 + j;
+        if (tile >= max(1, qb - w8 + 1) && tile <= qb - 1) mask |= 1 << j;
       }
     } else {
       tile = lo4 + (i - nF - n8); mode = ModeQ4;
-      for (int h = 0; h <= has1; ++h) {
-        const int qb = b0 + h;
-        if (tile >= max(1, qb - w4 + 1) && tile <= qb - w8) mask |= 1 << h;
+      for (int j = 0; j < nb; ++j) {
+        const int qb = q0 + j;
+        if (tile >= max(1, qb - w4 + 1) && tile <= qb - w8) mask |= 1 << j;
       }
     }
   }
@@ -302,13 +308,13 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
     if (allow_smem(prefill_kernel<__half>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
     configured = 1;
   }
-  const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, pairs = (rows + 1) / 2;
+  const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
   CUtensorMap map8, map4;
   if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
   if (make_q_map(&map4, int4 ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
-  const dim3 grid((unsigned)((int64_t)pairs * units));
+  const dim3 grid((unsigned)((int64_t)quads * units));
 #define TRI_LAUNCH(T)                                                                                                      \
   prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, bands, static_cast<const uint8_t*>(k8),       \
       static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8), qa8, \
