@@ -176,6 +176,27 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
     if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
   }
 }
+// The same with the waiting done by the hardware: try_wait with a suspend-time hint parks the warp until
+// the phase completes or the hint (in ns) runs out, so a warp that waits issues one instruction per ~20 us
+// instead of a polling loop that competes with working warps for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
+  }
+}
 // 1-D bulk copy global -> shared; dst, src and bytes are multiples of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

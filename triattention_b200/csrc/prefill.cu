@@ -80,6 +80,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
                  "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void tmem_fill16(uint32_t taddr, uint32_t v) {   // 16 columns of this warp's 32 lanes = v
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
+               ::"r"(taddr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
@@ -87,25 +91,22 @@ constexpr int PrefillThreads = 640;   // producer, issuer, 2 widening warps, 16 
 constexpr int ProbeThreads = 128;
 constexpr int MaxSteps = 2 * MaxTiles + 8;
 constexpr int SmQ8 = 0, SmQ4 = 32768, SmP = 65536;              // 2 Q tiles each; P: [tile][buffer] x 16 KB fp16
-constexpr int SmK = SmP + 4 * 16384, SmV8 = SmK + 3 * K8Bytes;   // three stages of K and raw V
-constexpr int SmV16 = SmV8 + 3 * V8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
+constexpr int SmK = SmP + 4 * 16384, SmV8 = SmK + 4 * K8Bytes;   // four stages of K, two of raw V
+constexpr int SmV16 = SmV8 + 2 * V8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
 constexpr int SmSteps = SmEnd, StepBytes = (3 * MaxSteps + 15) / 16 * 16;  // visiting order: uint16 tile|mode, uint8 mask
 constexpr int PrefillShared = SmSteps + StepBytes + 1024;       // + slack to align the base to 1024 bytes
 constexpr uint32_t TmemCols = 512, TmemO = 0, TmemS = 256;      // O: [tile] x 128 columns; S: [tile][buffer] x 64
 constexpr float RefSlack = 8.f;   // a row's reference exponent moves when a tile's maximum exceeds it by this (log2)
+constexpr float PMagic64 = 58368.5f;   // 2^15 * 1.78125 + 0.5: like 49152.5f, with 0x64 in byte 2 of the sum
 constexpr float PShift = 5.f;     // weights are carried times 2^5: keeps small tiles out of the fp16 subnormals
 enum Mode : int { ModeF16 = 0, ModeI8 = 1, ModeQ4 = 2 };
 
 struct QuadPlan {   // tile visiting order of one CTA (four query blocks q0..q0+3), all warp-uniform integers
   int q0, nb, nF, lo8, n8, lo4, n4, w8, w4;
-  int f_tile[5], f_mask[5];
   __device__ void build(int quad, int rows, int w8_, int w4_) {
     w8 = w8_; w4 = w4_;
     q0 = 4 * quad; nb = min(4, rows - q0);
-    nF = 0;
-    f_tile[nF] = 0; f_mask[nF] = (1 << nb) - 1; ++nF;      // sink tile; it is also block 0's diagonal tile
-    for (int j = 0; j < nb; ++j)
-      if (q0 + j > 0) { f_tile[nF] = q0 + j; f_mask[nF] = 1 << j; ++nF; }
+    nF = 1 + nb - (q0 == 0 ? 1 : 0);   // the sink tile (all blocks; it is also block 0's diagonal tile), then one diagonal tile per block
     // prefill_sm80.cu:281-283 per block, then the union of the contiguous ranges
     int lo = 1 << 30, hi = 0, lq = 1 << 30, hq = 0;
     for (int j = 0; j < nb; ++j) {
@@ -118,7 +119,13 @@ struct QuadPlan {   // tile visiting order of one CTA (four query blocks q0..q0+
   }
   __device__ int steps() const { return nF + n8 + n4; }
   __device__ void get(int i, int& tile, int& mode, int& mask) const {
-    if (i < nF) { tile = f_tile[i]; mode = ModeF16; mask = f_mask[i]; return; }
+    if (i < nF) {
+      mode = ModeF16;
+      if (i == 0) { tile = 0; mask = (1 << nb) - 1; return; }
+      const int j = i - 1 + (q0 == 0 ? 1 : 0);
+      tile = q0 + j; mask = 1 << j;
+      return;
+    }
     mask = 0;
     if (i < nF + n8) {
       tile = lo8 + (i - nF); mode = ModeI8;

@@ -7,8 +7,16 @@
 //   warp 1        issuer:   all tcgen05.mma of the CTA (one elected thread)
 //   warps 2-3     widen the INT8 V codes of a step to fp16 in shared memory (the P.V operand)
 //   warps 4-19    softmax: tile X = (warp-4)/8, two threads per query row; warp w reads TMEM lanes
-//                 32*(w%4)..+31, warps w and w+4 of a tile share 32 rows and split the 64 key columns and
-//                 the 128 output channels in halves
+//                 32*(w%4)..+31 (the hardware ties a warp to that lane quadrant), warps w and w+4 of a tile
+//                 share 32 rows and split the 64 key columns and the 128 output channels in halves; their
+//                 only exchange per step is the row's partial maximum (shared memory + a 64-thread barrier).
+//                 Four softmax warps per scheduler are what it takes to keep the exponential unit busy:
+//                 one warp alone issues an ex2 every ~15 cycles, the unit takes one every ~8.
+//
+// Integer scores are read as floats without a conversion: the score accumulators in TMEM are preset to
+// 0x4B400000 (the bits of 12582912.0f, the bias the reference adds in registers, prefill_sm80.cu:27) by the
+// softmax threads, the QK^T MMAs accumulate on top, and for |score| < 2^22 the result read as a float IS
+// 12582912 + score.  Row maxima are taken on those floats with the three-input max.
 //
 // Per step (one 64-key tile) and MMA tile:
 //   S[128x64]  = Q8 . K8^T            4 x kind::i8 (M128 N64 K32), s32 accumulators (bit-equal to the reference's)
@@ -22,23 +30,32 @@
 // here with one extra fp16 rounding (2^-12 relative) of each weight, far inside the output tolerance.
 // Sink and diagonal tiles use fp16 weights and the fp16 V blob exactly like the reference.
 //
-// Every wait is an mbarrier wait with a time limit and the CTA-wide abort flag; there is no bar.sync
-// between the initial and the final __syncthreads, so a role that gives up cannot strand another.
+// Every mbarrier wait has a time limit and obeys the CTA-wide abort flag.  The only other barrier inside
+// the main loop is the 64-thread bar.sync of a softmax warp pair; both warps of a pair walk the same step
+// list and reach it the same number of times even after an abort (they then skip everything else).
 #pragma once
 // (included inside namespace tri)
 
 struct PrefillBarriers {
   uint64_t q;               // Q tiles landed
-  uint64_t kv_full[3];      // K + raw V of a stage landed (transaction bytes)
-  uint64_t kv_empty[3];     // stage reusable: QK^T done (tcgen05.commit) + both widening warps done
+  uint64_t k_full[4];       // K tile + its scales landed (transaction bytes)
+  uint64_t k_empty[4];      // K stage reusable: QK^T of both tiles done (tcgen05.commit)
+  uint64_t v8_full[2];      // raw INT8 V tile landed
+  uint64_t v8_empty[2];     // raw V stage reusable: both widening warps done
   uint64_t v16_full[2];     // fp16 V operand ready: two widening warps, or TMA of the fp16 blob + one plain arrive
   uint64_t v16_empty[2];    // all P.V of the step done
   uint64_t s_full[2][2];    // [tile][buffer] scores in TMEM
-  uint64_t p_full[2][2];    // [tile][buffer] P operand written by the 8 softmax warps of the tile
+  uint64_t s_init;          // both score buffers of both tiles hold the bias (16 softmax warps)
+  uint64_t p_full[2][2];    // [tile][buffer] P operand written by the 8 softmax warps of the tile; score buffer re-biased
   uint64_t o_done[2][2];    // [tile][buffer] P.V of that P buffer done
-  uint64_t pair[2][4];      // [tile][lane quadrant] the two warps that share 32 rows exchanged their partial maxima
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -53,6 +70,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   __shared__ __align__(8) PrefillBarriers bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float k_scales[8][4];   // ring: the four K scales of the tiles of the last 8 steps, fetched with the tile
   __shared__ float xchg[2][2][2][128];   // [tile][parity][column half][row]: partial maxima, at the end denominators
   uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -78,11 +96,12 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   }
   if (tid == 0) {
     mbar_init(&bars.q, 1);
-    for (int s = 0; s < 3; ++s) { mbar_init(&bars.kv_full[s], 1); mbar_init(&bars.kv_empty[s], 3); }
+    mbar_init(&bars.s_init, 16);
+    for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&bars.v8_full[s], 1); mbar_init(&bars.v8_empty[s], 2); }
     for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 2); mbar_init(&bars.v16_empty[s], 1); }
     for (int x = 0; x < 2; ++x) {
       for (int s = 0; s < 2; ++s) { mbar_init(&bars.s_full[x][s], 1); mbar_init(&bars.p_full[x][s], 8); mbar_init(&bars.o_done[x][s], 1); }
-      for (int qd = 0; qd < 4; ++qd) mbar_init(&bars.pair[x][qd], 2);
     }
     mbar_fence_init();
     abort_flag = 0;
@@ -95,7 +114,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   const uint32_t tmem = tmem_slot;
   auto tile_of = [&](int i) { return (int)(step_tm[i] & 0xfffu); };
   auto mode_of = [&](int i) { return (int)(step_tm[i] >> 12); };
-  auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_abortable(bar, parity & 1u, abortp); };
+  auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_parked(bar, parity & 1u, abortp); };
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------------
@@ -106,65 +125,84 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         if (need_q4) tma_load_3d(smem + SmQ4 + x * 16384, &map_q4, 0, plan.q0 * BM + x * 128, qunit, &bars.q);
       }
       for (int i = 0; i < nsteps; ++i) {
-        const int tile = tile_of(i), mode = mode_of(i), s = i % 3, vb = i & 1;
-        if (i >= 3 && !wait(&bars.kv_empty[s], i / 3 - 1)) break;
+        const int tile = tile_of(i), mode = mode_of(i), s = i & 3, vb = i & 1;
+        if (i >= 4 && !wait(&bars.k_empty[s], (i >> 2) - 1)) break;
         const int64_t ht = kvunit * tiles + tile;
+        mbar_expect_tx(&bars.k_full[s], K8Bytes + 16);
+        bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bars.k_full[s]);
+        bulk_g2s(&k_scales[i & 7][0], (mode == ModeQ4 ? ka4 : ka8) + ht * 4, 16, &bars.k_full[s]);
         if (mode == ModeF16) {
           if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
-          mbar_expect_tx(&bars.kv_full[s], K8Bytes);
-          bulk_g2s(smem + SmK + s * K8Bytes, k8 + ht * K8Bytes, K8Bytes, &bars.kv_full[s]);
           mbar_expect_tx(&bars.v16_full[vb], V16Bytes);   // first arrival; the second one follows the copy's issue
           bulk_g2s(smem + SmV16 + vb * V16Bytes, v16 + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
           mbar_arrive_cta(&bars.v16_full[vb]);
+          mbar_arrive_cta(&bars.v8_full[vb]);   // nothing to fetch: keeps the phase of the raw V stage in step with the step index
         } else {
-          mbar_expect_tx(&bars.kv_full[s], K8Bytes + V8Bytes);
-          bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bars.kv_full[s]);
-          bulk_g2s(smem + SmV8 + s * V8Bytes, v8 + ht * V8Bytes, V8Bytes, &bars.kv_full[s]);
+          // raw V stages are used by steps i, i+2, ... whatever their mode: the widening warps pass every step
+          if (i >= 2 && !wait(&bars.v8_empty[vb], (i - 2) >> 1)) break;
+          mbar_expect_tx(&bars.v8_full[vb], V8Bytes);
+          bulk_g2s(smem + SmV8 + vb * V8Bytes, v8 + ht * V8Bytes, V8Bytes, &bars.v8_full[vb]);
         }
       }
     }
   } else if (warp == 1) {
     // ---- issuer -----------------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t q8_addr = smem_u32(smem + SmQ8), q4_addr = smem_u32(smem + SmQ4);
-      int nqk[2] = {0, 0}, npv[2] = {0, 0};
+      // Descriptors are built once; per MMA only the 16-byte-unit address field (low word) moves.
+      const uint64_t dq8 = smem_desc(smem_u32(smem + SmQ8), 0, 1024, Layout128B), dq4 = smem_desc(smem_u32(smem + SmQ4), 0, 1024, Layout128B);
+      const uint64_t dk = smem_desc(smem_u32(smem + SmK), 128, 1024, LayoutNone), dp = smem_desc(smem_u32(smem + SmP), 128, 1024, LayoutNone);
+      const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
+      auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };   // stays inside the 14-bit field
+      // Order on the tensor pipe per step i: QK^T of step i+1 for both tiles (into the score buffers that the softmax
+      // warps released one step ago), then P.V of step i for tile 0 and tile 1 as their softmax warps hand P over.
+      int nqk0 = 0, nqk1 = 0, npv0 = 0, npv1 = 0;
       auto issue_qk = [&](int i) -> bool {
-        const int mode = mode_of(i), mask = step_mask[i], s = i % 3;
-        if (!wait(&bars.kv_full[s], i / 3)) return false;
+        const int mode = mode_of(i), mask = step_mask[i], s = i & 3;
+        if (!wait(&bars.k_full[s], i >> 2)) return false;
         tc_fence_after();
-        const uint32_t ka_ = smem_u32(smem + SmK + s * K8Bytes);
-        for (int x = 0; x < 2; ++x) {
-          if (((mask >> (2 * x)) & 3) == 0) continue;
-          const int sb = nqk[x] & 1;
-          const uint32_t qa_ = (mode == ModeQ4 ? q4_addr : q8_addr) + x * 16384;
+        const uint64_t dqm = mode == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
+        if (mask & 3) {
+          const int sb = nqk0 & 1;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_i8(tmem + TmemS + x * 128 + sb * 64, smem_desc(qa_ + kk * 32, 0, 1024, Layout128B),
-                    smem_desc(ka_ + kk * 256, 128, 1024, LayoutNone), IdescQK, kk > 0);
-          tc_commit(&bars.s_full[x][sb]);
-          ++nqk[x];
+          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);   // on top of the bias
+          tc_commit(&bars.s_full[0][sb]);
+          ++nqk0;
         }
-        tc_commit(&bars.kv_empty[s]);
+        if (mask & 12) {
+          const int sb = nqk1 & 1;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + 128 + sb * 64, at(dqm, 16384 + kk * 32), at(dks, kk * 256), IdescQK, 1u);
+          tc_commit(&bars.s_full[1][sb]);
+          ++nqk1;
+        }
+        tc_commit(&bars.k_empty[s]);
         return true;
       };
-      bool ok = wait(&bars.q, 0) && issue_qk(0);
+      bool ok = wait(&bars.q, 0) && wait(&bars.s_init, 0) && issue_qk(0);
       for (int i = 0; ok && i < nsteps; ++i) {
         if (i + 1 < nsteps && !issue_qk(i + 1)) break;   // the next scores are computed while this step's softmax runs
         const int mask = step_mask[i], vb = i & 1;
         if (!wait(&bars.v16_full[vb], i >> 1)) break;
-        const uint32_t va = smem_u32(smem + SmV16 + vb * V16Bytes);
-        for (int x = 0; x < 2 && ok; ++x) {
-          if (((mask >> (2 * x)) & 3) == 0) continue;
-          const int pb = npv[x] & 1;
-          if (!wait(&bars.p_full[x][pb], npv[x] >> 1)) { ok = false; break; }
+        const uint64_t dvs = at(dv, vb * V16Bytes);
+        if (mask & 3) {
+          const int pb = npv0 & 1;
+          if (!wait(&bars.p_full[0][pb], npv0 >> 1)) break;
           tc_fence_after();
-          const uint32_t pa = smem_u32(smem + SmP + (2 * x + pb) * 16384);
+          const uint64_t dps = at(dp, pb * 16384);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem + TmemO + x * 128, smem_desc(pa + kk * 256, 128, 1024, LayoutNone),
-                     smem_desc(va + kk * 256, 128, 1024, LayoutNone), IdescPV16, (npv[x] > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(&bars.o_done[x][pb]);
-          ++npv[x];
+          for (int kk = 0; kk < 4; ++kk) umma_f16(tmem + TmemO, at(dps, kk * 256), at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&bars.o_done[0][pb]);
+          ++npv0;
+        }
+        if (mask & 12) {
+          const int pb = npv1 & 1;
+          if (!wait(&bars.p_full[1][pb], npv1 >> 1)) break;
+          tc_fence_after();
+          const uint64_t dps = at(dp, (2 + pb) * 16384);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) umma_f16(tmem + TmemO + 128, at(dps, kk * 256), at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&bars.o_done[1][pb]);
+          ++npv1;
         }
         tc_commit(&bars.v16_empty[vb]);
       }
@@ -178,11 +216,13 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const int ct = tid - 64;   // 0..63
     const __half2 bias = __half2half2(__float2half(1152.f));
     for (int i = 0; i < nsteps; ++i) {
-      const int mode = mode_of(i), s = i % 3, vb = i & 1;
-      if (!wait(&bars.kv_full[s], i / 3)) break;
+      const int mode = mode_of(i), vb = i & 1;
+      // every step, also those without a raw V tile: a parity wait only works for a waiter that is at most one
+      // phase behind, so these warps must not run ahead of the producer
+      if (!wait(&bars.v8_full[vb], i >> 1)) break;
       if (mode != ModeF16) {
         if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
-        const uint4* src = reinterpret_cast<const uint4*>(smem + SmV8 + s * V8Bytes);
+        const uint4* src = reinterpret_cast<const uint4*>(smem + SmV8 + vb * V8Bytes);
         uint8_t* dst = smem + SmV16 + vb * V16Bytes;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -208,13 +248,14 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       __syncwarp();
       if (lane == 0) {
         if (mode != ModeF16) mbar_arrive_cta(&bars.v16_full[vb]);
-        mbar_arrive_cta(&bars.kv_empty[s]);
+        mbar_arrive_cta(&bars.v8_empty[vb]);
       }
     }
   } else {
     // ---- softmax ------------------------------------------------------------------------------------
     const int sw = warp - 4, x = sw / 8, quad = sw % 4, ch = (sw % 8) / 4;
     const int row = quad * 32 + lane, half = row / 64, blk = 2 * x + half;
+    const int pair_id = 1 + 4 * x + quad;   // named barrier of the two warps that share these 32 rows
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
     const int bh = plan.q0 + blk, qi = bh * BM + (row & 63);
     const bool row_valid = blk < plan.nb && qi < tokens;
@@ -223,97 +264,110 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
     float ref = -FLT_MAX, denom = 0.f;   // reference exponent of the row; this thread's share of the denominator
     int n = 0;                           // steps of this tile so far
-    bool zero_rows[2] = {false, false};  // this thread's rows of P buffer [.] are known to be zero
-    auto load_kscale = [&](int i) {
-      return __ldg(reinterpret_cast<const float4*>((mode_of(i) == ModeQ4 ? ka4 : ka8) + (kvunit * tiles + tile_of(i)) * 4));
-    };
+    int zero_rows = 0;                   // bit b: this thread's part of its row of P buffer b is known to be zero
+    const uint32_t bias = (uint32_t)Magic;
+    // this thread's 32 columns of both score buffers start at the bias
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_fill16(lane_base + TmemS + x * 128 + (c >> 1) * 64 + 32 * ch + 16 * (c & 1), bias);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cta(&bars.s_init);
+
     int inext = 0;   // next step in which this tile takes part
     while (inext < nsteps && ((step_mask[inext] >> (2 * x)) & 3) == 0) ++inext;
-    float4 ks_next = inext < nsteps ? load_kscale(inext) : make_float4(0.f, 0.f, 0.f, 0.f);
     bool ok = true;
     while (inext < nsteps) {
       const int i = inext;
       const int tile = tile_of(i), mode = mode_of(i), mx = (step_mask[i] >> (2 * x)) & 3;
-      const float ks[4] = {ks_next.x, ks_next.y, ks_next.z, ks_next.w};
       ++inext;
       while (inext < nsteps && ((step_mask[inext] >> (2 * x)) & 3) == 0) ++inext;
-      if (inext < nsteps) ks_next = load_kscale(inext);   // in flight while this step computes
       const int sb = n & 1;
-      if (!(ok = wait(&bars.s_full[x][sb], n >> 1))) break;
-      tc_fence_after();
-      const bool active = (mx >> half) & 1;   // uniform per warp
+      const bool active = (mx >> half) & 1;   // uniform for the warp pair
       const bool diag = mode == ModeF16 && tile == bh;
       const float qs = mode == ModeQ4 ? qs4 : qs8;
-      const float slope[2] = {qs * ks[2 * ch], qs * ks[2 * ch + 1]};   // this thread's two 16-key groups
       const int key0 = tile * BN + 32 * ch;
       const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 32 * ch;
       auto dead = [&](int key) { return key >= tokens || key > qi || qi >= tokens; };   // diagonal tile only
+      uint8_t* prow = smem + SmP + (2 * x + sb) * 16384 + (row / 8) * 1024 + (row % 8) * 16 + (4 * ch) * 128;   // core matrices [row/8][key/8]
 
-      // pass 1: partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253)
-      float part = -CUDART_INF_F;
+      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1));
+      if (ok) tc_fence_after();
+      // The tile's K scales came with the tile (the ring slot is not reused before step i+8, and the producer
+      // cannot be more than 4 steps ahead of a softmax warp).
+      const float4 ks = *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
+      const float slope[2] = {qs * (ch ? ks.z : ks.x), qs * (ch ? ks.w : ks.y)};   // this thread's two 16-key groups
+      float tmax = -CUDART_INF_F;
       if (active) {
+        // partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253), then the row's
+        float part = -CUDART_INF_F;
+        if (ok) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t a[16];
-          tmem_ld16(s_addr + 16 * cc, a);
-          tmem_ld_wait();
-          int mxi = INT_MIN;
-          if (diag) {
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t a[16];   // 12582912 + score as float bits
+            tmem_ld16(s_addr + 16 * cc, a);
+            tmem_ld_wait();
+            float m = 0.f;   // below every biased score
+            if (diag) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) if (!dead(key0 + 16 * cc + j)) mxi = max(mxi, (int)a[j]);
-          } else {
+              for (int j = 0; j < 16; ++j) if (!dead(key0 + 16 * cc + j)) m = fmaxf(m, __uint_as_float(a[j]));
+            } else {
+              m = __uint_as_float(a[0]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) mxi = max(mxi, (int)a[j]);
+              for (int j = 1; j < 15; j += 2) m = fmax3(m, __uint_as_float(a[j]), __uint_as_float(a[j + 1]));
+              m = fmaxf(m, __uint_as_float(a[15]));
+            }
+            if (m > 0.f) part = fmaxf(part, slope[cc] * (m - 12582912.f));
           }
-          if (mxi != INT_MIN) part = fmaxf(part, slope[cc] * (float)mxi);
+        }
+        xchg[x][sb][ch][row] = part;
+        pair_sync(pair_id);
+        tmax = fmaxf(xchg[x][sb][0][row], xchg[x][sb][1][row]);
+      }
+      if (ok && active) {
+        // move the row's reference exponent when this tile towers over it, and rescale what O holds
+        const bool move = tmax > ref + RefSlack;
+        float factor = 1.f;
+        if (move) {
+          factor = ref > -FLT_MAX ? exp2f(ref - tmax) : 0.f;
+          ref = tmax;
+          denom *= factor;
+        }
+        if (n > 0 && __any_sync(0xffffffffu, move)) {
+          ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1));
+          if (ok) {
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[16];
+              const uint32_t o_addr = lane_base + TmemO + x * 128 + 64 * ch + 16 * c;
+              tmem_ld16(o_addr, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+              tmem_st16(o_addr, o);
+            }
+          }
         }
       }
-      xchg[x][n & 1][ch][row] = part;
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cta(&bars.pair[x][quad]);
-      if (!(ok = wait(&bars.pair[x][quad], n))) break;
-      const float tmax = fmaxf(xchg[x][n & 1][0][row], xchg[x][n & 1][1][row]);
-
-      // move the row's reference exponent when this tile towers over it, and rescale what O holds
-      const bool move = active && tmax > ref + RefSlack;
-      float factor = 1.f;
-      if (move) {
-        factor = ref > -FLT_MAX ? exp2f(ref - tmax) : 0.f;
-        ref = tmax;
-        denom *= factor;
-      }
-      if (n > 0 && __any_sync(0xffffffffu, move)) {
-        if (!(ok = wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1))) break;
-        tc_fence_after();
+      if (ok && n >= 2) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][sb], (n - 2) >> 1));   // P buffer sb is free again
+      if (ok && !active) {
+        tmem_fill16(s_addr, bias);        // the QK^T MMA accumulated on this half's rows too
+        tmem_fill16(s_addr + 16, bias);
+        if (!((zero_rows >> sb) & 1)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t a[16];
-          const uint32_t o_addr = lane_base + TmemO + x * 128 + 64 * ch + 16 * c;
-          tmem_ld16(o_addr, a);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) * factor);
-          tmem_st16(o_addr, a);
+          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(prow + c * 128) = make_uint4(0u, 0u, 0u, 0u);
+          zero_rows |= 1 << sb;
         }
-        tmem_st_wait();
-      }
-      if (n >= 2 && !(ok = wait(&bars.o_done[x][sb], (n - 2) >> 1))) break;   // P buffer sb is free again
-
-      uint8_t* prow = smem + SmP + (2 * x + sb) * 16384 + (row / 8) * 1024 + (row % 8) * 16;   // core matrices [row/8][key/8]
-      if (!active) {
-        if (!zero_rows[sb]) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(prow + (4 * ch + c) * 128) = make_uint4(0u, 0u, 0u, 0u);
-          zero_rows[sb] = true;
-        }
-      } else if (mode == ModeF16) {
-        zero_rows[sb] = false;
+      } else if (ok && mode == ModeF16) {
+        zero_rows &= ~(1 << sb);
         float sum = 0.f;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t a[16];
           tmem_ld16(s_addr + 16 * cc, a);
           tmem_ld_wait();
+          tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
           const float off = fmaf(-slope[cc], 12582912.f, PShift - ref);
           uint32_t w[8];
 #pragma unroll
@@ -321,21 +375,21 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             float e[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              e[u] = exp2f(fmaf(slope[cc], __int_as_float((int)a[j + u] + Magic), off));
+              e[u] = exp2f(fmaf(slope[cc], __uint_as_float(a[j + u]), off));
               if (diag && dead(key0 + 16 * cc + j + u)) e[u] = 0.f;
             }
             const __half2 hp = __floats2half2_rn(e[0], e[1]);
             sum += __low2float(hp) + __high2float(hp);
             w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
           }
-          *reinterpret_cast<uint4*>(prow + (4 * ch + 2 * cc) * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(prow + (4 * ch + 2 * cc + 1) * 128) = make_uint4(w[4], w[5], w[6], w[7]);
+          *reinterpret_cast<uint4*>(prow + (2 * cc) * 128) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(prow + (2 * cc + 1) * 128) = make_uint4(w[4], w[5], w[6], w[7]);
         }
         denom += sum;
-      } else {
+      } else if (ok) {
         // prefill_sm80.cu:386-414: u8 codes of 2^(score - base); band tiles are never masked
-        zero_rows[sb] = false;
-        const float ks_max = fmaxf(fmaxf(ks[0], ks[1]), fmaxf(ks[2], ks[3]));
+        zero_rows &= ~(1 << sb);
+        const float ks_max = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
         float base = tmax;
         base += tile_base_margin(qs * ks_max, base);
         // weight of one code step, rounded to fp16 once: numerator (tensor core) and denominator use the same value
@@ -344,72 +398,80 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         int rs = 0;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
+          // The code is byte 1 of fma(2^x, 255, 2^15 + ... + 0.5) exactly as in the reference (prefill_sm80.cu:78-88);
+          // this constant of the same binade also leaves 0x64 in byte 2, so that bytes 1-2 of the word are the
+          // fp16 number 1024 + code.
+          // Eight keys at a time (one 16-byte run of the P operand) to keep the live registers low.
           uint32_t a[16];
           tmem_ld16(s_addr + 16 * cc, a);
           tmem_ld_wait();
-          uint32_t w[16];
-          if (mode == ModeQ4) {
-            // (float)acc without the conversion unit: exact for |acc| < 2^22
+          tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
+          const float off = mode == ModeQ4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              w[j] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], __int_as_float((int)a[j] + Magic) - 12582912.f, -base)), 255.f, PMagicHalf));
-          } else {
-            const float off = fmaf(-slope[cc], 12582912.f, -base);
+          for (int hb = 0; hb < 2; ++hb) {
+            uint32_t w[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              w[j] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], __int_as_float((int)a[j] + Magic), off)), 255.f, PMagicHalf));
+            for (int u = 0; u < 8; ++u) {
+              const int j = 4 * hb + (u & 3) + 8 * (u >> 2);
+              const float sc = __uint_as_float(a[j]);
+              // INT4 scores: (float)acc, exact for |acc| < 2^22, then one rounding like the reference's conversion
+              const float arg = mode == ModeQ4 ? fmaf(slope[cc], sc - 12582912.f, off) : fmaf(slope[cc], sc, off);
+              w[u] = __float_as_uint(fmaf(exp2f(arg), 255.f, PMagic64));
+            }
+            // positions 4s..4s+3 of a 16-key run hold keys kperm(s, 0..3), like the V8 blob
+            const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[4], w[5], 0x6521);   // (1024 + code) x 2 as fp16
+            const uint32_t h2 = __byte_perm(w[2], w[3], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
+            rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
+            rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
+            rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);
+            rs = (int)__dp4a(h3, 0x00010001u, (uint32_t)rs);
+            const __half2 p0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), s2, nb2);   // (1024 + code) * s - 1024 * s
+            const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), s2, nb2);
+            const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), s2, nb2);
+            const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), s2, nb2);
+            *reinterpret_cast<uint4*>(prow + (2 * cc + hb) * 128) =
+                make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                           *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
           }
-          uint32_t hw[8];
-#pragma unroll
-          for (int sidx = 0; sidx < 4; ++sidx) {   // positions 4s..4s+3 of the run hold keys kperm(s, 0..3), like the V8 blob
-            const uint32_t pw = pack_bytes(w[2 * sidx], w[2 * sidx + 1], w[2 * sidx + 8], w[2 * sidx + 9]);
-            rs = (int)__dp4a(pw, 0x01010101u, (uint32_t)rs);
-            const uint32_t lo = __byte_perm(pw, 0x64646464u, 0x4140), hi = __byte_perm(pw, 0x64646464u, 0x4342);
-            const __half2 pl = __hfma2(*reinterpret_cast<const __half2*>(&lo), s2, nb2);   // (1024 + code) * s - 1024 * s
-            const __half2 ph = __hfma2(*reinterpret_cast<const __half2*>(&hi), s2, nb2);
-            hw[2 * sidx] = *reinterpret_cast<const uint32_t*>(&pl);
-            hw[2 * sidx + 1] = *reinterpret_cast<const uint32_t*>(&ph);
-          }
-          *reinterpret_cast<uint4*>(prow + (4 * ch + 2 * cc) * 128) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-          *reinterpret_cast<uint4*>(prow + (4 * ch + 2 * cc + 1) * 128) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
         }
         denom = fmaf((float)rs, __half2float(sh), denom);
       }
-      fence_proxy_async_smem();   // P (generic-proxy stores) must be visible to the tensor core's async proxy
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cta(&bars.p_full[x][sb]);
+      if (ok) {
+        tmem_st_wait();
+        fence_proxy_async_smem();   // P (generic-proxy stores) must be visible to the tensor core's async proxy
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(&bars.p_full[x][sb]);
+      }
       ++n;
     }
 
     // ---- epilogue: O / denominator, de-normalised (prefill_sm80.cu:466-487) ----------------------------
-    if (ok && n > 0) ok = wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1);
-    if (ok && n > 0) {
-      tc_fence_after();
+    if (n > 0) {
+      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1));
       xchg[x][n & 1][ch][row] = denom;
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cta(&bars.pair[x][quad]);
-      ok = wait(&bars.pair[x][quad], n);
-    }
-    if (ok && n > 0) {
-      const float total = xchg[x][n & 1][0][row] + xchg[x][n & 1][1][row];
-      const float inv = total > 0.f ? 1.f / total : 0.f;
-      const float* mean = vstat + kvunit * StatFloats + 64 * ch;
-      const float* scale = mean + D;
-      Out* dst = out + b * osb + h * osh + (int64_t)qi * ost + 64 * ch;
+      pair_sync(pair_id);
+      if (ok) {
+        tc_fence_after();
+        const float total = xchg[x][n & 1][0][row] + xchg[x][n & 1][1][row];
+        const float inv = total > 0.f ? 1.f / total : 0.f;
+        const float* mean = vstat + kvunit * StatFloats + 64 * ch;
+        const float* scale = mean + D;
+        Out* dst = out + b * osb + h * osh + (int64_t)qi * ost + 64 * ch;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t a[16];
-        tmem_ld16(lane_base + TmemO + x * 128 + 64 * ch + 16 * c, a);
-        tmem_ld_wait();
-        if (row_valid) {
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld16(lane_base + TmemO + x * 128 + 64 * ch + 16 * c, o);
+          tmem_ld_wait();
+          if (row_valid) {
 #pragma unroll
-          for (int v = 0; v < 2; ++v) {
-            Out vals[8];
+            for (int v = 0; v < 2; ++v) {
+              Out vals[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              vals[j] = to_out<Out>(fmaf(__uint_as_float(a[8 * v + j]) * inv, __ldg(scale + 16 * c + 8 * v + j), __ldg(mean + 16 * c + 8 * v + j)));
-            *reinterpret_cast<uint4*>(dst + 16 * c + 8 * v) = *reinterpret_cast<const uint4*>(vals);
+              for (int j = 0; j < 8; ++j)
+                vals[j] = to_out<Out>(fmaf(__uint_as_float(o[8 * v + j]) * inv, __ldg(scale + 16 * c + 8 * v + j), __ldg(mean + 16 * c + 8 * v + j)));
+              *reinterpret_cast<uint4*>(dst + 16 * c + 8 * v) = *reinterpret_cast<const uint4*>(vals);
+            }
           }
         }
       }
