@@ -396,44 +396,47 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         const __half sh = __float2half_rn(exp2f(base - ref + PShift) * (1.f / 255.f));
         const __half2 s2 = __half2half2(sh), nb2 = __half2half2(__hneg(__hmul(sh, __float2half(1024.f))));
         int rs = 0;
+        // The code is byte 1 of fma(2^x, 255, 2^15 + ... + 0.5) exactly as in the reference (prefill_sm80.cu:78-88);
+        // this constant of the same binade also leaves 0x64 in byte 2, so that bytes 1-2 of the word are the
+        // fp16 number 1024 + code.  Eight keys at a time (one 16-byte run of the P operand) to keep the live
+        // registers low.  The INT4 pass takes (float)acc (exact for |acc| < 2^22) and rounds once like the
+        // reference's conversion; the INT8 pass keeps the bias inside the fma like the reference does.
+        auto codes = [&](auto int4_pass) {
+          constexpr bool Int4 = decltype(int4_pass)::value;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          // The code is byte 1 of fma(2^x, 255, 2^15 + ... + 0.5) exactly as in the reference (prefill_sm80.cu:78-88);
-          // this constant of the same binade also leaves 0x64 in byte 2, so that bytes 1-2 of the word are the
-          // fp16 number 1024 + code.
-          // Eight keys at a time (one 16-byte run of the P operand) to keep the live registers low.
-          uint32_t a[16];
-          tmem_ld16(s_addr + 16 * cc, a);
-          tmem_ld_wait();
-          tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
-          const float off = mode == ModeQ4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t a[16];
+            tmem_ld16(s_addr + 16 * cc, a);
+            tmem_ld_wait();
+            tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
+            const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
 #pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            uint32_t w[8];
+            for (int hb = 0; hb < 2; ++hb) {
+              uint32_t w[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int j = 4 * hb + (u & 3) + 8 * (u >> 2);
-              const float sc = __uint_as_float(a[j]);
-              // INT4 scores: (float)acc, exact for |acc| < 2^22, then one rounding like the reference's conversion
-              const float arg = mode == ModeQ4 ? fmaf(slope[cc], sc - 12582912.f, off) : fmaf(slope[cc], sc, off);
-              w[u] = __float_as_uint(fmaf(exp2f(arg), 255.f, PMagic64));
+              for (int u = 0; u < 8; ++u) {
+                const int j = 4 * hb + (u & 3) + 8 * (u >> 2);
+                const float sc = Int4 ? __uint_as_float(a[j]) - 12582912.f : __uint_as_float(a[j]);
+                w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
+              }
+              // positions 4s..4s+3 of a 16-key run hold keys kperm(s, 0..3), like the V8 blob
+              const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[4], w[5], 0x6521);   // (1024 + code) x 2 as fp16
+              const uint32_t h2 = __byte_perm(w[2], w[3], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
+              rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
+              rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
+              rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);
+              rs = (int)__dp4a(h3, 0x00010001u, (uint32_t)rs);
+              const __half2 p0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), s2, nb2);   // (1024 + code) * s - 1024 * s
+              const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), s2, nb2);
+              const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), s2, nb2);
+              const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), s2, nb2);
+              *reinterpret_cast<uint4*>(prow + (2 * cc + hb) * 128) =
+                  make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                             *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
             }
-            // positions 4s..4s+3 of a 16-key run hold keys kperm(s, 0..3), like the V8 blob
-            const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[4], w[5], 0x6521);   // (1024 + code) x 2 as fp16
-            const uint32_t h2 = __byte_perm(w[2], w[3], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
-            rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
-            rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
-            rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);
-            rs = (int)__dp4a(h3, 0x00010001u, (uint32_t)rs);
-            const __half2 p0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), s2, nb2);   // (1024 + code) * s - 1024 * s
-            const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), s2, nb2);
-            const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), s2, nb2);
-            const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), s2, nb2);
-            *reinterpret_cast<uint4*>(prow + (2 * cc + hb) * 128) =
-                make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
-                           *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
           }
-        }
+        };
+        if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
         denom = fmaf((float)rs, __half2float(sh), denom);
       }
       if (ok) {
