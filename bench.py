@@ -259,10 +259,70 @@ def run_prefill(args):
                           clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))))
 
 
+def run_model(args):
+    """Secondary metric: BASELINE config 4 end to end.  Random-init Llama-3.2-3B architecture (28 layers, hidden 3072,
+    24 / 8 heads, head_dim 128, intermediate 8192 as in the public 3B configuration, vocab 128256), bf16 weights
+    ~ N(0, 0.02); batch x prompt token ids uniform from a seed; greedy new tokens; per-layer seeded map of 5 INT8 /
+    2 INT4 / 1 BF16 KV heads.  Prints tokens/s of the prompt pass and of the decode loop, layer-by-layer from Python
+    and with the decode step captured in a CUDA graph."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from triattention_b200.maps import INF, from_bands
+    from triattention_b200.models import TriAttention
+    torch.cuda.set_device(0)
+    batch = args.batch if args.batch != CONFIG["batch"] else 16
+    prompt, new, layers, hq, hk = args.tokens if args.tokens != 16384 else 4096, args.new_tokens, 28, 24, 8
+    cfg = LlamaConfig(hidden_size=3072, intermediate_size=8192, num_hidden_layers=layers, num_attention_heads=hq,
+                      num_key_value_heads=hk, head_dim=128, vocab_size=128256, max_position_embeddings=prompt + new + 8,
+                      rope_theta=500000.0, tie_word_embeddings=True)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    for prm in model.parameters():
+        prm.data.normal_(0.0, 0.02, generator=None)
+    rng = np.random.default_rng(2)
+    bands, bf16 = {}, {}
+    for layer in range(layers):
+        kinds = rng.permutation(np.array(["int8"] * 5 + ["int4"] * 2 + ["bf16"]))
+        bands[str(layer)] = [[1, INF] if kind == "int4" else [INF, INF] for kind in kinds for _ in range(hq // hk)]
+        bf16[str(layer)] = [i for i, kind in enumerate(kinds) if kind == "bf16"]
+    engine = TriAttention(model, from_bands(bands, model, bf16), max_new_tokens=new + 1)
+    ids = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=torch.Generator().manual_seed(1)).cuda()
+
+    def timed_generate(graph):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        with torch.inference_mode():
+            model(input_ids=ids, use_cache=False, logits_to_keep=1)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        rows = engine.generate(ids, new, eos=(), cuda_graph=graph)   # runs the prompt pass again, then the decode loop
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        assert len(rows) == batch and all(len(r) == new for r in (rows if batch > 1 else [rows]))
+        prefill_s = t1 - t0
+        return prefill_s, (t2 - t1) - prefill_s
+
+    timed_generate(False)   # warm-up (library handles, caches, clocks)
+    with ClockSampler(0) as clocks:
+        prefill_s, eager_s = timed_generate(False)
+        _, graph_s = timed_generate(True)
+    engine.module.check_device_error()
+    print(json.dumps(dict(metric="generate_tokens_per_s", value=batch * (new - 1) / graph_s, unit="tokens/s", n_gpus=1,
+                          higher_is_better=True, dtype="bf16 model, int8 / int4 / bf16 KV cache", data="synthetic",
+                          config=dict(workload=f"end to end C4: random-init Llama-3.2-3B architecture, batch {batch} x {prompt} prompt "
+                                               f"tokens, {new} greedy new tokens, per-layer map 5 INT8 / 2 INT4 / 1 BF16 KV heads"),
+                          prompt_tokens_per_s=batch * prompt / prefill_s, prompt_pass_s=prefill_s,
+                          decode_tokens_per_s_cuda_graph=batch * (new - 1) / graph_s,
+                          decode_tokens_per_s_layer_by_layer=batch * (new - 1) / eager_s,
+                          decode_loop_s=dict(cuda_graph=graph_s, layer_by_layer=eager_s), clocks=clocks.summary())))
+
+
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                        help="decode = the benchmark contract (BASELINE config 2); prefill = config 3, secondary metric")
+    parser.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+                        help="decode = the benchmark contract (BASELINE config 2); prefill = config 3, secondary metric; "
+                             "model = config 4 end to end through the Hugging Face hook, secondary metric")
+    parser.add_argument("--new-tokens", type=int, default=128, help="greedy new tokens of the model workload")
     parser.add_argument("--tokens", type=int, default=16384, help="prompt length of the prefill workload")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
@@ -283,6 +343,10 @@ def main():
     if args.workload == "prefill":
         if rank == 0:
             run_prefill(args)
+        return
+    if args.workload == "model":
+        if rank == 0:
+            run_model(args)
         return
     torch.cuda.set_device(local)
     dist = None

@@ -55,3 +55,18 @@ def test_generate_batched_and_single():
     assert isinstance(single, list) and len(single) == 6 and all(isinstance(t, int) for t in single)
     stop = engine.generate(ids[:1], 6, eos={single[2]})
     assert stop == single[:single.index(single[2])]
+
+
+@torch.inference_mode()
+def test_generate_cuda_graph_matches_eager():
+    """One captured decode step replayed per token gives the same tokens as the layer-by-layer loop."""
+    from triattention_b200.maps import per_kv_head
+    from triattention_b200.models import TriAttention
+    model = tiny_llama()
+    engine = TriAttention(model, per_kv_head(["int8", "int4"], 2), max_new_tokens=12)
+    ids = torch.randint(0, 1024, (3, 150), generator=torch.Generator().manual_seed(5)).cuda()
+    eager = engine.generate(ids, 12, eos=())
+    graph = engine.generate(ids, 12, eos=(), cuda_graph=True)
+    assert graph == eager
+    stop = eager[0][4]
+    assert engine.generate(ids, 12, eos={stop}, cuda_graph=True) == engine.generate(ids, 12, eos={stop})

@@ -76,22 +76,59 @@ class TriAttention:
         use_attention(model, "triattention", attention)
 
     @torch.inference_mode()
-    def generate(self, ids, max_new_tokens, eos=()):
+    def generate(self, ids, max_new_tokens, eos=(), cuda_graph=False):
+        """Greedy decoding (models.py:72-85 of the reference, batched).  cuda_graph=True captures one decode step of
+        the whole model (every layer's projections, the two decode launches per layer, argmax, position and step
+        counters) in a CUDA graph and replays it per token: the reference launches layer by layer from Python and
+        synchronises with the host for every token."""
         batch, device = ids.shape[0], ids.device
         out = self.model(input_ids=ids, use_cache=False, logits_to_keep=1)
         eos_t = torch.tensor(sorted(eos), dtype=torch.long, device=device)
         alive = torch.ones(batch, dtype=torch.bool, device=device)
         history = []
+        token = out.logits[:, -1].argmax(-1)
+        replay = None
+        if cuda_graph and max_new_tokens > 1:
+            tok = token[:, None].clone()
+            pos = torch.full((batch, 1), ids.shape[1], device=device)
+
+            def step():
+                logits = self.model(input_ids=tok, position_ids=pos, use_cache=False).logits
+                tok.copy_(logits[:, -1].argmax(-1)[:, None])
+                pos.add_(1)
+                self.decode_cache.advance()
+
+            # One eager run on a side stream first (library workspaces, lazy initialisation).  It appends this token's
+            # K / V to the tails at the current step index, which the captured step then simply writes again; the
+            # counters it moved are put back.
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+                tok.copy_(token[:, None])
+                pos.sub_(1)
+                self.decode_cache.step.sub_(1)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            replay = graph.replay
         for i in range(max_new_tokens):
-            token = out.logits[:, -1].argmax(-1)
             if eos_t.numel():
                 alive &= ~torch.isin(token, eos_t)
                 if batch == 1 and not bool(alive[0]):
                     break
             history.append(torch.where(alive, token, torch.full_like(token, -1)))
-            position = torch.full((batch, 1), ids.shape[1] + i, device=device)
-            out = self.model(input_ids=token[:, None], position_ids=position, use_cache=False)
-            self.decode_cache.advance()
+            if i + 1 == max_new_tokens:
+                break
+            if replay is not None:
+                replay()
+                token = tok[:, 0].clone()
+            else:
+                position = torch.full((batch, 1), ids.shape[1] + i, device=device)
+                out = self.model(input_ids=token[:, None], position_ids=position, use_cache=False)
+                self.decode_cache.advance()
+                token = out.logits[:, -1].argmax(-1)
         self.module.check_device_error(device)
         if not history:
             return [] if batch == 1 else [[] for _ in range(batch)]
