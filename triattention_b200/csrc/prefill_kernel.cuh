@@ -302,20 +302,21 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         // partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253), then the row's
         float part = -CUDART_INF_F;
         if (ok) {
+          uint32_t a[2][16];   // 12582912 + score as float bits
+          tmem_ld16(s_addr, a[0]);
+          tmem_ld16(s_addr + 16, a[1]);
+          tmem_ld_wait();
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
-            uint32_t a[16];   // 12582912 + score as float bits
-            tmem_ld16(s_addr + 16 * cc, a);
-            tmem_ld_wait();
             float m = 0.f;   // below every biased score
             if (diag) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) if (!dead(key0 + 16 * cc + j)) m = fmaxf(m, __uint_as_float(a[j]));
+              for (int j = 0; j < 16; ++j) if (!dead(key0 + 16 * cc + j)) m = fmaxf(m, __uint_as_float(a[cc][j]));
             } else {
-              m = __uint_as_float(a[0]);
+              m = __uint_as_float(a[cc][0]);
 #pragma unroll
-              for (int j = 1; j < 15; j += 2) m = fmax3(m, __uint_as_float(a[j]), __uint_as_float(a[j + 1]));
-              m = fmaxf(m, __uint_as_float(a[15]));
+              for (int j = 1; j < 15; j += 2) m = fmax3(m, __uint_as_float(a[cc][j]), __uint_as_float(a[cc][j + 1]));
+              m = fmaxf(m, __uint_as_float(a[cc][15]));
             }
             if (m > 0.f) part = fmaxf(part, slope[cc] * (m - 12582912.f));
           }
@@ -350,7 +351,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           }
         }
       }
-      if (ok && n >= 2) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][sb], (n - 2) >> 1));   // P buffer sb is free again
+      // P buffer sb was last read by the P.V of this tile's step n-2.  The issuer put that P.V on the tensor pipe
+      // before the QK^T of step n, the pipe completes in issue order, and the scores of step n have been seen
+      // above: the buffer is free, no wait needed.
       if (ok && !active) {
         tmem_fill16(s_addr, bias);        // the QK^T MMA accumulated on this half's rows too
         tmem_fill16(s_addr + 16, bias);
