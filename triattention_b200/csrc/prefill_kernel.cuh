@@ -392,6 +392,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       } else if (ok) {
         // prefill_sm80.cu:386-414: u8 codes of 2^(score - base); band tiles are never masked
         zero_rows &= ~(1 << sb);
+        uint32_t a[2][16];   // the scores again (in flight while the tile's base and weight scale are computed)
+        tmem_ld16(s_addr, a[0]);
+        tmem_ld16(s_addr + 16, a[1]);
         const float ks_max = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
         float base = tmax;
         base += tile_base_margin(qs * ks_max, base);
@@ -406,12 +409,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         // reference's conversion; the INT8 pass keeps the bias inside the fma like the reference does.
         auto codes = [&](auto int4_pass) {
           constexpr bool Int4 = decltype(int4_pass)::value;
+          tmem_ld_wait();
+          tmem_fill16(s_addr, bias);        // ready for the QK^T of two steps ahead
+          tmem_fill16(s_addr + 16, bias);
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
-            uint32_t a[16];
-            tmem_ld16(s_addr + 16 * cc, a);
-            tmem_ld_wait();
-            tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
                 const int j = 4 * hb + (u & 3) + 8 * (u >> 2);
-                const float sc = Int4 ? __uint_as_float(a[j]) - 12582912.f : __uint_as_float(a[j]);
+                const float sc = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
                 w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
               }
               // positions 4s..4s+3 of a 16-key run hold keys kperm(s, 0..3), like the V8 blob
