@@ -1,7 +1,7 @@
 """Record golden vectors from the reference's own CUDA extension (oracle/_ref) on a B200.
 
 Run on the GPU box from the repository root:
-    python tests/golden/make_golden.py gpurun_out/golden
+    python tests/golden/make_golden.py <output directory>
 and copy the produced ``*.npz`` into ``tests/golden/``.  Inputs are regenerated from seeds by
 ``triattention_oracle.synth`` (numpy, deterministic), so only the reference's outputs are stored.
 """
@@ -81,4 +81,4 @@ def main(out_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    main(sys.argv[1] if len(sys.argv) > 1 else "golden_out")
