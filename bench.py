@@ -243,6 +243,10 @@ def run_prefill(args):
             torch.cuda.synchronize()
             extra += 1
     module.check_device_error()
+    # KV-write traffic: Q once, K and V twice (statistics pass + quantising pass), every operand buffer written once
+    _, written = pre.write(0, q, k, v)
+    write_bytes = q.nbytes + 2 * k.nbytes + 2 * v.nbytes + sum(x.nbytes for name, x in written.items()
+                                                                 if x is not None and name != "partial")
     rows = (t + 63) // 64
     ops = b * hq * (rows * (rows + 1) // 2) * 2 * 64 * 64 * 128 * 2
     tops = ops / ((ms_all - ms_write) / 1e3) / 1e12
@@ -255,7 +259,8 @@ def run_prefill(args):
                                         kernel="prefill_kernel", ms_per_launch=ms_all - ms_write, ops_per_launch=ops,
                                         peak_source="nominal dense INT8 (2 x bf16 nominal); no measured INT8 peak in MEASURED_PEAKS.json",
                                         traffic=None),
-                          kv_write_ms=ms_write,
+                          kv_write_ms=ms_write, kv_write_bytes=write_bytes, kv_write_gbs=write_bytes / (ms_write / 1e3) / 1e9,
+                          kv_write_frac_of_measured_hbm=write_bytes / (ms_write / 1e3) / 1e9 / peak_hbm()[0],
                           clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))))
 
 

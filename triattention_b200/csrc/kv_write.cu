@@ -92,15 +92,20 @@ __device__ __forceinline__ void load16_bf16(const __nv_bfloat16* src, float (&x)
     x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+// rn_even(p) & 0xff for |p| < 2^22 without the conversion unit: p + 12582912.0f rounds p to an integer exactly like
+// cvt.rni (one rounding, ties to even), and the low byte of the sum's bit pattern is the two's-complement code.
+__device__ __forceinline__ uint32_t rn_bits(float p) { return __float_as_uint(__fadd_rn(p, 12582912.f)); }
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+  return __byte_perm(__byte_perm(w0, w1, 0x0040), __byte_perm(w2, w3, 0x0040), 0x5410);
+}
+// 16 codes rn_even(x * inv) as bytes: the product is rounded to fp32 first (a separate multiply, as in the
+// reference's __float2int_rn(x * inv), common_device.cuh:14), then to an integer.
 __device__ __forceinline__ uint4 codes16(const float (&x)[16], float inv) {
   uint32_t w[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) word |= (uint32_t)(__float2int_rn(x[4 * j + b] * inv) & 0xff) << (8 * b);
-    w[j] = word;
-  }
+  for (int j = 0; j < 4; ++j)
+    w[j] = pack_low_bytes(rn_bits(__fmul_rn(x[4 * j], inv)), rn_bits(__fmul_rn(x[4 * j + 1], inv)),
+                          rn_bits(__fmul_rn(x[4 * j + 2], inv)), rn_bits(__fmul_rn(x[4 * j + 3], inv)));
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
@@ -234,9 +239,10 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
       const int ch = (i / 64) * 8 + i % 8, k8b = (i / 8) % 8;
       uint32_t w[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        w[j] = (uint32_t)__half_as_ushort(__float2half_rn(vn[k8b * 8 + 2 * j][ch])) |
-               ((uint32_t)__half_as_ushort(__float2half_rn(vn[k8b * 8 + 2 * j + 1][ch])) << 16);
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h = __floats2half2_rn(vn[k8b * 8 + 2 * j][ch], vn[k8b * 8 + 2 * j + 1][ch]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
       *reinterpret_cast<uint4*>(v16 + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
@@ -245,14 +251,11 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
       const int ch = (i / 32) * 8 + i % 8, blk = (i / 8) % 4;
       uint32_t w[4];
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        uint32_t word = 0;
+      for (int s = 0; s < 4; ++s) {   // clamp(rn(x)) == rn(clamp(x)): rounding is monotonic and the bounds are integers
+        uint32_t b4[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int qv = max(-127, min(127, __float2int_rn(vn[blk * 16 + kperm(s, b)][ch])));
-          word |= (uint32_t)(qv & 0xff) << (8 * b);
-        }
-        w[s] = word;
+        for (int b = 0; b < 4; ++b) b4[b] = rn_bits(fminf(fmaxf(vn[blk * 16 + kperm(s, b)][ch], -127.f), 127.f));
+        w[s] = pack_low_bytes(b4[0], b4[1], b4[2], b4[3]);
       }
       *reinterpret_cast<uint4*>(v8 + ht * V8Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -266,9 +269,9 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
       uint32_t word = 0;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        const int lo = max(-7, min(7, __float2int_rn(vn[kc * 32 + kperm(s, b)][ch] * (7.f / 127.f))));
-        const int hi = max(-7, min(7, __float2int_rn(vn[kc * 32 + 16 + kperm(s, b)][ch] * (7.f / 127.f))));
-        word |= (uint32_t)((lo & 0xf) | ((hi & 0xf) << 4)) << (8 * b);
+        const uint32_t lo = rn_bits(fminf(fmaxf(__fmul_rn(vn[kc * 32 + kperm(s, b)][ch], 7.f / 127.f), -7.f), 7.f));
+        const uint32_t hi = rn_bits(fminf(fmaxf(__fmul_rn(vn[kc * 32 + 16 + kperm(s, b)][ch], 7.f / 127.f), -7.f), 7.f));
+        word |= ((lo & 0xfu) | ((hi & 0xfu) << 4)) << (8 * b);
       }
       w[s] = word;
     }
