@@ -92,11 +92,11 @@ __device__ __forceinline__ void rotate128_x16(float (&x)[16], int l8) {
   }
 #pragma unroll
   for (int bit = 1; bit < 8; bit <<= 1) {
-    const bool upper = l8 & bit;
+    const float sign = (l8 & bit) ? -1.f : 1.f;   // upper lane: partner - own; lower lane: own + partner
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float y = __shfl_xor_sync(0xffffffffu, x[i], bit);
-      x[i] = upper ? y - x[i] : x[i] + y;
+      x[i] = fmaf(x[i], sign, y);                 // one rounding of y +- x, like the add / subtract it replaces
     }
   }
 #pragma unroll

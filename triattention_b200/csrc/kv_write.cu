@@ -42,7 +42,14 @@ __global__ void __launch_bounds__(D) stats_partial_kernel(const __nv_bfloat16* k
   }
   float sum = 0.f, hi = -FLT_MAX, lo = FLT_MAX;
   int t = blockIdx.x;
-  // loads are issued eight at a time; the adds stay sequential in token order
+  // loads are issued 32 at a time (the kernel is bound by their latency); the adds stay sequential in token order
+  for (; t + 31 * StatBlocks < tokens; t += 32 * StatBlocks) {
+    float x[32];
+#pragma unroll
+    for (int u = 0; u < 32; ++u) x[u] = __bfloat162float(base[(int64_t)(t + u * StatBlocks) * st]);
+#pragma unroll
+    for (int u = 0; u < 32; ++u) { sum += x[u]; hi = fmaxf(hi, x[u]); lo = fminf(lo, x[u]); }
+  }
   for (; t + 7 * StatBlocks < tokens; t += 8 * StatBlocks) {
     float x[8];
 #pragma unroll
@@ -70,8 +77,14 @@ __global__ void __launch_bounds__(D) stats_finalize_kernel(const float* partial_
   if (!(which == 1 && v_identity)) {
     const float* in = partial + unit * StatBlocks * 3 * D + c;
     float sum = 0.f, hi = -FLT_MAX, lo = FLT_MAX;
-    for (int b = 0; b < StatBlocks; ++b) {
-      sum += in[b * 3 * D]; hi = fmaxf(hi, in[b * 3 * D + D]); lo = fminf(lo, in[b * 3 * D + 2 * D]);
+    for (int b0 = 0; b0 < StatBlocks; b0 += 16) {   // 48 loads in flight; the sum stays sequential in block order
+      float ps[16], ph[16], pl[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        ps[u] = in[(b0 + u) * 3 * D]; ph[u] = in[(b0 + u) * 3 * D + D]; pl[u] = in[(b0 + u) * 3 * D + 2 * D];
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { sum += ps[u]; hi = fmaxf(hi, ph[u]); lo = fminf(lo, pl[u]); }
     }
     mean = sum / tokens;
     const float range = fmaxf(hi - mean, mean - lo);
