@@ -48,6 +48,15 @@ __device__ __forceinline__ void umma_f16(uint32_t d, uint64_t a, uint64_t b, uin
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {   // A in tensor memory
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
@@ -74,15 +83,14 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t cfmt, uint32_t afmt, 
 constexpr uint32_t LayoutNone = 0, Layout128B = 2;
 constexpr uint32_t IdescQK = instr_desc(2, 1, 1, 128, 64);    // s8 x s8 -> s32
 constexpr uint32_t IdescPV16 = instr_desc(1, 0, 0, 128, 128); // f16 x f16 -> f32
+// One fp16 MMA (M128 N64 K16) of constant operands, 16 products of 3072 * 256, writes 12582912.0f = 0x4B400000 into a
+// score buffer; the INT8 QK^T MMAs then accumulate on those bits, so a score read as a float is 12582912 + score.
+constexpr uint32_t IdescBias = instr_desc(1, 0, 0, 128, 64);
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
                  "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_fill16(uint32_t taddr, uint32_t v) {   // 16 columns of this warp's 32 lanes = v
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
-               ::"r"(taddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -90,8 +98,9 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 constexpr int PrefillThreads = 640;   // producer, issuer, 2 widening warps, 16 softmax warps
 constexpr int ProbeThreads = 128;
 constexpr int MaxSteps = 2 * MaxTiles + 8;
-constexpr int SmQ8 = 0, SmQ4 = 32768, SmP = 65536;              // 2 Q tiles each; P: [tile][buffer] x 16 KB fp16
-constexpr int SmK = SmP + 4 * 16384, SmV8 = SmK + 4 * K8Bytes;   // four stages of K, two of raw V
+constexpr int SmQ8 = 0, SmQ4 = 32768;                            // 2 Q tiles each
+constexpr int SmBiasA = 65536, SmBiasB = SmBiasA + 4096;         // constant fp16 operands of the bias MMA (see IdescBias)
+constexpr int SmK = SmBiasB + 2048 + 2048, SmV8 = SmK + 4 * K8Bytes;   // four stages of K (1024-byte aligned), two of raw V
 constexpr int SmV16 = SmV8 + 2 * V8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
 constexpr int SmSteps = SmEnd, StepBytes = (3 * MaxSteps + 15) / 16 * 16;  // visiting order: uint16 tile|mode, uint8 mask
 constexpr int PrefillShared = SmSteps + StepBytes + 1024;       // + slack to align the base to 1024 bytes

@@ -13,10 +13,16 @@
 //                 Four softmax warps per scheduler are what it takes to keep the exponential unit busy:
 //                 one warp alone issues an ex2 every ~15 cycles, the unit takes one every ~8.
 //
-// Integer scores are read as floats without a conversion: the score accumulators in TMEM are preset to
-// 0x4B400000 (the bits of 12582912.0f, the bias the reference adds in registers, prefill_sm80.cu:27) by the
-// softmax threads, the QK^T MMAs accumulate on top, and for |score| < 2^22 the result read as a float IS
-// 12582912 + score.  Row maxima are taken on those floats with the three-input max.
+// Integer scores are read as floats without a conversion: before the INT8 MMAs of a step the issuer presets the
+// score buffer to 0x4B400000 (the bits of 12582912.0f, the bias the reference adds in registers,
+// prefill_sm80.cu:27) with one fp16 MMA of constant operands, the QK^T MMAs accumulate on top, and for
+// |score| < 2^22 the result read as a float IS 12582912 + score.  Row maxima are taken on those floats with the
+// three-input max.
+//
+// P never touches shared memory: a softmax thread writes its fp16 weights over the first half of its own 32
+// score columns (tcgen05.st) once it has read them, and the P.V MMAs take their A operand from tensor memory.
+// The tensor pipe completes in issue order, so the bias MMA of two steps later overwrites P only after P.V
+// has used it.  With A in tensor memory an M128 N128 K16 MMA takes 65 cycles instead of 108 (measured).
 //
 // Per step (one 64-key tile) and MMA tile:
 //   S[128x64]  = Q8 . K8^T            4 x kind::i8 (M128 N64 K32), s32 accumulators (bit-equal to the reference's)
@@ -45,8 +51,7 @@ struct PrefillBarriers {
   uint64_t v16_full[2];     // fp16 V operand ready: two widening warps, or TMA of the fp16 blob + one plain arrive
   uint64_t v16_empty[2];    // all P.V of the step done
   uint64_t s_full[2][2];    // [tile][buffer] scores in TMEM
-  uint64_t s_init;          // both score buffers of both tiles hold the bias (16 softmax warps)
-  uint64_t p_full[2][2];    // [tile][buffer] P operand written by the 8 softmax warps of the tile; score buffer re-biased
+  uint64_t p_full[2][2];    // [tile][buffer] P written over the score buffer by the 8 softmax warps of the tile
   uint64_t o_done[2][2];    // [tile][buffer] P.V of that P buffer done
 };
 
@@ -94,9 +99,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     step_tm[i] = (uint16_t)(tile | (mode << 12));
     step_mask[i] = (uint8_t)mask;
   }
+  for (int i = tid; i < (4096 + 2048) / 4; i += PrefillThreads)   // 3072.0 (0x6A00) for A, 256.0 (0x5C00) for B
+    reinterpret_cast<uint32_t*>(smem + SmBiasA)[i] = i < 1024 ? 0x6A006A00u : 0x5C005C00u;
+  fence_proxy_async_smem();
   if (tid == 0) {
     mbar_init(&bars.q, 1);
-    mbar_init(&bars.s_init, 16);
     for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&bars.v8_full[s], 1); mbar_init(&bars.v8_empty[s], 2); }
     for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 2); mbar_init(&bars.v16_empty[s], 1); }
@@ -150,7 +157,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     if (lane == 0) {
       // Descriptors are built once; per MMA only the 16-byte-unit address field (low word) moves.
       const uint64_t dq8 = smem_desc(smem_u32(smem + SmQ8), 0, 1024, Layout128B), dq4 = smem_desc(smem_u32(smem + SmQ4), 0, 1024, Layout128B);
-      const uint64_t dk = smem_desc(smem_u32(smem + SmK), 128, 1024, LayoutNone), dp = smem_desc(smem_u32(smem + SmP), 128, 1024, LayoutNone);
+      const uint64_t dk = smem_desc(smem_u32(smem + SmK), 128, 1024, LayoutNone);
+      const uint64_t dba = smem_desc(smem_u32(smem + SmBiasA), 128, 256, LayoutNone), dbb = smem_desc(smem_u32(smem + SmBiasB), 128, 256, LayoutNone);
       const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
       auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };   // stays inside the 14-bit field
       // Order on the tensor pipe per step i: QK^T of step i+1 for both tiles (into the score buffers that the softmax
@@ -163,13 +171,15 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         const uint64_t dqm = mode == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
         if (mask & 3) {
           const int sb = nqk0 & 1;
+          umma_f16(tmem + TmemS + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);   // on top of the bias
+          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
           tc_commit(&bars.s_full[0][sb]);
           ++nqk0;
         }
         if (mask & 12) {
           const int sb = nqk1 & 1;
+          umma_f16(tmem + TmemS + 128 + sb * 64, dba, dbb, IdescBias, 0u);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + 128 + sb * 64, at(dqm, 16384 + kk * 32), at(dks, kk * 256), IdescQK, 1u);
           tc_commit(&bars.s_full[1][sb]);
@@ -178,7 +188,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         tc_commit(&bars.k_empty[s]);
         return true;
       };
-      bool ok = wait(&bars.q, 0) && wait(&bars.s_init, 0) && issue_qk(0);
+      bool ok = wait(&bars.q, 0) && issue_qk(0);
       for (int i = 0; ok && i < nsteps; ++i) {
         if (i + 1 < nsteps && !issue_qk(i + 1)) break;   // the next scores are computed while this step's softmax runs
         const int mask = step_mask[i], vb = i & 1;
@@ -188,9 +198,12 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           const int pb = npv0 & 1;
           if (!wait(&bars.p_full[0][pb], npv0 >> 1)) break;
           tc_fence_after();
-          const uint64_t dps = at(dp, pb * 16384);
+          // P: key group kk (16 keys = 8 columns of fp16 pairs) sits in the first half of the 32 score columns of the
+          // thread that computed it: columns 0-15 (keys 0-31) and 32-47 (keys 32-63) of score buffer pb
+          const uint32_t pt = tmem + TmemS + pb * 64;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_f16(tmem + TmemO, at(dps, kk * 256), at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ts(tmem + TmemO, pt + (kk >> 1) * 32 + (kk & 1) * 8, at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&bars.o_done[0][pb]);
           ++npv0;
         }
@@ -198,9 +211,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           const int pb = npv1 & 1;
           if (!wait(&bars.p_full[1][pb], npv1 >> 1)) break;
           tc_fence_after();
-          const uint64_t dps = at(dp, (2 + pb) * 16384);
+          const uint32_t pt = tmem + TmemS + 128 + pb * 64;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_f16(tmem + TmemO + 128, at(dps, kk * 256), at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ts(tmem + TmemO + 128, pt + (kk >> 1) * 32 + (kk & 1) * 8, at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&bars.o_done[1][pb]);
           ++npv1;
         }
@@ -264,16 +278,6 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
     float ref = -FLT_MAX, denom = 0.f;   // reference exponent of the row; this thread's share of the denominator
     int n = 0;                           // steps of this tile so far
-    int zero_rows = 0;                   // bit b: this thread's part of its row of P buffer b is known to be zero
-    const uint32_t bias = (uint32_t)Magic;
-    // this thread's 32 columns of both score buffers start at the bias
-#pragma unroll
-    for (int c = 0; c < 4; ++c) tmem_fill16(lane_base + TmemS + x * 128 + (c >> 1) * 64 + 32 * ch + 16 * (c & 1), bias);
-    tmem_st_wait();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive_cta(&bars.s_init);
-
     int inext = 0;   // next step in which this tile takes part
     while (inext < nsteps && ((step_mask[inext] >> (2 * x)) & 3) == 0) ++inext;
     bool ok = true;
@@ -289,7 +293,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const int key0 = tile * BN + 32 * ch;
       const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 32 * ch;
       auto dead = [&](int key) { return key >= tokens || key > qi || qi >= tokens; };   // diagonal tile only
-      uint8_t* prow = smem + SmP + (2 * x + sb) * 16384 + (row / 8) * 1024 + (row % 8) * 16 + (4 * ch) * 128;   // core matrices [row/8][key/8]
+      // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, key order = the
+      // position order of the V operand
 
       if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1));
       if (ok) tc_fence_after();
@@ -355,22 +360,16 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       // before the QK^T of step n, the pipe completes in issue order, and the scores of step n have been seen
       // above: the buffer is free, no wait needed.
       if (ok && !active) {
-        tmem_fill16(s_addr, bias);        // the QK^T MMA accumulated on this half's rows too
-        tmem_fill16(s_addr + 16, bias);
-        if (!((zero_rows >> sb) & 1)) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(prow + c * 128) = make_uint4(0u, 0u, 0u, 0u);
-          zero_rows |= 1 << sb;
-        }
+        const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing to the tile's P.V
+        tmem_st8(s_addr, zero);
+        tmem_st8(s_addr + 8, zero);
       } else if (ok && mode == ModeF16) {
-        zero_rows &= ~(1 << sb);
         float sum = 0.f;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t a[16];
           tmem_ld16(s_addr + 16 * cc, a);
           tmem_ld_wait();
-          tmem_fill16(s_addr + 16 * cc, bias);   // ready for the QK^T of two steps ahead
           const float off = fmaf(-slope[cc], 12582912.f, PShift - ref);
           uint32_t w[8];
 #pragma unroll
@@ -385,13 +384,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             sum += __low2float(hp) + __high2float(hp);
             w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
           }
-          *reinterpret_cast<uint4*>(prow + (2 * cc) * 128) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(prow + (2 * cc + 1) * 128) = make_uint4(w[4], w[5], w[6], w[7]);
+          tmem_st8(s_addr + 8 * cc, w);
         }
         denom += sum;
       } else if (ok) {
         // prefill_sm80.cu:386-414: u8 codes of 2^(score - base); band tiles are never masked
-        zero_rows &= ~(1 << sb);
         uint32_t a[2][16];   // the scores again (in flight while the tile's base and weight scale are computed)
         tmem_ld16(s_addr, a[0]);
         tmem_ld16(s_addr + 16, a[1]);
@@ -410,11 +407,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         auto codes = [&](auto int4_pass) {
           constexpr bool Int4 = decltype(int4_pass)::value;
           tmem_ld_wait();
-          tmem_fill16(s_addr, bias);        // ready for the QK^T of two steps ahead
-          tmem_fill16(s_addr + 16, bias);
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
+            uint32_t pw[8];   // the 16 weights of this key group, two per word
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
               uint32_t w[8];
@@ -435,18 +431,17 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), s2, nb2);
               const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), s2, nb2);
               const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), s2, nb2);
-              *reinterpret_cast<uint4*>(prow + (2 * cc + hb) * 128) =
-                  make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
-                             *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
+              pw[4 * hb] = *reinterpret_cast<const uint32_t*>(&p0); pw[4 * hb + 1] = *reinterpret_cast<const uint32_t*>(&p1);
+              pw[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&p2); pw[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&p3);
             }
+            tmem_st8(s_addr + 8 * cc, pw);
           }
         };
         if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
         denom = fmaf((float)rs, __half2float(sh), denom);
       }
       if (ok) {
-        tmem_st_wait();
-        fence_proxy_async_smem();   // P (generic-proxy stores) must be visible to the tensor core's async proxy
+        tmem_st_wait();   // P is in tensor memory before the issuer is told
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cta(&bars.p_full[x][sb]);
