@@ -43,10 +43,12 @@ int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int hea
 /* Per-channel affine normalisation of V and packing into FP16 / INT8 / INT4 tile blobs.
  * Replaces pack_v(v,partial,vstat,v16p,v8p,v4p), triattention/kernels/cuda/common_host.cuh:27-45.
  * vstat f32 [B*Hkv,3,128] = (mean, scale, 1/scale); (0,1,1) when neither v8 nor v4 is requested.
- * v16 [B*Hkv,tiles,16384 B], v8 [..,8192 B], v4 [..,4096 B]; each may be NULL. */
+ * v16 [B*Hkv,tiles,16384 B], v8 [..,8192 B], v4 [..,4096 B]; each may be NULL.
+ * v8h [B*Hkv,tiles,16384 B] (may be NULL; no counterpart in the reference): the INT8 codes again as fp16 numbers
+ * in the v16 layout, the P.V operand of tri_attention, whose tensor-core weights are fp16. */
 int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
                int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
-               float* partial, float* vstat, void* v16, void* v8, void* v4, void* stream);
+               float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, void* stream);
 
 /* Banded causal prefill attention (tcgen05).
  * Replaces attention(order,bands,groups,entries,v16p,v8p,v4p,vstat,q8,k8p,qa8,ka8,q4,k4p,qa4,ka4,out,scale),
@@ -55,8 +57,9 @@ int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
  *   reference and is not provided.
  * bands int32 [Hq,2] = (w8,w4) in tile distances; a head with w8 < 1 is skipped (un-quantised BF16
  * extension heads are computed by the caller).  out is bf16 (or fp16 when out_is_half) [B,Hq,T,128]
- * with element strides.  device_error: int32 word, set non-zero if a bounded wait ran out. */
-int tri_attention(const int32_t* bands, const void* v16, const void* v8, const float* vstat,
+ * with element strides.  v8h: the fp16 rendering of the INT8 V codes from tri_pack_v (where the reference passes
+ * its v8p).  device_error: int32 word, set non-zero if a bounded wait ran out. */
+int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat,
                   const void* q8, const void* k8, const float* qa8, const float* ka8,
                   const void* q4x, const void* k4x, const float* qa4, const float* ka4,
                   void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,

@@ -217,4 +217,4 @@ def test_argument_errors_without_gpu():
     lib = load_library()
     assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 12)) == -1
     assert b"null" in lib.tri_last_error()
-    assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 6)) == -1
+    assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 7)) == -1

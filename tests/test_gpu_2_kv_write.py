@@ -27,7 +27,7 @@ def run_write(module, q, k, v, want4=True):
     qd, kd, vd = bf16_cuda(q), bf16_cuda(k), bf16_cuda(v)
     module.prepare_qk(qd, kd, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
                       ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
-    module.pack_v(vd, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"])
+    module.pack_v(vd, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"])
     torch.cuda.synchronize()
     cpu = lambda x: x.detach().cpu().numpy()
     blob = lambda x, n: cpu(x).reshape(b, hk, tiles, n)
@@ -36,6 +36,9 @@ def run_write(module, q, k, v, want4=True):
                kstat=cpu(ops["kstat"]).reshape(b, hk, 3, 128), vstat=cpu(ops["vstat"]).reshape(b, hk, 3, 128),
                v16=layouts.unpack_v16(blob(ops["v16"], 16384)), v8=layouts.unpack_v8(blob(ops["v8"], 8192)),
                v4=layouts.unpack_v4(blob(ops["v4"], 4096)))
+    # the fp16 rendering of the INT8 codes (the tensor-core operand of the prefill) holds exactly the codes
+    v8h = layouts.unpack_v16(blob(ops["v8h"], 16384))
+    assert (v8h.astype(np.float32) == res["v8"].astype(np.float32)).all()
     if want4:
         res.update(q4=cpu(ops["q4x"]).reshape(b, hq, t, 128), qa4=cpu(ops["qa4"]).reshape(b, hq, t),
                    k4x=layouts.unpack_k8(blob(ops["k4x"], 8192)), k4=layouts.unpack_k4(blob(ops["k4"], 4096)),

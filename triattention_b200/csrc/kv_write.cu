@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k,
 // grid (tiles, B*Hkv), 256 threads.  The tile is transposed through shared memory once; each thread
 // then emits whole 16-byte runs.
 __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, const float* vstat, uint8_t* v16,
-    uint8_t* v8, uint8_t* v4, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
+    uint8_t* v8, uint8_t* v4, uint8_t* v8h, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
   __shared__ float vn[BN][D + 1];
   const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x, tid = threadIdx.x;
   const __nv_bfloat16* base = v + (unit / heads) * vsb + (unit % heads) * vsh;
@@ -257,6 +257,22 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
         w[j] = *reinterpret_cast<const uint32_t*>(&h);
       }
       *reinterpret_cast<uint4*>(v16 + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (v8h != nullptr) {
+    // The INT8 codes once more, as fp16 numbers in the V16 layout: the P.V operand of the tcgen05 prefill, whose
+    // weights are fp16.  rn(clamp(x)) as a float: adding and subtracting 12582912.0f rounds to the integer exactly.
+    for (int i = tid; i < 1024; i += 256) {
+      const int ch = (i / 64) * 8 + i % 8, k8b = (i / 8) % 8;
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float c0 = __fadd_rn(__fadd_rn(fminf(fmaxf(vn[k8b * 8 + 2 * j][ch], -127.f), 127.f), 12582912.f), -12582912.f);
+        const float c1 = __fadd_rn(__fadd_rn(fminf(fmaxf(vn[k8b * 8 + 2 * j + 1][ch], -127.f), 127.f), 12582912.f), -12582912.f);
+        const __half2 h = __floats2half2_rn(c0, c1);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(v8h + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
   if (v8 != nullptr) {
@@ -329,20 +345,20 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
 }
 
 extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, int64_t v_stride_b, int64_t v_stride_h,
-    int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* stream) {
+    int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, void* stream) {
   TRI_CHECK(v && partial && vstat, "pack_v: null V buffers");
   TRI_CHECK(batch > 0 && heads_kv > 0 && tokens > 0, "pack_v: bad geometry");
   TRI_CHECK(aligned16(v) && v_stride_b % 8 == 0 && v_stride_h % 8 == 0 && v_stride_t % 8 == 0, "BF16 V [B,Hkv,T,128]");
-  TRI_CHECK(aligned16(v16) && aligned16(v8) && aligned16(v4) && aligned16(vstat), "packed V alignment");
+  TRI_CHECK(aligned16(v16) && aligned16(v8) && aligned16(v4) && aligned16(v8h) && aligned16(vstat), "packed V alignment");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tiles = (tokens + BN - 1) / BN, uk = batch * heads_kv;
   const auto* vp = static_cast<const __nv_bfloat16*>(v);
-  const int identity = (v8 == nullptr && v4 == nullptr) ? 1 : 0;  // common_host.cuh:39
+  const int identity = (v8 == nullptr && v4 == nullptr && v8h == nullptr) ? 1 : 0;  // common_host.cuh:39
   if (!identity)
     stats_partial_kernel<<<dim3(StatBlocks, uk, 2), D, 0, s>>>(nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
         v_stride_b, v_stride_h, v_stride_t);
   stats_finalize_kernel<<<dim3(uk, 2), D, 0, s>>>(nullptr, partial, nullptr, vstat, tokens, identity);
   pack_v_kernel<<<dim3(tiles, uk), 256, 0, s>>>(vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
-      static_cast<uint8_t*>(v4), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
+      static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
   return tri_launch_status("pack_v");
 }

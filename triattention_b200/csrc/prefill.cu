@@ -9,7 +9,7 @@
 // dimension added.
 //
 // Shape of the computation: see prefill_kernel.cuh (one CTA per 256 query rows of a Q head, warp
-// specialised: TMA producer, MMA issuer, V widening, softmax).  The two 128-row MMA tiles of a CTA are made
+// specialised: TMA producer, MMA issuer, softmax).  The two 128-row MMA tiles of a CTA are made
 // of four 64-row query blocks that follow the reference's tile lists (sink tile, own diagonal tile, INT8
 // band, INT4 band); a tile that only some blocks visit runs with the other blocks' weights at zero.
 // INT4 QK uses the 4-bit codes widened to int8 by the write kernel (K4X blobs, Q4X rows), so the
@@ -95,13 +95,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
-constexpr int PrefillThreads = 640;   // producer, issuer, 2 widening warps, 16 softmax warps
+constexpr int PrefillThreads = 576;   // producer, issuer, 16 softmax warps
 constexpr int ProbeThreads = 128;
 constexpr int MaxSteps = 2 * MaxTiles + 8;
 constexpr int SmQ8 = 0, SmQ4 = 32768;                            // 2 Q tiles each
 constexpr int SmBiasA = 65536, SmBiasB = SmBiasA + 4096;         // constant fp16 operands of the bias MMA (see IdescBias)
-constexpr int SmK = SmBiasB + 2048 + 2048, SmV8 = SmK + 4 * K8Bytes;   // four stages of K (1024-byte aligned), two of raw V
-constexpr int SmV16 = SmV8 + 2 * V8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
+constexpr int SmK = SmBiasB + 2048 + 2048;                       // four stages of K (1024-byte aligned)
+constexpr int SmV16 = SmK + 4 * K8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
 constexpr int SmSteps = SmEnd, StepBytes = (3 * MaxSteps + 15) / 16 * 16;  // visiting order: uint16 tile|mode, uint8 mask
 constexpr int PrefillShared = SmSteps + StepBytes + 1024;       // + slack to align the base to 1024 bytes
 constexpr uint32_t TmemCols = 512, TmemO = 0, TmemS = 256;      // O: [tile] x 128 columns; S: [tile][buffer] x 64
@@ -305,7 +305,7 @@ template <typename K> static int allow_smem(K kernel, int bytes) {
 
 using namespace tri;
 
-extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8, const float* vstat, const void* q8,
+extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat, const void* q8,
     const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4, const float* ka4,
     void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
     int heads_kv, int tokens, double scale, int* device_error, void* stream) {
@@ -316,7 +316,7 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   TRI_CHECK(int4 == (k4x != nullptr) && int4 == (qa4 != nullptr) && int4 == (ka4 != nullptr), "INT4 Q/K operands (all or none)");
   TRI_CHECK(aligned16(out) && out_stride_t % 8 == 0 && out_stride_h % 8 == 0 && out_stride_b % 8 == 0,
             "output [B,Hq,T,128] aligned");
-  TRI_CHECK(aligned16(q8) && aligned16(q4x) && aligned16(k8) && aligned16(k4x) && aligned16(v16) && aligned16(v8),
+  TRI_CHECK(aligned16(q8) && aligned16(q4x) && aligned16(k8) && aligned16(k4x) && aligned16(v16) && aligned16(v8h),
             "attention: operands must be 16-byte aligned");
   static int configured = 0;
   if (!configured) {
@@ -333,7 +333,7 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   const dim3 grid((unsigned)((int64_t)quads * units));
 #define TRI_LAUNCH(T)                                                                                                      \
   prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, bands, static_cast<const uint8_t*>(k8),       \
-      static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8), qa8, \
+      static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8h), qa8, \
       qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, heads_q, heads_kv, tokens, units,       \
       sm_log2, device_error)
   if (out_is_half) TRI_LAUNCH(__half); else TRI_LAUNCH(__nv_bfloat16);

@@ -1,12 +1,11 @@
 // The banded prefill kernel (tcgen05), warp-specialised.  Included by prefill.cu after the PTX wrappers,
 // descriptors, shared-memory plan and QuadPlan.
 //
-// One CTA (640 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
+// One CTA (576 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
 // each made of two 64-row query blocks, so every K / V tile that is fetched feeds four query blocks.
-//   warp 0        producer: TMA copies of Q (once) and of the K / V blobs of every step, three stages ahead
+//   warp 0        producer: TMA copies of Q (once) and of the K / V blobs of every step (K four steps ahead, V two)
 //   warp 1        issuer:   all tcgen05.mma of the CTA (one elected thread)
-//   warps 2-3     widen the INT8 V codes of a step to fp16 in shared memory (the P.V operand)
-//   warps 4-19    softmax: tile X = (warp-4)/8, two threads per query row; warp w reads TMEM lanes
+//   warps 2-17    softmax: tile X = (warp-2)/8, two threads per query row; warp w reads TMEM lanes
 //                 32*(w%4)..+31 (the hardware ties a warp to that lane quadrant), warps w and w+4 of a tile
 //                 share 32 rows and split the 64 key columns and the 128 output channels in halves; their
 //                 only exchange per step is the row's partial maximum (shared memory + a 64-thread barrier).
@@ -46,9 +45,7 @@ struct PrefillBarriers {
   uint64_t q;               // Q tiles landed
   uint64_t k_full[4];       // K tile + its scales landed (transaction bytes)
   uint64_t k_empty[4];      // K stage reusable: QK^T of both tiles done (tcgen05.commit)
-  uint64_t v8_full[2];      // raw INT8 V tile landed
-  uint64_t v8_empty[2];     // raw V stage reusable: both widening warps done
-  uint64_t v16_full[2];     // fp16 V operand ready: two widening warps, or TMA of the fp16 blob + one plain arrive
+  uint64_t v16_full[2];     // fp16 V operand landed (fp16 V' blob of sink / diagonal tiles, fp16 code blob otherwise)
   uint64_t v16_empty[2];    // all P.V of the step done
   uint64_t s_full[2][2];    // [tile][buffer] scores in TMEM
   uint64_t p_full[2][2];    // [tile][buffer] P written over the score buffer by the 8 softmax warps of the tile
@@ -65,11 +62,11 @@ __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// grid = quads * batch * heads_q CTAs, heaviest query rows first; 640 threads; one CTA per SM.
+// grid = quads * batch * heads_q CTAs, heaviest query rows first; 576 threads; one CTA per SM.
 template <typename Out>
 __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
     const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
-    const float* ka4, const uint8_t* v16, const uint8_t* v8, const float* qa8, const float* qa4, const float* vstat, Out* out,
+    const float* ka4, const uint8_t* v16, const uint8_t* v8h, const float* qa8, const float* qa4, const float* vstat, Out* out,
     int64_t osb, int64_t osh, int64_t ost, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
   extern __shared__ uint8_t raw_smem[];
   __shared__ __align__(8) PrefillBarriers bars;
@@ -105,8 +102,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   if (tid == 0) {
     mbar_init(&bars.q, 1);
     for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&bars.v8_full[s], 1); mbar_init(&bars.v8_empty[s], 2); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 2); mbar_init(&bars.v16_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 1); mbar_init(&bars.v16_empty[s], 1); }
     for (int x = 0; x < 2; ++x) {
       for (int s = 0; s < 2; ++s) { mbar_init(&bars.s_full[x][s], 1); mbar_init(&bars.p_full[x][s], 8); mbar_init(&bars.o_done[x][s], 1); }
     }
@@ -138,18 +134,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         mbar_expect_tx(&bars.k_full[s], K8Bytes + 16);
         bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bars.k_full[s]);
         bulk_g2s(&k_scales[i & 7][0], (mode == ModeQ4 ? ka4 : ka8) + ht * 4, 16, &bars.k_full[s]);
-        if (mode == ModeF16) {
-          if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
-          mbar_expect_tx(&bars.v16_full[vb], V16Bytes);   // first arrival; the second one follows the copy's issue
-          bulk_g2s(smem + SmV16 + vb * V16Bytes, v16 + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
-          mbar_arrive_cta(&bars.v16_full[vb]);
-          mbar_arrive_cta(&bars.v8_full[vb]);   // nothing to fetch: keeps the phase of the raw V stage in step with the step index
-        } else {
-          // raw V stages are used by steps i, i+2, ... whatever their mode: the widening warps pass every step
-          if (i >= 2 && !wait(&bars.v8_empty[vb], (i - 2) >> 1)) break;
-          mbar_expect_tx(&bars.v8_full[vb], V8Bytes);
-          bulk_g2s(smem + SmV8 + vb * V8Bytes, v8 + ht * V8Bytes, V8Bytes, &bars.v8_full[vb]);
-        }
+        // the fp16 P.V operand of the step: V' itself for sink / diagonal tiles, the INT8 codes as fp16 numbers otherwise
+        if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
+        mbar_expect_tx(&bars.v16_full[vb], V16Bytes);
+        bulk_g2s(smem + SmV16 + vb * V16Bytes, (mode == ModeF16 ? v16 : v8h) + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
       }
     }
   } else if (warp == 1) {
@@ -221,53 +209,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         tc_commit(&bars.v16_empty[vb]);
       }
     }
-  } else if (warp < 4) {
-    // ---- V widening: int8 codes of the raw V stage -> fp16 operand ----------------------------------
-    // A 16-byte unit of the V8 blob (one channel, 16 key positions) becomes two 16-byte units of the
-    // fp16 operand (8 key positions each) in the same position order, which is the order the softmax
-    // warps write P in.  Code c is built as the fp16 number 1024 + (c ^ 0x80) by byte shuffles; the
-    // subtraction of 1152 is exact.
-    const int ct = tid - 64;   // 0..63
-    const __half2 bias = __half2half2(__float2half(1152.f));
-    for (int i = 0; i < nsteps; ++i) {
-      const int mode = mode_of(i), vb = i & 1;
-      // every step, also those without a raw V tile: a parity wait only works for a waiter that is at most one
-      // phase behind, so these warps must not run ahead of the producer
-      if (!wait(&bars.v8_full[vb], i >> 1)) break;
-      if (mode != ModeF16) {
-        if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
-        const uint4* src = reinterpret_cast<const uint4*>(smem + SmV8 + vb * V8Bytes);
-        uint8_t* dst = smem + SmV16 + vb * V16Bytes;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int unit = ct + 64 * u;                 // [ch/8][key/16][ch%8]
-          const int cg = unit >> 5, run = (unit >> 3) & 3, r8 = unit & 7;
-          const uint4 raw = src[unit];
-          const uint32_t in[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
-          uint32_t o[8];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t lo = __byte_perm(in[k], 0x64646464u, 0x4140), hi = __byte_perm(in[k], 0x64646464u, 0x4342);
-            const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
-            const __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
-            o[2 * k] = *reinterpret_cast<const uint32_t*>(&a);
-            o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&c);
-          }
-          uint8_t* d = dst + cg * 1024 + (2 * run) * 128 + r8 * 16;
-          *reinterpret_cast<uint4*>(d) = make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4*>(d + 128) = make_uint4(o[4], o[5], o[6], o[7]);
-        }
-        fence_proxy_async_smem();
-      }
-      __syncwarp();
-      if (lane == 0) {
-        if (mode != ModeF16) mbar_arrive_cta(&bars.v16_full[vb]);
-        mbar_arrive_cta(&bars.v8_empty[vb]);
-      }
-    }
   } else {
     // ---- softmax ------------------------------------------------------------------------------------
-    const int sw = warp - 4, x = sw / 8, quad = sw % 4, ch = (sw % 8) / 4;
+    const int sw = warp - 2, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
     const int row = quad * 32 + lane, half = row / 64, blk = 2 * x + half;
     const int pair_id = 1 + 4 * x + quad;   // named barrier of the two warps that share these 32 rows
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
@@ -293,8 +237,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const int key0 = tile * BN + 32 * ch;
       const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 32 * ch;
       auto dead = [&](int key) { return key >= tokens || key > qi || qi >= tokens; };   // diagonal tile only
-      // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, key order = the
-      // position order of the V operand
+      // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, keys in natural
+      // order like both fp16 V blobs
 
       if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1));
       if (ok) tc_fence_after();
@@ -416,13 +360,12 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               uint32_t w[8];
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
-                const int j = 4 * hb + (u & 3) + 8 * (u >> 2);
+                const int j = 8 * hb + u;
                 const float sc = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
                 w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
               }
-              // positions 4s..4s+3 of a 16-key run hold keys kperm(s, 0..3), like the V8 blob
-              const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[4], w[5], 0x6521);   // (1024 + code) x 2 as fp16
-              const uint32_t h2 = __byte_perm(w[2], w[3], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
+              const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[2], w[3], 0x6521);   // (1024 + code) x 2 as fp16
+              const uint32_t h2 = __byte_perm(w[4], w[5], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
               rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
               rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
               rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);

@@ -21,7 +21,7 @@ _P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_dou
 # name -> argtypes, in the order of include/triattention_b200.h
 SIGNATURES = {
     "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
-    "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P],
+    "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
@@ -111,27 +111,28 @@ class Module:
                                                 kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4), _ptr(ka4),
                                                 _stream()))
 
-    def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None):
+    def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None, v8h=None):
         self._bhtd(v, "V")
         b, hk, t, _ = v.shape
         tiles = (t + 63) // 64
-        for buf, size in ((v16, 16384), (v8, 8192), (v4, 4096)):
+        for buf, size in ((v16, 16384), (v8, 8192), (v4, 4096), (v8h, 16384)):
             if buf is not None and buf.numel() * buf.element_size() != b * hk * tiles * size:
                 raise RuntimeError("packed V size")
         if partial.numel() < b * hk * 64 * 3 * 128 or vstat.numel() != b * hk * 3 * 128:
             raise RuntimeError("V statistics buffers")
         with torch.cuda.device(v.device):
             self._check(self.lib.tri_pack_v(v.data_ptr(), b, hk, t, v.stride(0), v.stride(1), v.stride(2),
-                                            partial.data_ptr(), vstat.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4), _stream()))
+                                            partial.data_ptr(), vstat.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4), _ptr(v8h),
+                                            _stream()))
 
-    def attention(self, bands, v16, v8, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
+    def attention(self, bands, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
         if not (out.dim() == 4 and out.stride(3) == 1 and out.dtype in (torch.bfloat16, torch.float16)):
             raise RuntimeError("output [B,Hq,T,128] aligned")
         b, hq, t, _ = out.shape
         if bands.dtype != torch.int32 or bands.numel() != hq * 2 or not bands.is_contiguous():
             raise RuntimeError("bands [Hq,2] or task tables")
         with torch.cuda.device(out.device):
-            self._check(self.lib.tri_attention(bands.data_ptr(), _ptr(v16), _ptr(v8), vstat.data_ptr(), q8.data_ptr(),
+            self._check(self.lib.tri_attention(bands.data_ptr(), _ptr(v16), _ptr(v8h), vstat.data_ptr(), q8.data_ptr(),
                                                k8.data_ptr(), qa8.data_ptr(), ka8.data_ptr(), _ptr(q4x), _ptr(k4x),
                                                _ptr(qa4), _ptr(ka4), out.data_ptr(), int(out.dtype == torch.float16),
                                                out.stride(0), out.stride(1), out.stride(2), b, hq, heads_kv, t,

@@ -95,6 +95,7 @@ class Prefill:
             k4=raw("k4", b * hk * rows * K4_BYTES) if (int4 and need_k4) else None,
             v16=raw("v16", b * hk * rows * V16_BYTES),
             v8=raw("v8", b * hk * rows * V8_BYTES) if (I8 in formats or Q4 in formats) else None,
+            v8h=raw("v8h", b * hk * rows * V16_BYTES) if (I8 in formats or Q4 in formats) else None,
             v4=raw("v4", b * hk * rows * V4_BYTES) if I4 in formats else None,
         )
         self.views[key] = ops
@@ -113,7 +114,7 @@ class Prefill:
         m = self.module
         m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
                      ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
-        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"])
+        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"])
         return table, ops
 
     def __call__(self, layer, q, k, v, scale):
@@ -122,7 +123,7 @@ class Prefill:
         table, ops = self.write(layer, q, k, v)
         q4 = Q4 in table.formats
         out = torch.empty((b, t, hq, 128), dtype=q.dtype, device=device).transpose(1, 2)
-        self.module.attention(table.bands, ops["v16"], ops["v8"], ops["vstat"], ops["q8"], ops["k8"], ops["qa"], ops["ka"],
+        self.module.attention(table.bands, ops["v16"], ops["v8h"], ops["vstat"], ops["q8"], ops["k8"], ops["qa"], ops["ka"],
                               ops["q4x"] if q4 else None, ops["k4x"] if q4 else None, ops["qa4"] if q4 else None,
                               ops["ka4"] if q4 else None, out, scale, hk)
         group = hq // hk
