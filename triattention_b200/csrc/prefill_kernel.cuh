@@ -247,11 +247,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const float4 ks = *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
       const float slope[2] = {qs * (ch ? ks.z : ks.x), qs * (ch ? ks.w : ks.y)};   // this thread's two 16-key groups
       float tmax = -CUDART_INF_F;
+      uint32_t a[2][16];   // this thread's 32 scores as float bits (12582912 + score); read once per step
       if (active) {
         // partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253), then the row's
         float part = -CUDART_INF_F;
         if (ok) {
-          uint32_t a[2][16];   // 12582912 + score as float bits
           tmem_ld16(s_addr, a[0]);
           tmem_ld16(s_addr + 16, a[1]);
           tmem_ld_wait();
@@ -297,6 +297,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
               tmem_st16(o_addr, o);
             }
+            tmem_ld16(s_addr, a[0]);        // the scores are read again here so that they need not survive the
+            tmem_ld16(s_addr + 16, a[1]);   // rescale in registers (it is rare)
+            tmem_ld_wait();
           }
         }
       }
@@ -311,9 +314,6 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         float sum = 0.f;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
-          uint32_t a[16];
-          tmem_ld16(s_addr + 16 * cc, a);
-          tmem_ld_wait();
           const float off = fmaf(-slope[cc], 12582912.f, PShift - ref);
           uint32_t w[8];
 #pragma unroll
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             float e[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              e[u] = exp2f(fmaf(slope[cc], __uint_as_float(a[j + u]), off));
+              e[u] = exp2f(fmaf(slope[cc], __uint_as_float(a[cc][j + u]), off));
               if (diag && dead(key0 + 16 * cc + j + u)) e[u] = 0.f;
             }
             const __half2 hp = __floats2half2_rn(e[0], e[1]);
@@ -333,9 +333,6 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         denom += sum;
       } else if (ok) {
         // prefill_sm80.cu:386-414: u8 codes of 2^(score - base); band tiles are never masked
-        uint32_t a[2][16];   // the scores again (in flight while the tile's base and weight scale are computed)
-        tmem_ld16(s_addr, a[0]);
-        tmem_ld16(s_addr + 16, a[1]);
         const float ks_max = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
         float base = tmax;
         base += tile_base_margin(qs * ks_max, base);
@@ -350,7 +347,6 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         // reference's conversion; the INT8 pass keeps the bias inside the fma like the reference does.
         auto codes = [&](auto int4_pass) {
           constexpr bool Int4 = decltype(int4_pass)::value;
-          tmem_ld_wait();
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
