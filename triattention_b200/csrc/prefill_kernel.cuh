@@ -1,11 +1,12 @@
 // The banded prefill kernel (tcgen05), warp-specialised.  Included by prefill.cu after the PTX wrappers,
 // descriptors, shared-memory plan and QuadPlan.
 //
-// One CTA (576 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
+// One CTA (608 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
 // each made of two 64-row query blocks, so every K / V tile that is fetched feeds four query blocks.
 //   warp 0        producer: TMA copies of Q (once) and of the K / V blobs of every step (K four steps ahead, V two)
-//   warp 1        issuer:   all tcgen05.mma of the CTA (one elected thread)
-//   warps 2-17    softmax: tile X = (warp-2)/8, two threads per query row; warp w reads TMEM lanes
+//   warp 1        issues the QK^T side: bias + INT8 MMAs of every step (one elected thread)
+//   warp 2        issues the P.V side (one elected thread)
+//   warps 3-18    softmax: tile X = (warp-3)/8, two threads per query row; warp w reads TMEM lanes
 //                 32*(w%4)..+31 (the hardware ties a warp to that lane quadrant), warps w and w+4 of a tile
 //                 share 32 rows and split the 64 key columns and the 128 output channels in halves; their
 //                 only exchange per step is the row's partial maximum (shared memory + a 64-thread barrier).
@@ -20,8 +21,7 @@
 //
 // P never touches shared memory: a softmax thread writes its fp16 weights over the first half of its own 32
 // score columns (tcgen05.st) once it has read them, and the P.V MMAs take their A operand from tensor memory.
-// The tensor pipe completes in issue order, so the bias MMA of two steps later overwrites P only after P.V
-// has used it.  With A in tensor memory an M128 N128 K16 MMA takes 65 cycles instead of 108 (measured).
+// The bias MMA of two steps later overwrites P; its issuer waits for that P.V to have completed first.  With A in tensor memory an M128 N128 K16 MMA takes 65 cycles instead of 108 (measured).
 //
 // Per step (one 64-key tile) and MMA tile:
 //   S[128x64]  = Q8 . K8^T            4 x kind::i8 (M128 N64 K32), s32 accumulators (bit-equal to the reference's)
@@ -62,7 +62,7 @@ __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// grid = quads * batch * heads_q CTAs, heaviest query rows first; 576 threads; one CTA per SM.
+// grid = quads * batch * heads_q CTAs, heaviest query rows first; 608 threads; one CTA per SM.
 template <typename Out>
 __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
     const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
@@ -141,24 +141,28 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       }
     }
   } else if (warp == 1) {
-    // ---- issuer -----------------------------------------------------------------------------------
+    // ---- QK^T issuer ----------------------------------------------------------------------------------
+    // Two threads issue MMAs, this one the score side: most of an issuing thread's time goes into its own
+    // dependent scalar instructions and into blocking on the pipe's queue, so one thread for all 18 MMAs of a
+    // step was the critical path of the CTA.  The tensor pipe orders nothing between the two threads; what this
+    // one needs from the other side it waits for explicitly: the score buffer of step n is free once the P.V of
+    // the tile's step n-2 (which read P out of it) has completed.
     if (lane == 0) {
       // Descriptors are built once; per MMA only the 16-byte-unit address field (low word) moves.
       const uint64_t dq8 = smem_desc(smem_u32(smem + SmQ8), 0, 1024, Layout128B), dq4 = smem_desc(smem_u32(smem + SmQ4), 0, 1024, Layout128B);
       const uint64_t dk = smem_desc(smem_u32(smem + SmK), 128, 1024, LayoutNone);
       const uint64_t dba = smem_desc(smem_u32(smem + SmBiasA), 128, 256, LayoutNone), dbb = smem_desc(smem_u32(smem + SmBiasB), 128, 256, LayoutNone);
-      const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
       auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };   // stays inside the 14-bit field
-      // Order on the tensor pipe per step i: QK^T of step i+1 for both tiles (into the score buffers that the softmax
-      // warps released one step ago), then P.V of step i for tile 0 and tile 1 as their softmax warps hand P over.
-      int nqk0 = 0, nqk1 = 0, npv0 = 0, npv1 = 0;
-      auto issue_qk = [&](int i) -> bool {
+      int nqk0 = 0, nqk1 = 0;
+      bool ok = wait(&bars.q, 0);
+      for (int i = 0; ok && i < nsteps; ++i) {
         const int mode = mode_of(i), mask = step_mask[i], s = i & 3;
-        if (!wait(&bars.k_full[s], i >> 2)) return false;
-        tc_fence_after();
+        if (!(ok = wait(&bars.k_full[s], i >> 2))) break;
         const uint64_t dqm = mode == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
         if (mask & 3) {
           const int sb = nqk0 & 1;
+          if (nqk0 >= 2 && !(ok = wait(&bars.o_done[0][sb], (nqk0 - 2) >> 1))) break;
+          tc_fence_after();
           umma_f16(tmem + TmemS + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
@@ -167,6 +171,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         }
         if (mask & 12) {
           const int sb = nqk1 & 1;
+          if (nqk1 >= 2 && !(ok = wait(&bars.o_done[1][sb], (nqk1 - 2) >> 1))) break;
+          tc_fence_after();
           umma_f16(tmem + TmemS + 128 + sb * 64, dba, dbb, IdescBias, 0u);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + 128 + sb * 64, at(dqm, 16384 + kk * 32), at(dks, kk * 256), IdescQK, 1u);
@@ -174,17 +180,22 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           ++nqk1;
         }
         tc_commit(&bars.k_empty[s]);
-        return true;
-      };
-      bool ok = wait(&bars.q, 0) && issue_qk(0);
+      }
+    }
+  } else if (warp == 2) {
+    // ---- P.V issuer -----------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
+      auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };
+      int npv0 = 0, npv1 = 0;
+      bool ok = true;
       for (int i = 0; ok && i < nsteps; ++i) {
-        if (i + 1 < nsteps && !issue_qk(i + 1)) break;   // the next scores are computed while this step's softmax runs
         const int mask = step_mask[i], vb = i & 1;
-        if (!wait(&bars.v16_full[vb], i >> 1)) break;
+        if (!(ok = wait(&bars.v16_full[vb], i >> 1))) break;
         const uint64_t dvs = at(dv, vb * V16Bytes);
         if (mask & 3) {
           const int pb = npv0 & 1;
-          if (!wait(&bars.p_full[0][pb], npv0 >> 1)) break;
+          if (!(ok = wait(&bars.p_full[0][pb], npv0 >> 1))) break;
           tc_fence_after();
           // P: key group kk (16 keys = 8 columns of fp16 pairs) sits in the first half of the 32 score columns of the
           // thread that computed it: columns 0-15 (keys 0-31) and 32-47 (keys 32-63) of score buffer pb
@@ -197,7 +208,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         }
         if (mask & 12) {
           const int pb = npv1 & 1;
-          if (!wait(&bars.p_full[1][pb], npv1 >> 1)) break;
+          if (!(ok = wait(&bars.p_full[1][pb], npv1 >> 1))) break;
           tc_fence_after();
           const uint32_t pt = tmem + TmemS + 128 + pb * 64;
 #pragma unroll
@@ -211,7 +222,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     }
   } else {
     // ---- softmax ------------------------------------------------------------------------------------
-    const int sw = warp - 2, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
+    const int sw = warp - 3, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
     const int row = quad * 32 + lane, half = row / 64, blk = 2 * x + half;
     const int pair_id = 1 + 4 * x + quad;   // named barrier of the two warps that share these 32 rows
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
@@ -303,9 +314,6 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           }
         }
       }
-      // P buffer sb was last read by the P.V of this tile's step n-2.  The issuer put that P.V on the tensor pipe
-      // before the QK^T of step n, the pipe completes in issue order, and the scores of step n have been seen
-      // above: the buffer is free, no wait needed.
       if (ok && !active) {
         const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing to the tile's P.V
         tmem_st8(s_addr, zero);
