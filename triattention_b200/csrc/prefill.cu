@@ -95,7 +95,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
-constexpr int PrefillThreads = 608;   // producer, QK^T issuer, P.V issuer, 16 softmax warps
+constexpr int PrefillThreads = 640;   // producer, 2 QK^T issuers, P.V issuer, 16 softmax warps (20 warps: 96 registers each)
 constexpr int ProbeThreads = 128;
 constexpr int MaxSteps = 2 * MaxTiles + 8;
 constexpr int SmQ8 = 0, SmQ4 = 32768;                            // 2 Q tiles each

@@ -1,12 +1,12 @@
 // The banded prefill kernel (tcgen05), warp-specialised.  Included by prefill.cu after the PTX wrappers,
 // descriptors, shared-memory plan and QuadPlan.
 //
-// One CTA (608 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
+// One CTA (640 threads, one per SM) owns 256 query rows of one Q head: two 128-row MMA tiles X = 0, 1,
 // each made of two 64-row query blocks, so every K / V tile that is fetched feeds four query blocks.
 //   warp 0        producer: TMA copies of Q (once) and of the K / V blobs of every step (K four steps ahead, V two)
-//   warp 1        issues the QK^T side: bias + INT8 MMAs of every step (one elected thread)
-//   warp 2        issues the P.V side (one elected thread)
-//   warps 3-18    softmax: tile X = (warp-3)/8, two threads per query row; warp w reads TMEM lanes
+//   warps 1-2     issue the QK^T side of MMA tile 0 / 1: bias + INT8 MMAs of every step (one elected thread each)
+//   warp 3        issues the P.V side of both tiles (one elected thread)
+//   warps 4-19    softmax: tile X = (warp-4)/8, two threads per query row; warp w reads TMEM lanes
 //                 32*(w%4)..+31 (the hardware ties a warp to that lane quadrant), warps w and w+4 of a tile
 //                 share 32 rows and split the 64 key columns and the 128 output channels in halves; their
 //                 only exchange per step is the row's partial maximum (shared memory + a 64-thread barrier).
@@ -44,9 +44,9 @@
 struct PrefillBarriers {
   uint64_t q;               // Q tiles landed
   uint64_t k_full[4];       // K tile + its scales landed (transaction bytes)
-  uint64_t k_empty[4];      // K stage reusable: QK^T of both tiles done (tcgen05.commit)
+  uint64_t k_empty[4];      // K stage reusable: QK^T of both tiles done (one tcgen05.commit per tile)
   uint64_t v16_full[2];     // fp16 V operand landed (fp16 V' blob of sink / diagonal tiles, fp16 code blob otherwise)
-  uint64_t v16_empty[2];    // all P.V of the step done
+  uint64_t v16_empty[2];    // P.V of both tiles done
   uint64_t s_full[2][2];    // [tile][buffer] scores in TMEM
   uint64_t p_full[2][2];    // [tile][buffer] P written over the score buffer by the 8 softmax warps of the tile
   uint64_t o_done[2][2];    // [tile][buffer] P.V of that P buffer done
@@ -62,7 +62,7 @@ __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// grid = quads * batch * heads_q CTAs, heaviest query rows first; 608 threads; one CTA per SM.
+// grid = quads * batch * heads_q CTAs, heaviest query rows first; 640 threads; one CTA per SM.
 template <typename Out>
 __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
     const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   fence_proxy_async_smem();
   if (tid == 0) {
     mbar_init(&bars.q, 1);
-    for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 1); }
+    for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 2); }
     for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 1); mbar_init(&bars.v16_empty[s], 1); }
     for (int x = 0; x < 2; ++x) {
       for (int s = 0; s < 2; ++s) { mbar_init(&bars.s_full[x][s], 1); mbar_init(&bars.p_full[x][s], 8); mbar_init(&bars.o_done[x][s], 1); }
@@ -140,53 +140,48 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         bulk_g2s(smem + SmV16 + vb * V16Bytes, (mode == ModeF16 ? v16 : v8h) + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
       }
     }
-  } else if (warp == 1) {
-    // ---- QK^T issuer ----------------------------------------------------------------------------------
-    // Two threads issue MMAs, this one the score side: most of an issuing thread's time goes into its own
-    // dependent scalar instructions and into blocking on the pipe's queue, so one thread for all 18 MMAs of a
-    // step was the critical path of the CTA.  The tensor pipe orders nothing between the two threads; what this
-    // one needs from the other side it waits for explicitly: the score buffer of step n is free once the P.V of
-    // the tile's step n-2 (which read P out of it) has completed.
+  } else if (warp < 3) {
+    // ---- QK^T issuers: warp 1 for MMA tile 0, warp 2 for tile 1 ---------------------------------------------
+    // Three threads issue MMAs (QK^T of tile 0, QK^T of tile 1, P.V): most of an issuing thread's time goes into its own dependent
+    // scalar instructions and into blocking on the pipe's queue, so a single thread for all 18 MMAs of a step was
+    // the critical path of the CTA.  The tensor pipe orders nothing between different issuing threads; what one
+    // needs from another it waits for explicitly: the score buffer of step n is free once the P.V of the tile's
+    // step n-2 (which read P out of it) has completed.
     if (lane == 0) {
+      const int x = warp - 1;
       // Descriptors are built once; per MMA only the 16-byte-unit address field (low word) moves.
-      const uint64_t dq8 = smem_desc(smem_u32(smem + SmQ8), 0, 1024, Layout128B), dq4 = smem_desc(smem_u32(smem + SmQ4), 0, 1024, Layout128B);
+      auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };   // stays inside the 14-bit field
+      const uint64_t dq8 = smem_desc(smem_u32(smem + SmQ8 + x * 16384), 0, 1024, Layout128B);
+      const uint64_t dq4 = smem_desc(smem_u32(smem + SmQ4 + x * 16384), 0, 1024, Layout128B);
       const uint64_t dk = smem_desc(smem_u32(smem + SmK), 128, 1024, LayoutNone);
       const uint64_t dba = smem_desc(smem_u32(smem + SmBiasA), 128, 256, LayoutNone), dbb = smem_desc(smem_u32(smem + SmBiasB), 128, 256, LayoutNone);
-      auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };   // stays inside the 14-bit field
-      int nqk0 = 0, nqk1 = 0;
+      const uint32_t st = tmem + TmemS + x * 128;
+      int nqk = 0;
       bool ok = wait(&bars.q, 0);
       for (int i = 0; ok && i < nsteps; ++i) {
-        const int mode = mode_of(i), mask = step_mask[i], s = i & 3;
+        const int s = i & 3;
+        // every step, also those this tile sits out: an issuer that ran four steps ahead would arrive twice on the
+        // same k_empty phase
         if (!(ok = wait(&bars.k_full[s], i >> 2))) break;
-        const uint64_t dqm = mode == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
-        if (mask & 3) {
-          const int sb = nqk0 & 1;
-          if (nqk0 >= 2 && !(ok = wait(&bars.o_done[0][sb], (nqk0 - 2) >> 1))) break;
+        if ((step_mask[i] >> (2 * x)) & 3) {
+          const int sb = nqk & 1;
+          if (nqk >= 2 && !(ok = wait(&bars.o_done[x][sb], (nqk - 2) >> 1))) break;
           tc_fence_after();
-          umma_f16(tmem + TmemS + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
+          const uint64_t dqm = mode_of(i) == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
+          umma_f16(st + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
-          tc_commit(&bars.s_full[0][sb]);
-          ++nqk0;
+          for (int kk = 0; kk < 4; ++kk) umma_i8(st + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
+          tc_commit(&bars.s_full[x][sb]);
+          ++nqk;
         }
-        if (mask & 12) {
-          const int sb = nqk1 & 1;
-          if (nqk1 >= 2 && !(ok = wait(&bars.o_done[1][sb], (nqk1 - 2) >> 1))) break;
-          tc_fence_after();
-          umma_f16(tmem + TmemS + 128 + sb * 64, dba, dbb, IdescBias, 0u);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_i8(tmem + TmemS + 128 + sb * 64, at(dqm, 16384 + kk * 32), at(dks, kk * 256), IdescQK, 1u);
-          tc_commit(&bars.s_full[1][sb]);
-          ++nqk1;
-        }
-        tc_commit(&bars.k_empty[s]);
+        tc_commit(&bars.k_empty[s]);   // one arrival per tile and step, also for steps the tile sits out
       }
     }
-  } else if (warp == 2) {
-    // ---- P.V issuer -----------------------------------------------------------------------------------
+  } else if (warp == 3) {
+    // ---- P.V issuer (both tiles) ------------------------------------------------------------------------------
     if (lane == 0) {
-      const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
       auto at = [](uint64_t desc, uint32_t byte_offset) { return desc + (uint64_t)(byte_offset >> 4); };
+      const uint64_t dv = smem_desc(smem_u32(smem + SmV16), 128, 1024, LayoutNone);
       int npv0 = 0, npv1 = 0;
       bool ok = true;
       for (int i = 0; ok && i < nsteps; ++i) {
@@ -222,7 +217,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     }
   } else {
     // ---- softmax ------------------------------------------------------------------------------------
-    const int sw = warp - 3, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
+    const int sw = warp - 4, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
     const int row = quad * 32 + lane, half = row / 64, blk = 2 * x + half;
     const int pair_id = 1 + 4 * x + quad;   // named barrier of the two warps that share these 32 rows
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
