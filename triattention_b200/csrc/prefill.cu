@@ -95,7 +95,8 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
-constexpr int PrefillThreads = 640;   // producer, 2 QK^T issuers, P.V issuer, 16 softmax warps (20 warps: 96 registers each)
+constexpr int RowSplit = 2;           // softmax threads per query row (1 or 2; measured on config 3: 4.47 ms with 2, 4.60 ms with 1)
+constexpr int PrefillThreads = (4 + 8 * RowSplit) * 32;   // producer, 2 QK^T issuers, P.V issuer, 8 * RowSplit softmax warps
 constexpr int ProbeThreads = 128;
 constexpr int MaxSteps = 2 * MaxTiles + 8;
 constexpr int SmQ8 = 0, SmQ4 = 32768;                            // 2 Q tiles each

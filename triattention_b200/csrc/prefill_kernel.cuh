@@ -57,6 +57,8 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// column (inside a score buffer) of the P words of key group kk: the first half of the columns of the thread that owns it
+__device__ __forceinline__ constexpr uint32_t p_column(int kk) { return RowSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; }
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     for (int s = 0; s < 4; ++s) { mbar_init(&bars.k_full[s], 1); mbar_init(&bars.k_empty[s], 2); }
     for (int s = 0; s < 2; ++s) { mbar_init(&bars.v16_full[s], 1); mbar_init(&bars.v16_empty[s], 1); }
     for (int x = 0; x < 2; ++x) {
-      for (int s = 0; s < 2; ++s) { mbar_init(&bars.s_full[x][s], 1); mbar_init(&bars.p_full[x][s], 8); mbar_init(&bars.o_done[x][s], 1); }
+      for (int s = 0; s < 2; ++s) { mbar_init(&bars.s_full[x][s], 1); mbar_init(&bars.p_full[x][s], 4 * RowSplit); mbar_init(&bars.o_done[x][s], 1); }
     }
     mbar_fence_init();
     abort_flag = 0;
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           const uint32_t pt = tmem + TmemS + pb * 64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ts(tmem + TmemO, pt + (kk >> 1) * 32 + (kk & 1) * 8, at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_ts(tmem + TmemO, pt + p_column(kk), at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&bars.o_done[0][pb]);
           ++npv0;
         }
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           const uint32_t pt = tmem + TmemS + 128 + pb * 64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ts(tmem + TmemO + 128, pt + (kk >> 1) * 32 + (kk & 1) * 8, at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_ts(tmem + TmemO + 128, pt + p_column(kk), at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&bars.o_done[1][pb]);
           ++npv1;
         }
@@ -217,7 +219,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     }
   } else {
     // ---- softmax ------------------------------------------------------------------------------------
-    const int sw = warp - 4, x = sw / 8, quad = warp % 4, ch = (sw % 8) / 4;
+    constexpr int G = 4 / RowSplit;   // 16-key groups per thread
+    const int sw = warp - 4, x = sw / (4 * RowSplit), quad = warp % 4, ch = (sw % (4 * RowSplit)) / 4;
     const int row = quad * 32 + lane, half = row / 64, blk = 2 * x + half;
     const int pair_id = 1 + 4 * x + quad;   // named barrier of the two warps that share these 32 rows
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
@@ -240,8 +243,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const bool active = (mx >> half) & 1;   // uniform for the warp pair
       const bool diag = mode == ModeF16 && tile == bh;
       const float qs = mode == ModeQ4 ? qs4 : qs8;
-      const int key0 = tile * BN + 32 * ch;
-      const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 32 * ch;
+      const int key0 = tile * BN + 16 * G * ch;
+      const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 16 * G * ch;
       auto dead = [&](int key) { return key >= tokens || key > qi || qi >= tokens; };   // diagonal tile only
       // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, keys in natural
       // order like both fp16 V blobs
@@ -251,18 +254,20 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       // The tile's K scales came with the tile (the ring slot is not reused before step i+8, and the producer
       // cannot be more than 4 steps ahead of a softmax warp).
       const float4 ks = *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
-      const float slope[2] = {qs * (ch ? ks.z : ks.x), qs * (ch ? ks.w : ks.y)};   // this thread's two 16-key groups
+      float slope[G];   // one per 16-key group of this thread
+      if constexpr (RowSplit == 2) { slope[0] = qs * (ch ? ks.z : ks.x); slope[1] = qs * (ch ? ks.w : ks.y); }
+      else { slope[0] = qs * ks.x; slope[1] = qs * ks.y; slope[G - 2] = qs * ks.z; slope[G - 1] = qs * ks.w; }
       float tmax = -CUDART_INF_F;
-      uint32_t a[2][16];   // this thread's 32 scores as float bits (12582912 + score); read once per step
+      uint32_t a[G][16];   // this thread's scores as float bits (12582912 + score); read once per step
       if (active) {
         // partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253), then the row's
         float part = -CUDART_INF_F;
         if (ok) {
-          tmem_ld16(s_addr, a[0]);
-          tmem_ld16(s_addr + 16, a[1]);
+#pragma unroll
+          for (int cc = 0; cc < G; ++cc) tmem_ld16(s_addr + 16 * cc, a[cc]);
           tmem_ld_wait();
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < G; ++cc) {
             float m = 0.f;   // below every biased score
             if (diag) {
 #pragma unroll
@@ -276,9 +281,13 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             if (m > 0.f) part = fmaxf(part, slope[cc] * (m - 12582912.f));
           }
         }
-        xchg[x][sb][ch][row] = part;
-        pair_sync(pair_id);
-        tmax = fmaxf(xchg[x][sb][0][row], xchg[x][sb][1][row]);
+        if constexpr (RowSplit == 2) {
+          xchg[x][sb][ch][row] = part;
+          pair_sync(pair_id);
+          tmax = fmaxf(xchg[x][sb][0][row], xchg[x][sb][1][row]);
+        } else {
+          tmax = part;
+        }
       }
       if (ok && active) {
         // move the row's reference exponent when this tile towers over it, and rescale what O holds
@@ -294,29 +303,29 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           if (ok) {
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2 * G; ++c) {
               uint32_t o[16];
-              const uint32_t o_addr = lane_base + TmemO + x * 128 + 64 * ch + 16 * c;
+              const uint32_t o_addr = lane_base + TmemO + x * 128 + 32 * G * ch + 16 * c;
               tmem_ld16(o_addr, o);
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
               tmem_st16(o_addr, o);
             }
-            tmem_ld16(s_addr, a[0]);        // the scores are read again here so that they need not survive the
-            tmem_ld16(s_addr + 16, a[1]);   // rescale in registers (it is rare)
-            tmem_ld_wait();
+#pragma unroll
+            for (int cc = 0; cc < G; ++cc) tmem_ld16(s_addr + 16 * cc, a[cc]);   // read again: the scores need not survive
+            tmem_ld_wait();                                                      // the (rare) rescale in registers
           }
         }
       }
       if (ok && !active) {
         const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing to the tile's P.V
-        tmem_st8(s_addr, zero);
-        tmem_st8(s_addr + 8, zero);
+#pragma unroll
+        for (int cc = 0; cc < G; ++cc) tmem_st8(s_addr + 8 * cc, zero);
       } else if (ok && mode == ModeF16) {
         float sum = 0.f;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < G; ++cc) {
           const float off = fmaf(-slope[cc], 12582912.f, PShift - ref);
           uint32_t w[8];
 #pragma unroll
@@ -351,7 +360,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         auto codes = [&](auto int4_pass) {
           constexpr bool Int4 = decltype(int4_pass)::value;
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < G; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
             uint32_t pw[8];   // the 16 weights of this key group, two per word
 #pragma unroll
@@ -394,19 +403,21 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     // ---- epilogue: O / denominator, de-normalised (prefill_sm80.cu:466-487) ----------------------------
     if (n > 0) {
       if (ok) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1));
-      xchg[x][n & 1][ch][row] = denom;
-      pair_sync(pair_id);
+      if constexpr (RowSplit == 2) {
+        xchg[x][n & 1][ch][row] = denom;
+        pair_sync(pair_id);
+      }
       if (ok) {
         tc_fence_after();
-        const float total = xchg[x][n & 1][0][row] + xchg[x][n & 1][1][row];
+        const float total = RowSplit == 2 ? xchg[x][n & 1][0][row] + xchg[x][n & 1][1][row] : denom;
         const float inv = total > 0.f ? 1.f / total : 0.f;
-        const float* mean = vstat + kvunit * StatFloats + 64 * ch;
+        const float* mean = vstat + kvunit * StatFloats + 32 * G * ch;
         const float* scale = mean + D;
-        Out* dst = out + b * osb + h * osh + (int64_t)qi * ost + 64 * ch;
+        Out* dst = out + b * osb + h * osh + (int64_t)qi * ost + 32 * G * ch;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2 * G; ++c) {
           uint32_t o[16];
-          tmem_ld16(lane_base + TmemO + x * 128 + 64 * ch + 16 * c, o);
+          tmem_ld16(lane_base + TmemO + x * 128 + 32 * G * ch + 16 * c, o);
           tmem_ld_wait();
           if (row_valid) {
 #pragma unroll
