@@ -31,3 +31,18 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
       return TRI_ERR_CUDA;                    \
     }                                         \
   } while (0)
+
+// Launch with programmatic stream serialisation: the kernel may become resident while its predecessor in
+// the stream is still running and orders itself with grid_dependency_wait() (common.cuh).  Hides the
+// launch latency between kernels that follow one another in a stream.
+template <typename... Params, typename... Args>
+static inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                                         Args... args) {
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = shared; cfg.stream = stream;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}

@@ -94,21 +94,6 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
 }
 
 
-// Launch with programmatic stream serialisation: the kernel may become resident while its predecessor in
-// the stream is still running and orders itself with grid_dependency_wait() (common.cuh).  Hides the
-// launch latency between the split pass and the merge, and between consecutive steps.
-template <typename... Params, typename... Args>
-static cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
-                                  Args... args) {
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = shared; cfg.stream = stream;
-  cfg.attrs = &attr; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
-}
-
 // ---- cache store: gather kept tiles of the prefill operands into the per-unit streams ------------
 // grid (max kept tiles, units), 256 threads.  K8 / V8 / V4 blobs are re-ordered from the prefill
 // operand layout (tcgen05 core matrices, csrc/common.cuh) into the decode layout (decode_kernel.cuh):

@@ -28,6 +28,8 @@ namespace tri {
 __global__ void __launch_bounds__(D) stats_partial_kernel(const __nv_bfloat16* k, const __nv_bfloat16* v,
     float* partial_k, float* partial_v, int tokens, int heads, int64_t ksb, int64_t ksh, int64_t kst,
     int64_t vsb, int64_t vsh, int64_t vst) {
+  grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
+  grid_launch_dependents();
   const int c = threadIdx.x, unit = blockIdx.y, which = blockIdx.z;
   const int b = unit / heads, h = unit % heads;
   const __nv_bfloat16* base;
@@ -68,6 +70,8 @@ __global__ void __launch_bounds__(D) stats_partial_kernel(const __nv_bfloat16* k
 // grid (units, 2), 128 threads.  common_device.cuh:44-56.
 __global__ void __launch_bounds__(D) stats_finalize_kernel(const float* partial_k, const float* partial_v,
     float* kstat, float* vstat, int tokens, int v_identity) {
+  grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
+  grid_launch_dependents();
   const int64_t unit = blockIdx.x;
   const int c = threadIdx.x, which = blockIdx.y;
   const float* partial = which == 0 ? partial_k : partial_v;
@@ -127,6 +131,8 @@ __device__ __forceinline__ uint4 codes16(const float (&x)[16], float inv) {
 // sign-extended to int8 so that the prefill kernel can feed them to the INT8 tensor-core path.
 __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q, int8_t* q8, float* qa, int8_t* q4x,
     float* qa4, int tokens, int heads, int64_t qsb, int64_t qsh, int64_t qst) {
+  grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
+  grid_launch_dependents();
   const int lane = threadIdx.x % 32, l8 = lane % 8;
   const int row = blockIdx.x * 16 + (threadIdx.x / 32) * 4 + lane / 8;
   const int unit = blockIdx.y;
@@ -163,6 +169,8 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
 // maximum is known.
 __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k, const float* kstat, uint8_t* k8,
     float* ka, uint8_t* k4x, uint8_t* k4, float* ka4, int tokens, int heads, int64_t ksb, int64_t ksh, int64_t kst) {
+  grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
+  grid_launch_dependents();
   const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x;
   const int col = threadIdx.x / 32, lane = threadIdx.x % 32, l8 = lane % 8, sub_row = lane / 8;
   const __nv_bfloat16* src = k + (unit / heads) * ksb + (unit % heads) * ksh + l8 * 16;
@@ -226,6 +234,8 @@ __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k,
 __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, const float* vstat, uint8_t* v16,
     uint8_t* v8, uint8_t* v4, uint8_t* v8h, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
   __shared__ float vn[BN][D + 1];
+  grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
+  grid_launch_dependents();
   const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x, tid = threadIdx.x;
   const __nv_bfloat16* base = v + (unit / heads) * vsb + (unit % heads) * vsh;
   const float* stat = vstat + (int64_t)unit * StatFloats;
@@ -334,12 +344,12 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
   const int tiles = (tokens + BN - 1) / BN, uq = batch * heads_q, uk = batch * heads_kv;
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
   const auto* kp = static_cast<const __nv_bfloat16*>(k);
-  quantize_q_kernel<<<dim3((tokens + 15) / 16, uq), 128, 0, s>>>(qp, static_cast<int8_t*>(q8), qa,
+  launch_chained(quantize_q_kernel, dim3((tokens + 15) / 16, uq), dim3(128), 0, s, qp, static_cast<int8_t*>(q8), qa,
       static_cast<int8_t*>(q4x), qa4, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
-  stats_partial_kernel<<<dim3(StatBlocks, uk, 1), D, 0, s>>>(kp, nullptr, partial, nullptr, tokens, heads_kv,
+  launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, partial, nullptr, tokens, heads_kv,
       k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
-  stats_finalize_kernel<<<dim3(uk, 1), D, 0, s>>>(partial, nullptr, kstat, nullptr, tokens, 0);
-  quantize_k_kernel<<<dim3(tiles, uk), 128, 0, s>>>(kp, kstat, static_cast<uint8_t*>(k8), ka,
+  launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, partial, nullptr, kstat, nullptr, tokens, 0);
+  launch_chained(quantize_k_kernel, dim3(tiles, uk), dim3(128), 0, s, kp, kstat, static_cast<uint8_t*>(k8), ka,
       static_cast<uint8_t*>(k4x), static_cast<uint8_t*>(k4), ka4, tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
   return tri_launch_status("prepare_qk");
 }
@@ -355,10 +365,10 @@ extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, in
   const auto* vp = static_cast<const __nv_bfloat16*>(v);
   const int identity = (v8 == nullptr && v4 == nullptr && v8h == nullptr) ? 1 : 0;  // common_host.cuh:39
   if (!identity)
-    stats_partial_kernel<<<dim3(StatBlocks, uk, 2), D, 0, s>>>(nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
+    launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 2), dim3(D), 0, s, nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
         v_stride_b, v_stride_h, v_stride_t);
-  stats_finalize_kernel<<<dim3(uk, 2), D, 0, s>>>(nullptr, partial, nullptr, vstat, tokens, identity);
-  pack_v_kernel<<<dim3(tiles, uk), 256, 0, s>>>(vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
+  launch_chained(stats_finalize_kernel, dim3(uk, 2), dim3(D), 0, s, nullptr, partial, nullptr, vstat, tokens, identity);
+  launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
       static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
   return tri_launch_status("pack_v");
 }
