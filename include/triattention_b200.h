@@ -50,6 +50,17 @@ int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
                int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
                float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, void* stream);
 
+/* Quantise K and V rows that arrive after the prompt with the prompt's statistics (no statistics pass): K8 blobs
+ * and scales as tri_prepare_qk writes them, V8 blobs as tri_pack_v writes them, rows >= tokens zero.  The decode cache
+ * uses it to turn 64 generated tokens of the BF16 tail into one more cached tile (no counterpart in the reference,
+ * whose tail is capped at 1024 tokens, triattention/kernels/cuda/common_host.cuh:56).
+ * k, v bf16 [B,Hkv,T,128] with element strides; kstat, vstat f32 [B*Hkv,3,128] (read only);
+ * k8 [B*Hkv,tiles,8192 B]; ka f32 [B*Hkv,tiles,4]; v8 [B*Hkv,tiles,8192 B]. */
+int tri_requantize_kv(const void* k, const void* v, int batch, int heads_kv, int tokens,
+                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                      int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+                      const float* kstat, const float* vstat, void* k8, float* ka, void* v8, void* stream);
+
 /* Banded causal prefill attention (tcgen05).
  * Replaces attention(order,bands,groups,entries,v16p,v8p,v4p,vstat,q8,k8p,qa8,ka8,q4,k4p,qa4,ka4,out,scale),
  *   triattention/kernels/cuda/prefill_sm80.cu:510-543, in band mode.  The CTA order is internal

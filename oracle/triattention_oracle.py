@@ -520,11 +520,21 @@ def decode_quantize_q(q, sl2):
     return q8, qs, q4, qs4
 
 
-def decode_partials(q, ops, tables, prompt, scale, splits_of):
+def fold_tail(ops, tail_k, tail_v):
+    """Not in the reference (its tail of generated tokens is capped, common_host.cuh:56): 64 tail rows become one
+    more cached tile, quantised with the prompt's statistics by the prompt's own rules (common_device.cuh:58-172).
+    tail_k, tail_v [Hkv,64,128] -> dict(k8 [Hkv,64,128], ka [Hkv,4], v8 [Hkv,64,128]).  parity unpinned."""
+    k8, ka, _, _ = quantize_k(tail_k, ops["kstat"][:, 0])
+    _, v8, _ = pack_v(tail_v, ops["vstat"])
+    return dict(k8=k8[:, 0], ka=ka[:, 0], v8=v8[:, 0])
+
+
+def decode_partials(q, ops, tables, prompt, scale, splits_of, appended=()):
     """decode_kernel, common_device.cuh:275-371.  q [Hq,128]; ops = logical operand dict from
     ``prefill(..., return_operands=True)``; tables from ``decode_tables``; ``splits_of(kh, n)`` returns
     the list of (first, last) index ranges over that head's kept tiles.  Returns per Q head a list of
-    (m, l, o[128]) partials in split order."""
+    (m, l, o[128]) partials in split order.  appended = tiles from ``fold_tail`` in order: they follow the
+    head's kept tiles, INT8 K and V, every Q head of the group attends, all 64 keys live."""
     hq = q.shape[0]
     hk = len(tables)
     g = hq // hk
@@ -534,10 +544,16 @@ def decode_partials(q, ops, tables, prompt, scale, splits_of):
     for kh in range(hk):
         tb = tables[kh]
         rows = slice(kh * g, (kh + 1) * g)
-        for first, last in splits_of(kh, len(tb["tiles"])):
+        kept = len(tb["tiles"])
+        for first, last in splits_of(kh, kept + len(appended)):
             st = dict(m=np.full(g, -FLT_MAX, np.float32), denom=np.zeros((g, 4), np.float32),
                       out=np.zeros((g, D), np.float32), corr=np.zeros(g, np.float32))
             for i in range(first, last):
+                if i >= kept:
+                    extra = appended[i - kept]
+                    _decode_tile(q8[rows], qs[rows], extra["k8"][kh], extra["ka"][kh], extra["v8"][kh], I8, 8,
+                                 0, 1 << 30, 0xFF, st)
+                    continue
                 tile, state, pv = int(tb["tiles"][i]), int(tb["state"][i]), int(tb["vfmt"][i])
                 vcodes = ops["v8"][kh, tile] if pv == I8 else ops["v4"][kh, tile]
                 if state == 4:
@@ -584,7 +600,7 @@ def decode_merge(q, parts, kmean, vstat, tail_k, tail_v, kcur, vcur, step, max_t
     return out
 
 
-def decode_step(q, ops, bands, prompt, scale, tail_k, tail_v, kcur, vcur, step, max_tail, per=None):
+def decode_step(q, ops, bands, prompt, scale, tail_k, tail_v, kcur, vcur, step, max_tail, per=None, appended=()):
     """One decode step of one sequence (kernels/decode.py:69-80).  ``per`` = kept tiles per split
     (kernels/decode.py:54-55); None = one split per head."""
     hk = ops["kstat"].shape[0]
@@ -594,7 +610,7 @@ def decode_step(q, ops, bands, prompt, scale, tail_k, tail_v, kcur, vcur, step, 
         step_ = n if per is None else per
         return [(a, min(n, a + step_)) for a in range(0, max(n, 1), max(step_, 1)) if a < n] or []
 
-    parts = decode_partials(q, ops, tables, prompt, scale, splits_of)
+    parts = decode_partials(q, ops, tables, prompt, scale, splits_of, appended)
     return decode_merge(q, parts, ops["kstat"][:, 0], ops["vstat"], tail_k, tail_v, kcur, vcur, step, max_tail, scale)
 
 

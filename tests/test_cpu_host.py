@@ -218,3 +218,35 @@ def test_argument_errors_without_gpu():
     assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 12)) == -1
     assert b"null" in lib.tri_last_error()
     assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 7)) == -1
+
+
+def test_plan_streams_appended_tiles():
+    """Tiles appended behind the prompt (DecodeCache(fold_tail=...)): the streams keep their place, the new tiles sit
+    where append_off says, are flagged as full and seen by every Q head, and every tile is in exactly one segment."""
+    dm, dm_inf = dec, maps.INF
+    bands = np.asarray([[dm_inf, dm_inf]] * 2 + [[1, dm_inf]] * 2 + [[dm_inf, dm_inf]] * 2, np.int64)
+    plans = [dm.plan_streams(bands, 3, 200, 2, bf16_kv=(2,), ctas=8, extra=e, reserve=3) for e in range(4)]
+    tile = dm.K8_BYTES + dm.V8_BYTES + 16
+    for e, p in enumerate(plans):
+        assert np.array_equal(p["unit_base"], plans[0]["unit_base"]) and p["pool_bytes"] == plans[0]["pool_bytes"]
+        assert np.array_equal(p["append_off"], plans[0]["append_off"])
+        assert list(p["count"]) == [4 + e, 4 + e, 7 + 2 * e]
+        for kh in range(3):
+            rows = p["tmeta"][p["tab_begin"][kh]:p["tab_begin"][kh] + p["count"][kh]]
+            old = plans[0]["tmeta"][plans[0]["tab_begin"][kh]:plans[0]["tab_begin"][kh] + plans[0]["count"][kh]]
+            assert np.array_equal(rows[:len(old)], old)
+            new = rows[len(old):]
+            step = 2 * dm.BF16_CHUNK_BYTES if kh == 2 else tile
+            assert all(int(r[1]) & dm.INFO_FULL and (int(r[1]) >> dm.INFO_ROW_SHIFT) & 0xFF == 0xFF for r in new)
+            assert all(bool(int(r[1]) & dm.INFO_BF16) == (kh == 2) and not int(r[1]) & (dm.INFO_K4 | dm.INFO_V4) for r in new)
+            offs = [int(r[0]) * 16 for r in new]
+            per = step // (2 if kh == 2 else 1)
+            assert offs == [int(p["append_off"][kh]) + i * per for i in range(len(new))]
+            assert not len(offs) or offs[-1] + per <= p["head_bytes"][kh]
+        covered = np.zeros((6, 16), np.int64)
+        for unit, first, n, _ in p["segments"]:
+            covered[unit, first:first + n] += 1
+        for unit in range(6):
+            assert (covered[unit, :p["unit_count"][unit]] == 1).all() and not covered[unit, p["unit_count"][unit]:].any()
+    with pytest.raises(ValueError):
+        dm.plan_streams(bands, 3, 200, 2, ctas=8, extra=1, split=(0, 2))

@@ -98,6 +98,29 @@ def test_decode_is_split_invariant_and_close_to_exact():
     assert np.abs(outs[0] - ex).max() < 0.05
 
 
+def test_folded_tail_tiles_stay_close_to_exact_attention():
+    """64 generated tokens quantised into one more tile (fold_tail): the result stays an attention over all keys."""
+    hq, hk, t = 4, 2, 130
+    q, k, v = orc.synth((hq, t, 128), 14), orc.synth((hk, t, 128), 15), orc.synth((hk, t, 128), 16)
+    bands = np.array([[orc.INF, orc.INF]] * 2 + [[1, orc.INF]] * 2)
+    _, ops = orc.prefill(q, k, v, bands, 0.0884, return_operands=True)
+    qd, kd, vd = orc.synth((hq, 66, 128), 17), orc.synth((hk, 66, 128), 18), orc.synth((hk, 66, 128), 19)
+    tk, tv = np.zeros((hk, 64, 128), np.float32), np.zeros((hk, 64, 128), np.float32)
+    tk[:], tv[:] = kd[:, :64], vd[:, :64]
+    tile = orc.fold_tail(ops, tk.copy(), tv.copy())
+    assert tile["k8"].shape == (hk, 64, 128) and tile["ka"].shape == (hk, 4) and np.abs(tile["v8"]).max() <= 127
+    outs = [orc.decode_step(qd[:, 64 + s], ops, bands, t, 0.0884, tk, tv, kd[:, 64 + s], vd[:, 64 + s], s, 64,
+                            appended=[tile]) for s in range(2)]
+    for s in range(2):
+        kk, vv = np.concatenate([k, kd[:, :65 + s]], 1), np.concatenate([v, vd[:, :65 + s]], 1)
+        ex = np.stack([orc.exact_decode(qd[h, 64 + s], kk[h // 2], vv[h // 2], 0.0884) for h in range(hq)])
+        assert np.abs(outs[s] - ex).max() < 0.06
+    # the split of the tile list must not matter with an appended tile either
+    tk2, tv2 = tk.copy(), tv.copy()
+    one = orc.decode_step(qd[:, 65], ops, bands, t, 0.0884, tk2, tv2, kd[:, 65], vd[:, 65], 1, 64, per=1, appended=[tile])
+    assert np.abs(one - outs[1]).max() < 1e-4
+
+
 def test_decode_tables_rules():
     bands = np.array([[2, 5], [1, 3], [orc.INF, orc.INF], [1, 1]])
     tabs = orc.decode_tables(bands, 2, 64 * 10)

@@ -183,3 +183,53 @@ def test_host_stepper_matches_device_calls(module):
     np.testing.assert_array_equal(got, want)
     with pytest.raises(RuntimeError):
         stepper.submit(torch.empty(1), outs[0], outs[0], outs[0], SCALE)
+
+
+def test_fold_tail_lifts_the_generation_cap(module):
+    """DecodeCache(fold_tail=N): every 64 generated tokens become one more cached tile (quantised with the prompt's
+    statistics), so generation runs past max_tail.  Quantised heads against the oracle's restatement of exactly
+    that, BF16 units against exact attention over all keys; 131 steps = two folds, ragged prompt end."""
+    hq, hk, t, steps = 6, 3, 200, 131
+    bands = np.asarray([[INF, INF]] * 2 + [[1, INF]] * 2 + [[INF, INF]] * 2, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=71, batch=2)
+    qd, kd, vd = make_inputs(hq, hk, steps, seed=72, batch=2)
+    cache = DecodeCache(module, max_tail=64, fold_tail=192)
+    pre = Prefill(module, bands_fn_of(bands, (2,)), cache)
+    kc, vc = bf16_cuda(k), bf16_cuda(v)
+    table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+    cache.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
+    got = []
+    for s in range(steps):
+        got.append(cache(0, bf16_cuda(qd[:, :, s:s + 1]), bf16_cuda(kd[:, :, s:s + 1]), bf16_cuda(vd[:, :, s:s + 1]),
+                         SCALE).float().cpu().numpy()[:, :, 0])
+        cache.advance()
+    module.check_device_error()
+    assert cache.layers[0]["extra"] == 2 and int(cache.step) == steps % 64
+    got = np.stack(got, 1)
+    for b in range(2):
+        o = oracle_ops(None, k[b], v[b])
+        tk, tv = np.zeros((hk, 64, 128), np.float32), np.zeros((hk, 64, 128), np.float32)
+        appended = []
+        for s in range(steps):
+            if s and s % 64 == 0:
+                appended.append(orc.fold_tail(o, tk.copy(), tv.copy()))
+            want = orc.decode_step(qd[b][:, s], o, bands, t, SCALE, tk, tv, kd[b][:, s], vd[b][:, s], s % 64, 64,
+                                   appended=appended)
+            assert_fp_close(got[b, s, :4], orc.to_bf16(want[:4]), f"b={b} step {s}")
+            for h in (4, 5):
+                kk, vv = np.concatenate([k[b, 2], kd[b, 2, :s + 1]]), np.concatenate([v[b, 2], vd[b, 2, :s + 1]])
+                assert_fp_close(got[b, s, h], orc.to_bf16(orc.exact_decode(qd[b, h, s], kk, vv, SCALE)), f"bf16 head {h} step {s}")
+    # against the un-folded cache (all generated tokens in the BF16 tail) only the 128 folded keys differ: INT8 codes
+    plain, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps, max_tail=256, bf16=(2,))
+    # (the softmax of these inputs is peaked, so INT8 logits move single elements by a few tenths; the check is that
+    # the two stay the same attention overall)
+    a, b = plain[:, 64:].astype(np.float64).ravel(), got[:, 64:].astype(np.float64).ravel()
+    assert np.array_equal(plain[:, :64], got[:, :64]) and a @ b / np.sqrt((a @ a) * (b @ b)) > 0.99
+    # the reserved room is a hard limit
+    small = DecodeCache(module, max_tail=64, fold_tail=64)
+    pre = Prefill(module, bands_fn_of(bands, (2,)), small)
+    table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+    small.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
+    small.generated = 128
+    with pytest.raises(RuntimeError):
+        small.fold(0), small.fold(0)

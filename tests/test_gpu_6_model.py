@@ -70,3 +70,21 @@ def test_generate_cuda_graph_matches_eager():
     assert graph == eager
     stop = eager[0][4]
     assert engine.generate(ids, 12, eos={stop}, cuda_graph=True) == engine.generate(ids, 12, eos={stop})
+
+
+@torch.inference_mode()
+def test_generate_fold_tail_runs_past_the_tail():
+    """fold_tail=True: the 64-row tail is folded into cached tiles twice on the way to 140 tokens.  Up to the first
+    fold the tokens are those of the un-folded engine (same arithmetic); a captured graph is refused."""
+    from triattention_b200.maps import per_kv_head
+    from triattention_b200.models import TriAttention
+    model = tiny_llama()
+    ids = torch.randint(0, 1024, (2, 150), generator=torch.Generator().manual_seed(7)).cuda()
+    plain = TriAttention(model, per_kv_head(["int8", "int4"], 2), max_new_tokens=140).generate(ids, 140, eos=())
+    engine = TriAttention(model, per_kv_head(["int8", "int4"], 2), max_new_tokens=140, fold_tail=True)
+    rows = engine.generate(ids, 140, eos=())
+    assert all(len(r) == 140 for r in rows) and all(r[:65] == p[:65] for r, p in zip(rows, plain))
+    assert all(engine.decode_cache.layers[layer]["extra"] == 2 for layer in range(3))
+    assert engine.generate(ids, 140, eos=()) == rows          # a second prompt starts from a fresh cache
+    with pytest.raises(RuntimeError):
+        engine.generate(ids, 8, eos=(), cuda_graph=True)

@@ -45,6 +45,9 @@ static_assert(DecodeShared <= 227 * 1024 && CombFloats * 4 >= 2048, "decode shar
 
 // tile_info bits
 constexpr uint32_t InfoTileMask = 0xfffu, InfoRowShift = 12, InfoK4 = 1u << 20, InfoV4 = 1u << 21, InfoBf16 = 1u << 22;
+// A tile appended after the prompt (generated keys folded into the cache) holds 64 live keys (32 for a BF16 chunk) wherever
+// the prompt ended: it is not masked against the prompt length.
+constexpr uint32_t InfoFull = 1u << 23;
 
 __device__ __forceinline__ uint32_t chunk_bytes(uint32_t info) {
   if (info & InfoBf16) return Bf16ChunkBytes;
@@ -311,7 +314,7 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
 // segments; segs[j] = {unit, first kept tile, tile count, partial slot}; unit = sequence*heads_kv + kv head.
 __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
     const uint8_t* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int2* tmeta,
-    const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt,
+    const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt_keys,
     float sm_log2, int stream_only, MergeArgs margs, int* err) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[DecodeStages], empty[DecodeStages];
@@ -437,6 +440,7 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
         const int tile = info & InfoTileMask;
         const unsigned rowmask = (info >> InfoRowShift) & 0xffu;
         const bool row_on = group < g && ((rowmask >> group) & 1u);
+        const int prompt = (info & InfoFull) ? 0x7fffffff : prompt_keys;
         if (stream_only) {
           // diagnostic: consume the ring without arithmetic (measures the copy pipeline alone)
         } else if (info & InfoBf16) {

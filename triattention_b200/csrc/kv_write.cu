@@ -372,3 +372,24 @@ extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, in
       static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
   return tri_launch_status("pack_v");
 }
+
+// Quantise K and V rows with statistics that already exist (the prompt's): the cache write for keys that arrive
+// after the prompt.  The same two kernels as above; no statistics pass, INT8 blobs only.
+extern "C" int tri_requantize_kv(const void* k, const void* v, int batch, int heads_kv, int tokens, int64_t k_stride_b,
+    int64_t k_stride_h, int64_t k_stride_t, int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t, const float* kstat,
+    const float* vstat, void* k8, float* ka, void* v8, void* stream) {
+  TRI_CHECK(k && v && kstat && vstat && k8 && ka && v8, "requantize_kv: null buffers");
+  TRI_CHECK(batch > 0 && heads_kv > 0 && tokens > 0 && (tokens + BN - 1) / BN <= MaxTiles, "requantize_kv: bad geometry");
+  TRI_CHECK(aligned16(k) && aligned16(v) && k_stride_b % 8 == 0 && k_stride_h % 8 == 0 && k_stride_t % 8 == 0 &&
+            v_stride_b % 8 == 0 && v_stride_h % 8 == 0 && v_stride_t % 8 == 0 && aligned16(k8) && aligned16(v8) &&
+            aligned16(kstat) && aligned16(vstat), "requantize_kv: BF16 K/V [B,Hkv,T,128], 16-byte aligned rows and blobs");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tiles = (tokens + BN - 1) / BN, uk = batch * heads_kv;
+  launch_chained(quantize_k_kernel, dim3(tiles, uk), dim3(128), 0, s, static_cast<const __nv_bfloat16*>(k), kstat,
+      static_cast<uint8_t*>(k8), ka, static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(nullptr),
+      static_cast<float*>(nullptr), tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
+  launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(v), vstat,
+      static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(v8), static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(nullptr),
+      tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
+  return tri_launch_status("requantize_kv");
+}

@@ -22,7 +22,8 @@ from triattention_b200.kernels.prefill import I4, I8
 NEAR_V8 = 16
 K8_BYTES, K4_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 8192, 4096
 BF16_CHUNK_KEYS, BF16_CHUNK_BYTES = 32, 16384
-INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16 = 12, 1 << 20, 1 << 21, 1 << 22
+INFO_ROW_SHIFT, INFO_K4, INFO_V4, INFO_BF16, INFO_FULL = 12, 1 << 20, 1 << 21, 1 << 22, 1 << 23
+FOLD_KEYS = 64      # generated tokens per appended tile (DecodeCache(fold_tail=...))
 MAX_GROUP = 8
 # Relative time of one tile on one SM, by kind, for the partition's cost model: (BF16 32-key chunk,
 # INT8-K/INT8-V tile, any other quantised tile).  Quantised tiles are bound by their arithmetic (the same
@@ -40,9 +41,13 @@ def tile_states(bands, heads_kv, tiles):
     return state.max(1), rowmask
 
 
-def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_costs=TILE_COSTS, split=None):
+def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_costs=TILE_COSTS, split=None, extra=0, reserve=0):
     """Host-side layout of one layer's cache and its partition over `ctas` persistent CTAs (numpy).
     split = (rank, world) keeps only this rank's part of every unit's kept-tile list (sequence split).
+    extra = tiles of 64 generated tokens appended behind the prompt's tiles (INT8 K and V, seen by every Q head
+    of the group, 64 live keys each: INFO_FULL; two 32-key chunks for a BF16 unit); reserve >= extra = how many
+    of them every unit's stream has room for, so that the streams do not move when a tile is appended
+    (append_off [Hkv] = where the first one goes).
 
     Returns a dict of numpy arrays: tmeta [N,2], tab_begin/count/head_bytes [Hkv], unit_base [U] (int64),
     unit_tab/unit_count/unit_flags [U], segments [S,4] = (unit, first kept tile, tile count, partial slot),
@@ -52,7 +57,10 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
     kv, rowmask = tile_states(bands, heads_kv, tiles)
     j = np.arange(tiles)
     v4 = ~((tiles - 1 - j < NEAR_V8) | (j == 0))
-    metas, sizes, costs, tab_begin, count, head_bytes = [], [], [], [], [], []
+    if extra < 0 or reserve < 0 or ((extra or reserve) and split is not None):
+        raise ValueError("appended tiles: extra, reserve >= 0, and not together with a sequence split")
+    reserve = max(reserve, extra)
+    metas, sizes, costs, tab_begin, count, head_bytes, append_off = [], [], [], [], [], [], []
     bf16_range = (0, (prompt + BF16_CHUNK_KEYS - 1) // BF16_CHUNK_KEYS)
     for kh in range(heads_kv):
         if kh in bf16_kv:
@@ -66,6 +74,14 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
             info = kept | ((rowmask[kh][kept] & 0xFF) << INFO_ROW_SHIFT) | np.where(k4, INFO_K4, 0) | np.where(v4[kept], INFO_V4, 0)
             size = np.where(k4, K4_BYTES, K8_BYTES) + np.where(v4[kept], V4_BYTES, V8_BYTES) + 16
             costs.append(np.where(~k4 & ~v4[kept], tile_costs[1], tile_costs[2]).astype(np.float64))
+        bf16_head = kh in bf16_kv
+        append_off.append(int(size.sum()))
+        if extra:
+            n_new = 2 * extra if bf16_head else extra
+            flags = (0xFF << INFO_ROW_SHIFT) | INFO_FULL | (INFO_BF16 if bf16_head else 0)
+            info = np.concatenate([info, np.full(n_new, flags, np.int64)])
+            size = np.concatenate([size, np.full(n_new, BF16_CHUNK_BYTES if bf16_head else K8_BYTES + V8_BYTES + 16, np.int64)])
+            costs[-1] = np.concatenate([costs[-1], np.full(n_new, tile_costs[0] if bf16_head else tile_costs[1], np.float64)])
         if split is not None:   # sequence split across GPUs: this rank keeps one contiguous, cost-balanced part
             rank, world = split
             cc = np.concatenate([[0], np.cumsum(costs[-1])])
@@ -79,7 +95,8 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
         metas.append(np.stack([off[:-1] // 16, info], 1))
         sizes.append(size)
         count.append(len(size))
-        head_bytes.append(int(-(-off[-1] // 128) * 128))
+        room = (reserve - extra) * (2 * BF16_CHUNK_BYTES if bf16_head else K8_BYTES + V8_BYTES + 16)
+        head_bytes.append(int(-(-(off[-1] + room) // 128) * 128))
     tmeta = np.concatenate(metas).astype(np.int32)
     head_off = np.concatenate([[0], np.cumsum(head_bytes)])
     seq_bytes = int(head_off[-1])
@@ -112,13 +129,21 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
                 unit_tab=np.asarray(tab_begin, np.int32)[kh_of], unit_count=np.asarray(count, np.int32)[kh_of],
                 unit_flags=unit_flags, segments=np.asarray(segments, np.int32).reshape(-1, 4), cta_segments=cta_segments,
                 unit_slots=np.asarray(unit_slots, np.int32).reshape(-1, 2), slots=len(segments),
+                append_off=np.asarray(append_off, np.int64),
                 pool_bytes=int(batch * seq_bytes), seq_bytes=seq_bytes, tiles=tiles, bf16_range=bf16_range,
                 payload_bytes=int(batch * sum(int(s.sum()) for s in sizes)))
 
 
 class DecodeCache:
-    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None, fused_merge=False):
-        """fused_merge: a whole step is one launch (the CTA that finishes a unit's last segment merges the unit).
+    def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None, fused_merge=False,
+                 fold_tail=0):
+        """fold_tail: 0 keeps the reference's behaviour (generated tokens stay in a BF16 tail of at most max_tail
+        <= 1024 rows).  N > 0 lifts that cap: room for N generated tokens is reserved behind every unit's stream, and
+        each time 64 tokens have gathered in the tail they are quantised with the prompt's statistics into one more
+        cached tile (INT8 K and V, attended by every Q head of the group; two BF16 chunks for an un-quantised unit)
+        and the tail starts again.  This changes numerics against the reference (those 64 keys are scored from INT8
+        codes instead of BF16 rows), hence off by default.  Not available together with split_group.
+        fused_merge: a whole step is one launch (the CTA that finishes a unit's last segment merges the unit).
         It pays when a step is launch-bound (few sequences, short caches); at full batch the merge sits on the
         critical path of the CTA that does it, so the default keeps the split pass and the merge as two launches
         chained by programmatic dependent launch.
@@ -130,6 +155,9 @@ class DecodeCache:
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
         self.split_group, self.split, self.fused_merge = split_group, None, bool(fused_merge)
+        self.reserve, self.generated, self.fold_buffers = -(-int(fold_tail) // FOLD_KEYS), 0, {}
+        if self.reserve and (split_group is not None or max_tail < FOLD_KEYS):
+            raise ValueError("fold_tail needs max_tail >= 64 and no split_group")
         if split_group is not None:
             import torch.distributed as dist
             self.split = (dist.get_rank(split_group), dist.get_world_size(split_group))
@@ -155,11 +183,11 @@ class DecodeCache:
             self.ctas = sms * max(1, self.module.decode_occupancy())
         return self.ctas
 
-    def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device):
-        key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device), self.split)
+    def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device, extra=0):
+        key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device), self.split, extra)
         if key not in self.plans:
             host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
-                                tile_costs=self.tile_costs, split=self.split)
+                                tile_costs=self.tile_costs, split=self.split, extra=extra, reserve=self.reserve)
             dev = {name: torch.from_numpy(host[name]).to(device) for name in
                    ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
             if bf16_kv:
@@ -175,6 +203,8 @@ class DecodeCache:
         entry = self.layers.get(layer)
         if entry is None or entry["pool"].numel() != host["pool_bytes"] or entry["plan"] is not host:
             units, slots = batch * heads_kv, max(1, host["slots"])
+            if self.reserve:
+                slots = units + self.wave(device)     # an upper bound for every number of appended tiles
             f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=device)
             entry = self.layers[layer] = dict(
                 plan=host, dev=dev, prompt=prompt,
@@ -192,9 +222,11 @@ class DecodeCache:
                              rank_slots=torch.stack([torch.arange(units, dtype=torch.int32) * world,
                                                      torch.full((units,), world, dtype=torch.int32)], 1).to(device))
         entry["kstat"], entry["vstat"] = ops["kstat"].clone(), ops["vstat"].clone()
+        entry.update(extra=0, geometry=(np.asarray(bands), heads_kv, prompt, batch, tuple(bf16_kv)))
         if self.step is None:
             self.step = torch.zeros(1, dtype=torch.int64, device=device)
         self.step.zero_()
+        self.generated = 0
         max_count = int(host["count"].max())
         if max_count > 0:
             self.module.cache_store(entry["pool"], dev["unit_base"], dev["unit_tab"], dev["unit_count"], dev["unit_flags"],
@@ -207,8 +239,42 @@ class DecodeCache:
             entry["kstat"][dev["bf16_units"].long()] = ident
             entry["vstat"][dev["bf16_units"].long()] = ident
 
+    def fold(self, layer):
+        """Quantise the first 64 rows of the layer's tail into one more tile of every unit's stream."""
+        e = self.layers[layer]
+        bands, heads_kv, prompt, batch, bf16_kv = e["geometry"]
+        if e["extra"] >= self.reserve:
+            raise RuntimeError("fold_tail: more generated tokens than the cache was given room for")
+        device, units, done = e["pool"].device, batch * heads_kv, e["extra"]
+        host, dev = e["plan"], e["dev"]
+        if not self.fold_buffers:
+            self.fold_buffers = dict(k8=torch.empty((units, K8_BYTES), dtype=torch.uint8, device=device),
+                                     v8=torch.empty((units, V8_BYTES), dtype=torch.uint8, device=device),
+                                     ka=torch.empty((units, 4), dtype=torch.float32, device=device))
+        buf = self.fold_buffers
+        rows = lambda t: t.view(batch, heads_kv, self.max_tail, 128)[:, :, :FOLD_KEYS]
+        key = ("fold", id(host), done)
+        if key not in self.plans:      # where the new tile of each unit goes, as a one-entry gather table per KV head
+            quant = host["append_off"] + done * (K8_BYTES + V8_BYTES + 16)
+            kh_of = np.arange(units) % heads_kv
+            tables = dict(tmeta=np.stack([quant // 16, np.zeros(heads_kv, np.int64)], 1).astype(np.int32),
+                          tab=kh_of.astype(np.int32), count=np.ones(units, np.int32),
+                          base_bf16=host["unit_base"] + (host["append_off"] + done * 2 * BF16_CHUNK_BYTES)[kh_of])
+            self.plans[key] = {name: torch.from_numpy(a).to(device) for name, a in tables.items()}
+        t = self.plans[key]
+        if len(bf16_kv) < heads_kv:
+            self.module.requantize_kv(rows(e["tail_k"]), rows(e["tail_v"]), e["kstat"], e["vstat"], buf["k8"], buf["ka"], buf["v8"])
+            self.module.cache_store(e["pool"], dev["unit_base"], t["tab"], t["count"], dev["unit_flags"], t["tmeta"], units, 1,
+                                    buf["k8"], None, buf["ka"], None, buf["v8"], None, 1)
+        if bf16_kv:
+            self.module.cache_store_bf16(e["pool"], t["base_bf16"], dev["bf16_units"], rows(e["tail_k"]), rows(e["tail_v"]), 0, 2)
+        e["extra"] = done + 1
+        e["plan"], e["dev"] = self.plan(bands, heads_kv, prompt, batch, bf16_kv, device, extra=done + 1)
+
     def __call__(self, layer, q, k, v, scale, phases=3, out=None):
         e = self.layers[layer]
+        if self.reserve and e["extra"] < self.generated // FOLD_KEYS:
+            self.fold(layer)
         d = e["dev"]
         out = torch.empty_like(q) if out is None else out
         run = lambda pm, pl, po, slots, ph: self.module.decode(
@@ -230,7 +296,11 @@ class DecodeCache:
         return out
 
     def advance(self):
-        self.step.add_(1)
+        self.generated += 1
+        if self.reserve and self.generated % FOLD_KEYS == 0:
+            self.step.zero_()       # the tail starts again; each layer folds its 64 rows at its next call
+        else:
+            self.step.add_(1)
 
     def stored(self, layer):
         return layer in self.layers

@@ -22,6 +22,7 @@ _P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_dou
 SIGNATURES = {
     "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P],
+    "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
@@ -124,6 +125,19 @@ class Module:
             self._check(self.lib.tri_pack_v(v.data_ptr(), b, hk, t, v.stride(0), v.stride(1), v.stride(2),
                                             partial.data_ptr(), vstat.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4), _ptr(v8h),
                                             _stream()))
+
+    def requantize_kv(self, k, v, kstat, vstat, k8, ka, v8):
+        """K8 / V8 blobs of rows that came after the prompt, with the prompt's statistics."""
+        self._bhtd(k, "K"), self._bhtd(v, "V")
+        b, hk, t, _ = k.shape
+        tiles = (t + 63) // 64
+        if v.shape != k.shape or k8.numel() != b * hk * tiles * 8192 or v8.numel() != b * hk * tiles * 8192 or \
+                ka.numel() != b * hk * tiles * 4 or kstat.numel() != b * hk * 384 or vstat.numel() != b * hk * 384:
+            raise RuntimeError("requantize_kv buffers")
+        with torch.cuda.device(k.device):
+            self._check(self.lib.tri_requantize_kv(k.data_ptr(), v.data_ptr(), b, hk, t, k.stride(0), k.stride(1), k.stride(2),
+                                                   v.stride(0), v.stride(1), v.stride(2), kstat.data_ptr(), vstat.data_ptr(),
+                                                   k8.data_ptr(), ka.data_ptr(), v8.data_ptr(), _stream()))
 
     def attention(self, bands, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
         if not (out.dim() == 4 and out.stride(3) == 1 and out.dtype in (torch.bfloat16, torch.float16)):

@@ -60,11 +60,15 @@ def use_attention(model, name, fn):
 
 
 class TriAttention:
-    def __init__(self, model, qk_map=None, max_new_tokens=256):
+    def __init__(self, model, qk_map=None, max_new_tokens=256, fold_tail=False):
+        """fold_tail=False is the reference: generated tokens stay in a BF16 tail, so max_new_tokens <= 1024
+        (models.py:58-70, common_host.cuh:56).  fold_tail=True lifts the cap: every 64 generated tokens are quantised
+        into one more cached tile (DecodeCache(fold_tail=...)); numerics then differ from the reference's."""
         self.model = model
         module = load_extension()
         self.module = module
-        self.decode_cache = DecodeCache(module, max_tail=max_new_tokens)
+        self.decode_cache = (DecodeCache(module, max_tail=64, fold_tail=max_new_tokens) if fold_tail
+                             else DecodeCache(module, max_tail=max_new_tokens))
         bands_fn = qk_map if callable(qk_map) else load_map(qk_map or preset(model), model)
         self.prefill = Prefill(module, bands_fn, self.decode_cache)
 
@@ -88,6 +92,8 @@ class TriAttention:
         history = []
         token = out.logits[:, -1].argmax(-1)
         replay = None
+        if cuda_graph and self.decode_cache.reserve:
+            raise RuntimeError("cuda_graph replays fixed cache tables; it cannot be combined with fold_tail")
         if cuda_graph and max_new_tokens > 1:
             tok = token[:, None].clone()
             pos = torch.full((batch, 1), ids.shape[1], device=device)
