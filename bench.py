@@ -312,6 +312,37 @@ def run_model(args):
         prefill_s, eager_s = timed_generate(False)
         _, graph_s = timed_generate(True)
     engine.module.check_device_error()
+
+    # Where the time goes: CUDA events around every call into the library during one more prompt pass and a few
+    # layer-by-layer decode steps (everything else is the model's own GEMMs and element-wise kernels).
+    spans = {}
+
+    def watch(name):
+        inner = getattr(engine.module, name)
+
+        def call(*a, **k):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            result = inner(*a, **k)
+            end.record()
+            spans.setdefault(name, []).append((begin, end))
+            return result
+        setattr(engine.module, name, call)
+        return inner
+
+    names = ("prepare_qk", "pack_v", "attention", "cache_store", "cache_store_bf16", "decode")
+    originals = {name: watch(name) for name in names}
+    few = min(new, 9)
+    engine.generate(ids, few, eos=())
+    torch.cuda.synchronize()
+    for name, inner in originals.items():
+        setattr(engine.module, name, inner)
+    ms = {name: sum(b.elapsed_time(e) for b, e in spans.get(name, [])) for name in names}
+    prompt_ms = sum(ms[name] for name in names if name != "decode")
+    library = dict(prompt_pass_ms=prompt_ms, prompt_pass_share=prompt_ms / (prefill_s * 1e3),
+                   decode_ms_per_step=ms["decode"] / max(1, few - 1),
+                   decode_share_of_graph_step=ms["decode"] / max(1, few - 1) / (graph_s * 1e3 / (new - 1)),
+                   by_call_ms={k: round(v, 3) for k, v in ms.items()})
     print(json.dumps(dict(metric="generate_tokens_per_s", value=batch * (new - 1) / graph_s, unit="tokens/s", n_gpus=1,
                           higher_is_better=True, dtype="bf16 model, int8 / int4 / bf16 KV cache", data="synthetic",
                           config=dict(workload=f"end to end C4: random-init Llama-3.2-3B architecture, batch {batch} x {prompt} prompt "
@@ -319,7 +350,8 @@ def run_model(args):
                           prompt_tokens_per_s=batch * prompt / prefill_s, prompt_pass_s=prefill_s,
                           decode_tokens_per_s_cuda_graph=batch * (new - 1) / graph_s,
                           decode_tokens_per_s_layer_by_layer=batch * (new - 1) / eager_s,
-                          decode_loop_s=dict(cuda_graph=graph_s, layer_by_layer=eager_s), clocks=clocks.summary())))
+                          decode_loop_s=dict(cuda_graph=graph_s, layer_by_layer=eager_s),
+                          time_inside_the_attention_library=library, clocks=clocks.summary())))
 
 
 def main():
