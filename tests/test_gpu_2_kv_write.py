@@ -119,3 +119,37 @@ def test_argument_errors(module):
     q = torch.zeros((1, 2, 8, 128), dtype=torch.float16, device="cuda")
     with pytest.raises(RuntimeError):
         module.prepare_qk(q, q, q, q, q, q, q, q)
+
+
+@pytest.mark.parametrize("rows", [64, 100])
+def test_requantize_with_given_statistics(module, rows):
+    """tri_requantize_kv: rows that arrive after the prompt, quantised with the prompt's statistics, give the
+    codes and scales the oracle's quantize_k / pack_v give for the same statistics (rows beyond the count are zero)."""
+    hq, hk, t, batch = 4, 2, 300, 2
+    q, k, v = make_inputs(hq, hk, t, seed=37, batch=batch)
+    _, kn, vn = make_inputs(hq, hk, rows, seed=38, batch=batch)
+    vn = vn * 1.7                                   # some values leave the prompt's range and are clamped
+    ops = Prefill(module, None).operands(batch, hq, hk, t, False, False, frozenset({F16, I8}), "cuda")
+    module.prepare_qk(bf16_cuda(q), bf16_cuda(k), ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"])
+    module.pack_v(bf16_cuda(v), ops["partial"], ops["vstat"], ops["v16"], ops["v8"], None, ops["v8h"])
+    tiles = (rows + 63) // 64
+    k8 = torch.empty((batch * hk, tiles, 8192), dtype=torch.uint8, device="cuda")
+    v8 = torch.empty_like(k8)
+    ka = torch.empty((batch * hk, tiles, 4), dtype=torch.float32, device="cuda")
+    stats = ops["kstat"].clone(), ops["vstat"].clone()
+    module.requantize_kv(bf16_cuda(kn), bf16_cuda(vn), ops["kstat"], ops["vstat"], k8, ka, v8)
+    torch.cuda.synchronize()
+    assert torch.equal(stats[0], ops["kstat"]) and torch.equal(stats[1], ops["vstat"])      # read only
+    cpu = lambda x: x.detach().cpu().numpy()
+    got_k = layouts.unpack_k8(cpu(k8).reshape(batch, hk, tiles, 8192))
+    got_v = layouts.unpack_v8(cpu(v8).reshape(batch, hk, tiles, 8192))
+    got_ka = cpu(ka).reshape(batch, hk, tiles, 4)
+    kstat, vstat = cpu(ops["kstat"]).reshape(batch, hk, 3, 128), cpu(ops["vstat"]).reshape(batch, hk, 3, 128)
+    for b in range(batch):
+        want_k, want_ka, _, _ = orc.quantize_k(kn[b], kstat[b][:, 0])
+        _, want_v, _ = orc.pack_v(orc.to_bf16(vn[b]), vstat[b])
+        assert ulp_diff(got_ka[b], want_ka).max() <= SCALE_ULP
+        for name, got, want in (("k8", got_k[b], want_k), ("v8", got_v[b], want_v)):
+            rate, big = code_mismatch(got, want)
+            assert big <= 1 and rate <= CODE_RATE, (name, rate, big)
+        assert np.abs(got_v[b]).max() == 127 and not got_k[b].reshape(hk, -1, 128)[:, rows:].any()

@@ -233,88 +233,113 @@ __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k,
 // then emits whole 16-byte runs.
 __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, const float* vstat, uint8_t* v16,
     uint8_t* v8, uint8_t* v4, uint8_t* v8h, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
-  __shared__ float vn[BN][D + 1];
+  // Row stride 132 floats: a thread stores its 8 channels of a row as two 16-byte words (two lanes of a quarter
+  // warp share a bank), and a warp that later reads 32 consecutive channels of one row hits 32 different banks.
+  __shared__ __align__(16) float vn[BN][D + 4];
   grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
   grid_launch_dependents();
   const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x, tid = threadIdx.x;
   const __nv_bfloat16* base = v + (unit / heads) * vsb + (unit % heads) * vsh;
   const float* stat = vstat + (int64_t)unit * StatFloats;
-  for (int i = tid; i < BN * D / 8; i += 256) {
-    const int r = i / (D / 8), c0 = (i % (D / 8)) * 8, t = tile * BN + r;
-    if (t < tokens) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(base + (int64_t)t * vst + c0);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  {
+    const int c0 = (tid % (D / 8)) * 8;     // the same 8 channels in every pass
+    float mean[8], inv[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        // vnorm, common_device.cuh:132-134: (v - mean) * (1/scale)
-        vn[r][c0 + 2 * j] = (__uint_as_float(w[j] << 16) - stat[c0 + 2 * j]) * stat[2 * D + c0 + 2 * j];
-        vn[r][c0 + 2 * j + 1] = (__uint_as_float(w[j] & 0xffff0000u) - stat[c0 + 2 * j + 1]) * stat[2 * D + c0 + 2 * j + 1];
+    for (int j = 0; j < 2; ++j) {
+      const float4 m = *reinterpret_cast<const float4*>(stat + c0 + 4 * j);
+      const float4 s = *reinterpret_cast<const float4*>(stat + 2 * D + c0 + 4 * j);
+      mean[4 * j] = m.x; mean[4 * j + 1] = m.y; mean[4 * j + 2] = m.z; mean[4 * j + 3] = m.w;
+      inv[4 * j] = s.x; inv[4 * j + 1] = s.y; inv[4 * j + 2] = s.z; inv[4 * j + 3] = s.w;
+    }
+#pragma unroll
+    for (int pass = 0; pass < BN * D / 8 / 256; ++pass) {
+      const int r = pass * (256 / (D / 8)) + tid / (D / 8), t = tile * BN + r;
+      float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (t < tokens) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(base + (int64_t)t * vst + c0);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // vnorm, common_device.cuh:132-134: (v - mean) * (1/scale)
+          y[2 * j] = (__uint_as_float(w[j] << 16) - mean[2 * j]) * inv[2 * j];
+          y[2 * j + 1] = (__uint_as_float(w[j] & 0xffff0000u) - mean[2 * j + 1]) * inv[2 * j + 1];
+        }
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) vn[r][c0 + j] = 0.f;
+      *reinterpret_cast<float4*>(&vn[r][c0]) = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(&vn[r][c0 + 4]) = make_float4(y[4], y[5], y[6], y[7]);
     }
   }
   __syncthreads();
   const int64_t ht = (int64_t)unit * tiles + tile;
+  // One thread = one channel and 32 keys, read from the transposed tile once for every output format
+  // (run = 16 bytes of a blob: 8 keys of a channel in V16 / V8H, 16 keys in V8, 32 keys in V4).
+  // (a warp holds 32 consecutive channels of one key half, so its reads of a row hit 32 different banks)
+  const int ch = tid % D, kc = tid / D;
+  float x[32];
+#pragma unroll
+  for (int kk = 0; kk < 32; ++kk) x[kk] = vn[kc * 32 + kk][ch];
   if (v16 != nullptr) {
-    for (int i = tid; i < 1024; i += 256) {   // run = (ch/8, key/8, ch%8): 8 keys of one channel
-      const int ch = (i / 64) * 8 + i % 8, k8b = (i / 8) % 8;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {          // run (ch/8, key/8, ch%8)
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const __half2 h = __floats2half2_rn(vn[k8b * 8 + 2 * j][ch], vn[k8b * 8 + 2 * j + 1][ch]);
+        const __half2 h = __floats2half2_rn(x[8 * q + 2 * j], x[8 * q + 2 * j + 1]);
         w[j] = *reinterpret_cast<const uint32_t*>(&h);
       }
-      *reinterpret_cast<uint4*>(v16 + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      const int run = (ch / 8) * 64 + (kc * 4 + q) * 8 + ch % 8;
+      *reinterpret_cast<uint4*>(v16 + ht * V16Bytes + (int64_t)run * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
-  if (v8h != nullptr) {
-    // The INT8 codes once more, as fp16 numbers in the V16 layout: the P.V operand of the tcgen05 prefill, whose
-    // weights are fp16.  rn(clamp(x)) as a float: adding and subtracting 12582912.0f rounds to the integer exactly.
-    for (int i = tid; i < 1024; i += 256) {
-      const int ch = (i / 64) * 8 + i % 8, k8b = (i / 8) % 8;
-      uint32_t w[4];
+  if (v8 != nullptr || v8h != nullptr) {
+    // clamp(rn(x)) == rn(clamp(x)): rounding is monotonic and the bounds are integers.  c[kk] = 12582912 + code as
+    // float bits: the low byte is the INT8 code, and minus 12582912.0f it is the code as a float.
+    uint32_t c[32];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float c0 = __fadd_rn(__fadd_rn(fminf(fmaxf(vn[k8b * 8 + 2 * j][ch], -127.f), 127.f), 12582912.f), -12582912.f);
-        const float c1 = __fadd_rn(__fadd_rn(fminf(fmaxf(vn[k8b * 8 + 2 * j + 1][ch], -127.f), 127.f), 12582912.f), -12582912.f);
-        const __half2 h = __floats2half2_rn(c0, c1);
-        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    for (int kk = 0; kk < 32; ++kk) c[kk] = rn_bits(fminf(fmaxf(x[kk], -127.f), 127.f));
+    if (v8h != nullptr) {
+      // The INT8 codes once more, as fp16 numbers in the V16 layout: the P.V operand of the tcgen05 prefill, whose
+      // weights are fp16.
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half2 h = __floats2half2_rn(__fadd_rn(__uint_as_float(c[8 * q + 2 * j]), -12582912.f),
+                                              __fadd_rn(__uint_as_float(c[8 * q + 2 * j + 1]), -12582912.f));
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        const int run = (ch / 8) * 64 + (kc * 4 + q) * 8 + ch % 8;
+        *reinterpret_cast<uint4*>(v8h + ht * V16Bytes + (int64_t)run * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(v8h + ht * V16Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-  }
-  if (v8 != nullptr) {
-    for (int i = tid; i < 512; i += 256) {    // run = (ch/8, key/16, ch%8): 16 keys in kperm order
-      const int ch = (i / 32) * 8 + i % 8, blk = (i / 8) % 4;
-      uint32_t w[4];
+    if (v8 != nullptr) {
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {   // clamp(rn(x)) == rn(clamp(x)): rounding is monotonic and the bounds are integers
-        uint32_t b4[4];
+      for (int h = 0; h < 2; ++h) {        // run (ch/8, key/16, ch%8): 16 keys in kperm order
+        uint32_t w[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) b4[b] = rn_bits(fminf(fmaxf(vn[blk * 16 + kperm(s, b)][ch], -127.f), 127.f));
-        w[s] = pack_low_bytes(b4[0], b4[1], b4[2], b4[3]);
+        for (int s = 0; s < 4; ++s)
+          w[s] = pack_low_bytes(c[16 * h + kperm(s, 0)], c[16 * h + kperm(s, 1)], c[16 * h + kperm(s, 2)], c[16 * h + kperm(s, 3)]);
+        const int run = (ch / 8) * 32 + (kc * 2 + h) * 8 + ch % 8;
+        *reinterpret_cast<uint4*>(v8 + ht * V8Bytes + (int64_t)run * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(v8 + ht * V8Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
-  if (v4 != nullptr) {
-    const int i = tid;                         // run = (ch/8, key/32, ch%8): 32 keys, two per byte
-    const int ch = (i / 16) * 8 + i % 8, kc = (i / 8) % 2;
+  if (v4 != nullptr) {                     // run (ch/8, key/32, ch%8): 32 keys, two per byte
     uint32_t w[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
       uint32_t word = 0;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        const uint32_t lo = rn_bits(fminf(fmaxf(__fmul_rn(vn[kc * 32 + kperm(s, b)][ch], 7.f / 127.f), -7.f), 7.f));
-        const uint32_t hi = rn_bits(fminf(fmaxf(__fmul_rn(vn[kc * 32 + 16 + kperm(s, b)][ch], 7.f / 127.f), -7.f), 7.f));
+        const uint32_t lo = rn_bits(fminf(fmaxf(__fmul_rn(x[kperm(s, b)], 7.f / 127.f), -7.f), 7.f));
+        const uint32_t hi = rn_bits(fminf(fmaxf(__fmul_rn(x[16 + kperm(s, b)], 7.f / 127.f), -7.f), 7.f));
         word |= ((lo & 0xfu) | ((hi & 0xfu) << 4)) << (8 * b);
       }
       w[s] = word;
     }
-    *reinterpret_cast<uint4*>(v4 + ht * V4Bytes + (int64_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    const int run = (ch / 8) * 16 + kc * 8 + ch % 8;
+    *reinterpret_cast<uint4*>(v4 + ht * V4Bytes + (int64_t)run * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
