@@ -126,38 +126,91 @@ __device__ __forceinline__ uint4 codes16(const float (&x)[16], float inv) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// grid (ceil(T/16), B*Hq), 128 threads: 4 rows per warp, 8 lanes per row.  q8/q4x are plain
-// [B*Hq][T][128] int8 (the reference's q8 layout, common_device.cuh:18); q4x holds the 4-bit codes
-// sign-extended to int8 so that the prefill kernel can feed them to the INT8 tensor-core path.
+// Sign flips of the rotation for a lane that holds features 32*l4 .. 32*l4+31 as 16 bf16 pairs: word j flips
+// bit 15 if feature 2j is negated and bit 31 if feature 2j+1 is (the sign words of prefill_sm80.cu:27).
+struct PairSigns { uint32_t w[4][16]; };
+constexpr PairSigns make_pair_signs() {
+  constexpr uint32_t words[4] = {0x9a3b5e71u, 0x2c6d8f13u, 0xe41b7a95u, 0x5f02c3d8u};
+  PairSigns t{};
+  for (int l = 0; l < 4; ++l)
+    for (int j = 0; j < 16; ++j)
+      t.w[l][j] = (((words[l] >> (2 * j)) & 1u) << 15) | (((words[l] >> (2 * j + 1)) & 1u) << 31);
+  return t;
+}
+__device__ const PairSigns kPairSigns = make_pair_signs();
+
+// grid (ceil(T/32), B*Hq), 128 threads: 8 rows per warp, 4 lanes per row, 32 features per lane: five butterfly
+// stages in registers, two across lanes (same butterflies in the same order as rotate128_x16, so the same bits).
+// The kernel is bound by the SM's load/store data path (shuffles, 16-byte global accesses) and by instruction
+// issue, not by HBM: 32 features per lane need 22 instructions and 8 shuffles per row-warp where 16 features
+// needed 28 and 12; a whole row per thread needs no shuffle, but its global accesses no longer coalesce and its
+// 159 registers leave too few warps.
+// q8/q4x are plain [B*Hq][T][128] int8 (the reference's q8 layout, common_device.cuh:18); q4x holds the 4-bit
+// codes sign-extended to int8 so that the prefill kernel can feed them to the INT8 tensor-core path.
 __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q, int8_t* q8, float* qa, int8_t* q4x,
     float* qa4, int tokens, int heads, int64_t qsb, int64_t qsh, int64_t qst) {
   grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
   grid_launch_dependents();
-  const int lane = threadIdx.x % 32, l8 = lane % 8;
-  const int row = blockIdx.x * 16 + (threadIdx.x / 32) * 4 + lane / 8;
+  const int lane = threadIdx.x % 32, l4 = lane % 4;
+  const int row = blockIdx.x * 32 + (threadIdx.x / 32) * 8 + lane / 4;
   const int unit = blockIdx.y;
   const bool live = row < tokens;
-  float x[16];
-  if (live) load16_bf16(q + (unit / heads) * qsb + (unit % heads) * qsh + (int64_t)row * qst + l8 * 16, x);
-  else {
+  float x[32];
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(q + (unit / heads) * qsb + (unit % heads) * qsh + (int64_t)row * qst + l4 * 32);
+    const uint4* flip = reinterpret_cast<const uint4*>(kPairSigns.w[l4]);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = 0.f;
+    for (int i = 0; i < 4; ++i) {
+      const uint4 a = live ? src[i] : make_uint4(0, 0, 0, 0), f = flip[i];
+      const uint32_t w[4] = {a.x ^ f.x, a.y ^ f.y, a.z ^ f.z, a.w ^ f.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+        x[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
   }
-  rotate128_x16(x, l8);
-  float m = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(x[i]));
+  for (int bit = 1; bit < 32; bit <<= 1) {
 #pragma unroll
-  for (int o = 4; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int i = 0; i < 32; ++i) {
+      if (!(i & bit)) {
+        const float lo = x[i], hi = x[i | bit];
+        x[i] = lo + hi; x[i | bit] = lo - hi;
+      }
+    }
+  }
+#pragma unroll
+  for (int bit = 1; bit < 4; bit <<= 1) {
+    const float sign = (l4 & bit) ? -1.f : 1.f;   // upper lane: partner - own; lower lane: own + partner
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float y = __shfl_xor_sync(0xffffffffu, x[i], bit);
+      x[i] = fmaf(x[i], sign, y);                 // one rounding of y +- x, like the add / subtract it replaces
+    }
+  }
+  float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    x[i] *= kRotScale; x[i + 1] *= kRotScale;
+    m0 = fmaxf(m0, fabsf(x[i])); m1 = fmaxf(m1, fabsf(x[i + 1]));
+  }
+  float m = fmaxf(m0, m1);
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
   if (!live) return;
   const int64_t r = (int64_t)unit * tokens + row;
   const float inv = m > 0.f ? 127.f / m : 0.f;
-  *reinterpret_cast<uint4*>(q8 + r * D + l8 * 16) = codes16(x, inv);
-  if (l8 == 0) qa[r] = m / 127.f;
+  uint4* d8 = reinterpret_cast<uint4*>(q8 + r * D + l4 * 32);
+  d8[0] = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv);
+  d8[1] = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv);
+  if (l4 == 0) qa[r] = m / 127.f;
   if (q4x != nullptr) {
     const float inv4 = m > 0.f ? 7.f / m : 0.f;
-    *reinterpret_cast<uint4*>(q4x + r * D + l8 * 16) = codes16(x, inv4);
-    if (l8 == 0) qa4[r] = m / 7.f;
+    uint4* d4 = reinterpret_cast<uint4*>(q4x + r * D + l4 * 32);
+    d4[0] = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv4);
+    d4[1] = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv4);
+    if (l4 == 0) qa4[r] = m / 7.f;
   }
 }
 
@@ -369,7 +422,7 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
   const int tiles = (tokens + BN - 1) / BN, uq = batch * heads_q, uk = batch * heads_kv;
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
   const auto* kp = static_cast<const __nv_bfloat16*>(k);
-  launch_chained(quantize_q_kernel, dim3((tokens + 15) / 16, uq), dim3(128), 0, s, qp, static_cast<int8_t*>(q8), qa,
+  launch_chained(quantize_q_kernel, dim3((tokens + 31) / 32, uq), dim3(128), 0, s, qp, static_cast<int8_t*>(q8), qa,
       static_cast<int8_t*>(q4x), qa4, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
   launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, partial, nullptr, tokens, heads_kv,
       k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
