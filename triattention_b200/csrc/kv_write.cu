@@ -126,21 +126,27 @@ __device__ __forceinline__ uint4 codes16(const float (&x)[16], float inv) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Sign flips of the rotation for a lane that holds features 32*l4 .. 32*l4+31 as 16 bf16 pairs: word j flips
-// bit 15 if feature 2j is negated and bit 31 if feature 2j+1 is (the sign words of prefill_sm80.cu:27).
+// A lane of quantize_q_kernel holds two runs of 16 features, 16*(l4 + 4k) .. +15 for k = 0, 1, as 8 bf16 pairs
+// each.  Sign flips of the rotation for them: word 8k+j flips bit 15 if the run's feature 2j is negated and bit 31
+// if feature 2j+1 is (the sign words of prefill_sm80.cu:27).
 struct PairSigns { uint32_t w[4][16]; };
 constexpr PairSigns make_pair_signs() {
   constexpr uint32_t words[4] = {0x9a3b5e71u, 0x2c6d8f13u, 0xe41b7a95u, 0x5f02c3d8u};
   PairSigns t{};
   for (int l = 0; l < 4; ++l)
-    for (int j = 0; j < 16; ++j)
-      t.w[l][j] = (((words[l] >> (2 * j)) & 1u) << 15) | (((words[l] >> (2 * j + 1)) & 1u) << 31);
+    for (int k = 0; k < 2; ++k)
+      for (int j = 0; j < 8; ++j) {
+        const int f = 16 * (l + 4 * k) + 2 * j;
+        t.w[l][8 * k + j] = (((words[f >> 5] >> (f & 31)) & 1u) << 15) | (((words[(f + 1) >> 5] >> ((f + 1) & 31)) & 1u) << 31);
+      }
   return t;
 }
 __device__ const PairSigns kPairSigns = make_pair_signs();
 
-// grid (ceil(T/32), B*Hq), 128 threads: 8 rows per warp, 4 lanes per row, 32 features per lane: five butterfly
-// stages in registers, two across lanes (same butterflies in the same order as rotate128_x16, so the same bits).
+// grid (ceil(T/32), B*Hq), 128 threads: 8 rows per warp, 4 lanes per row, 32 features per lane.  The lane index is
+// feature bits 4-5: butterflies on bits 0-3 in registers, bits 4-5 across lanes, bit 6 in registers again (the same
+// butterflies in the same order as rotate128_x16, so the same bits).  With this assignment the four lanes of a
+// row read 128 contiguous bytes per load and write 64 contiguous bytes per store.
 // The kernel is bound by the SM's load/store data path (shuffles, 16-byte global accesses) and by instruction
 // issue, not by HBM: 32 features per lane need 22 instructions and 8 shuffles per row-warp where 16 features
 // needed 28 and 12; a whole row per thread needs no shuffle, but its global accesses no longer coalesce and its
@@ -155,13 +161,14 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
   const int row = blockIdx.x * 32 + (threadIdx.x / 32) * 8 + lane / 4;
   const int unit = blockIdx.y;
   const bool live = row < tokens;
-  float x[32];
+  float x[32];   // x[16k + e] = feature 16*(l4 + 4k) + e
   {
-    const uint4* src = reinterpret_cast<const uint4*>(q + (unit / heads) * qsb + (unit % heads) * qsh + (int64_t)row * qst + l4 * 32);
+    const __nv_bfloat16* src = q + (unit / heads) * qsb + (unit % heads) * qsh + (int64_t)row * qst + l4 * 16;
     const uint4* flip = reinterpret_cast<const uint4*>(kPairSigns.w[l4]);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 a = live ? src[i] : make_uint4(0, 0, 0, 0), f = flip[i];
+    for (int i = 0; i < 4; ++i) {          // 16-byte piece i: run k = i/2, features 8*(i%2) .. +7 of it
+      const uint4 a = live ? *reinterpret_cast<const uint4*>(src + (i / 2) * 64 + (i % 2) * 8) : make_uint4(0, 0, 0, 0);
+      const uint4 f = flip[i];
       const uint32_t w[4] = {a.x ^ f.x, a.y ^ f.y, a.z ^ f.z, a.w ^ f.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -170,8 +177,7 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
       }
     }
   }
-#pragma unroll
-  for (int bit = 1; bit < 32; bit <<= 1) {
+  auto in_registers = [&](int bit) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       if (!(i & bit)) {
@@ -179,9 +185,10 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
         x[i] = lo + hi; x[i | bit] = lo - hi;
       }
     }
-  }
+  };
+  in_registers(1); in_registers(2); in_registers(4); in_registers(8);          // feature bits 0-3
 #pragma unroll
-  for (int bit = 1; bit < 4; bit <<= 1) {
+  for (int bit = 1; bit < 4; bit <<= 1) {                                       // feature bits 4-5
     const float sign = (l4 & bit) ? -1.f : 1.f;   // upper lane: partner - own; lower lane: own + partner
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -189,6 +196,7 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
       x[i] = fmaf(x[i], sign, y);                 // one rounding of y +- x, like the add / subtract it replaces
     }
   }
+  in_registers(16);                                                             // feature bit 6
   float m0 = 0.f, m1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
@@ -201,15 +209,15 @@ __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q,
   if (!live) return;
   const int64_t r = (int64_t)unit * tokens + row;
   const float inv = m > 0.f ? 127.f / m : 0.f;
-  uint4* d8 = reinterpret_cast<uint4*>(q8 + r * D + l4 * 32);
-  d8[0] = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv);
-  d8[1] = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv);
+  int8_t* d8 = q8 + r * D + l4 * 16;
+  *reinterpret_cast<uint4*>(d8) = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv);
+  *reinterpret_cast<uint4*>(d8 + 64) = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv);
   if (l4 == 0) qa[r] = m / 127.f;
   if (q4x != nullptr) {
     const float inv4 = m > 0.f ? 7.f / m : 0.f;
-    uint4* d4 = reinterpret_cast<uint4*>(q4x + r * D + l4 * 32);
-    d4[0] = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv4);
-    d4[1] = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv4);
+    int8_t* d4 = q4x + r * D + l4 * 16;
+    *reinterpret_cast<uint4*>(d4) = codes16(reinterpret_cast<const float(&)[16]>(x[0]), inv4);
+    *reinterpret_cast<uint4*>(d4 + 64) = codes16(reinterpret_cast<const float(&)[16]>(x[16]), inv4);
     if (l4 == 0) qa4[r] = m / 7.f;
   }
 }
