@@ -37,12 +37,28 @@ INF = 1 << 20
 CONFIG = dict(workload="decode C2: 24 Q / 8 KV heads, head_dim 128, batch 32, cache 8192 tokens, one layer-step",
               heads_q=24, heads_kv=8, batch=32, cache_tokens=8192, map="seed 1: 4 INT8 / 2 INT4 / 2 BF16 KV heads",
               l2="inputs larger than L2 (551 MB of cache per step per GPU)")
+CONFIG["kinds"] = ["int8"] * 4 + ["int4"] * 2 + ["bf16"] * 2
+# BASELINE config 5 (--workload decode-long): a secondary line, same metric
+CONFIG_LONG = dict(workload="decode C5: 32 Q / 8 KV heads, head_dim 128, batch 64, cache 131072 tokens, one layer-step",
+                   heads_q=32, heads_kv=8, batch=64, cache_tokens=131072, map="seed 1: 4 INT4 / 3 INT8 / 1 BF16 KV heads",
+                   l2="inputs larger than L2 (13.47 GB of cache per step per GPU)",
+                   kinds=["int4"] * 4 + ["int8"] * 3 + ["bf16"])
 FALLBACK_HBM_GBS = 6650.0
 
 
 def kv_kinds(seed=1):
-    kinds = np.array(["int8"] * 4 + ["int4"] * 2 + ["bf16"] * 2)
-    return [str(x) for x in np.random.default_rng(seed).permutation(kinds)]
+    return [str(x) for x in np.random.default_rng(seed).permutation(np.array(CONFIG["kinds"]))]
+
+
+def synth_cuda(shape, seed, fraction=0.01, factor=20.0):
+    """synth() generated on the GPU (the long workload's prompts are 270 M values per sequence)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32)
+    h = shape[0]
+    pick = torch.randperm(h * 128, generator=g, device="cuda")[: int(round(fraction * h * 128))]
+    scale = torch.ones(h * 128, device="cuda")
+    scale[pick] = factor
+    return (x * scale.view(h, 1, 128)).to(torch.bfloat16)
 
 
 def synth(shape, seed, fraction=0.01, factor=20.0):
@@ -100,8 +116,9 @@ class ClockSampler:
                     samples=len(rows))
 
 
-def build_cache(batch, seed0, tile_costs=None, fused_merge=False):
-    """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan)."""
+def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None):
+    """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan).
+    part = sequences written per pass (None = all at once); with it the prompts are generated on the GPU."""
     from triattention_b200.kernels.decode import DecodeCache
     from triattention_b200.kernels.extension import load_extension
     from triattention_b200.kernels.prefill import Prefill
@@ -110,14 +127,18 @@ def build_cache(batch, seed0, tile_costs=None, fused_merge=False):
     module = load_extension()
     cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, **({"tile_costs": tile_costs} if tile_costs else {}))
     pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
-    k = torch.empty((batch, hk, t, 128), dtype=torch.bfloat16, device="cuda")
+    make = synth_cuda if part else (lambda shape, seed: synth(shape, seed).cuda())
+    step = part or batch
+    k = torch.empty((step, hk, t, 128), dtype=torch.bfloat16, device="cuda")
     v = torch.empty_like(k)
-    for b in range(batch):
-        k[b] = synth((hk, t, 128), 2 * (seed0 + b)).cuda()
-        v[b] = synth((hk, t, 128), 2 * (seed0 + b) + 1).cuda()
-    q = torch.zeros((1, 1, 1, 128), dtype=torch.bfloat16, device="cuda").expand(batch, hq, t, 128)   # Q does not enter the cache
-    table, ops = pre.write(0, q, k, v)
-    cache.store(0, t, ops, table.host, k, v, table.bf16_kv)
+    q = torch.zeros((1, 1, 1, 128), dtype=torch.bfloat16, device="cuda").expand(step, hq, t, 128)   # Q does not enter the cache
+    for first in range(0, batch, step):
+        n = min(step, batch - first)
+        for b in range(n):
+            k[b] = make((hk, t, 128), 2 * (seed0 + first + b))
+            v[b] = make((hk, t, 128), 2 * (seed0 + first + b) + 1)
+        table, ops = pre.write(0, q[:n], k[:n], v[:n])
+        cache.store(0, t, ops, table.host, k[:n], v[:n], table.bf16_kv, first_sequence=first, sequences=batch)
     torch.cuda.synchronize()
     pre.buffers.clear(), pre.views.clear()
     del k, v, ops
@@ -162,10 +183,9 @@ def timed(fn, steps, dist, finish=None):
 
 class CpuPort:
     """The CPU oracle port on one sequence of the workload: one decode step of 24 heads over 8192 cached tokens."""
-    SAMPLE = ("1 of the 32 sequences per step, one layer-step (24 heads over 8192 cached tokens); numpy/IEEE "
-              "restatement of the reference's CUDA arithmetic")
-
     def __init__(self, threads):
+        self.SAMPLE = (f"1 of the {CONFIG['batch']} sequences per step, one layer-step ({CONFIG['heads_q']} heads over "
+                       f"{CONFIG['cache_tokens']} cached tokens); numpy/IEEE restatement of the reference's CUDA arithmetic")
         sys.path.insert(0, str(ROOT / "oracle"))
         import triattention_oracle as orc
         self.orc, self.threads = orc, threads
@@ -224,7 +244,7 @@ def run_prefill(args):
     from triattention_b200.maps import per_kv_head
     torch.cuda.set_device(0)
     module = load_extension()
-    b, hq, hk, t = (args.batch if args.batch != CONFIG["batch"] else 2), 28, 4, args.tokens
+    b, hq, hk, t = args.batch, 28, 4, args.tokens
     kinds = [str(x) for x in np.random.default_rng(1).permutation(np.array(["int8", "int8", "int8", "int4"]))]
     q = torch.stack([synth((hq, t, 128), 10 + i) for i in range(b)]).cuda()
     k = torch.stack([synth((hk, t, 128), 20 + i) for i in range(b)]).cuda()
@@ -274,7 +294,7 @@ def run_model(args):
     from triattention_b200.maps import INF, from_bands
     from triattention_b200.models import TriAttention
     torch.cuda.set_device(0)
-    batch = args.batch if args.batch != CONFIG["batch"] else 16
+    batch = args.batch
     prompt, new, layers, hq, hk = args.tokens if args.tokens != 16384 else 4096, args.new_tokens, 28, 24, 8
     cfg = LlamaConfig(hidden_size=3072, intermediate_size=8192, num_hidden_layers=layers, num_attention_heads=hq,
                       num_key_value_heads=hk, head_dim=128, vocab_size=128256, max_position_embeddings=prompt + new + 8,
@@ -356,9 +376,10 @@ def run_model(args):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
-                        help="decode = the benchmark contract (BASELINE config 2); prefill = config 3, secondary metric; "
-                             "model = config 4 end to end through the Hugging Face hook, secondary metric")
+    parser.add_argument("--workload", default="decode", choices=["decode", "decode-long", "prefill", "model"],
+                        help="decode = the benchmark contract (BASELINE config 2); decode-long = config 5 (64 sequences x "
+                             "131072 cached tokens, 13.5 GB per step), prefill = config 3, model = config 4 end to end "
+                             "through the Hugging Face hook: secondary metrics")
     parser.add_argument("--new-tokens", type=int, default=128, help="greedy new tokens of the model workload")
     parser.add_argument("--tokens", type=int, default=16384, help="prompt length of the prefill workload")
     parser.add_argument("--gpus", type=int, default=1)
@@ -369,9 +390,20 @@ def main():
     parser.add_argument("--tile-costs", default="", help="override the decode partition's cost model: bf16,k8v8,other (relative)")
     parser.add_argument("--fused-merge", action="store_true",
                         help="one launch per step: the CTA that finishes a unit's last segment merges it")
-    parser.add_argument("--batch", type=int, default=CONFIG["batch"],
-                        help="sequences per GPU; anything but 32 is a reduced case for profiler captures, flagged in the output")
+    parser.add_argument("--batch", type=int, default=None,
+                        help="sequences per GPU; anything but the configuration's is a reduced case for profiler captures, "
+                             "flagged in the output")
     args = parser.parse_args()
+    long_case = args.workload == "decode-long"
+    if long_case:
+        CONFIG.clear()
+        CONFIG.update(CONFIG_LONG)
+        if args.steps == 200:
+            args.steps = 50
+        if args.cpu_steps == 10:
+            args.cpu_steps = 2      # one sequence-step of the CPU port over 131072 tokens takes seconds
+    if args.batch is None:
+        args.batch = {"model": 16, "prefill": 2}.get(args.workload, CONFIG["batch"])
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -393,7 +425,8 @@ def main():
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
     warmup = max(3, args.warmup)
     costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
-    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs, fused_merge=args.fused_merge)
+    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs, fused_merge=args.fused_merge,
+                                      part=2 if long_case else None)
     scale = 128 ** -0.5
     # decode-step inputs: device-resident copies for `value`, pinned host copies for `e2e`
     host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (rank * batch + b)) for b in range(batch)]).pin_memory()

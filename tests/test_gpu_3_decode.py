@@ -233,3 +233,33 @@ def test_fold_tail_lifts_the_generation_cap(module):
     small.generated = 128
     with pytest.raises(RuntimeError):
         small.fold(0), small.fold(0)
+
+
+def test_store_in_parts_equals_store_at_once(module):
+    """A cache filled one group of sequences at a time (long prompts) holds the same bytes and statistics."""
+    hq, hk, t, batch = 6, 3, 330, 4
+    bands = np.asarray([[INF, INF]] * 2 + [[1, INF]] * 2 + [[INF, INF]] * 2, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=81, batch=batch)
+    qd, kd, vd = make_inputs(hq, hk, 1, seed=82, batch=batch)
+    kc, vc, qc = bf16_cuda(k), bf16_cuda(v), bf16_cuda(q)
+    whole = DecodeCache(module, max_tail=4)
+    pre = Prefill(module, bands_fn_of(bands, (2,)), whole)
+    table, ops = pre.write(0, qc, kc, vc)
+    whole.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
+    parts = DecodeCache(module, max_tail=4)
+    pre2 = Prefill(module, bands_fn_of(bands, (2,)), parts)
+    for first, n in ((0, 1), (1, 2), (3, 1)):
+        sl = slice(first, first + n)
+        table, ops = pre2.write(0, qc[sl], kc[sl], vc[sl])
+        parts.store(0, t, ops, table.host, kc[sl], vc[sl], table.bf16_kv, first_sequence=first, sequences=batch)
+    a, b = whole.layers[0], parts.layers[0]
+    assert torch.equal(a["kstat"], b["kstat"]) and torch.equal(a["vstat"], b["vstat"])
+    plan = a["plan"]
+    for unit, base in enumerate(plan["unit_base"]):            # every unit's stream, without the alignment padding behind it
+        used = int(plan["append_off"][unit % hk])
+        assert torch.equal(a["pool"][int(base):int(base) + used], b["pool"][int(base):int(base) + used]), unit
+    args = (0, bf16_cuda(qd), bf16_cuda(kd), bf16_cuda(vd), SCALE)
+    assert torch.equal(whole(*args), parts(*args))
+    module.check_device_error()
+    with pytest.raises(RuntimeError):
+        DecodeCache(module, max_tail=4).store(0, t, ops, table.host, kc[3:], vc[3:], table.bf16_kv, first_sequence=3, sequences=batch)

@@ -196,13 +196,23 @@ class DecodeCache:
             self.plans[key] = host, dev
         return self.plans[key]
 
-    def store(self, layer, prompt, ops, bands, k, v, bf16_kv=()):
-        """Build the layer's cache streams from the prefill operands (one gather launch, plus one for BF16 units)."""
-        batch, heads_kv, device = k.shape[0], k.shape[1], k.device
+    def store(self, layer, prompt, ops, bands, k, v, bf16_kv=(), first_sequence=0, sequences=None):
+        """Build the layer's cache streams from the prefill operands (one gather launch, plus one for BF16 units).
+        A cache of `sequences` sequences can be filled in parts (long prompts, whose write-path operands for the
+        whole batch would not fit beside the cache): every call brings k.shape[0] sequences starting at
+        first_sequence; the call with first_sequence = 0 (re)allocates."""
+        part, heads_kv, device = k.shape[0], k.shape[1], k.device
+        batch = part if sequences is None else int(sequences)
+        if not 0 <= first_sequence <= batch - part:
+            raise ValueError("store: sequences outside the cache")
         host, dev = self.plan(bands, heads_kv, prompt, batch, bf16_kv, device)
         entry = self.layers.get(layer)
-        if entry is None or entry["pool"].numel() != host["pool_bytes"] or entry["plan"] is not host:
-            units, slots = batch * heads_kv, max(1, host["slots"])
+        fresh = entry is None or entry["pool"].numel() != max(16, host["pool_bytes"]) or entry["plan"] is not host
+        if fresh and first_sequence != 0:
+            raise RuntimeError("store: the part with first_sequence = 0 comes first")
+        units = batch * heads_kv
+        if fresh:
+            slots = max(1, host["slots"])
             if self.reserve:
                 slots = units + self.wave(device)     # an upper bound for every number of appended tiles
             f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=device)
@@ -211,7 +221,8 @@ class DecodeCache:
                 pool=torch.empty(max(16, host["pool_bytes"]), dtype=torch.uint8, device=device),
                 tail_k=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
                 tail_v=torch.zeros((units, self.max_tail, 128), dtype=torch.bfloat16, device=device),
-                pm=f32(slots, MAX_GROUP), pl=f32(slots, MAX_GROUP), po=f32(slots, MAX_GROUP, 128), unit_done=None)
+                pm=f32(slots, MAX_GROUP), pl=f32(slots, MAX_GROUP), po=f32(slots, MAX_GROUP, 128), unit_done=None,
+                kstat=f32(units, 3, 128), vstat=f32(units, 3, 128))
             if self.split is None and self.fused_merge and int(host["unit_slots"][:, 1].min()) >= 1:
                 entry["unit_done"] = torch.zeros(units, dtype=torch.int32, device=device)   # segments finished per unit
             if self.split is not None:   # folded triples of this rank, and of all ranks after the all-gather
@@ -221,7 +232,9 @@ class DecodeCache:
                              go=f32(world, units, MAX_GROUP, 128),
                              rank_slots=torch.stack([torch.arange(units, dtype=torch.int32) * world,
                                                      torch.full((units,), world, dtype=torch.int32)], 1).to(device))
-        entry["kstat"], entry["vstat"] = ops["kstat"].clone(), ops["vstat"].clone()
+        lo, n = first_sequence * heads_kv, part * heads_kv        # this call's units
+        entry["kstat"][lo:lo + n] = ops["kstat"].view(n, 3, 128)
+        entry["vstat"][lo:lo + n] = ops["vstat"].view(n, 3, 128)
         entry.update(extra=0, geometry=(np.asarray(bands), heads_kv, prompt, batch, tuple(bf16_kv)))
         if self.step is None:
             self.step = torch.zeros(1, dtype=torch.int64, device=device)
@@ -229,15 +242,17 @@ class DecodeCache:
         self.generated = 0
         max_count = int(host["count"].max())
         if max_count > 0:
-            self.module.cache_store(entry["pool"], dev["unit_base"], dev["unit_tab"], dev["unit_count"], dev["unit_flags"],
-                                    dev["tmeta"], batch * heads_kv, max_count, ops["k8"], ops["k4"], ops["ka"], ops["ka4"],
-                                    ops["v8"], ops["v4"], host["tiles"])
+            self.module.cache_store(entry["pool"], dev["unit_base"][lo:lo + n], dev["unit_tab"][lo:lo + n],
+                                    dev["unit_count"][lo:lo + n], dev["unit_flags"][lo:lo + n], dev["tmeta"], n, max_count,
+                                    ops["k8"], ops["k4"], ops["ka"], ops["ka4"], ops["v8"], ops["v4"], host["tiles"])
         if bf16_kv:
+            mine = dev["bf16_units"][(dev["bf16_units"] >= lo) & (dev["bf16_units"] < lo + n)]
             if host["bf16_range"][1] > 0:
-                self.module.cache_store_bf16(entry["pool"], dev["unit_base"], dev["bf16_units"], k, v, *host["bf16_range"])
+                self.module.cache_store_bf16(entry["pool"], dev["unit_base"][lo:lo + n], (mine - lo).to(torch.int32), k, v,
+                                             *host["bf16_range"])
             ident = torch.tensor([0.0, 1.0, 1.0], device=device)[None, :, None]
-            entry["kstat"][dev["bf16_units"].long()] = ident
-            entry["vstat"][dev["bf16_units"].long()] = ident
+            entry["kstat"][mine.long()] = ident
+            entry["vstat"][mine.long()] = ident
 
     def fold(self, layer):
         """Quantise the first 64 rows of the layer's tail into one more tile of every unit's stream."""
