@@ -116,7 +116,7 @@ class ClockSampler:
                     samples=len(rows))
 
 
-def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None):
+def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, split_group=None):
     """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan).
     part = sequences written per pass (None = all at once); with it the prompts are generated on the GPU."""
     from triattention_b200.kernels.decode import DecodeCache
@@ -125,7 +125,8 @@ def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None):
     from triattention_b200.maps import per_kv_head
     hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
     module = load_extension()
-    cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, **({"tile_costs": tile_costs} if tile_costs else {}))
+    cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, split_group=split_group,
+                        **({"tile_costs": tile_costs} if tile_costs else {}))
     pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
     make = synth_cuda if part else (lambda shape, seed: synth(shape, seed).cuda())
     step = part or batch
@@ -390,6 +391,9 @@ def main():
     parser.add_argument("--tile-costs", default="", help="override the decode partition's cost model: bf16,k8v8,other (relative)")
     parser.add_argument("--fused-merge", action="store_true",
                         help="one launch per step: the CTA that finishes a unit's last segment merges it")
+    parser.add_argument("--split", action="store_true",
+                        help="with --gpus N: the SAME sequences on every GPU, every unit's tile range cut N ways (sequence "
+                             "split, one all-gather of folded partials per step); strong scaling, a diagnostic")
     parser.add_argument("--batch", type=int, default=None,
                         help="sequences per GPU; anything but the configuration's is a reduced case for profiler captures, "
                              "flagged in the output")
@@ -421,20 +425,26 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=timedelta(seconds=120))
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
     warmup = max(3, args.warmup)
     costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
-    module, cache, plan = build_cache(batch, seed0=rank * batch, tile_costs=costs, fused_merge=args.fused_merge,
-                                      part=2 if long_case else None)
+    split = args.split and world > 1
+    seed0 = 0 if split else rank * batch
+    module, cache, plan = build_cache(batch, seed0=seed0, tile_costs=costs, fused_merge=args.fused_merge,
+                                      part=2 if (long_case and not split) else None,
+                                      split_group=dist.group.WORLD if split else None)
     scale = 128 ** -0.5
     # decode-step inputs: device-resident copies for `value`, pinned host copies for `e2e`
-    host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (rank * batch + b)) for b in range(batch)]).pin_memory()
+    host = [torch.stack([synth((h, 1, 128), 100 + i + 1000 * (seed0 + b)) for b in range(batch)]).pin_memory()
             for i, h in enumerate((hq, hk, hk))]
     qd, kd, vd = (x.cuda() for x in host)
     out = torch.empty_like(qd)
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    warmup = warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), warmup)
+    # With a collective inside the step every rank must run the same number of steps: no time-based loops then.
+    warmup = warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), max(warmup, 300) if split else warmup,
+                     seconds=0.0 if split else 0.3)
     module.check_device_error()
     with ClockSampler(local) as clocks:
         ms_total = timed(lambda i: cache(0, qd, kd, vd, scale, out=out), args.steps, dist)
@@ -454,7 +464,9 @@ def main():
         # a short timed region gives nvidia-smi (100 ms period) little to sample: keep the same load running,
         # untimed, until a handful of samples are in
         t_extra, extra = time.time(), 0
-        while len(clocks.rows) < 8 and time.time() - t_extra < 4.0:
+        for burst in range(5 if split else 10 ** 6):
+            if not split and not (len(clocks.rows) < 8 and time.time() - t_extra < 4.0):
+                break
             for i in range(200):
                 cache(0, qd, kd, vd, scale, out=out)
             torch.cuda.synchronize()
@@ -465,14 +477,14 @@ def main():
     if rank != 0:
         dist.destroy_process_group()
         return
-    tokens = batch * world
+    tokens = batch if split else batch * world
     peak, peak_kind = peak_hbm()
     bytes_per_launch = plan["payload_bytes"]
     kernel_s = ms_kernel / args.steps / 1e3
     achieved = bytes_per_launch / kernel_s / 1e9
     line = dict(metric="decode_tokens_per_s", value=tokens * args.steps / (ms_total / 1e3), unit="tokens/s", n_gpus=world,
-                steps=args.steps, warmup=warmup, ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak",
-                vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG,
+                steps=args.steps, warmup=warmup, ms_per_step=ms_total / args.steps, higher_is_better=True,
+                scaling="strong" if split else "weak", vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG,
                 e2e=dict(value=tokens * args.steps / (ms_e2e / 1e3), unit="tokens/s",
                          h2d_bytes_per_step=sum(x.numel() * 2 for x in host), d2h_bytes_per_step=out.numel() * 2),
                 gpu_launches=(1 if cache.layers[0]["unit_done"] is not None else 2) * args.steps,
@@ -486,6 +498,8 @@ def main():
                               ctas=int(plan["cta_segments"].shape[0] - 1), segments=int(plan["segments"].shape[0])),
                 hbm_gbs_whole_step=bytes_per_launch / (ms_total / args.steps / 1e3) / 1e9,
                 clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))
+    if split:
+        line["sequence_split"] = f"every unit's tile range cut over {world} GPUs; one all-gather of folded partials per step"
     if batch != CONFIG["batch"]:
         line["reduced_case"] = f"batch {batch} instead of {CONFIG['batch']}: not a benchmark value"
     if args.cpu_steps > 0:

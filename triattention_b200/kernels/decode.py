@@ -225,11 +225,17 @@ class DecodeCache:
                 kstat=f32(units, 3, 128), vstat=f32(units, 3, 128))
             if self.split is None and self.fused_merge and int(host["unit_slots"][:, 1].min()) >= 1:
                 entry["unit_done"] = torch.zeros(units, dtype=torch.int32, device=device)   # segments finished per unit
-            if self.split is not None:   # folded triples of this rank, and of all ranks after the all-gather
-                world = self.split[1]
-                entry.update(fm=f32(units, MAX_GROUP), fl=f32(units, MAX_GROUP), fo=f32(units, MAX_GROUP, 128),
-                             gm=f32(world, units, MAX_GROUP), gl=f32(world, units, MAX_GROUP),
-                             go=f32(world, units, MAX_GROUP, 128),
+            if self.split is not None:
+                # Folded triples of this rank in ONE buffer (m | l | o), so that a step needs one all-gather, and
+                # those of all ranks after it.
+                world, ug = self.split[1], units * MAX_GROUP
+                mine, every = f32(ug * 130), f32(world, ug * 130)
+                entry.update(folded=mine, gathered=every,
+                             fm=mine[:ug].view(units, MAX_GROUP), fl=mine[ug:2 * ug].view(units, MAX_GROUP),
+                             fo=mine[2 * ug:].view(units, MAX_GROUP, 128),
+                             gm=every[:, :ug].unflatten(1, (units, MAX_GROUP)),
+                             gl=every[:, ug:2 * ug].unflatten(1, (units, MAX_GROUP)),
+                             go=every[:, 2 * ug:].unflatten(1, (units, MAX_GROUP, 128)),
                              rank_slots=torch.stack([torch.arange(units, dtype=torch.int32) * world,
                                                      torch.full((units,), world, dtype=torch.int32)], 1).to(device))
         lo, n = first_sequence * heads_kv, part * heads_kv        # this call's units
@@ -296,7 +302,7 @@ class DecodeCache:
             q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"], d["cta_segments"],
             slots, e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, pm, pl, po, e["prompt"], scale, ph,
             unit_done=e["unit_done"] if ph == 3 else None)
-        if self.split is None:
+        if self.split is None or phases != 3:      # (single phases: each kernel timed alone, on this rank's part)
             run(e["pm"], e["pl"], e["po"], d["unit_slots"], phases)
             return out
         # sequence split: local split pass, fold to one triple per (unit, Q head), all-gather over the group,
@@ -304,8 +310,7 @@ class DecodeCache:
         import torch.distributed as dist
         run(e["pm"], e["pl"], e["po"], d["unit_slots"], 1)
         self.module.decode_fold(e["pm"], e["pl"], e["po"], d["unit_slots"], e["fm"], e["fl"], e["fo"], q.shape[1] // k.shape[1])
-        for mine, gathered in ((e["fm"], e["gm"]), (e["fl"], e["gl"]), (e["fo"], e["go"])):
-            dist.all_gather_into_tensor(gathered, mine[None], group=self.split_group)
+        dist.all_gather_into_tensor(e["gathered"], e["folded"][None], group=self.split_group)
         merged = [g.transpose(0, 1).contiguous() for g in (e["gm"], e["gl"], e["go"])]   # [unit][rank][...]
         run(merged[0], merged[1], merged[2], e["rank_slots"], 2)
         return out
