@@ -265,9 +265,13 @@ def run_prefill(args):
             extra += 1
     module.check_device_error()
     # KV-write traffic: Q once, K and V twice (statistics pass + quantising pass), every operand buffer written once
-    _, written = pre.write(0, q, k, v)
-    write_bytes = q.nbytes + 2 * k.nbytes + 2 * v.nbytes + sum(x.nbytes for name, x in written.items()
-                                                                 if x is not None and name != "partial")
+    # (Q codes only for the heads whose band needs them: BandTable.q_modes)
+    table, written = pre.write(0, q, k, v)
+    modes = table.q_modes.cpu()
+    share = dict(q8=float((modes & 1).ne(0).float().mean()), q4x=float((modes & 2).ne(0).float().mean()))
+    share.update(qa=share["q8"], qa4=share["q4x"])
+    write_bytes = q.nbytes + 2 * k.nbytes + 2 * v.nbytes + int(sum(x.nbytes * share.get(name, 1.0) for name, x in written.items()
+                                                                     if x is not None and name != "partial"))
     rows = (t + 63) // 64
     ops = b * hq * (rows * (rows + 1) // 2) * 2 * 64 * 64 * 128 * 2
     tops = ops / ((ms_all - ms_write) / 1e3) / 1e12

@@ -33,12 +33,15 @@ int tri_abi_version(void);
  * q8 int8 [B*Hq,T,128]; qa f32 [B*Hq,T]; k8 K8 blobs [B*Hkv,tiles,8192 B]; ka f32 [B*Hkv,tiles,4];
  * partial f32 [B*Hkv,64,3,128] scratch; kstat f32 [B*Hkv,3,128] (mean, -, -).
  * INT4 outputs, all or none: q4x int8 [B*Hq,T,128] (4-bit codes as int8), qa4, k4x K4X blobs
- * [B*Hkv,tiles,8192 B], ka4; k4 (optional with the others) packed K4 blobs [B*Hkv,tiles,4096 B]. */
+ * [B*Hkv,tiles,8192 B], ka4; k4 (optional with the others) packed K4 blobs [B*Hkv,tiles,4096 B].
+ * q_modes int32 [Hq] on the device or NULL (no counterpart in the reference, which quantises every head both ways):
+ * what tri_attention will read of each Q head, bit 0 = the INT8 codes, bit 1 = the INT4 codes; rows of q8 / q4x
+ * (and qa / qa4) whose bit is clear are left untouched.  NULL = every head, both. */
 int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int heads_kv, int tokens,
                    int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
                    int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
                    void* q8, float* qa, void* k8, float* ka, float* partial, float* kstat,
-                   void* q4x, float* qa4, void* k4x, void* k4, float* ka4, void* stream);
+                   void* q4x, float* qa4, void* k4x, void* k4, float* ka4, const int32_t* q_modes, void* stream);
 
 /* Per-channel affine normalisation of V and packing into FP16 / INT8 / INT4 tile blobs.
  * Replaces pack_v(v,partial,vstat,v16p,v8p,v4p), triattention/kernels/cuda/common_host.cuh:27-45.

@@ -215,7 +215,7 @@ def test_library_exports_every_declared_symbol():
 def test_argument_errors_without_gpu():
     """Validation happens before any CUDA call, so it can be exercised on CPU."""
     lib = load_library()
-    assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 12)) == -1
+    assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 13)) == -1
     assert b"null" in lib.tri_last_error()
     assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 7)) == -1
 

@@ -153,3 +153,28 @@ def test_requantize_with_given_statistics(module, rows):
             rate, big = code_mismatch(got, want)
             assert big <= 1 and rate <= CODE_RATE, (name, rate, big)
         assert np.abs(got_v[b]).max() == 127 and not got_k[b].reshape(hk, -1, 128)[:, rows:].any()
+
+
+def test_q_modes_skip_what_the_attention_does_not_read(module):
+    """q_modes: a head without an INT4 band gets no INT4 codes, an un-quantised head no codes at all; what is written
+    equals the unmasked run, and the prefill result does not change."""
+    from triattention_b200.kernels.prefill import BandTable
+    hq, hk, t = 6, 3, 200
+    q, k, v = make_inputs(hq, hk, t, seed=43, batch=2)
+    full = run_write(module, q, k, v)
+    bands = np.asarray([[INF, INF]] * 2 + [[1, INF]] * 2 + [[INF, INF]] * 2, np.int64)
+    table = BandTable.build(bands, (t + 63) // 64, hk, "cuda", bf16_kv=(2,))
+    assert table.q_modes.tolist() == [1, 1, 3, 3, 0, 0]
+    ops = Prefill(module, None).operands(2, hq, hk, t, True, True, frozenset({F16, I8, I4}), "cuda")
+    for name in ("q8", "q4x"):
+        ops[name].fill_(-128)
+    ops["qa"].fill_(-1.0), ops["qa4"].fill_(-1.0)
+    module.prepare_qk(bf16_cuda(q), bf16_cuda(k), ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"],
+                      ops["q4x"], ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"], q_modes=table.q_modes)
+    torch.cuda.synchronize()
+    q8, q4 = ops["q8"].cpu().numpy().reshape(2, hq, t, 128), ops["q4x"].cpu().numpy().reshape(2, hq, t, 128)
+    qa, qa4 = ops["qa"].cpu().numpy().reshape(2, hq, t), ops["qa4"].cpu().numpy().reshape(2, hq, t)
+    assert (q8[:, :4] == full["q8"][:, :4]).all() and (qa[:, :4] == full["qa"][:, :4]).all()
+    assert (q4[:, 2:4] == full["q4"][:, 2:4]).all() and (qa4[:, 2:4] == full["qa4"][:, 2:4]).all()
+    assert (q8[:, 4:] == -128).all() and (qa[:, 4:] == -1).all()                    # un-quantised heads: untouched
+    assert (q4[:, :2] == -128).all() and (q4[:, 4:] == -128).all() and (qa4[:, :2] == -1).all()

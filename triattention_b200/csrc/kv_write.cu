@@ -154,12 +154,17 @@ __device__ const PairSigns kPairSigns = make_pair_signs();
 // q8/q4x are plain [B*Hq][T][128] int8 (the reference's q8 layout, common_device.cuh:18); q4x holds the 4-bit
 // codes sign-extended to int8 so that the prefill kernel can feed them to the INT8 tensor-core path.
 __global__ void __launch_bounds__(128) quantize_q_kernel(const __nv_bfloat16* q, int8_t* q8, float* qa, int8_t* q4x,
-    float* qa4, int tokens, int heads, int64_t qsb, int64_t qsh, int64_t qst) {
+    float* qa4, const int32_t* q_modes, int tokens, int heads, int64_t qsb, int64_t qsh, int64_t qst) {
   grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
   grid_launch_dependents();
   const int lane = threadIdx.x % 32, l4 = lane % 4;
   const int row = blockIdx.x * 32 + (threadIdx.x / 32) * 8 + lane / 4;
   const int unit = blockIdx.y;
+  // what the attention will read of this head: bit 0 = INT8 codes, bit 1 = INT4 codes (a head without an INT4 band
+  // needs none, an un-quantised head neither)
+  const int mode = q_modes != nullptr ? q_modes[unit % heads] : 3;
+  if (!(mode & 1)) return;
+  if (!(mode & 2)) q4x = nullptr;
   const bool live = row < tokens;
   float x[32];   // x[16k + e] = feature 16*(l4 + 4k) + e
   {
@@ -414,7 +419,7 @@ using namespace tri;
 extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int heads_kv, int tokens,
     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t, int64_t k_stride_b, int64_t k_stride_h,
     int64_t k_stride_t, void* q8, float* qa, void* k8, float* ka, float* partial, float* kstat, void* q4x,
-    float* qa4, void* k4x, void* k4, float* ka4, void* stream) {
+    float* qa4, void* k4x, void* k4, float* ka4, const int32_t* q_modes, void* stream) {
   TRI_CHECK(q && k && q8 && qa && k8 && ka && partial && kstat, "prepare_qk: null Q/K buffers");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && tokens > 0 && heads_q % heads_kv == 0, "prepare_qk: bad geometry");
   TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
@@ -431,7 +436,7 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
   const auto* kp = static_cast<const __nv_bfloat16*>(k);
   launch_chained(quantize_q_kernel, dim3((tokens + 31) / 32, uq), dim3(128), 0, s, qp, static_cast<int8_t*>(q8), qa,
-      static_cast<int8_t*>(q4x), qa4, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
+      static_cast<int8_t*>(q4x), qa4, q_modes, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
   launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, partial, nullptr, tokens, heads_kv,
       k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
   launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, partial, nullptr, kstat, nullptr, tokens, 0);

@@ -20,7 +20,7 @@ _P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_dou
 
 # name -> argtypes, in the order of include/triattention_b200.h
 SIGNATURES = {
-    "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P],
     "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
@@ -92,7 +92,8 @@ class Module:
         return x
 
     # -- reference surface ---------------------------------------------------------------------
-    def prepare_qk(self, q, k, q8, qa, k8, ka, partial, kstat, q4x=None, qa4=None, k4x=None, ka4=None, k4=None):
+    def prepare_qk(self, q, k, q8, qa, k8, ka, partial, kstat, q4x=None, qa4=None, k4x=None, ka4=None, k4=None,
+                   q_modes=None):
         self._bhtd(q, "Q"), self._bhtd(k, "K")
         b, hq, t, _ = q.shape
         hk, tiles = k.shape[1], (t + 63) // 64
@@ -105,12 +106,15 @@ class Module:
         int4 = q4x is not None
         if not (int4 == (qa4 is not None) == (k4x is not None) == (ka4 is not None)) or (k4 is not None and not int4):
             raise RuntimeError("INT4 Q/K buffers (all or none)")
+        if q_modes is not None and not (q_modes.is_cuda and q_modes.dtype == torch.int32 and q_modes.numel() == hq
+                                        and q_modes.is_contiguous()):
+            raise RuntimeError("q_modes int32 [Hq] on the device")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_prepare_qk(q.data_ptr(), k.data_ptr(), b, hq, hk, t, q.stride(0), q.stride(1),
                                                 q.stride(2), k.stride(0), k.stride(1), k.stride(2), q8.data_ptr(),
                                                 qa.data_ptr(), k8.data_ptr(), ka.data_ptr(), partial.data_ptr(),
                                                 kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4), _ptr(ka4),
-                                                _stream()))
+                                                _ptr(q_modes), _stream()))
 
     def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None, v8h=None):
         self._bhtd(v, "V")

@@ -27,6 +27,7 @@ class BandTable:
     formats: frozenset
     host: torch.Tensor       # int32 [Hq,2] as given by the map
     bf16_kv: tuple = ()
+    q_modes: torch.Tensor = None   # int32 [Hq] on the device: bit 0 = the head's INT8 Q codes are read, bit 1 = its INT4 codes
 
     @classmethod
     def build(cls, bands, rows, kv_heads, device, bf16_kv=()):
@@ -49,7 +50,10 @@ class BandTable:
         host = b.to(torch.int32).contiguous()
         dev = host.clone()
         dev[~quant] = 0
-        return cls(order.to(torch.int32).to(device), dev.to(device), frozenset(formats), host, tuple(sorted(bf16_kv)))
+        modes = torch.zeros(b.shape[0], dtype=torch.int32)
+        modes[quant] = 1 + 2 * (n4 > 0).any(dim=1).to(torch.int32)
+        return cls(order.to(torch.int32).to(device), dev.to(device), frozenset(formats), host, tuple(sorted(bf16_kv)),
+                   modes.to(device))
 
 
 class Prefill:
@@ -113,7 +117,7 @@ class Prefill:
         ops = self.operands(b, hq, hk, t, int4, need_k4, formats, device)
         m = self.module
         m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
-                     ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
+                     ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"], q_modes=table.q_modes)
         m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"])
         return table, ops
 
