@@ -38,6 +38,9 @@ SIGNATURES = {
 }
 
 
+ABI_VERSION = 2      # tri_abi_version() of the library these signatures describe
+
+
 def load_library() -> ctypes.CDLL:
     """dlopen the library and declare every entry point (no GPU needed for this)."""
     if not LIBRARY.is_file():
@@ -48,6 +51,9 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = argtypes, ctypes.c_int
     lib.tri_last_error.argtypes, lib.tri_last_error.restype = [], ctypes.c_char_p
+    if lib.tri_abi_version() != ABI_VERSION:     # a library built from older sources takes other arguments
+        raise RuntimeError(f"{LIBRARY.name} has ABI version {lib.tri_abi_version()}, this package wants {ABI_VERSION}: "
+                           "rebuild it with `python -m triattention_b200.build`")
     return lib
 
 
