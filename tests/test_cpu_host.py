@@ -250,3 +250,12 @@ def test_plan_streams_appended_tiles():
             assert (covered[unit, :p["unit_count"][unit]] == 1).all() and not covered[unit, p["unit_count"][unit]:].any()
     with pytest.raises(ValueError):
         dm.plan_streams(bands, 3, 200, 2, ctas=8, extra=1, split=(0, 2))
+
+
+def test_band_table_q_modes():
+    """Which Q codes the attention reads per head: INT8 codes for every quantised head, INT4 codes only where the band
+    has an INT4 part for some query block, nothing for heads of un-quantised KV groups."""
+    bands = [[maps.INF, maps.INF]] * 2 + [[1, maps.INF]] * 2 + [[2, 2]] * 2 + [[3, 9]] * 2
+    table = BandTable.build(bands, 40, 4, "cpu", bf16_kv=(0,))
+    assert table.q_modes.tolist() == [0, 0, 3, 3, 1, 1, 3, 3]
+    assert BandTable.build(bands, 3, 4, "cpu").q_modes.tolist() == [1, 1, 3, 3, 1, 1, 1, 1]   # 3 tiles: [3, 9] never gets past w8
