@@ -1,4 +1,4 @@
-"""Benchmark of the quantised-attention decode path (BASELINE config 2) on N B200s.
+"""Benchmark of the quantised-attention decode path (benchmark configuration 2) on N B200s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -38,7 +38,7 @@ CONFIG = dict(workload="decode C2: 24 Q / 8 KV heads, head_dim 128, batch 32, ca
               heads_q=24, heads_kv=8, batch=32, cache_tokens=8192, map="seed 1: 4 INT8 / 2 INT4 / 2 BF16 KV heads",
               l2="inputs larger than L2 (551 MB of cache per step per GPU)")
 CONFIG["kinds"] = ["int8"] * 4 + ["int4"] * 2 + ["bf16"] * 2
-# BASELINE config 5 (--workload decode-long): a secondary line, same metric
+# benchmark configuration 5 (--workload decode-long): a secondary line, same metric
 CONFIG_LONG = dict(workload="decode C5: 32 Q / 8 KV heads, head_dim 128, batch 64, cache 131072 tokens, one layer-step",
                    heads_q=32, heads_kv=8, batch=64, cache_tokens=131072, map="seed 1: 4 INT4 / 3 INT8 / 1 BF16 KV heads",
                    l2="inputs larger than L2 (13.47 GB of cache per step per GPU)",
@@ -238,7 +238,7 @@ def run_reference(args, rank):
 
 
 def run_prefill(args):
-    """Secondary metric: INT8 TOP/s of the banded prefill (BASELINE config 3: 28 Q / 4 KV heads, batch 2,
+    """Secondary metric: INT8 TOP/s of the banded prefill (benchmark configuration 3: 28 Q / 4 KV heads, batch 2,
     16384 tokens, 3 INT8 + 1 INT4 KV heads) including the fused KV-cache write.  One GPU, one JSON line."""
     from triattention_b200.kernels.extension import load_extension
     from triattention_b200.kernels.prefill import Prefill
@@ -290,7 +290,7 @@ def run_prefill(args):
 
 
 def run_model(args):
-    """Secondary metric: BASELINE config 4 end to end.  Random-init Llama-3.2-3B architecture (28 layers, hidden 3072,
+    """Secondary metric: benchmark configuration 4 end to end.  Random-init Llama-3.2-3B architecture (28 layers, hidden 3072,
     24 / 8 heads, head_dim 128, intermediate 8192 as in the public 3B configuration, vocab 128256), bf16 weights
     ~ N(0, 0.02); batch x prompt token ids uniform from a seed; greedy new tokens; per-layer seeded map of 5 INT8 /
     2 INT4 / 1 BF16 KV heads.  Prints tokens/s of the prompt pass and of the decode loop, layer-by-layer from Python
@@ -382,7 +382,7 @@ def run_model(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--workload", default="decode", choices=["decode", "decode-long", "prefill", "model"],
-                        help="decode = the benchmark contract (BASELINE config 2); decode-long = config 5 (64 sequences x "
+                        help="decode = the benchmark contract (benchmark configuration 2); decode-long = config 5 (64 sequences x "
                              "131072 cached tokens, 13.5 GB per step), prefill = config 3, model = config 4 end to end "
                              "through the Hugging Face hook: secondary metrics")
     parser.add_argument("--new-tokens", type=int, default=128, help="greedy new tokens of the model workload")

@@ -176,7 +176,7 @@ def test_plan_work_list_covers_every_tile_once():
 
 
 def test_plan_c2_byte_model():
-    """BASELINE config 2: 8 KV heads (4 INT8, 2 INT4, 2 BF16), cache of 8192 tokens, batch 32."""
+    """benchmark configuration 2: 8 KV heads (4 INT8, 2 INT4, 2 BF16), cache of 8192 tokens, batch 32."""
     bands = np.array([[maps.INF, maps.INF]] * 12 + [[1, maps.INF]] * 6 + [[maps.INF, maps.INF]] * 6)
     plan = dec.plan_streams(bands, 8, 8192, batch=32, bf16_kv=(6, 7), ctas=444)
     assert plan["head_bytes"].tolist() == [1644544] * 4 + [1128448] * 2 + [4194304] * 2

@@ -80,7 +80,7 @@ def test_prefill_vs_reference(module, ref_ext, hq, hk, t, bands):
 
 
 def test_prefill_c1_config(module, ref_ext):
-    """BASELINE config 1: 8 Q / 2 KV heads, T=512, outlier dims x16, map [INT8, INT4]."""
+    """benchmark configuration 1: 8 Q / 2 KV heads, T=512, outlier dims x16, map [INT8, INT4]."""
     q = orc.synth((8, 512, 128), 0, outlier_dims=(7, 42, 77, 113), outlier_scale=16.0)[None]
     k = orc.synth((2, 512, 128), 1, outlier_dims=(7, 42, 77, 113), outlier_scale=16.0)[None]
     v = orc.synth((2, 512, 128), 2)[None]

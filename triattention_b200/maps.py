@@ -59,7 +59,7 @@ def uniform(w8, w4):
 
 
 def per_kv_head(kinds, group):
-    """Map in BASELINE vocabulary: one of "int8" / "int4" / "bf16" per KV head, expanded to Q-head bands
+    """Map in the vocabulary of the benchmark configurations: one of "int8" / "int4" / "bf16" per KV head, expanded to Q-head bands
     (INT8 -> [INF, INF], INT4 -> [1, INF]) plus the BF16 head list.  Layer independent."""
     table = {"int8": [INF, INF], "int4": [1, INF], "bf16": [INF, INF]}
     rows = [table[kind] for kind in kinds for _ in range(group)]
