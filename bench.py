@@ -391,7 +391,8 @@ def main():
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--cpu-steps", type=int, default=10, help="timed steps of the CPU baseline leg (0 = skip)")
+    parser.add_argument("--cpu-steps", type=int, default=100,
+                        help="timed steps of the CPU baseline leg (0 = skip); the default is about 10 s of CPU work")
     parser.add_argument("--tile-costs", default="", help="override the decode partition's cost model: bf16,k8v8,other (relative)")
     parser.add_argument("--fused-merge", action="store_true",
                         help="one launch per step: the CTA that finishes a unit's last segment merges it")
@@ -408,8 +409,8 @@ def main():
         CONFIG.update(CONFIG_LONG)
         if args.steps == 200:
             args.steps = 50
-        if args.cpu_steps == 10:
-            args.cpu_steps = 2      # one sequence-step of the CPU port over 131072 tokens takes seconds
+        if args.cpu_steps == 100:
+            args.cpu_steps = 6      # one sequence-step of the CPU port over 131072 tokens takes two seconds
     if args.batch is None:
         args.batch = {"model": 16, "prefill": 2}.get(args.workload, CONFIG["batch"])
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
