@@ -67,8 +67,7 @@ int tri_requantize_kv(const void* k, const void* v, int batch, int heads_kv, int
 /* Banded causal prefill attention (tcgen05).
  * Replaces attention(order,bands,groups,entries,v16p,v8p,v4p,vstat,q8,k8p,qa8,ka8,q4,k4p,qa4,ka4,out,scale),
  *   triattention/kernels/cuda/prefill_sm80.cu:510-543, in band mode.  The CTA order is internal
- *   (heaviest query blocks first); task-table mode (groups/entries) has no Python caller in the
- *   reference and is not provided.
+ *   (heaviest query blocks first); task-table mode (groups/entries) is tri_attention_tasks.
  * bands int32 [Hq,2] = (w8,w4) in tile distances; a head with w8 < 1 is skipped (un-quantised BF16
  * extension heads are computed by the caller).  out is bf16 (or fp16 when out_is_half) [B,Hq,T,128]
  * with element strides.  v8h: the fp16 rendering of the INT8 V codes from tri_pack_v (where the reference passes
@@ -79,6 +78,21 @@ int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const 
                   void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
                   int batch, int heads_q, int heads_kv, int tokens, double scale,
                   int* device_error, void* stream);
+
+/* Task-table mode of the prefill attention: every (Q head, query block) brings four explicit tile lists.
+ * Replaces attention(order,None,groups,entries,...), triattention/kernels/cuda/prefill_sm80.cu:287-292,510-543
+ *   (no caller in the reference; kept for interface completeness as a CUDA-core kernel, not a tensor-core one).
+ * groups int32 [Hq*rows*4+1] = offsets into entries int32 [...] of tile numbers; block (h, qb) runs
+ * entries[groups[i]..groups[i+1]) for i = (h*rows+qb)*4 + pass: pass 0 INT8 scores / fp16 weights / V16, pass 1 INT8
+ * scores / 8-bit P / V8, pass 2 INT8 scores / 4-bit P / V4, pass 3 INT4 scores (q4x, k4x) / 8-bit P / V8.  Only the
+ * last tile of a pass is masked, and only if it is the block's diagonal tile.  The tables are shared by the batch.
+ * A tile number outside the prompt is skipped and recorded in device_error (3).  Other operands as tri_attention,
+ * with the INT8 V blobs themselves (v8) instead of their fp16 rendering, plus v4. */
+int tri_attention_tasks(const int32_t* groups, const int32_t* entries, const void* v16, const void* v8, const void* v4,
+                        const float* vstat, const void* q8, const void* k8, const float* qa8, const float* ka8,
+                        const void* q4x, const void* k4x, const float* qa4, const float* ka4, void* out, int out_is_half,
+                        int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
+                        int heads_kv, int tokens, double scale, int* device_error, void* stream);
 
 /* Gather the kept tiles of the prefill operands into per-(sequence, KV head) cache streams.
  * Replaces the index_select gathers of DecodeCache.store, triattention/kernels/decode.py:46-61.

@@ -295,8 +295,10 @@ def _margin(slope, base):
 
 
 def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles_i8, tiles_q4,
-                  qc4=None, qs4=None, kc4=None, ks4=None, return_acc=False):
-    """One (Q head, query block): prefill_sm80.cu:259-488 in band mode.
+                  qc4=None, qs4=None, kc4=None, ks4=None, return_acc=False, tiles_i4=(), v4=None):
+    """One (Q head, query block): prefill_sm80.cu:259-488.  Band mode gives three tile lists; the task-table mode
+    (:287-292, :478-481) gives four, the extra one (tiles_i4, run third) being INT8 scores with 4-bit P codes
+    against the INT4 V codes v4.  In every pass only the LAST tile is masked, and only if it is the diagonal one.
 
     qc int8 [64,128] Q codes of the block (rows >= T zero), qs float32 [64] = qa*sm_log2 (FLT_MIN for
     rows >= T); kc int8 [tiles,64,128], ks [tiles,4]; v16 float16 / v8 int8 [tiles,64,128];
@@ -351,6 +353,15 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
         ks_max = ksc.max()
         base = np.where(tile_max > -np.inf, tile_max, m).astype(np.float32)
         base = base + _margin(q_scale * ks_max, base)
+        if pv == I4:   # :392-441 with levels = 15: no bias on the integer sums, restore factor 127/7
+            bq = exp2_32(base - m) / f32(15)
+            arg = fma32(slope, accf + MAGIC_F, fma32(-slope, MAGIC_F, -base[:, None]))
+            e = np.where(dead, f32(0), exp2_32(arg))
+            p4 = (np.floor(fma32(e, f32(15), f32(49152.5)).astype(np.float64) - 49152.0).astype(np.int64)) & 0xFF
+            d = p4 @ v4[tile].astype(np.int64)
+            out = fma32(d.astype(np.float32), (bq * (f32(127) / f32(7))).astype(np.float32)[:, None], out)
+            denom = fma32(p4.sum(1).astype(np.float32), bq, denom * alpha)
+            return
         bq = exp2_32(base - m) / f32(255)
         if q4pass:
             arg = fma32(slope, accf, -base[:, None])
@@ -364,17 +375,20 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
         corr = fma32(MAGIC_F, bq, corr)
         denom = fma32(p8.sum(1).astype(np.float32), bq, denom * alpha)
 
+    none = np.zeros(BM, bool)
     for i, t in enumerate(tiles_f16):
-        visit(t, qc, qs, kc, ks, F16, t == qb, False, False)
+        visit(t, qc, qs, kc, ks, F16, t == qb and i == len(tiles_f16) - 1, none, False)
     for i, t in enumerate(tiles_i8):
         last = i == len(tiles_i8) - 1
         flush = (not last) and (pv8_done + i) % 16 == 15
-        visit(t, qc, qs, kc, ks, I8, t == qb, np.full(BM, flush), False)
+        visit(t, qc, qs, kc, ks, I8, t == qb and last, np.full(BM, flush), False)
     pv8_done += len(tiles_i8)
+    for i, t in enumerate(tiles_i4):
+        visit(t, qc, qs, kc, ks, I4, t == qb and i == len(tiles_i4) - 1, none, False)
     for i, t in enumerate(tiles_q4):
         last = i == len(tiles_q4) - 1
         flush = (not last) and (pv8_done + i) % 16 == 15
-        visit(t, qc4, qs4, kc4, ks4, I8, t == qb, np.full(BM, flush), True)
+        visit(t, qc4, qs4, kc4, ks4, I8, t == qb and last, np.full(BM, flush), True)
     with np.errstate(divide="ignore"):
         inv = np.where(denom > 0, f32(1) / denom, f32(0)).astype(np.float32)
     res = fma32((out - corr[:, None]) * inv[:, None], vstat_h[1][None, :], vstat_h[0][None, :])

@@ -53,6 +53,28 @@ class RefRunner:
         o.update(out=out, packed=packed, rows=rows, t=t, hq=hq, hk=hk, vcodes=vcodes, int4=int4)
         return o
 
+    def prefill_tasks(self, q, k, v, groups, entries, scale):
+        """Task-table mode (prefill_sm80.cu:287-292,520-523): every operand format is prepared, the attention gets
+        groups / entries instead of bands.  groups int32 [Hq*rows*4+1], entries int32 [...] (numpy)."""
+        _, hq, t, _ = q.shape
+        hk, rows, dev = k.shape[1], (t + 63) // 64, q.device
+        u32 = lambda n: torch.empty(n, dtype=torch.uint32, device=dev)
+        f32 = lambda n: torch.empty(n, dtype=torch.float32, device=dev)
+        o = dict(q8=torch.empty((1, hq, t, 128), dtype=torch.int8, device=dev), qa=f32(hq * t), kp=u32(hk * rows * 2048),
+                 ka=f32(hk * rows * 4), partial=f32(hk * 64 * 3 * 128), kstat=f32(hk * 3 * 128),
+                 vstat=torch.empty((1, hk, 3, 128), dtype=torch.float32, device=dev),
+                 q4=torch.empty(hq * t * 64, dtype=torch.uint8, device=dev), qa4=f32(hq * t), k4=u32(hk * rows * 1024),
+                 ka4=f32(hk * rows * 4))
+        packed = {F16: u32(hk * rows * 4096), I8: u32(hk * rows * 2048), I4: u32(hk * rows * 1024)}
+        self.mod.prepare_qk(q, k, o["q8"], o["qa"], o["kp"], o["ka"], o["partial"], o["kstat"], o["q4"], o["qa4"], o["k4"], o["ka4"])
+        self.mod.pack_v(v, o["partial"], o["vstat"], packed[F16], packed[I8], packed[I4])
+        order = torch.from_numpy(orc.cta_order(hq, hk, rows)).to(dev)
+        out = torch.empty((1, t, hq, 128), dtype=torch.bfloat16, device=dev).transpose(1, 2)
+        self.mod.attention(order, None, torch.from_numpy(np.asarray(groups, np.int32)).to(dev),
+                           torch.from_numpy(np.asarray(entries, np.int32)).to(dev), packed[F16], packed[I8], packed[I4],
+                           o["vstat"], o["q8"], o["kp"], o["qa"], o["ka"], o["q4"], o["k4"], o["qa4"], o["ka4"], out, float(scale))
+        return out
+
     def decode_setup(self, o, bands, max_tail, per):
         """kernels/decode.py:24-67 restated with numpy; returns the buffers `decode` needs."""
         t, hk, tiles, dev = o["t"], o["hk"], o["rows"], o["qa"].device

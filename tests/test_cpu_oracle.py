@@ -121,6 +121,24 @@ def test_folded_tail_tiles_stay_close_to_exact_attention():
     assert np.abs(one - outs[1]).max() < 1e-4
 
 
+def test_task_table_passes_cover_exact_attention():
+    """Task-table mode: when the four passes together name every causal tile once, the block is an attention over all
+    keys (sink in the fp16 pass, the others spread over the INT8, INT4-V and INT4-score passes, diagonal last)."""
+    hq, hk, t = 2, 1, 330
+    q, k, v = orc.synth((hq, t, 128), 31), orc.synth((hk, t, 128), 32), orc.synth((hk, t, 128), 33)
+    _, o = orc.prefill(q, k, v, np.array([[orc.INF, orc.INF]] * hq), 0.0884, return_operands=True)
+    vstat = orc.channel_stats(v)
+    v16, v8, v4 = orc.pack_v(v, vstat)
+    ex = orc.exact_attention(q, k, v, 0.0884)
+    sl2, qb = orc.sm_log2(0.0884), 4
+    rows = slice(qb * 64, (qb + 1) * 64)
+    for h in range(hq):
+        res = orc.prefill_block(o["q8"][h, rows], o["qa"][h, rows] * sl2, o["k8"][0], o["ka"][0], v16[0], v8[0], vstat[0], t, qb,
+                                [0], [1], [3, 4], o["q4"][h, rows], o["qa4"][h, rows] * sl2, o["k4"][0], o["ka4"][0],
+                                tiles_i4=[2], v4=v4[0])
+        assert np.abs(res - ex[h, rows]).max() < 0.12      # 4-bit weights and 4-bit V on one tile, 4-bit scores on two
+
+
 def test_decode_tables_rules():
     bands = np.array([[2, 5], [1, 3], [orc.INF, orc.INF], [1, 1]])
     tabs = orc.decode_tables(bands, 2, 64 * 10)

@@ -18,7 +18,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIBRARY = ROOT / "libtriattn_sm100a.so"
-SOURCES = ("abi.cu", "kv_write.cu", "decode.cu", "prefill.cu")
+SOURCES = ("abi.cu", "kv_write.cu", "decode.cu", "prefill.cu", "tasks.cu")
 FLAGS = ("-O3", "-std=c++17", "--use_fast_math", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC")
 

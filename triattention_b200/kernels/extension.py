@@ -24,6 +24,7 @@ SIGNATURES = {
     "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P],
     "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
+    "tri_attention_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
     "tri_decode": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
@@ -89,7 +90,8 @@ class Module:
         word = int(self.error_word(device).item())
         if word:
             self.error_word(device).zero_()
-            raise RuntimeError(f"TriAttention kernel reported device error {word} (1 = barrier wait ran out)")
+            raise RuntimeError(f"TriAttention kernel reported device error {word} (1 = barrier wait ran out, "
+                               "3 = tile number outside the prompt in a task table)")
 
     @staticmethod
     def _bhtd(x, name):
@@ -161,6 +163,24 @@ class Module:
                                                _ptr(qa4), _ptr(ka4), out.data_ptr(), int(out.dtype == torch.float16),
                                                out.stride(0), out.stride(1), out.stride(2), b, hq, heads_kv, t,
                                                float(scale), self.error_word(out.device).data_ptr(), _stream()))
+        return out
+
+    def attention_tasks(self, groups, entries, v16, v8, v4, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
+        """Task-table mode (the reference's attention(order, None, groups, entries, ...)): four explicit tile lists per
+        (Q head, query block).  groups / entries int32 on the device."""
+        if not (out.dim() == 4 and out.stride(3) == 1 and out.dtype in (torch.bfloat16, torch.float16)):
+            raise RuntimeError("output [B,Hq,T,128] aligned")
+        b, hq, t, _ = out.shape
+        rows = (t + 63) // 64
+        if groups.dtype != torch.int32 or entries.dtype != torch.int32 or groups.numel() != hq * rows * 4 + 1:
+            raise RuntimeError("bands [Hq,2] or task tables")
+        with torch.cuda.device(out.device):
+            self._check(self.lib.tri_attention_tasks(groups.data_ptr(), entries.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4),
+                                                     vstat.data_ptr(), q8.data_ptr(), k8.data_ptr(), qa8.data_ptr(),
+                                                     ka8.data_ptr(), _ptr(q4x), _ptr(k4x), _ptr(qa4), _ptr(ka4),
+                                                     out.data_ptr(), int(out.dtype == torch.float16), out.stride(0),
+                                                     out.stride(1), out.stride(2), b, hq, heads_kv, t, float(scale),
+                                                     self.error_word(out.device).data_ptr(), _stream()))
         return out
 
     def cache_store(self, pool, unit_base, unit_tab, unit_count, unit_flags, tmeta, units, max_count, k8, k4, ka, ka4,
