@@ -431,7 +431,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         from datetime import timedelta
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=timedelta(seconds=120))
+        # (a collective inside the step, --split, gets a short timeout: a rank that falls out of step then ends the run
+        # within minutes)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=timedelta(seconds=120 if args.split else 600))
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
     warmup = max(3, args.warmup)
     costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
