@@ -20,6 +20,8 @@ extern "C" {
 #endif
 
 enum { TRI_OK = 0, TRI_ERR_ARGUMENT = -1, TRI_ERR_CUDA = -2, TRI_ERR_DEVICE = -3 };
+/* Values of the device error word (`device_error` arguments): 1 = a bounded barrier wait ran out, 3 = a tile number
+ * outside the prompt in a task table, 4 = a partial slot outside the partial buffers. */
 
 /* Message of the last failing call made by this host thread. */
 const char* tri_last_error(void);
@@ -141,17 +143,46 @@ int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void
                int* device_error, void* stream);
 
 /* Fold a unit's segment partials into one (m, l, o) per Q head: fm, fl f32 [U,8], fo f32 [U,8,128].
- * Used when the tile range of a unit is split across GPUs: each rank folds, the triples are all-gathered
- * and tri_decode(phases = 2) merges them with one slot per rank.  Extends the split merge of
+ * Stand-alone form of the fold that tri_decode_partials does inside the split pass; kept for callers that
+ * already hold segment partials.  Extends the split merge of
  * triattention/kernels/cuda/common_device.cuh:418-438 across devices; the reference is single-GPU. */
 int tri_decode_fold(const float* pm, const float* pl, const float* po, const int32_t* unit_slots,
                     float* fm, float* fl, float* fo, int units, int group, void* stream);
+
+/* Sequence split across GPUs, this GPU's part: the split pass of tri_decode over this rank's tiles, and in
+ * the same launch the fold of every unit's segments to one (m, l, o) per Q head (the CTA that finishes a
+ * unit's last segment folds it): fold_m, fold_l f32 [U,8], fold_o f32 [U,8,128] — what the ranks exchange.
+ * unit_done int32 [U], zero before the first call, left at zero.  A unit without any segment on this rank is
+ * not touched: give its fold entries m = -FLT_MAX, l = 0, o = 0 once.  No counterpart in the reference (single GPU). */
+int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool,
+                        const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags,
+                        const int32_t* tmeta, const int32_t* segments, const int32_t* cta_segments, int num_ctas,
+                        const int32_t* unit_slots, float* pm, float* pl, float* po, int32_t* unit_done,
+                        float* fold_m, float* fold_l, float* fold_o, int batch, int heads_q, int heads_kv,
+                        int prompt, double scale, int* device_error, void* stream);
+
+/* The merge of tri_decode alone, over partials that may lie strided: split s of unit u is read at
+ * pm[(first*8 + r) + s*split_stride], pl likewise, po[(first*8 + r)*128 + ch + s*split_stride] with
+ * (first, count) = unit_slots[u].  split_stride = 0 means the dense buffers of the split pass.  With
+ * triples all-gathered as [rank][m | l | o] and unit_slots[u] = (u, world), split_stride = the floats per rank:
+ * the gathered buffer is merged in place, no re-layout.  Other arguments as tri_decode.
+ * Replaces decode_merge_kernel, triattention/kernels/cuda/common_device.cuh:373-469. */
+int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
+                     const float* po, int64_t split_stride, const int32_t* unit_slots, const float* kstat,
+                     const float* vstat, void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t,
+                     const void* kcur, const void* vcur, int64_t cur_stride_b, int64_t cur_stride_h,
+                     const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                     int batch, int heads_q, int heads_kv, int max_tail, double scale,
+                     int* device_error, void* stream);
 
 /* tri_decode for callers that cannot allocate device memory (a runtime that gave all of HBM to its KV
  * pool up front, a binding that can only pass buffers it was handed).  Same arguments as tri_decode
  * without pm / pl / po and without phases: the split-KV partials live in a fixed 4,259,840-byte array
  * inside the library, held by every GPU that loads it until the process exits.  num_slots = number of
- * rows of `segments`; more than 1024 is refused with TRI_ERR_ARGUMENT (use tri_decode then).  The call
+ * rows of `segments`; more than 1024 is refused with TRI_ERR_ARGUMENT (use tri_decode then).  The slot
+ * numbers in `segments[:,3]` and `unit_slots` must be 0 .. num_slots-1 (what a plan from plan_streams holds);
+ * the kernels check every slot against the array's capacity and, for one outside it, store and read nothing
+ * and set the device error word to 4.  A cudaDeviceReset invalidates the cached address.  The call
  * makes no allocation of any kind.  The first call on each device looks up the array's device address
  * (with that device current), so make that first call outside any stream capture.  All calls on a device
  * share the array: calls that can overlap on the GPU (different streams) race on it, so keep them on
@@ -176,15 +207,6 @@ int tri_decode_occupancy(void);
 int tri_qk_accumulators(const int32_t* requests, int num_requests, const void* q8, const void* q4x, const void* k8,
                         const void* k4x, int32_t* acc, int batch, int heads_q, int heads_kv, int tokens,
                         int* device_error, void* stream);
-
-/* Single-tile tensor-core probe used by the tests to pin the operand-layout conventions:
- * D[128 x ncols] = A . B^T from caller-built shared-memory images and descriptor fields.
- * No counterpart in the reference. */
-int tri_umma_probe(const void* a_img, int a_bytes, const void* b_img, int b_bytes,
-                   uint32_t a_lbo, uint32_t a_sbo, uint32_t a_layout, uint32_t a_step,
-                   uint32_t b_lbo, uint32_t b_sbo, uint32_t b_layout, uint32_t b_step,
-                   uint32_t idesc, int f16_kind, int ksteps, int ncols, uint32_t* out,
-                   int* device_error, void* stream);
 
 #ifdef __cplusplus
 }

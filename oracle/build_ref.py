@@ -9,6 +9,9 @@ this repository) and writes one pybind11 module, ``oracle/_ref/triattention_ref.
 The module can only *run* on a GPU.  GPU parity tests import it as the authoritative oracle and
 ``tests/golden/make_golden.py`` uses it to record golden vectors.  Product code never imports it.
 
+The reference checkout is named by ``--reference`` or the ``TRIATTENTION_REFERENCE`` environment variable; without
+either, a directory called ``reference`` beside this repository is used if it holds the sources.
+
 Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--force]
 """
 from __future__ import annotations
@@ -24,6 +27,15 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 NAME = "triattention_ref"
+
+
+def find_reference() -> Path | None:
+    """The reference checkout: $TRIATTENTION_REFERENCE, else a `reference` directory beside this repository."""
+    named = os.environ.get("TRIATTENTION_REFERENCE")
+    for candidate in ([Path(named)] if named else []) + [HERE.parent.parent / "reference"]:
+        if (candidate / "triattention" / "kernels" / "cuda" / "prefill_sm80.cu").is_file():
+            return candidate
+    return None
 
 
 def command(reference: Path) -> list[str]:
@@ -83,9 +95,10 @@ def load():
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default=os.environ.get("TRIATTENTION_REFERENCE", "/root/reference"))
+    parser.add_argument("--reference", default=None)
     parser.add_argument("--force", action="store_true")
     args = parser.parse_args()
-    path = build(Path(args.reference), args.force)
+    where = Path(args.reference) if args.reference else find_reference()
+    path = build(where, args.force) if where is not None else None
     print(path if path else "reference sources not found; nothing built")
     sys.exit(0)

@@ -1,4 +1,4 @@
-"""Host-side (numpy) packers / unpackers for the tile blob layouts of the sm_100a kernels.
+"""Test helpers: host-side (numpy) packers / unpackers for the tile blob layouts of the sm_100a kernels.
 
 The kernels keep quantised K/V in 128-byte core-matrix order (see ``csrc/common.cuh``); the reference
 keeps them in mma.sync fragment order (``triattention/kernels/cuda/common_device.cuh:101-130,142-171``).

@@ -12,7 +12,7 @@ import torch
 import triattention_oracle as orc
 from triattention_b200 import maps
 from triattention_b200.kernels import decode as dec
-from triattention_b200.kernels import layouts
+import layouts
 from triattention_b200.kernels.extension import SIGNATURES, load_library
 from triattention_b200.kernels.prefill import F16, I8, Q4, BandTable
 
@@ -208,7 +208,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
         if name in SIGNATURES:
             assert len(SIGNATURES[name]) == nargs, (name, len(SIGNATURES[name]), nargs)
-    assert lib.tri_abi_version() == 2
+    assert lib.tri_abi_version() == 3
     assert isinstance(lib.tri_last_error(), bytes)
 
 
@@ -218,6 +218,36 @@ def test_argument_errors_without_gpu():
     assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 13)) == -1
     assert b"null" in lib.tri_last_error()
     assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 7)) == -1
+
+
+def test_error_word_is_keyed_by_the_device_that_ran_the_kernel(monkeypatch):
+    """"cuda" without an index means the current device, not device 0: on rank r > 0 the kernels write the word of
+    cuda:r, and the check must read that one."""
+    import torch
+    from triattention_b200.kernels.extension import Module
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 3)
+    assert Module._device_index("cuda") == 3 and Module._device_index(torch.device("cuda")) == 3
+    assert Module._device_index("cuda:1") == 1 and Module._device_index(torch.device("cuda", 5)) == 5
+    assert Module._device_index(2) == 2
+    m = Module(lib=None)
+    m._errors = {0: torch.zeros(1, dtype=torch.int32), 3: torch.full((1,), 4, dtype=torch.int32)}
+    with pytest.raises(RuntimeError, match="device error 4 on cuda:3"):
+        m.check_device_error()                  # no argument: every device this process launched on
+    assert int(m._errors[3].item()) == 0        # reported once, then cleared
+    m.check_device_error()
+    m._errors[3].fill_(1)
+    m.check_device_error("cuda:0")              # another device's word is not this call's business
+    with pytest.raises(RuntimeError, match="device error 1"):
+        m.check_device_error("cuda")            # the current device (3)
+
+
+def test_decode_entry_points_validate_before_any_cuda_call():
+    lib = load_library()
+    assert lib.tri_decode_merge(*([None] * 1), 0, 0, *([None] * 3), 0, *([None] * 5), 0, 0, None, None, 0, 0, None, None, 0, 0,
+                                1, 8, 2, 4, 0.088, None, None) == -1
+    assert b"decode_merge" in lib.tri_last_error()
+    assert lib.tri_decode_partials(None, 0, 0, *([None] * 7), 4, *([None] * 8), 1, 8, 2, 64, 0.088, None, None) == -1
+    assert b"decode_partials" in lib.tri_last_error()
 
 
 def test_plan_streams_appended_tiles():

@@ -187,3 +187,29 @@ def test_oracle_matches_reference_golden(name):
             od = orc.decode_step(qd[:, step], ops, bands, t, scale, tk, tv, kd[:, step], vd[:, step], step, 8, per)
             r = fp_report(orc.to_bf16(od), from_bits(g[f"decode_bits_per{per}"][step]))
             assert r["worst_excess"] <= 0 and r["cos"] >= 0.9999 and r["mean_abs"] <= ABS_TOL / 4, (per, step, r)
+
+
+@pytest.mark.parametrize("name", ["small", "c1"])
+def test_decode_partials_match_reference_golden(name):
+    """The split partials (m, l, o) that the reference's decode_kernel left behind after the third recorded step at two
+    kept tiles per split (pm, pl, po of common_device.cuh:355-370): the restatement's decode_partials gives the same
+    triples, so the split pass is pinned on its own and not only through the merged output."""
+    path = GOLDEN / f"{name}.npz"
+    if not path.is_file():
+        pytest.skip(f"{path.name} has not been recorded yet")
+    import make_golden
+    g = np.load(path)
+    hq, hk, t, _, _, _, _ = make_golden.CASES[name]
+    q, k, v, bands, qd, _, _ = make_golden.inputs(name)
+    scale, per, splits = 1.0 / np.sqrt(128.0), 2, int(g["splits"])
+    _, ops = orc.prefill(q, k, v, bands, scale, return_operands=True)
+    tables = orc.decode_tables(bands, hk, t)
+    parts = orc.decode_partials(qd[:, 2], ops, tables, t, scale,
+                                lambda kh, n: [(a, min(n, a + per)) for a in range(0, n, per)])
+    pm, pl, po = g["pm"].reshape(hq, splits), g["pl"].reshape(hq, splits), g["po"].reshape(hq, splits, 128)
+    for h in range(hq):
+        assert len(parts[h]) == splits
+        for s, (m, l, o) in enumerate(parts[h]):
+            assert abs(m - pm[h, s]) <= 1e-4 * max(1.0, abs(m)), (h, s, m, pm[h, s])
+            assert abs(l - pl[h, s]) <= 1e-4 * abs(l), (h, s, l, pl[h, s])
+            assert np.abs(o - po[h, s]).max() <= 1e-3 * np.abs(o).max(), (h, s)

@@ -5,7 +5,7 @@ import torch
 
 import triattention_oracle as orc
 from ref_harness import RefRunner, ref_logical
-from triattention_b200.kernels import layouts
+import layouts
 from triattention_b200.kernels.prefill import F16, I4, I8, Q4, Prefill
 from triattention_b200.maps import INF
 from util import bf16_cuda, code_mismatch, make_inputs, ulp_diff
@@ -18,13 +18,14 @@ SCALE_ULP, CODE_RATE = 4, 2e-3
 
 
 def run_write(module, q, k, v, want4=True):
-    """Product write path on [B,H,T,128] float32 inputs; returns logical numpy arrays per batch."""
+    """Product write path on [B,H,T,128] inputs (float32 numpy holding bf16 values, or bf16 CUDA tensors); returns
+    logical numpy arrays per batch."""
     b, hq, t, _ = q.shape
     hk, tiles = k.shape[1], (t + 63) // 64
     pre = Prefill(module, None)
     formats = frozenset({F16, I8, I4})
     ops = pre.operands(b, hq, hk, t, want4, want4, formats, "cuda")
-    qd, kd, vd = bf16_cuda(q), bf16_cuda(k), bf16_cuda(v)
+    qd, kd, vd = (x if torch.is_tensor(x) else bf16_cuda(x) for x in (q, k, v))
     module.prepare_qk(qd, kd, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
                       ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"])
     module.pack_v(vd, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"])
@@ -77,6 +78,25 @@ def test_write_vs_oracle(module, hq, hk, t, batch):
     print("code mismatch rates vs IEEE oracle", worst)
 
 
+def assert_write_equals_reference(got, b, o):
+    """Every code and every scale / statistic bit pattern of sequence b of a product write (run_write) equals what the
+    reference extension left in its operand buffers `o` (RefRunner.prefill) for the same sequence."""
+    ref = ref_logical(o)
+    compared = []
+    for name in ("qa", "ka", "qa4", "ka4"):
+        if name in ref:
+            assert (got[name][b].view(np.uint32) == ref[name].view(np.uint32)).all(), name
+            compared.append(name)
+    assert (got["kstat"][b][:, 0].view(np.uint32) == ref["kstat"][:, 0].view(np.uint32)).all()
+    assert (got["vstat"][b].view(np.uint32) == ref["vstat"].view(np.uint32)).all()
+    for name in ("q8", "q4", "k8", "k4", "v8", "v4"):
+        if name in ref:
+            assert (got[name][b] == ref[name]).all(), (name, code_mismatch(got[name][b], ref[name]))
+            compared.append(name)
+    assert (got["v16"][b].view(np.uint16) == ref["v16"].view(np.uint16)).all()
+    return compared
+
+
 @pytest.mark.parametrize("hq,hk,t", [(4, 2, 200), (8, 2, 512), (2, 1, 65), (24, 8, 1024)])
 def test_write_bit_exact_vs_reference(module, ref_ext, hq, hk, t):
     """Codes and scale bit patterns equal the reference kernels' on the same GPU."""
@@ -87,16 +107,7 @@ def test_write_bit_exact_vs_reference(module, ref_ext, hq, hk, t):
     for b in range(2):
         o = run.prefill(bf16_cuda(q[b])[None], bf16_cuda(k[b])[None], bf16_cuda(v[b])[None], bands, 0.088, with_decode=True)
         torch.cuda.synchronize()
-        ref = ref_logical(o)
-        for name in ("qa", "ka", "qa4", "ka4"):
-            if name in ref:
-                assert (got[name][b].view(np.uint32) == ref[name].view(np.uint32)).all(), name
-        assert (got["kstat"][b][:, 0].view(np.uint32) == ref["kstat"][:, 0].view(np.uint32)).all()
-        assert (got["vstat"][b].view(np.uint32) == ref["vstat"].view(np.uint32)).all()
-        for name in ("q8", "q4", "k8", "k4", "v8", "v4"):
-            if name in ref:
-                assert (got[name][b] == ref[name]).all(), (name, code_mismatch(got[name][b], ref[name]))
-        assert (got["v16"][b].view(np.uint16) == ref["v16"].view(np.uint16)).all()
+        assert_write_equals_reference(got, b, o)
 
 
 def test_write_strided_inputs(module):

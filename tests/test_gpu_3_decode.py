@@ -263,3 +263,46 @@ def test_store_in_parts_equals_store_at_once(module):
     module.check_device_error()
     with pytest.raises(RuntimeError):
         DecodeCache(module, max_tail=4).store(0, t, ops, table.host, kc[3:], vc[3:], table.bf16_kv, first_sequence=3, sequences=batch)
+
+
+@pytest.mark.parametrize("world,ctas", [(2, None), (3, 5)])
+def test_sequence_split_emulated_on_one_gpu(module, world, ctas):
+    """The sequence-split path without a process group: `world` caches each hold one part of every unit's tile range
+    (what the ranks of a split group hold), each runs its split pass with the in-kernel fold (tri_decode_partials), the
+    folded triples are stacked [rank][m | l | o] as an all-gather would leave them, and tri_decode_merge reads that
+    buffer in place by stride.  Against the un-split decode over three steps, with a BF16 unit, an INT4 band and a
+    short prompt part so that some ranks hold no tile of some units."""
+    hq, hk, t, batch = 6, 3, 900, 2
+    bands = np.asarray([[INF, INF]] * 2 + [[2, 5]] * 2 + [[INF, INF]] * 2, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=71, batch=batch)
+    qd, kd, vd = make_inputs(hq, hk, 3, seed=72, batch=batch)
+    whole, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3, bf16=(2,))
+    kc, vc = bf16_cuda(k), bf16_cuda(v)
+    caches = []
+    for rank in range(world):
+        cache = DecodeCache(module, max_tail=8, split=(rank, world), ctas=ctas)
+        pre = Prefill(module, bands_fn_of(bands, (2,)), cache)
+        table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+        cache.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
+        caches.append(cache)
+    # the fused fold equals the stand-alone fold kernel bit for bit (same arithmetic, same order)
+    outs = []
+    for s in range(3):
+        qs, ks, vs = (bf16_cuda(x[:, :, s:s + 1]) for x in (qd, kd, vd))
+        folded = []
+        for cache in caches:
+            e = cache.layers[0]
+            mine = cache.partials(0, qs, ks, SCALE).clone()
+            fm, fl, fo = torch.empty_like(e["fm"]), torch.empty_like(e["fl"]), torch.empty_like(e["fo"])
+            module.decode_fold(e["pm"], e["pl"], e["po"], e["dev"]["unit_slots"], fm, fl, fo, hq // hk)
+            assert torch.equal(torch.cat([fm.flatten(), fl.flatten(), fo.flatten()]), mine)
+            folded.append(mine)
+        outs_rank = []
+        for cache in caches:        # every rank merges the same gathered buffer with its own (replicated) tail
+            cache.layers[0]["gathered"].copy_(torch.stack(folded))
+            outs_rank.append(cache.merge_gathered(0, qs, ks, vs, SCALE).float().cpu().numpy()[:, :, 0])
+            cache.advance()
+        assert all((o == outs_rank[0]).all() for o in outs_rank)
+        outs.append(outs_rank[0])
+    module.check_device_error()
+    assert_fp_close(np.stack(outs, 1), whole, f"sequence split over {world} parts vs whole units")

@@ -5,7 +5,7 @@ import torch
 
 import triattention_oracle as orc
 from ref_harness import RefRunner
-from triattention_b200.kernels import layouts
+import layouts
 from triattention_b200.kernels.prefill import Prefill
 from triattention_b200.maps import INF, from_bands, per_kv_head
 from util import assert_fp_close, bf16_cuda, make_inputs

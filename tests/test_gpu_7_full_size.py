@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from ref_harness import RefRunner
+from test_gpu_2_kv_write import assert_write_equals_reference, run_write
 from triattention_b200.kernels.decode import DecodeCache
 from triattention_b200.kernels.prefill import Prefill
 from triattention_b200.maps import INF, from_bands
@@ -68,6 +69,15 @@ def assert_close_by_channel_range(got, ref, v, group, what):
     assert plain <= 1e-5 * err.numel(), (what, plain)   # and the unscaled bound holds for all but a few in 10^5
 
 
+def check_codes(module, o, q, k, v):
+    """Bit-exactness of the KV-cache write at this size, with the x20 outlier channels: INT8 and INT4 codes of Q, K and V,
+    the fp16 V bits, and the bit patterns of every scale and statistic, against the operand buffers the reference
+    extension filled for the same sequence.  The statistics blocks add 128 to 2,048 rows each at these lengths, so
+    the summation order is exercised far beyond the small cases."""
+    compared = assert_write_equals_reference(run_write(module, q, k, v), 0, o)
+    assert {"q8", "q4", "k8", "k4", "v8", "v4", "qa", "qa4", "ka", "ka4"} <= set(compared), compared
+
+
 def test_prefill_config3_size_vs_reference(module, ref_ext):
     hq, hk, t = 28, 4, 16384
     kinds = ["int8", "int8", "int4", "int8"]
@@ -75,7 +85,9 @@ def test_prefill_config3_size_vs_reference(module, ref_ext):
     q, k, v = synth_cuda((1, hq, t, 128), 1), synth_cuda((1, hk, t, 128), 2), synth_cuda((1, hk, t, 128), 3)
     got = Prefill(module, from_bands({"0": bands.tolist()}, None))(0, q, k, v, SCALE)
     module.check_device_error()
-    ref = RefRunner(ref_ext).prefill(q, k, v, bands, SCALE, with_decode=False)["out"]
+    o = RefRunner(ref_ext).prefill(q, k, v, bands, SCALE)
+    check_codes(module, o, q, k, v)
+    ref = o["out"]
     assert_close_by_channel_range(got, ref, v, hq // hk, "prefill at 16384 tokens")
     check_convex(got, v, hq // hk)
 
@@ -98,7 +110,9 @@ def test_decode_config2_size_vs_reference(module, ref_ext):
     qd, kd, vd = synth_cuda((1, hq, 1, 128), 14), synth_cuda((1, hk, 1, 128), 15), synth_cuda((1, hk, 1, 128), 16)
     got = run_decode(module, q, k, v, bands, bf16, qd, kd, vd)
     run = RefRunner(ref_ext)
-    st = run.decode_setup(run.prefill(q, k, v, bands, SCALE), bands, max_tail=4, per=8)
+    o = run.prefill(q, k, v, bands, SCALE)
+    check_codes(module, o, q, k, v)
+    st = run.decode_setup(o, bands, max_tail=4, per=8)
     ref = run.decode(st, qd, kd, vd, SCALE)
     heads = quantised_q_heads(kinds, hq // hk)
     assert_fp_close(got.float().cpu().numpy()[0, heads], ref.float().cpu().numpy()[0, heads], "decode over 8192 tokens")
@@ -123,6 +137,7 @@ def test_max_length_prefill_and_decode_vs_reference(module, ref_ext):
     qd, kd, vd = synth_cuda((1, hq, 1, 128), 24), synth_cuda((1, hk, 1, 128), 25), synth_cuda((1, hk, 1, 128), 26)
     run = RefRunner(ref_ext)
     o = run.prefill(q, k, v, bands, SCALE)
+    check_codes(module, o, q, k, v)
     got = Prefill(module, from_bands({"0": bands.tolist()}, None))(0, q, k, v, SCALE)
     module.check_device_error()
     assert_close_by_channel_range(got, o["out"], v, hq // hk, "prefill at 131072 tokens")

@@ -3,9 +3,11 @@
 Such a caller (a serving runtime that handed all of HBM to its KV pool at start-up, or a language binding
 that can only forward buffers it was given) has nowhere to put the split-KV partials that tri_decode
 expects from its caller.  tri_decode_static keeps them in a fixed array inside the library.  This file
-checks, through the C ABI, that two calls in a row give what tri_decode gives on the same inputs, and that
-a plan too large for the fixed array is refused.  It is collected last on purpose: a run that stops at
-the first failure has already run every other test.
+checks, through the C ABI, that two calls in a row give bit for bit what tri_decode gives on the same inputs
+(same kernels, same plan), that a plan too large for the fixed array is refused, and that a plan whose slot
+numbers point outside the array is caught by the kernels' own bounds check (error word 4, nothing stored there)
+rather than written past the array.  It is collected last on purpose: a run that stops at the first failure
+has already run every other test.
 """
 import numpy as np
 import pytest
@@ -31,12 +33,13 @@ def build(module, hq, hk, t, bands, batch, seed, bf16=()):
     return cache
 
 
-def static_step(module, cache, q, k, v):
+def static_step(module, cache, q, k, v, segments=None, unit_slots=None):
     e, d = cache.layers[0], cache.layers[0]["dev"]
-    out = torch.empty_like(q)
-    module.decode_static(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
-                         d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v,
-                         cache.step, out, e["prompt"], SCALE)
+    out = torch.zeros_like(q)
+    module.decode_static(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"],
+                         d["segments"] if segments is None else segments, d["cta_segments"],
+                         d["unit_slots"] if unit_slots is None else unit_slots, e["kstat"], e["vstat"], e["tail_k"],
+                         e["tail_v"], k, v, cache.step, out, e["prompt"], SCALE)
     return out
 
 
@@ -52,6 +55,7 @@ def test_two_calls_match_the_allocating_entry_point(module):
         module.check_device_error()
         assert np.isfinite(got).all()
         assert_fp_close(got, want, f"static decode, call {s}")
+        assert (got == want).all(), f"static decode, call {s}: not bit-equal to tri_decode"
         cache.advance()
 
 
@@ -64,3 +68,26 @@ def test_plans_beyond_the_fixed_array_are_refused(module):
         static_step(module, cache, q, k, v)
     cache(0, q, k, v, SCALE)                 # the allocating entry point still takes it
     module.check_device_error()
+
+
+def test_slot_numbers_outside_the_array_are_caught_on_the_device(module):
+    """A caller-built plan whose slot column is not 0 .. num_slots-1: the host check sees only the number of rows, so
+    the kernels compare every slot with the array's capacity, skip the access and report error 4."""
+    hq, hk, t, batch = 4, 2, 300, 2
+    cache = build(module, hq, hk, t, [[INF, INF]] * 4, batch, seed=11)
+    q, k, v = (bf16_cuda(x) for x in make_inputs(hq, hk, 1, seed=12, batch=batch))
+    d = cache.layers[0]["dev"]
+    want = static_step(module, cache, q, k, v)
+    module.check_device_error()
+    for shift_segments, shift_units in ((True, True), (False, True)):
+        segments, unit_slots = d["segments"].clone(), d["unit_slots"].clone()
+        if shift_segments:
+            segments[:, 3] += 1 << 20           # far beyond the 1024 slots of the array
+        if shift_units:
+            unit_slots[:, 0] += 1 << 20
+        static_step(module, cache, q, k, v, segments, unit_slots)
+        with pytest.raises(RuntimeError, match="device error 4"):
+            module.check_device_error()
+    again = static_step(module, cache, q, k, v)     # the library and the array are intact afterwards
+    module.check_device_error()
+    assert torch.equal(again, want)

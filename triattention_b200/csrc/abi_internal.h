@@ -32,6 +32,23 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
     }                                         \
   } while (0)
 
+// One-time configuration that CUDA keeps per device and context (the opt-in to more than 48 KB of dynamic shared
+// memory of a kernel): remembered per device ordinal, so that a process driving several GPUs configures each of
+// them.  Two host threads making their first call on a device at the same time both set the same attribute
+// value, which is harmless; the flags are atomics so that neither reads a torn value.
+#include <atomic>
+struct TriPerDevice {
+  static constexpr int MaxDevices = 64;
+  std::atomic<bool> done[MaxDevices];
+  // returns the current device's ordinal if it still needs configuring, -1 if it is configured, -2 on error
+  int pending() {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MaxDevices) return -2;
+    return done[device].load(std::memory_order_acquire) ? -1 : device;
+  }
+  void mark(int device) { done[device].store(true, std::memory_order_release); }
+};
+
 // Launch with programmatic stream serialisation: the kernel may become resident while its predecessor in
 // the stream is still running and orders itself with grid_dependency_wait() (common.cuh).  Hides the
 // launch latency between kernels that follow one another in a stream.

@@ -45,7 +45,7 @@ __host__ __device__ __forceinline__ int kperm(int s, int b) { return 2 * s + (b 
 
 // ---- error word shared by kernels with bounded waits ----------------------------------------
 // Kernels never trap or spin forever: a wait that runs out records a code here and the CTA leaves.
-enum DeviceError : int { ErrNone = 0, ErrBarrierTimeout = 1, ErrTmemAlloc = 2 };
+enum DeviceError : int { ErrNone = 0, ErrBarrierTimeout = 1, ErrTmemAlloc = 2, ErrBadTask = 3, ErrBadSlot = 4 };
 
 // ---- rotation (prefill_sm80.cu:95-115) --------------------------------------------------------
 __device__ __constant__ uint32_t kRotationSigns[4] = {0x9a3b5e71u, 0x2c6d8f13u, 0xe41b7a95u, 0x5f02c3d8u};

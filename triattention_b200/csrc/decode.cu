@@ -13,84 +13,108 @@
 
 namespace tri {
 
-// grid (heads_q, batch), 256 threads.  common_device.cuh:373-469 with per-unit split ranges.
-constexpr int MergeThreads = 256;
+// ---- merge: split partials + BF16 tail -> output, one CTA per (sequence, KV head) unit -------------------
+// Replaces decode_merge_kernel of the reference (common_device.cuh:373-469: one CTA per Q head), same arithmetic:
+// tail scores q.(k - kmean) in fp32 on the un-rotated rows, base-2 running maximum over partials and tail,
+// de-normalisation of the cached part (acc * vscale + l * vmean), then the tail's exact P.V.
+// Organisation: grid = units, 8 warps.  The unit's tail K rows are read ONCE for all g Q heads of the group
+// (warps split the rows, a lane holds 4 features of the row and of each head's q); after that warp r owns Q head
+// r: it walks the unit's partials (a lane holds 4 of the 128 channels, so one partial is one 512-byte row per
+// warp) and then the tail's V rows, and writes its head's output row.
+// Partials are addressed as pm[first * 8 + s * ml_stride + r], po[(first * 8 + r) * 128 + s * o_stride + ch] for
+// split s of the unit: ml_stride = 8, o_stride = 1024 for the dense [slot][8] buffers of the split pass; other
+// strides let the merge read triples gathered from several GPUs in place ([rank][unit][8]).
+constexpr int MergeThreads = 256, MergeWarps = MergeThreads / 32;
 __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float* pm, const float* pl, const float* po,
-    const int2* unit_slots, const float* vstat, const float* kstat, const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
-    __nv_bfloat16* ktail, __nv_bfloat16* vtail, int64_t tsu, int64_t tst, const __nv_bfloat16* kcur,
-    const __nv_bfloat16* vcur, int64_t csb, int64_t csh, const int64_t* step, __nv_bfloat16* out, int64_t osb, int64_t osh,
-    int heads_q, int heads_kv, int max_tail, float sm_log2) {
-  constexpr int W = MergeThreads / 32;
-  __shared__ float ts[1024];
-  __shared__ __align__(16) float ew[1024];
-  __shared__ float wmax[W], wl[W];
-  __shared__ __align__(16) float wo[W][D];
-  const int hq = blockIdx.x, b = blockIdx.y, g = heads_q / heads_kv, kh = hq / g, r = hq % g;
-  const int unit = b * heads_kv + kh, tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    int64_t ml_stride, int64_t o_stride, const int2* unit_slots, int slot_limit, const float* vstat, const float* kstat,
+    const __nv_bfloat16* q, int64_t qsb, int64_t qsh, __nv_bfloat16* ktail, __nv_bfloat16* vtail, int64_t tsu, int64_t tst,
+    const __nv_bfloat16* kcur, const __nv_bfloat16* vcur, int64_t csb, int64_t csh, const int64_t* step, __nv_bfloat16* out,
+    int64_t osb, int64_t osh, int heads_q, int heads_kv, int max_tail, float sm_log2, int* err) {
+  __shared__ float ts[MaxGroup][1024];   // tail scores, then tail weights, per Q head of the group
+  const int unit = blockIdx.x, b = unit / heads_kv, kh = unit % heads_kv, g = heads_q / heads_kv;
+  const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   grid_launch_dependents();   // the next step's split pass may set up its barriers behind this kernel
   grid_dependency_wait();     // the split pass has written all partials
+  const int2 sl = unit_slots[unit];
+  if (sl.x < 0 || sl.y < 0 || sl.x + sl.y > slot_limit) {   // the unit's slots do not fit the partial buffers
+    if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
+    return;
+  }
   const int prior = min((int)*step, max_tail - 1), tail = prior + 1;
-  const float* mean = vstat + (int64_t)unit * StatFloats;
-  const float* scale = mean + D;
   const __nv_bfloat16* kc = kcur + b * csb + kh * csh;
   const __nv_bfloat16* vc = vcur + b * csb + kh * csh;
   __nv_bfloat16* kt = ktail + unit * tsu;
   __nv_bfloat16* vt = vtail + unit * tsu;
-  if (r == 0 && tid < D) {
+  if (tid < D) {   // append the current token to the tail (read back only by later steps)
     kt[prior * tst + tid] = kc[tid];
     vt[prior * tst + tid] = vc[tid];
   }
-  const __nv_bfloat16* qrow = q + b * qsb + hq * qsh;
-  float qv[4], kmean[4];
+  // ---- tail scores for all heads of the group: one pass over the tail's K rows --------------------------
+  {
+    float qv[MaxGroup][4], kmean[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) { qv[i] = __bfloat162float(qrow[lane * 4 + i]); kmean[i] = kstat[(int64_t)unit * StatFloats + lane * 4 + i]; }
-  for (int t = warp; t < tail; t += W) {
-    const __nv_bfloat16* kv = t < prior ? kt + t * tst : kc;
-    float part = 0.f;
+    for (int i = 0; i < 4; ++i) kmean[i] = kstat[(int64_t)unit * StatFloats + lane * 4 + i];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) part = fmaf(qv[i], __bfloat162float(kv[lane * 4 + i]) - kmean[i], part);
+    for (int r = 0; r < MaxGroup; ++r) {
+      const __nv_bfloat16* qrow = q + b * qsb + (int64_t)(kh * g + min(r, g - 1)) * qsh + lane * 4;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (lane == 0) ts[t] = part * sm_log2;
+      for (int i = 0; i < 4; ++i) qv[r][i] = __bfloat162float(qrow[i]);
+    }
+    for (int t = warp; t < tail; t += MergeWarps) {
+      const __nv_bfloat16* kv = (t < prior ? kt + t * tst : kc) + lane * 4;
+      float kd[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kd[i] = __bfloat162float(kv[i]) - kmean[i];
+#pragma unroll
+      for (int r = 0; r < MaxGroup; ++r) {
+        if (r < g) {
+          float part = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) part = fmaf(qv[r][i], kd[i], part);
+#pragma unroll
+          for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+          if (lane == 0) ts[r][t] = part * sm_log2;
+        }
+      }
+    }
   }
   __syncthreads();
-  const int2 sl = unit_slots[unit];
-  const int sbeg = sl.x, splits = sl.y;
+  // ---- warp r merges Q head r ---------------------------------------------------------------------------
+  const int r = warp;
+  if (r >= g) return;
+  const int64_t first = (int64_t)sl.x * MaxGroup + r;
   float m = -FLT_MAX;
-  for (int s = tid; s < splits; s += MergeThreads) m = fmaxf(m, pm[(int64_t)(sbeg + s) * MaxGroup + r]);
-  for (int t = tid; t < tail; t += MergeThreads) m = fmaxf(m, ts[t]);
+  for (int s = lane; s < sl.y; s += 32) m = fmaxf(m, pm[first + s * ml_stride]);
+  for (int t = lane; t < tail; t += 32) m = fmaxf(m, ts[r][t]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (lane == 0) wmax[warp] = m;
-  __syncthreads();
-  m = wmax[0];
-#pragma unroll
-  for (int w = 1; w < W; ++w) m = fmaxf(m, wmax[w]);
-  for (int t = tid; t < tail; t += MergeThreads) ew[t] = exp2f(ts[t] - m);
-  float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s = warp; s < splits; s += W) {
-    const int64_t idx = (int64_t)(sbeg + s) * MaxGroup + r;
-    const float w = exp2f(pm[idx] - m);
-    l = fmaf(pl[idx], w, l);
-    const float4 p = *reinterpret_cast<const float4*>(po + idx * D + lane * 4);
-    o[0] = fmaf(p.x, w, o[0]); o[1] = fmaf(p.y, w, o[1]); o[2] = fmaf(p.z, w, o[2]); o[3] = fmaf(p.w, w, o[3]);
+  for (int t = lane; t < tail; t += 32) ts[r][t] = exp2f(ts[r][t] - m);
+  __syncwarp();
+  float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < sl.y; ++s) {
+    const float w = exp2f(pm[first + s * ml_stride] - m);
+    total = fmaf(pl[first + s * ml_stride], w, total);
+    const float4 p = *reinterpret_cast<const float4*>(po + first * D + s * o_stride + lane * 4);
+    acc[0] = fmaf(p.x, w, acc[0]); acc[1] = fmaf(p.y, w, acc[1]); acc[2] = fmaf(p.z, w, acc[2]); acc[3] = fmaf(p.w, w, acc[3]);
   }
-  if (lane == 0) wl[warp] = l;
-  *reinterpret_cast<float4*>(&wo[warp][lane * 4]) = make_float4(o[0], o[1], o[2], o[3]);
-  __syncthreads();
-  if (tid >= D) return;
-  float total = 0.f, acc = 0.f;
-#pragma unroll
-  for (int w = 0; w < W; ++w) { total += wl[w]; acc += wo[w][tid]; }
-  acc = acc * scale[tid] + total * mean[tid];
-  for (int t = 0; t < prior; ++t) {
-    const float e = ew[t];
+  const float4 mean = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + lane * 4);
+  const float4 scale = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + D + lane * 4);
+  acc[0] = acc[0] * scale.x + total * mean.x; acc[1] = acc[1] * scale.y + total * mean.y;
+  acc[2] = acc[2] * scale.z + total * mean.z; acc[3] = acc[3] * scale.w + total * mean.w;
+  for (int t = 0; t < tail; ++t) {
+    const float e = ts[r][t];
+    const uint2 raw = *reinterpret_cast<const uint2*>((t < prior ? vt + (int64_t)t * tst : vc) + lane * 4);
+    const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
     total += e;
-    acc = fmaf(e, __bfloat162float(vt[(int64_t)t * tst + tid]), acc);
+    acc[0] = fmaf(e, v01.x, acc[0]); acc[1] = fmaf(e, v01.y, acc[1]); acc[2] = fmaf(e, v23.x, acc[2]); acc[3] = fmaf(e, v23.y, acc[3]);
   }
-  total += ew[prior];
-  acc = fmaf(ew[prior], __bfloat162float(vc[tid]), acc);
-  out[b * osb + hq * osh + tid] = __float2bfloat16(acc / total);
+  const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc[0] / total, acc[1] / total);
+  const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc[2] / total, acc[3] / total);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&o01);
+  packed.y = *reinterpret_cast<const uint32_t*>(&o23);
+  *reinterpret_cast<uint2*>(out + b * osb + (int64_t)(kh * g + r) * osh + lane * 4) = packed;
 }
 
 
@@ -163,10 +187,12 @@ __global__ void __launch_bounds__(256) cache_store_bf16_kernel(uint8_t* pool, co
 }
 
 static int configure_decode() {
-  static int done = 0;   // per process; the attribute is per function
-  if (!done) {
+  static TriPerDevice configured;   // the attribute belongs to the (function, device) pair
+  const int device = configured.pending();
+  TRI_CHECK(device != -2, "decode: no current CUDA device");
+  if (device >= 0) {
     TRI_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeShared), "decode");
-    done = 1;
+    configured.mark(device);
   }
   return TRI_OK;
 }
@@ -182,6 +208,74 @@ extern "C" int tri_decode_occupancy(void) {
   return blocks;
 }
 
+namespace tri {
+// Arguments shared by the decode entry points, after validation.
+struct DecodeCall {
+  const __nv_bfloat16* q; int64_t qsb, qsh;
+  const uint8_t* pool; const int64_t* unit_base; const int32_t* unit_tab; const int32_t* unit_flags; const int2* tmeta;
+  const int4* segments; const int32_t* cta_segments; int num_ctas; const int2* unit_slots;
+  const float* kstat; const float* vstat; __nv_bfloat16* tail_k; __nv_bfloat16* tail_v; int64_t tsu, tst;
+  const __nv_bfloat16* kcur; const __nv_bfloat16* vcur; int64_t csb, csh; const int64_t* step;
+  __nv_bfloat16* out; int64_t osb, osh; int batch, heads_q, heads_kv, prompt, max_tail; float sm_log2; int* err;
+};
+
+static cudaError_t launch_split(const DecodeCall& c, float* pm, float* pl, float* po, int slot_limit, int stream_only,
+                                const MergeArgs& margs, cudaStream_t s, bool chained) {
+  if (chained)
+    return launch_chained(decode_kernel, dim3(c.num_ctas), dim3(DecodeThreads), DecodeShared, s, c.q, c.qsb, c.qsh, c.pool,
+                          c.unit_base, c.unit_tab, c.unit_flags, c.tmeta, c.segments, c.cta_segments, pm, pl, po, c.heads_q,
+                          c.heads_kv, c.prompt, c.sm_log2, stream_only, slot_limit, margs, c.err);
+  decode_kernel<<<c.num_ctas, DecodeThreads, DecodeShared, s>>>(c.q, c.qsb, c.qsh, c.pool, c.unit_base, c.unit_tab, c.unit_flags,
+      c.tmeta, c.segments, c.cta_segments, pm, pl, po, c.heads_q, c.heads_kv, c.prompt, c.sm_log2, stream_only, slot_limit, margs,
+      c.err);
+  return cudaSuccess;
+}
+
+static cudaError_t launch_merge(const DecodeCall& c, const float* pm, const float* pl, const float* po, int64_t ml_stride,
+                                int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained) {
+  const dim3 grid(c.batch * c.heads_kv);
+  if (chained)
+    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, unit_slots,
+                          slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb,
+                          c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
+  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
+      c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
+      c.heads_kv, c.max_tail, c.sm_log2, c.err);
+  return cudaSuccess;
+}
+
+static MergeArgs fused_merge_args(const DecodeCall& c, int32_t* unit_done) {
+  MergeArgs m{};
+  m.unit_slots = c.unit_slots; m.unit_done = unit_done; m.vstat = c.vstat; m.kstat = c.kstat; m.ktail = c.tail_k;
+  m.vtail = c.tail_v; m.tsu = c.tsu; m.tst = c.tst; m.kcur = c.kcur; m.vcur = c.vcur; m.csb = c.csb; m.csh = c.csh;
+  m.step = c.step; m.out = c.out; m.osb = c.osb; m.osh = c.osh; m.max_tail = c.max_tail;
+  return m;
+}
+constexpr int NoSlotLimit = 0x7fffffff;   // caller-allocated partials: their size is the caller's contract
+}  // namespace tri
+
+// Validation common to tri_decode, tri_decode_partials, tri_decode_merge and tri_decode_static.
+#define TRI_DECODE_COMMON_CHECKS(name)                                                                                       \
+  TRI_CHECK(q && unit_slots && kstat && vstat && tail_k && tail_v && kcur && vcur && step && out && device_error,           \
+            name ": null buffers");                                                                                          \
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&         \
+            max_tail >= 1 && max_tail <= 1024 && prompt > 0, "decode geometry/buffers");                                     \
+  TRI_CHECK((reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 && q_stride_h % 4 == 0 &&                     \
+            (reinterpret_cast<uintptr_t>(kcur) & 7u) == 0 && (reinterpret_cast<uintptr_t>(vcur) & 7u) == 0 &&               \
+            cur_stride_b % 4 == 0 && cur_stride_h % 4 == 0 && (reinterpret_cast<uintptr_t>(tail_k) & 7u) == 0 &&            \
+            (reinterpret_cast<uintptr_t>(tail_v) & 7u) == 0 && tail_stride_u % 4 == 0 && tail_stride_t % 4 == 0 &&          \
+            (reinterpret_cast<uintptr_t>(out) & 7u) == 0 && out_stride_b % 4 == 0 && out_stride_h % 4 == 0 &&               \
+            aligned16(vstat) && aligned16(kstat), name ": alignment (rows of q, kcur, vcur, the tails and out 8-byte aligned)")
+
+#define TRI_DECODE_CALL()                                                                                                    \
+  DecodeCall{static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool), unit_base,    \
+             unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),           \
+             cta_segments, num_ctas, reinterpret_cast<const int2*>(unit_slots), kstat, vstat,                               \
+             static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v), tail_stride_u, tail_stride_t,        \
+             static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur), cur_stride_b, cur_stride_h,  \
+             step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, batch, heads_q, heads_kv, prompt, max_tail, \
+             (float)(scale * 1.4426950408889634), device_error}
+
 extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
     const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments, const int32_t* cta_segments,
     int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
@@ -189,37 +283,70 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
     int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl,
     float* po, int32_t* unit_done, int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int phases,
     int* device_error, void* stream) {
-  TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && kstat &&
-            vstat && tail_k && tail_v && kcur && vcur && step && out && pm && pl && po && device_error, "decode: null buffers");
-  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
-            max_tail >= 1 && max_tail <= 1024 && prompt > 0 && num_ctas >= 0, "decode geometry/buffers");
-  TRI_CHECK(aligned16(pool) && aligned16(po) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 &&
-            q_stride_h % 4 == 0, "decode: alignment");
+  TRI_DECODE_COMMON_CHECKS("decode");
+  TRI_CHECK(pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && pm && pl && po && num_ctas >= 0,
+            "decode: null buffers");
+  TRI_CHECK(aligned16(pool) && aligned16(po), "decode: alignment");
   if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const float sm_log2 = (float)(scale * 1.4426950408889634);
-  const auto* qp = static_cast<const __nv_bfloat16*>(q);
+  const DecodeCall call = TRI_DECODE_CALL();
   // One launch when both phases are wanted and the caller provides the per-unit completion counters: the CTA
   // that finishes a unit's last segment merges it.  Otherwise the split pass and the merge are two launches.
   const bool fused = phases == 3 && unit_done != nullptr && num_ctas > 0;
-  MergeArgs margs{};
-  if (fused)
-    margs = MergeArgs{reinterpret_cast<const int2*>(unit_slots), unit_done, vstat, kstat, static_cast<__nv_bfloat16*>(tail_k),
-                      static_cast<__nv_bfloat16*>(tail_v), tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur),
-                      static_cast<const __nv_bfloat16*>(vcur), cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out),
-                      out_stride_b, out_stride_h, max_tail};
+  const MergeArgs margs = fused ? fused_merge_args(call, unit_done) : MergeArgs{};
   if (num_ctas > 0 && (phases & 1))
-    launch_chained(decode_kernel, dim3(num_ctas), dim3(DecodeThreads), DecodeShared, s, qp, q_stride_b, q_stride_h,
-        static_cast<const uint8_t*>(pool), unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta),
-        reinterpret_cast<const int4*>(segments), cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2,
-        (phases & 4) ? 1 : 0, margs, device_error);
+    TRI_CUDA(launch_split(call, pm, pl, po, NoSlotLimit, (phases & 4) ? 1 : 0, margs, s, true), "decode");
   if ((phases & 2) && !fused)
-    launch_chained(decode_merge_kernel, dim3(heads_q, batch), dim3(MergeThreads), 0, s, pm, pl, po,
-        reinterpret_cast<const int2*>(unit_slots), vstat, kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
-        tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),
-        cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, heads_q, heads_kv,
-        max_tail, sm_log2);
+    TRI_CUDA(launch_merge(call, pm, pl, po, MaxGroup, (int64_t)MaxGroup * D, call.unit_slots, NoSlotLimit, s, true), "decode");
   return tri_launch_status("decode");
+}
+
+extern "C" int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool,
+    const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
+    const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, float* pm, float* pl, float* po, int32_t* unit_done,
+    float* fold_m, float* fold_l, float* fold_o, int batch, int heads_q, int heads_kv, int prompt, double scale,
+    int* device_error, void* stream) {
+  TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && pm && pl &&
+            po && unit_done && fold_m && fold_l && fold_o && device_error, "decode_partials: null buffers");
+  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup && prompt > 0 &&
+            num_ctas >= 0, "decode geometry/buffers");
+  TRI_CHECK(aligned16(pool) && aligned16(po) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 &&
+            q_stride_h % 4 == 0, "decode_partials: alignment");
+  if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
+  if (num_ctas == 0) return TRI_OK;
+  DecodeCall call{};
+  call.q = static_cast<const __nv_bfloat16*>(q); call.qsb = q_stride_b; call.qsh = q_stride_h;
+  call.pool = static_cast<const uint8_t*>(pool); call.unit_base = unit_base; call.unit_tab = unit_tab; call.unit_flags = unit_flags;
+  call.tmeta = reinterpret_cast<const int2*>(tmeta); call.segments = reinterpret_cast<const int4*>(segments);
+  call.cta_segments = cta_segments; call.num_ctas = num_ctas; call.unit_slots = reinterpret_cast<const int2*>(unit_slots);
+  call.batch = batch; call.heads_q = heads_q; call.heads_kv = heads_kv; call.prompt = prompt;
+  call.sm_log2 = (float)(scale * 1.4426950408889634); call.err = device_error;
+  MergeArgs margs{};
+  margs.unit_slots = call.unit_slots; margs.unit_done = unit_done; margs.fold_m = fold_m; margs.fold_l = fold_l; margs.fold_o = fold_o;
+  TRI_CUDA(launch_split(call, pm, pl, po, NoSlotLimit, 0, margs, static_cast<cudaStream_t>(stream), true), "decode_partials");
+  return tri_launch_status("decode_partials");
+}
+
+extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
+    const float* po, int64_t split_stride, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k,
+    void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b,
+    int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, int batch, int heads_q,
+    int heads_kv, int max_tail, double scale, int* device_error, void* stream) {
+  const int prompt = 1;
+  TRI_DECODE_COMMON_CHECKS("decode_merge");
+  TRI_CHECK(pm && pl && po && aligned16(po) && split_stride >= 0 && split_stride % 4 == 0, "decode_merge: partials");
+  DecodeCall call{};
+  call.q = static_cast<const __nv_bfloat16*>(q); call.qsb = q_stride_b; call.qsh = q_stride_h;
+  call.kstat = kstat; call.vstat = vstat; call.tail_k = static_cast<__nv_bfloat16*>(tail_k); call.tail_v = static_cast<__nv_bfloat16*>(tail_v);
+  call.tsu = tail_stride_u; call.tst = tail_stride_t; call.kcur = static_cast<const __nv_bfloat16*>(kcur);
+  call.vcur = static_cast<const __nv_bfloat16*>(vcur); call.csb = cur_stride_b; call.csh = cur_stride_h; call.step = step;
+  call.out = static_cast<__nv_bfloat16*>(out); call.osb = out_stride_b; call.osh = out_stride_h; call.batch = batch;
+  call.heads_q = heads_q; call.heads_kv = heads_kv; call.max_tail = max_tail; call.sm_log2 = (float)(scale * 1.4426950408889634);
+  call.err = device_error;
+  const int64_t ml = split_stride ? split_stride : MaxGroup, os = split_stride ? split_stride : (int64_t)MaxGroup * D;
+  TRI_CUDA(launch_merge(call, pm, pl, po, ml, os, reinterpret_cast<const int2*>(unit_slots), NoSlotLimit,
+                        static_cast<cudaStream_t>(stream), true), "decode_merge");
+  return tri_launch_status("decode_merge");
 }
 
 extern "C" int tri_cache_store(void* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_count,
@@ -314,14 +441,11 @@ extern "C" int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_st
     void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur,
     int64_t cur_stride_b, int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,
     int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int* device_error, void* stream) {
-  TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && kstat &&
-            vstat && tail_k && tail_v && kcur && vcur && step && out && device_error, "decode_static: null buffers");
-  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup &&
-            max_tail >= 1 && max_tail <= 1024 && prompt > 0 && num_ctas > 0 && num_slots > 0, "decode geometry/buffers");
+  TRI_DECODE_COMMON_CHECKS("decode_static");
+  TRI_CHECK(pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && num_ctas > 0 && num_slots > 0 &&
+            aligned16(pool), "decode_static: null buffers");
   TRI_CHECK(num_slots <= StaticSlots,
             "decode_static: more than 1024 partial slots (segments); use tri_decode with caller-allocated partials");
-  TRI_CHECK(aligned16(pool) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 && q_stride_h % 4 == 0,
-            "decode: alignment");
   if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
   float* scratch = static_partials_for_current_device();
   if (scratch == nullptr) {
@@ -329,20 +453,15 @@ extern "C" int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_st
     return TRI_ERR_CUDA;
   }
   // Nothing in the array has to start at zero: the split pass writes every (slot, Q head) entry that the
-  // merge reads, so the previous call's contents are simply overwritten.
+  // merge reads, so the previous call's contents are simply overwritten.  Both kernels get the array's capacity:
+  // a slot number at or beyond it (a plan whose slot column is not 0 .. num_slots-1) is not stored to or read
+  // from; the kernel records ErrBadSlot in the device error word instead.
   float* pm = scratch;
   float* pl = scratch + (size_t)StaticSlots * MaxGroup;
   float* po = scratch + (size_t)StaticSlots * MaxGroup * 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const float sm_log2 = (float)(scale * 1.4426950408889634);
-  const auto* qp = static_cast<const __nv_bfloat16*>(q);
-  decode_kernel<<<num_ctas, DecodeThreads, DecodeShared, s>>>(qp, q_stride_b, q_stride_h, static_cast<const uint8_t*>(pool),
-      unit_base, unit_tab, unit_flags, reinterpret_cast<const int2*>(tmeta), reinterpret_cast<const int4*>(segments),
-      cta_segments, pm, pl, po, heads_q, heads_kv, prompt, sm_log2, 0, MergeArgs{}, device_error);
-  decode_merge_kernel<<<dim3(heads_q, batch), MergeThreads, 0, s>>>(pm, pl, po, reinterpret_cast<const int2*>(unit_slots), vstat,
-      kstat, qp, q_stride_b, q_stride_h, static_cast<__nv_bfloat16*>(tail_k), static_cast<__nv_bfloat16*>(tail_v),
-      tail_stride_u, tail_stride_t, static_cast<const __nv_bfloat16*>(kcur), static_cast<const __nv_bfloat16*>(vcur),
-      cur_stride_b, cur_stride_h, step, static_cast<__nv_bfloat16*>(out), out_stride_b, out_stride_h, heads_q, heads_kv,
-      max_tail, sm_log2);
+  const DecodeCall call = TRI_DECODE_CALL();
+  TRI_CUDA(launch_split(call, pm, pl, po, StaticSlots, 0, MergeArgs{}, s, false), "decode_static");
+  TRI_CUDA(launch_merge(call, pm, pl, po, MaxGroup, (int64_t)MaxGroup * D, call.unit_slots, StaticSlots, s, false), "decode_static");
   return tri_launch_status("decode_static");
 }

@@ -218,6 +218,7 @@ __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t 
 // Arguments of the merge (tail, statistics, output), passed by value to the kernel when the merge is fused.
 struct MergeArgs {
   const int2* unit_slots; int32_t* unit_done;      // unit_done == nullptr: no fused merge
+  float* fold_m; float* fold_l; float* fold_o;     // fold_m != nullptr: fold the unit's segments to one triple instead of merging
   const float* vstat; const float* kstat;
   __nv_bfloat16* ktail; __nv_bfloat16* vtail; int64_t tsu, tst;
   const __nv_bfloat16* kcur; const __nv_bfloat16* vcur; int64_t csb, csh;
@@ -310,12 +311,36 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
   }
 }
 
-// grid = persistent CTAs (one per SM), 160 threads.  cta_seg[c]..cta_seg[c+1] indexes the CTA's
+// Fold of one unit by the consumer warps of the CTA that finished the unit's last segment: one (m, l, o) per
+// Q head from the unit's segment partials, written at [unit][MaxGroup] of the fold buffers.  Used when a unit's
+// tile range is split across GPUs: the folded triples are what the ranks exchange.  Same arithmetic and order as
+// decode_fold_kernel; no V de-normalisation, no tail.
+__device__ __forceinline__ void fold_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
+    int unit, int g) {
+  const int2 sl = a.unit_slots[unit];
+  for (int e = threadIdx.x; e < g * D; e += ConsumerWarps * 32) {
+    const int r = e / D, ch = e % D;
+    float big = -FLT_MAX;
+    for (int s = 0; s < sl.y; ++s) big = fmaxf(big, __ldcg(pm + (int64_t)(sl.x + s) * MaxGroup + r));
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < sl.y; ++s) {
+      const int64_t idx = (int64_t)(sl.x + s) * MaxGroup + r;
+      const float w = exp2f(__ldcg(pm + idx) - big);
+      o = fmaf(__ldcg(po + idx * D + ch), w, o);
+      l = fmaf(__ldcg(pl + idx), w, l);
+    }
+    const int64_t dst = (int64_t)unit * MaxGroup + r;
+    a.fold_o[dst * D + ch] = o;
+    if (ch == 0) { a.fold_m[dst] = big; a.fold_l[dst] = l; }
+  }
+}
+
+// grid = persistent CTAs (one per SM), 224 threads.  cta_seg[c]..cta_seg[c+1] indexes the CTA's
 // segments; segs[j] = {unit, first kept tile, tile count, partial slot}; unit = sequence*heads_kv + kv head.
 __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
     const uint8_t* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int2* tmeta,
     const int4* segs, const int32_t* cta_seg, float* pm, float* pl, float* po, int heads_q, int heads_kv, int prompt_keys,
-    float sm_log2, int stream_only, MergeArgs margs, int* err) {
+    float sm_log2, int stream_only, int slot_limit, MergeArgs margs, int* err) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full[DecodeStages], empty[DecodeStages];
   __shared__ uint32_t stage_info[DecodeStages];
@@ -368,7 +393,7 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
       }
     }
   } else {
-    // ---- consumers: warp w owns tiles t = w, w+4, ... of the CTA's list ------------------------------
+    // ---- consumers: warp w owns tiles t = w, w + ConsumerWarps, ... of the CTA's list -----------------
     uint8_t* q8buf = smem + SmComb + warp * CombFloats * 4;
     uint8_t* q4buf = q8buf + 1024;
     float* comb = reinterpret_cast<float*>(smem + SmComb);
@@ -467,7 +492,10 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
         *reinterpret_cast<float2*>(mine + group * D + cb * 8 + sub * 2) = make_float2(st.out[cb][0] - st.corr, st.out[cb][1] - st.corr);
       if (sub == 0) { mine[MaxGroup * D + group] = st.m; mine[MaxGroup * D + MaxGroup + group] = den; }
       consumer_sync();
-      {
+      if (slot < 0 || slot >= slot_limit) {
+        // a plan whose slot column does not fit the partial buffers: record it and store nothing
+        if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
+      } else {
         for (int e = tid; e < g * D; e += ConsumerWarps * 32) {   // one (Q head, channel) per consumer thread
           const int r = e / D, ch = e % D;
           float mw[ConsumerWarps], big = -FLT_MAX;
@@ -499,7 +527,14 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
         consumer_sync();
         if (merge_flag) {
           __threadfence();
-          merge_unit_by_consumers(margs, pm, pl, po, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+          const int2 sl = margs.unit_slots[unit];
+          if (sl.x < 0 || sl.y < 0 || sl.x + sl.y > slot_limit) {
+            if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
+          } else if (margs.fold_m != nullptr) {
+            fold_unit_by_consumers(margs, pm, pl, po, unit, g);
+          } else {
+            merge_unit_by_consumers(margs, pm, pl, po, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+          }
         }
       }
     }

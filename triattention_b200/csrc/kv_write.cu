@@ -10,9 +10,10 @@
 // result bits depend on it: the 64-way strided partial sums, their in-order total, the butterflies of
 // the rotation, and the scale expressions.
 //
-// Design: everything here is HBM-bound byte work.  The Walsh-Hadamard transform runs in registers
-// with 16 features per lane (8 lanes per row): 4 in-register radix-2 stages and 3 shuffle stages,
-// so every lane ends up owning one 16-byte run of codes and stores it with one 128-bit store.
+// Design: everything here is HBM-bound byte work.  The Walsh-Hadamard transform runs in registers:
+// Q rows with 32 features per lane (4 lanes per row: 5 in-register radix-2 stages, 2 shuffle stages), K rows
+// with 16 features per lane (8 lanes per row: 4 in-register stages, 3 shuffle stages), so every lane ends up
+// owning whole 16-byte runs of codes and stores them with 128-bit stores.
 // K needs the whole-prompt channel mean and V the whole-prompt mean and range before any code can be
 // produced, so the write is two phases: statistics (K and V together), then codes (K, V).
 #include "common.cuh"

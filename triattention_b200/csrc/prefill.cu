@@ -16,88 +16,16 @@
 // integer accumulators equal the reference's s4 x s4 MMAs exactly.
 // Q arrives by TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle), K/V tiles by TMA bulk
 // copies of pre-tiled blobs (cp.async.bulk).  Every wait is bounded.
-#include "common.cuh"
+#include "tcgen05.cuh"
 #include "abi_internal.h"
-#include <cuda.h>
 #include <type_traits>
 
 namespace tri {
 
-// ---- tcgen05 / TMA tensor wrappers --------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {   // A in tensor memory
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-               ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets in 16-byte
-// units, descriptor version 1, layout type (0 = no swizzle, 2 = 128-byte swizzle).
-__host__ __device__ constexpr uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | ((uint64_t)1 << 46) | ((uint64_t)layout << 61);
-}
-// Instruction descriptor: accumulator format (1 = f32, 2 = s32), A/B formats (i8: 0 = u8, 1 = s8;
-// f16: 0 = f16, 1 = bf16), both operands K-major, N/8 and M/16.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t cfmt, uint32_t afmt, uint32_t bfmt, uint32_t m, uint32_t n) {
-  return (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-constexpr uint32_t LayoutNone = 0, Layout128B = 2;
-constexpr uint32_t IdescQK = instr_desc(2, 1, 1, 128, 64);    // s8 x s8 -> s32
-constexpr uint32_t IdescPV16 = instr_desc(1, 0, 0, 128, 128); // f16 x f16 -> f32
-// One fp16 MMA (M128 N64 K16) of constant operands, 16 products of 3072 * 256, writes 12582912.0f = 0x4B400000 into a
-// score buffer; the INT8 QK^T MMAs then accumulate on those bits, so a score read as a float is 12582912 + score.
-constexpr uint32_t IdescBias = instr_desc(1, 0, 0, 128, 64);
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
 constexpr int RowSplit = 2;           // softmax threads per query row (1 or 2; measured on config 3: 4.47 ms with 2, 4.60 ms with 1)
 constexpr int PrefillThreads = (4 + 8 * RowSplit) * 32;   // producer, 2 QK^T issuers, P.V issuer, 8 * RowSplit softmax warps
-constexpr int ProbeThreads = 128;
+constexpr int ProbeThreads = 128;   // qk_accum_kernel
 constexpr int MaxSteps = 2 * MaxTiles + 8;
 constexpr int SmQ8 = 0, SmQ4 = 32768;                            // 2 Q tiles each
 constexpr int SmBiasA = 65536, SmBiasB = SmBiasA + 4096;         // constant fp16 operands of the bias MMA (see IdescBias)
@@ -215,56 +143,6 @@ __global__ void __launch_bounds__(ProbeThreads) qk_accum_kernel(const __grid_con
   if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
-// ---- generic single-tile tensor-core probe: D[128 x n] = A . B^T from caller-built operand images ---
-// One CTA.  The images are copied verbatim to 1024-byte aligned shared memory; descriptor fields come
-// from the caller so that the tests can pin the layout conventions used above.
-__global__ void __launch_bounds__(ProbeThreads) umma_probe_kernel(const uint8_t* a_img, int a_bytes, const uint8_t* b_img,
-    int b_bytes, uint32_t a_lbo, uint32_t a_sbo, uint32_t a_layout, uint32_t a_step, uint32_t b_lbo, uint32_t b_sbo,
-    uint32_t b_layout, uint32_t b_step, uint32_t idesc, int f16_kind, int ksteps, int ncols, uint32_t* out, int* err) {
-  extern __shared__ uint8_t raw_smem[];
-  __shared__ __align__(8) uint64_t bar;
-  __shared__ uint32_t tmem_slot;
-  uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
-  const int tid = threadIdx.x, warp = tid / 32;
-  for (int i = tid; i < a_bytes / 16; i += ProbeThreads) reinterpret_cast<uint4*>(smem)[i] = reinterpret_cast<const uint4*>(a_img)[i];
-  for (int i = tid; i < b_bytes / 16; i += ProbeThreads)
-    reinterpret_cast<uint4*>(smem + 32768)[i] = reinterpret_cast<const uint4*>(b_img)[i];
-  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
-  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
-  fence_proxy_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
-  if (tid == 0) {
-    const uint32_t aa = smem_u32(smem), ba = smem_u32(smem + 32768);
-    for (int kk = 0; kk < ksteps; ++kk) {
-      const uint64_t ad = smem_desc(aa + kk * a_step, a_lbo, a_sbo, a_layout), bd = smem_desc(ba + kk * b_step, b_lbo, b_sbo, b_layout);
-      if (f16_kind) umma_f16(tmem, ad, bd, idesc, kk > 0);
-      else umma_i8(tmem, ad, bd, idesc, kk > 0);
-    }
-    tc_commit(&bar);
-  }
-  __syncwarp();
-  bool ok = mbar_wait(&bar, 0);
-  ok = __syncthreads_and(ok);
-  if (ok) {
-    tc_fence_after();
-    for (int c = 0; c < ncols / 16; ++c) {
-      uint32_t a[16];
-      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c * 16, a);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) out[(int64_t)tid * ncols + c * 16 + j] = a[j];
-    }
-  } else if (tid == 0) {
-    atomicExch(err, ErrBarrierTimeout);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
-}
-
 // ---- host side ----------------------------------------------------------------------------------
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -319,11 +197,13 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
             "output [B,Hq,T,128] aligned");
   TRI_CHECK(aligned16(q8) && aligned16(q4x) && aligned16(k8) && aligned16(k4x) && aligned16(v16) && aligned16(v8h),
             "attention: operands must be 16-byte aligned");
-  static int configured = 0;
-  if (!configured) {
+  static TriPerDevice configured;
+  const int device = configured.pending();
+  TRI_CHECK(device != -2, "attention: no current CUDA device");
+  if (device >= 0) {
     if (allow_smem(prefill_kernel<__nv_bfloat16>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
     if (allow_smem(prefill_kernel<__half>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
-    configured = 1;
+    configured.mark(device);
   }
   const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
   CUtensorMap map8, map4;
@@ -346,10 +226,12 @@ extern "C" int tri_qk_accumulators(const int32_t* requests, int num_requests, co
     const void* k4x, int32_t* acc, int batch, int heads_q, int heads_kv, int tokens, int* device_error, void* stream) {
   TRI_CHECK(requests && q8 && k8 && acc && device_error && num_requests > 0, "qk_accumulators: null buffers");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && tokens > 0, "qk_accumulators: bad geometry");
-  static int configured = 0;
-  if (!configured) {
+  static TriPerDevice configured;
+  const int device = configured.pending();
+  TRI_CHECK(device != -2, "qk_accumulators: no current CUDA device");
+  if (device >= 0) {
     if (allow_smem(qk_accum_kernel, 16384 + K8Bytes + 1024) != TRI_OK) return TRI_ERR_CUDA;
-    configured = 1;
+    configured.mark(device);
   }
   const int units = batch * heads_q;
   CUtensorMap map8, map4;
@@ -359,21 +241,4 @@ extern "C" int tri_qk_accumulators(const int32_t* requests, int num_requests, co
       reinterpret_cast<const int4*>(requests), static_cast<const uint8_t*>(k8), static_cast<const uint8_t*>(k4x ? k4x : k8), acc,
       heads_q, heads_kv, tokens, device_error);
   return tri_launch_status("qk_accumulators");
-}
-
-extern "C" int tri_umma_probe(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint32_t a_lbo, uint32_t a_sbo,
-    uint32_t a_layout, uint32_t a_step, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_layout, uint32_t b_step, uint32_t idesc,
-    int f16_kind, int ksteps, int ncols, uint32_t* out, int* device_error, void* stream) {
-  TRI_CHECK(a_img && b_img && out && device_error, "umma_probe: null buffers");
-  TRI_CHECK(a_bytes > 0 && a_bytes <= 32768 && b_bytes > 0 && b_bytes <= 32768 && a_bytes % 16 == 0 && b_bytes % 16 == 0 &&
-            ksteps > 0 && ksteps <= 8 && ncols >= 16 && ncols <= 256 && ncols % 16 == 0, "umma_probe: sizes");
-  static int configured = 0;
-  if (!configured) {
-    if (allow_smem(umma_probe_kernel, 65536 + 1024) != TRI_OK) return TRI_ERR_CUDA;
-    configured = 1;
-  }
-  umma_probe_kernel<<<1, ProbeThreads, 65536 + 1024, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(a_img),
-      a_bytes, static_cast<const uint8_t*>(b_img), b_bytes, a_lbo, a_sbo, a_layout, a_step, b_lbo, b_sbo, b_layout, b_step, idesc,
-      f16_kind, ksteps, ncols, out, device_error);
-  return tri_launch_status("umma_probe");
 }

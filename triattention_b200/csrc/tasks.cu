@@ -15,7 +15,6 @@
 
 namespace tri {
 
-constexpr int ErrBadTask = 3;   // a tile number outside the prompt in a task table
 
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
   int d;

@@ -136,7 +136,7 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
 
 class DecodeCache:
     def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None, fused_merge=False,
-                 fold_tail=0):
+                 fold_tail=0, split=None):
         """fold_tail: 0 keeps the reference's behaviour (generated tokens stay in a BF16 tail of at most max_tail
         <= 1024 rows).  N > 0 lifts that cap: room for N generated tokens is reserved behind every unit's stream, and
         each time 64 tokens have gathered in the tail they are quantised with the prompt's statistics into one more
@@ -149,14 +149,16 @@ class DecodeCache:
         chained by programmatic dependent launch.
         split_group: a torch.distributed process group over which every unit's tile range is split
         (long-context decode): each rank streams its part, the folded (m, l, o) triples are all-gathered over
-        NCCL and every rank runs the final merge.  None = this process holds whole units."""
+        NCCL and every rank runs the final merge.  None = this process holds whole units.
+        split = (rank, world) without a process group: this cache holds that part of every unit and the caller moves
+        the folded triples itself (`partials`, `merge_gathered`)."""
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
-        self.split_group, self.split, self.fused_merge = split_group, None, bool(fused_merge)
+        self.split_group, self.split, self.fused_merge = split_group, None if split is None else tuple(split), bool(fused_merge)
         self.reserve, self.generated, self.fold_buffers = -(-int(fold_tail) // FOLD_KEYS), 0, {}
-        if self.reserve and (split_group is not None or max_tail < FOLD_KEYS):
+        if self.reserve and (split_group is not None or split is not None or max_tail < FOLD_KEYS):
             raise ValueError("fold_tail needs max_tail >= 64 and no split_group")
         if split_group is not None:
             import torch.distributed as dist
@@ -227,16 +229,17 @@ class DecodeCache:
                 entry["unit_done"] = torch.zeros(units, dtype=torch.int32, device=device)   # segments finished per unit
             if self.split is not None:
                 # Folded triples of this rank in ONE buffer (m | l | o), so that a step needs one all-gather, and
-                # those of all ranks after it.
+                # those of all ranks after it ([rank][m | l | o]), which the merge reads in place by stride.
                 world, ug = self.split[1], units * MAX_GROUP
                 mine, every = f32(ug * 130), f32(world, ug * 130)
-                entry.update(folded=mine, gathered=every,
+                mine[:ug] = torch.finfo(torch.float32).min     # a unit without tiles on this rank keeps (-max, 0, 0)
+                mine[ug:] = 0
+                entry.update(folded=mine, gathered=every, rank_stride=ug * 130,
+                             unit_done=torch.zeros(units, dtype=torch.int32, device=device),
                              fm=mine[:ug].view(units, MAX_GROUP), fl=mine[ug:2 * ug].view(units, MAX_GROUP),
                              fo=mine[2 * ug:].view(units, MAX_GROUP, 128),
-                             gm=every[:, :ug].unflatten(1, (units, MAX_GROUP)),
-                             gl=every[:, ug:2 * ug].unflatten(1, (units, MAX_GROUP)),
-                             go=every[:, 2 * ug:].unflatten(1, (units, MAX_GROUP, 128)),
-                             rank_slots=torch.stack([torch.arange(units, dtype=torch.int32) * world,
+                             gm=every[0, :ug], gl=every[0, ug:2 * ug], go=every[0, 2 * ug:],
+                             rank_slots=torch.stack([torch.arange(units, dtype=torch.int32),
                                                      torch.full((units,), world, dtype=torch.int32)], 1).to(device))
         lo, n = first_sequence * heads_kv, part * heads_kv        # this call's units
         entry["kstat"][lo:lo + n] = ops["kstat"].view(n, 3, 128)
@@ -303,17 +306,33 @@ class DecodeCache:
             slots, e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, pm, pl, po, e["prompt"], scale, ph,
             unit_done=e["unit_done"] if ph == 3 else None)
         if self.split is None or phases != 3:      # (single phases: each kernel timed alone, on this rank's part)
+            if self.split is not None and (phases & 2):
+                raise RuntimeError("a sequence-split cache merges gathered triples: use phases=1 or the whole step")
             run(e["pm"], e["pl"], e["po"], d["unit_slots"], phases)
             return out
-        # sequence split: local split pass, fold to one triple per (unit, Q head), all-gather over the group,
-        # then the usual merge with one slot per rank
+        # sequence split: one launch streams this rank's tiles and folds every unit to one triple per Q head, one
+        # all-gather moves the triples over NVLink, and the merge reads the gathered [rank][m | l | o] buffer in place
         import torch.distributed as dist
-        run(e["pm"], e["pl"], e["po"], d["unit_slots"], 1)
-        self.module.decode_fold(e["pm"], e["pl"], e["po"], d["unit_slots"], e["fm"], e["fl"], e["fo"], q.shape[1] // k.shape[1])
+        self.partials(layer, q, k, scale)
         dist.all_gather_into_tensor(e["gathered"], e["folded"][None], group=self.split_group)
-        merged = [g.transpose(0, 1).contiguous() for g in (e["gm"], e["gl"], e["go"])]   # [unit][rank][...]
-        run(merged[0], merged[1], merged[2], e["rank_slots"], 2)
-        return out
+        return self.merge_gathered(layer, q, k, v, scale, out)
+
+    def partials(self, layer, q, k, scale):
+        """Sequence split, this rank's part: fills and returns the layer's `folded` buffer (m | l | o, one triple per
+        unit and Q head), which the ranks exchange."""
+        e = self.layers[layer]
+        d = e["dev"]
+        self.module.decode_partials(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
+                                    d["cta_segments"], d["unit_slots"], e["pm"], e["pl"], e["po"], e["unit_done"], e["fm"],
+                                    e["fl"], e["fo"], k.shape[1], e["prompt"], scale)
+        return e["folded"]
+
+    def merge_gathered(self, layer, q, k, v, scale, out=None):
+        """Sequence split, after the exchange: merges the layer's `gathered` buffer ([rank][m | l | o]) with the tail."""
+        e = self.layers[layer]
+        out = torch.empty_like(q) if out is None else out
+        return self.module.decode_merge(q, e["gm"], e["gl"], e["go"], e["rank_stride"], e["rank_slots"], e["kstat"],
+                                        e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, scale)
 
     def advance(self):
         self.generated += 1

@@ -32,14 +32,16 @@ SIGNATURES = {
     "tri_decode_static": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P,
                           _L, _L, _I, _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_fold": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "tri_decode_partials": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L, _I, _I, _I, _I,
+                         _D, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
-    "tri_umma_probe": [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, _P, _P],
     "tri_abi_version": [],
 }
 
 
-ABI_VERSION = 2      # tri_abi_version() of the library these signatures describe
+ABI_VERSION = 3      # tri_abi_version() of the library these signatures describe
 
 
 def load_library() -> ctypes.CDLL:
@@ -79,19 +81,32 @@ class Module:
             raise RuntimeError(self.lib.tri_last_error().decode())
         return status
 
+    @staticmethod
+    def _device_index(device):
+        """Index of a CUDA device given as torch.device / str / int; "cuda" means the current device."""
+        d = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        return torch.cuda.current_device() if d.index is None else d.index
+
     def error_word(self, device):
-        key = torch.device(device).index or 0
+        """The int32 word on `device` that kernels with bounded waits write their error code to (one per GPU)."""
+        key = self._device_index(device)
         if key not in self._errors:
-            self._errors[key] = torch.zeros(1, dtype=torch.int32, device=device)
+            self._errors[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
         return self._errors[key]
 
-    def check_device_error(self, device="cuda"):
-        """Synchronise and raise if a kernel reported a bounded wait that ran out."""
-        word = int(self.error_word(device).item())
-        if word:
-            self.error_word(device).zero_()
-            raise RuntimeError(f"TriAttention kernel reported device error {word} (1 = barrier wait ran out, "
-                               "3 = tile number outside the prompt in a task table)")
+    def check_device_error(self, device=None):
+        """Synchronise and raise if a kernel reported an error (a bounded wait that ran out, a bad table entry).
+        device=None checks the word of every GPU this process has launched on."""
+        keys = sorted(self._errors) if device is None else [self._device_index(device)]
+        for key in keys:
+            if key not in self._errors:
+                continue
+            word = int(self._errors[key].item())
+            if word:
+                self._errors[key].zero_()
+                raise RuntimeError(f"TriAttention kernel reported device error {word} on cuda:{key} (1 = barrier wait ran "
+                                   "out, 3 = tile number outside the prompt in a task table, 4 = partial slot outside the "
+                                   "buffer)")
 
     @staticmethod
     def _bhtd(x, name):
@@ -233,7 +248,15 @@ class Module:
         """Decode step whose split-KV partials live in the library's own fixed device array, for callers that
         cannot allocate GPU memory.  Refuses plans with more than 1024 segments; calls that may overlap on the
         GPU must not share a device."""
+        if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1):
+            raise RuntimeError("q [B,Hq,1,128]")
         b, hq, hk = q.shape[0], q.shape[1], kcur.shape[1]
+        if not (hq % hk == 0 and hq // hk <= 8 and tail_k.shape[1] <= 1024 and step.dtype == torch.int64 and step.is_cuda and
+                kcur.stride(3) == 1 and vcur.stride(1) == kcur.stride(1) and vcur.stride(0) == kcur.stride(0) and
+                segments.dtype == torch.int32 and cta_segments.dtype == torch.int32 and tmeta.dtype == torch.int32 and
+                unit_base.dtype == torch.int64 and unit_slots.dtype == torch.int32 and
+                tail_v.stride() == tail_k.stride() and out.stride(3) == 1):
+            raise RuntimeError("decode geometry/buffers")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_decode_static(
                 q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
@@ -250,6 +273,35 @@ class Module:
                                                  fm.data_ptr(), fl.data_ptr(), fo.data_ptr(), unit_slots.shape[0], group,
                                                  _stream()))
 
+    def decode_partials(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, pm, pl, po,
+                        unit_done, fm, fl, fo, heads_kv, prompt, scale):
+        """This GPU's part of a sequence-split decode step: split pass + in-kernel fold to one triple per (unit, Q head)."""
+        if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1 and
+                unit_done.dtype == torch.int32 and fm.dtype == torch.float32 and fo.is_contiguous()):
+            raise RuntimeError("decode geometry/buffers")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_decode_partials(
+                q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
+                unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(), cta_segments.data_ptr(), cta_segments.numel() - 1,
+                unit_slots.data_ptr(), pm.data_ptr(), pl.data_ptr(), po.data_ptr(), unit_done.data_ptr(), fm.data_ptr(),
+                fl.data_ptr(), fo.data_ptr(), q.shape[0], q.shape[1], heads_kv, int(prompt), float(scale),
+                self.error_word(q.device).data_ptr(), _stream()))
+
+    def decode_merge(self, q, pm, pl, po, split_stride, unit_slots, kstat, vstat, tail_k, tail_v, kcur, vcur, step, out, scale):
+        """The merge alone, over partials that may lie strided (triples gathered from several GPUs, merged in place)."""
+        if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1 and
+                kcur.stride(3) == 1 and vcur.stride(0) == kcur.stride(0) and vcur.stride(1) == kcur.stride(1) and
+                tail_v.stride() == tail_k.stride() and out.stride(3) == 1 and step.dtype == torch.int64):
+            raise RuntimeError("decode geometry/buffers")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_decode_merge(
+                q.data_ptr(), q.stride(0), q.stride(1), pm.data_ptr(), pl.data_ptr(), po.data_ptr(), int(split_stride),
+                unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(), tail_k.data_ptr(), tail_v.data_ptr(),
+                tail_k.stride(0), tail_k.stride(1), kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
+                step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), q.shape[0], q.shape[1], kcur.shape[1],
+                tail_k.shape[1], float(scale), self.error_word(q.device).data_ptr(), _stream()))
+        return out
+
     def decode_occupancy(self):
         return self._check(self.lib.tri_decode_occupancy())
 
@@ -261,15 +313,6 @@ class Module:
                                                      k8.data_ptr(), _ptr(k4x), acc.data_ptr(), batch, heads_q, heads_kv,
                                                      tokens, self.error_word(q8.device).data_ptr(), _stream()))
         return acc
-
-    def umma_probe(self, a_img, b_img, a_desc, b_desc, idesc, f16_kind, ksteps, ncols):
-        """a_desc/b_desc = (lbo bytes, sbo bytes, layout type, byte advance per K step)."""
-        out = torch.zeros((128, ncols), dtype=torch.int32, device=a_img.device)
-        with torch.cuda.device(a_img.device):
-            self._check(self.lib.tri_umma_probe(a_img.data_ptr(), a_img.numel(), b_img.data_ptr(), b_img.numel(), *a_desc,
-                                                *b_desc, idesc, int(f16_kind), ksteps, ncols, out.data_ptr(),
-                                                self.error_word(a_img.device).data_ptr(), _stream()))
-        return out
 
 
 @functools.cache
