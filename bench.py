@@ -13,8 +13,19 @@ Printed JSON (one line, rank 0): value = tokens/s with all inputs resident in HB
 the public DecodeCache call with host buffers (pinned H2D of q/k/v and D2H of the output inside the
 timed region); roofline = algorithmic cache bytes per launch / CUDA-event time of the split-KV kernel
 against the measured HBM copy peak; cpu_baseline = the CPU oracle port on a bounded sample.
-`--impl reference` times that CPU port alone (the reference has no CPU or sm_100 implementation of its
-own to run; its CUDA extension is used only as the parity oracle in the tests).
+After that timed region, outside it, the same line gets secondary records (each can be skipped with --no-extras):
+  prefill     configuration 3 (28 Q / 4 KV heads, batch 2, 16384 tokens): INT8 TOP/s of the prefill kernel against the
+              nominal dense INT8 peak and against i8_peak, and the KV-cache write in GB/s            (1 GPU runs)
+  i8_peak     what back-to-back tcgen05 kind::i8 MMAs (M128 N256 K32, operands in shared memory) sustain on this GPU
+  ref_ext     the reference's own CUDA extension (its sm_80 source compiled for sm_100, what a B200 runs today) timed
+              on the same inputs: decode as 32 sequential batch-1 calls, prefill as 2 calls           (1 GPU runs)
+  sharded_c5  configuration 5 (32 Q / 8 KV heads, 64 sequences x 131072 cached tokens) placed on the N GPUs by byte
+              cost (sharding.shard_grid), each rank holding only its own units' cache, one decode step including the
+              all-gather of the outputs; efficiency against the same step on one GPU, measured in the same run
+  split       4 sequences x 131072 tokens with every unit's tile range cut over the N GPUs (fold in the split pass, one
+              NCCL all-gather of (m, l, o) triples, strided merge) against one GPU                     (N > 1 runs)
+`--impl reference` times the CPU port alone (the reference has no CPU implementation of its own to run; its CUDA
+extension is timed in the ref_ext record above and is the parity oracle of the tests).
 """
 from __future__ import annotations
 
@@ -46,8 +57,15 @@ CONFIG_LONG = dict(workload="decode C5: 32 Q / 8 KV heads, head_dim 128, batch 6
 FALLBACK_HBM_GBS = 6650.0
 
 
-def kv_kinds(seed=1):
-    return [str(x) for x in np.random.default_rng(seed).permutation(np.array(CONFIG["kinds"]))]
+def kv_kinds(seed=1, cfg=None):
+    return [str(x) for x in np.random.default_rng(seed).permutation(np.array((cfg or CONFIG)["kinds"]))]
+
+
+def unit_kv(b, h, t, which):
+    """K (which = 0) or V (1) of one (sequence, KV head) unit of the long workload, generated on the GPU from a seed
+    of its own, so that a unit holds the same values whichever GPU it is placed on: N(0,1) with one of the 128
+    channels (1 %) scaled x20."""
+    return synth_cuda((1, t, 128), 2 * (b * 64 + h) + which)[0]
 
 
 def synth_cuda(shape, seed, fraction=0.01, factor=20.0):
@@ -116,18 +134,31 @@ class ClockSampler:
                     samples=len(rows))
 
 
-def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, split_group=None):
-    """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (cache, plan).
-    part = sequences written per pass (None = all at once); with it the prompts are generated on the GPU."""
+def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, split_group=None, cfg=None, heads=None,
+                sequences=None):
+    """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (module, cache, plan).
+    part = sequences written per pass (None = all at once); with it the prompts are generated on the GPU.
+    cfg = the configuration (default: the benchmark's); heads / sequences = the KV heads and sequence numbers this
+    GPU holds (unit sharding; with them every unit is generated from its own seed, see unit_kv)."""
+    from triattention_b200 import sharding
     from triattention_b200.kernels.decode import DecodeCache
     from triattention_b200.kernels.extension import load_extension
     from triattention_b200.kernels.prefill import Prefill
     from triattention_b200.maps import per_kv_head
-    hq, hk, t = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"]
+    cfg = cfg or CONFIG
+    hq, hk, t = cfg["heads_q"], cfg["heads_kv"], cfg["cache_tokens"]
+    g = hq // hk
     module = load_extension()
     cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, split_group=split_group,
                         **({"tile_costs": tile_costs} if tile_costs else {}))
-    pre = Prefill(module, per_kv_head(kv_kinds(), hq // hk), cache)
+    fn = per_kv_head(kv_kinds(cfg=cfg), g)
+    by_unit = heads is not None
+    if by_unit:
+        shard = sharding.Shard(0, slice(0, batch), tuple(heads))
+        fn = sharding.slice_map(fn, shard, g, hq)
+        hk, hq = len(heads), len(heads) * g
+    sequences = list(range(seed0, seed0 + batch)) if sequences is None else list(sequences)
+    pre = Prefill(module, fn, cache)
     make = synth_cuda if part else (lambda shape, seed: synth(shape, seed).cuda())
     step = part or batch
     k = torch.empty((step, hk, t, 128), dtype=torch.bfloat16, device="cuda")
@@ -136,8 +167,12 @@ def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, spl
     for first in range(0, batch, step):
         n = min(step, batch - first)
         for b in range(n):
-            k[b] = make((hk, t, 128), 2 * (seed0 + first + b))
-            v[b] = make((hk, t, 128), 2 * (seed0 + first + b) + 1)
+            if by_unit:
+                for i, h in enumerate(heads):
+                    k[b, i], v[b, i] = unit_kv(sequences[first + b], h, t, 0), unit_kv(sequences[first + b], h, t, 1)
+            else:
+                k[b] = make((hk, t, 128), 2 * sequences[first + b])
+                v[b] = make((hk, t, 128), 2 * sequences[first + b] + 1)
         table, ops = pre.write(0, q[:n], k[:n], v[:n])
         cache.store(0, t, ops, table.host, k[:n], v[:n], table.bf16_kv, first_sequence=first, sequences=batch)
     torch.cuda.synchronize()
@@ -237,25 +272,66 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
-def run_prefill(args):
-    """Secondary metric: INT8 TOP/s of the banded prefill (benchmark configuration 3: 28 Q / 4 KV heads, batch 2,
-    16384 tokens, 3 INT8 + 1 INT4 KV heads) including the fused KV-cache write.  One GPU, one JSON line."""
+def measure_i8_peak(seconds=0.1):
+    """Back-to-back tcgen05 kind::i8 MMAs (M128 N256 K32, operands resident in shared memory), one CTA per SM, timed
+    with CUDA events: the INT8 tensor throughput this GPU sustains when it does nothing else (tests/probe/i8_peak.cu)."""
+    import ctypes
+    sys.path.insert(0, str(ROOT / "tests"))
+    try:
+        from probe import build_probe
+        lib = build_probe.load()
+    except (ImportError, OSError, FileNotFoundError) as e:
+        return dict(unavailable=f"probe library not built: {e}")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    err, ops = torch.zeros(1, dtype=torch.int32, device="cuda"), ctypes.c_int64()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(iterations):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        if lib.tri_i8_peak(sms, iterations, ctypes.byref(ops), err.data_ptr(), stream) != 0:
+            raise RuntimeError(lib.tri_probe_last_error().decode())
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop)
+
+    run(2000)
+    ms = run(20000)                                        # sizes the long run
+    iterations = int(min(1 << 22, max(20000, 20000 * seconds * 1e3 / ms)))
+    with ClockSampler(0) as clocks:
+        ms = min(run(iterations) for _ in range(2))
+        per_cta = ops.value                                # of the timed launch (every launch overwrites it)
+        run(iterations * 4)                                # the same load a little longer, for the clock sampler
+    if int(err.item()):
+        return dict(unavailable="the peak kernel's bounded wait ran out")
+    tops = sms * per_cta / (ms / 1e3) / 1e12
+    return dict(tops=tops, ms=ms, mma="tcgen05.mma kind::i8 M128 N256 K32, A and B in shared memory", ctas=sms,
+                mmas_per_cta=4 * iterations, nominal_tops=4500.0, frac_of_nominal=tops / 4500.0, clocks=clocks.summary())
+
+
+def prefill_inputs(b, hq, hk, t):
+    kinds = [str(x) for x in np.random.default_rng(1).permutation(np.array(["int8", "int8", "int8", "int4"]))]
+    q = torch.stack([synth_cuda((hq, t, 128), 10 + i) for i in range(b)])
+    k = torch.stack([synth_cuda((hk, t, 128), 20 + i) for i in range(b)])
+    v = torch.stack([synth_cuda((hk, t, 128), 30 + i) for i in range(b)])
+    return kinds, q, k, v
+
+
+def measure_prefill(b, t, steps, warmup, peak=None):
+    """INT8 TOP/s of the banded prefill (benchmark configuration 3: 28 Q / 4 KV heads, batch 2, 16384 tokens, 3 INT8 +
+    1 INT4 KV heads) and the KV-cache write in GB/s.  One GPU."""
     from triattention_b200.kernels.extension import load_extension
     from triattention_b200.kernels.prefill import Prefill
     from triattention_b200.maps import per_kv_head
-    torch.cuda.set_device(0)
     module = load_extension()
-    b, hq, hk, t = args.batch, 28, 4, args.tokens
-    kinds = [str(x) for x in np.random.default_rng(1).permutation(np.array(["int8", "int8", "int8", "int4"]))]
-    q = torch.stack([synth((hq, t, 128), 10 + i) for i in range(b)]).cuda()
-    k = torch.stack([synth((hk, t, 128), 20 + i) for i in range(b)]).cuda()
-    v = torch.stack([synth((hk, t, 128), 30 + i) for i in range(b)]).cuda()
+    hq, hk = 28, 4
+    kinds, q, k, v = prefill_inputs(b, hq, hk, t)
     pre = Prefill(module, per_kv_head(kinds, hq // hk))
     scale = 128 ** -0.5
-    warmup = warm_up(lambda: pre(0, q, k, v, scale), max(3, args.warmup))
+    ran = warm_up(lambda: pre(0, q, k, v, scale), max(3, warmup))
     module.check_device_error()
-    steps = max(1, min(args.steps, 20))
-    with ClockSampler(0) as clocks:
+    steps = max(1, min(steps, 20))
+    with ClockSampler(torch.cuda.current_device()) as clocks:
         ms_all = timed(lambda i: pre(0, q, k, v, scale), steps, None) / steps
         ms_write = timed(lambda i: pre.write(0, q, k, v), steps, None) / steps
         t_extra, extra = time.time(), 0
@@ -276,17 +352,195 @@ def run_prefill(args):
     ops = b * hq * (rows * (rows + 1) // 2) * 2 * 64 * 64 * 128 * 2
     tops = ops / ((ms_all - ms_write) / 1e3) / 1e12
     nominal = 4500.0
-    print(json.dumps(dict(metric="prefill_int8_tops", value=ops / (ms_all / 1e3) / 1e12, unit="TOP/s", n_gpus=1, steps=steps,
-                          warmup=warmup, ms_per_step=ms_all, higher_is_better=True, dtype="int8 (QK^T) / fp16 (P.V)", data="synthetic",
-                          config=dict(workload=f"prefill C3: 28 Q / 4 KV heads, batch {b}, {t} tokens, map {kinds}, incl. KV write",
-                                      l2="operands larger than L2"),
-                          roofline=dict(bound="tensor", achieved=tops, peak=nominal, unit="TOP/s", frac=tops / nominal,
-                                        kernel="prefill_kernel", ms_per_launch=ms_all - ms_write, ops_per_launch=ops,
-                                        peak_source="nominal dense INT8 (2 x bf16 nominal); no measured INT8 peak in MEASURED_PEAKS.json",
-                                        traffic=None),
-                          kv_write_ms=ms_write, kv_write_bytes=write_bytes, kv_write_gbs=write_bytes / (ms_write / 1e3) / 1e9,
-                          kv_write_frac_of_measured_hbm=write_bytes / (ms_write / 1e3) / 1e9 / peak_hbm()[0],
-                          clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))))
+    roofline = dict(bound="tensor", achieved=tops, peak=nominal, unit="TOP/s", frac=tops / nominal, kernel="prefill_kernel",
+                    ms_per_launch=ms_all - ms_write, ops_per_launch=ops, peak_source="nominal dense INT8 (2 x bf16 nominal)",
+                    traffic=None)
+    if peak and "tops" in peak:
+        roofline.update(measured_i8_tops=peak["tops"], frac_of_measured_i8=tops / peak["tops"])
+    pre.buffers.clear(), pre.views.clear()
+    return dict(metric="prefill_int8_tops", value=ops / (ms_all / 1e3) / 1e12, unit="TOP/s", steps=steps, warmup=warmup,
+                warmup_steps_run=ran, ms_per_step=ms_all, dtype="int8 (QK^T) / fp16 high + low parts (P.V)",
+                config=dict(workload=f"prefill C3: 28 Q / 4 KV heads, batch {b}, {t} tokens, map {kinds}, incl. KV write",
+                            l2="operands larger than L2"),
+                roofline=roofline, kv_write_ms=ms_write, kv_write_bytes=write_bytes,
+                kv_write_gbs=write_bytes / (ms_write / 1e3) / 1e9,
+                kv_write_frac_of_measured_hbm=write_bytes / (ms_write / 1e3) / 1e9 / peak_hbm()[0],
+                clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))
+
+
+def run_prefill(args):
+    """--workload prefill: the prefill record alone, as its own JSON line."""
+    torch.cuda.set_device(0)
+    peak = measure_i8_peak()
+    line = measure_prefill(args.batch, args.tokens, args.steps, args.warmup, peak)
+    line.update(n_gpus=1, higher_is_better=True, data="synthetic", i8_peak=peak)
+    print(json.dumps(line))
+
+
+def measure_ref_ext(steps):
+    """The kernel to beat: the reference's own CUDA extension (its sm_80 source compiled for sm_100, which is what its
+    loader runs on a B200, kernels/extension.py:23-25,45), driven like its Python executors drive it, on this
+    benchmark's inputs.  The reference is batch 1, so the 32 sequences of a decode step are 32 calls one after the
+    other and the 2 sequences of the prefill 2 calls; its kernels have no un-quantised head kind, so the BF16 KV heads
+    of configuration 2 are INT8 heads here (fewer bytes than the product streams for them).  Baseline leg only."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    try:
+        import build_ref
+        from ref_harness import RefRunner
+        run = RefRunner(build_ref.load())
+    except (ImportError, OSError, FileNotFoundError) as e:
+        return dict(unavailable=f"reference extension not built: {e}")
+    scale = 128 ** -0.5
+    out = dict(kernel="prefill_sm80.cu compiled with -gencode arch=compute_100,code=sm_100 (the reference's own flags)")
+    # decode, configuration 2
+    hq, hk, t, batch = CONFIG["heads_q"], CONFIG["heads_kv"], CONFIG["cache_tokens"], CONFIG["batch"]
+    bands = np.array([[1, INF] if kind == "int4" else [INF, INF] for kind in kv_kinds() for _ in range(hq // hk)], np.int64)
+    zero_q = torch.zeros((1, 1, 1, 128), dtype=torch.bfloat16, device="cuda").expand(1, hq, t, 128)
+    states = []
+    for b in range(batch):
+        k, v = synth((hk, t, 128), 2 * b).cuda()[None], synth((hk, t, 128), 2 * b + 1).cuda()[None]
+        o = run.prefill(zero_q, k, v, bands, scale, attention=False)
+        states.append(run.decode_setup(o, bands, max_tail=256))
+        del o
+    qd, kd, vd = (torch.stack([synth((h, 1, 128), 100 + i + 1000 * b) for b in range(batch)]).cuda() for i, h in enumerate((hq, hk, hk)))
+    step = lambda i: [run.decode(states[b], qd[b:b + 1], kd[b:b + 1], vd[b:b + 1], scale) for b in range(batch)]
+    for i in range(3):
+        step(i)
+    ms = timed(step, steps, None) / steps
+    out.update(decode_tokens_per_s=batch / (ms / 1e3), decode_ms_per_step=ms, decode_calls_per_step=batch,
+               decode_splits_of_tiles=int(states[0]["per"]),
+               decode_workload=f"{CONFIG['workload']}; BF16 KV heads run as INT8 heads; 32 sequential batch-1 calls")
+    del states
+    torch.cuda.empty_cache()
+    # prefill, configuration 3
+    hq, hk, t, b = 28, 4, 16384, 2
+    kinds, q, k, v = prefill_inputs(b, hq, hk, t)
+    bands = np.array([[1, INF] if kind == "int4" else [INF, INF] for kind in kinds for _ in range(hq // hk)], np.int64)
+    call = lambda i: [run.prefill(q[j:j + 1], k[j:j + 1], v[j:j + 1], bands, scale, with_decode=True) for j in range(b)]
+    call(0)
+    reps = max(1, min(steps, 5))
+    ms = timed(call, reps, None) / reps
+    rows = (t + 63) // 64
+    ops = b * hq * (rows * (rows + 1) // 2) * 2 * 64 * 64 * 128 * 2
+    out.update(prefill_ms=ms, prefill_tops=ops / (ms / 1e3) / 1e12,
+               prefill_workload=f"prefill C3: 28 Q / 4 KV heads, batch {b} as {b} calls, {t} tokens, map {kinds}, incl. its KV write")
+    return out
+
+
+def long_inputs(cfg, batch):
+    """Decode-step inputs of the long workload for sequences 0 .. batch-1, the same on every rank."""
+    hq, hk = cfg["heads_q"], cfg["heads_kv"]
+    return [torch.stack([synth_cuda((h, 1, 128), 5000 + 10 * b + i) for b in range(batch)]) for i, h in enumerate((hq, hk, hk))]
+
+
+def time_steps(step, steps, dist, warm=5):
+    for i in range(warm):          # count-based: with a collective in the step every rank runs the same number
+        step(i)
+    torch.cuda.synchronize()
+    return timed(step, steps, dist) / steps
+
+
+def measure_sharded_c5(rank, world, dist, steps):
+    """Configuration 5 (32 Q / 8 KV heads, 64 sequences x 131072 cached tokens, 4 INT4 / 3 INT8 / 1 BF16 KV heads) as
+    ONE job on N GPUs: sharding.shard_grid places (batch slice) x (KV-head group) rectangles by the per-head cache
+    bytes under the mixed map, every rank writes and holds only its own units' cache, and a step is the rank's decode
+    plus the all-gather that gives every rank the whole output.  Strong scaling: efficiency = t(1 GPU) / (N x t(N)),
+    the one-GPU time measured by rank 0 in this same run on the same data."""
+    from triattention_b200 import sharding
+    from triattention_b200.maps import per_kv_head
+    cfg = CONFIG_LONG
+    hq, hk, t, batch = cfg["heads_q"], cfg["heads_kv"], cfg["cache_tokens"], cfg["batch"]
+    g, scale = hq // hk, 128 ** -0.5
+    kinds = kv_kinds(cfg=cfg)
+    fn = per_kv_head(kinds, g)
+    costs = sharding.head_costs(fn(0, hq).numpy(), hk, t, fn.bf16_kv_heads(0))
+    qd, kd, vd = long_inputs(cfg, batch)
+    record = dict(workload=cfg["workload"], map=kinds, scaling="strong", head_cache_bytes_per_sequence=[int(c) for c in costs])
+    one = None
+    if rank == 0:
+        module, cache, plan = build_cache(batch, 0, part=2, cfg=cfg, heads=list(range(hk)))
+        out = torch.empty_like(qd)
+        ms1 = time_steps(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, None)
+        module.check_device_error()
+        one = dict(ms=ms1, out=out.clone(), bytes=int(plan["payload_bytes"]))
+        record.update(one_gpu_ms_per_step=ms1, one_gpu_tokens_per_s=batch / (ms1 / 1e3),
+                      one_gpu_gbs=one["bytes"] / (ms1 / 1e3) / 1e9, cache_bytes_per_step=one["bytes"])
+        del cache, plan
+        torch.cuda.empty_cache()
+    if world == 1:
+        record.update(n_gpus=1, tokens_per_s=record["one_gpu_tokens_per_s"], ms_per_step=record["one_gpu_ms_per_step"],
+                      per_gpu_gbs=record["one_gpu_gbs"], efficiency=1.0, shards=[dict(sequences=[0, batch], kv_heads=list(range(hk)))])
+        return record
+    dist.barrier()
+    shards = sharding.shard_grid(batch, costs, world)
+    mine = shards[rank]
+    heads, qh = list(mine.kv_heads), list(mine.q_heads(g))
+    nb = mine.batch.stop - mine.batch.start
+    module, cache, plan = build_cache(nb, 0, part=2, cfg=cfg, heads=heads, sequences=range(mine.batch.start, mine.batch.stop))
+    take = lambda x, hs: x[mine.batch].index_select(1, torch.as_tensor(hs, device=x.device)).contiguous()
+    ql, kl, vl = take(qd, qh), take(kd, heads), take(vd, heads)
+    out_local = torch.empty_like(ql)
+    gather = sharding.OutputGatherer(shards, g, batch, hq, out_local)
+    full = [None]
+
+    def step(i):
+        cache(0, ql, kl, vl, scale, out=out_local)
+        full[0] = gather(out_local)
+
+    ms = time_steps(step, steps, dist)
+    ms_local = time_steps(lambda i: cache(0, ql, kl, vl, scale, out=out_local), steps, dist)
+    module.check_device_error()
+    loads = torch.tensor([float(plan["payload_bytes"])], device="cuda")
+    every = [torch.zeros_like(loads) for _ in range(world)]
+    dist.all_gather(every, loads)
+    loads = [float(x.item()) for x in every]
+    if rank == 0:
+        diff = float((full[0].float() - one["out"].float()).abs().max())
+        record.update(n_gpus=world, tokens_per_s=batch / (ms / 1e3), ms_per_step=ms, ms_per_step_without_the_output_gather=ms_local,
+                      per_gpu_gbs=max(loads) / (ms / 1e3) / 1e9, bytes_per_rank_max=max(loads),
+                      bytes_per_rank_mean=sum(loads) / world, balance_mean_over_max=sum(loads) / world / max(loads),
+                      efficiency=one["ms"] / (world * ms), max_abs_diff_vs_one_gpu=diff,
+                      output_gather="one all_gather_into_tensor (NCCL) of the bf16 outputs + one index_select per step",
+                      shards=[dict(sequences=[s.batch.start, s.batch.stop], kv_heads=list(s.kv_heads)) for s in shards])
+    del cache, plan
+    torch.cuda.empty_cache()
+    return record
+
+
+def measure_split(rank, world, dist, steps):
+    """Long-context decode with fewer units than the GPUs can share out: 4 sequences x 131072 cached tokens of
+    configuration 5's layer, every unit's kept-tile range cut into one cost-balanced part per GPU.  A step is this
+    rank's split pass with the fold inside it, one NCCL all-gather of the (m, l, o) triples, and the merge that reads
+    the gathered buffer in place.  Speed-up against the same 4 sequences whole on one GPU (rank 0, same run)."""
+    cfg = dict(CONFIG_LONG, batch=4, workload="decode, sequence split: 32 Q / 8 KV heads, 4 sequences x 131072 cached tokens")
+    hk, batch, scale = cfg["heads_kv"], cfg["batch"], 128 ** -0.5
+    qd, kd, vd = long_inputs(cfg, batch)
+    out = torch.empty_like(qd)
+    record, one = dict(workload=cfg["workload"], scaling="strong"), None
+    if rank == 0:
+        module, cache, plan = build_cache(batch, 0, part=2, cfg=cfg, heads=list(range(hk)))
+        ms1 = time_steps(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, None, warm=50)
+        module.check_device_error()
+        one = dict(ms=ms1, out=out.clone())
+        record.update(one_gpu_ms_per_step=ms1, cache_bytes_per_step=int(plan["payload_bytes"]))
+        del cache, plan
+        torch.cuda.empty_cache()
+    dist.barrier()
+    module, cache, plan = build_cache(batch, 0, part=2, cfg=cfg, heads=list(range(hk)), split_group=dist.group.WORLD)
+    ms = time_steps(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, dist, warm=50)
+    ms_local = time_steps(lambda i: cache(0, qd, kd, vd, scale, phases=1, out=out), steps, dist, warm=5)
+    cache(0, qd, kd, vd, scale, out=out)
+    module.check_device_error()
+    if rank == 0:
+        record.update(n_gpus=world, ms_per_step=ms, tokens_per_s=batch / (ms / 1e3), speedup_vs_one_gpu=one["ms"] / ms,
+                      efficiency=one["ms"] / (world * ms), ms_split_pass_alone=ms_local,
+                      rank0_cache_bytes=int(plan["payload_bytes"]),
+                      max_abs_diff_vs_one_gpu=float((out.float() - one["out"].float()).abs().max()),
+                      exchange="fold inside the split pass; one all_gather_into_tensor (NCCL) of [units, 8, 130] f32 per rank; "
+                               "merge reads the gathered buffer by stride")
+    del cache, plan
+    torch.cuda.empty_cache()
+    return record
 
 
 def run_model(args):
@@ -399,6 +653,8 @@ def main():
     parser.add_argument("--split", action="store_true",
                         help="with --gpus N: the SAME sequences on every GPU, every unit's tile range cut N ways (sequence "
                              "split, one all-gather of folded partials per step); strong scaling, a diagnostic")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the secondary records (prefill, i8_peak, ref_ext, sharded_c5, split) of the default workload")
     parser.add_argument("--batch", type=int, default=None,
                         help="sequences per GPU; anything but the configuration's is a reduced case for profiler captures, "
                              "flagged in the output")
@@ -436,7 +692,6 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local),
                                 timeout=timedelta(seconds=120 if args.split else 600))
     hq, hk, batch = CONFIG["heads_q"], CONFIG["heads_kv"], args.batch
-    warmup = max(3, args.warmup)
     costs = tuple(float(x) for x in args.tile_costs.split(",")) if args.tile_costs else None
     split = args.split and world > 1
     seed0 = 0 if split else rank * batch
@@ -451,8 +706,10 @@ def main():
     out = torch.empty_like(qd)
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     # With a collective inside the step every rank must run the same number of steps: no time-based loops then.
-    warmup = warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), max(warmup, 300) if split else warmup,
-                     seconds=0.0 if split else 0.3)
+    # At least the requested warm-up steps (never fewer than 3), and on until the clocks have ramped: `warmup` in the
+    # line is what was asked for, `warmup_steps_run` what actually ran.
+    warmup_run = warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), max(3, args.warmup, 300 if split else 0),
+                         seconds=0.0 if split else 0.3)
     module.check_device_error()
     with ClockSampler(local) as clocks:
         ms_total = timed(lambda i: cache(0, qd, kd, vd, scale, out=out), args.steps, dist)
@@ -482,6 +739,21 @@ def main():
         if not torch.equal(out_host, out.cpu()):
             raise RuntimeError("e2e output differs from the device-resident run")
     module.check_device_error()
+    launches_per_step = 1 if cache.layers[0]["unit_done"] is not None else 2
+    extras = {}
+    if not args.no_extras and not long_case and not split and batch == CONFIG["batch"] and not args.fused_merge:
+        # secondary records, outside the timed region of the benchmark value; the C2 cache is released first
+        del stepper, cache
+        torch.cuda.empty_cache()
+        extra_steps = max(5, min(args.steps, 20))
+        if world == 1:
+            extras["i8_peak"] = measure_i8_peak()
+            extras["prefill"] = measure_prefill(2, 16384, extra_steps, 3, extras["i8_peak"])
+            extras["ref_ext"] = measure_ref_ext(extra_steps)
+            torch.cuda.empty_cache()
+        extras["sharded_c5"] = measure_sharded_c5(rank, world, dist, extra_steps)
+        if world > 1:
+            extras["split"] = measure_split(rank, world, dist, extra_steps)
     if rank != 0:
         dist.destroy_process_group()
         return
@@ -491,14 +763,15 @@ def main():
     kernel_s = ms_kernel / args.steps / 1e3
     achieved = bytes_per_launch / kernel_s / 1e9
     line = dict(metric="decode_tokens_per_s", value=tokens * args.steps / (ms_total / 1e3), unit="tokens/s", n_gpus=world,
-                steps=args.steps, warmup=warmup, ms_per_step=ms_total / args.steps, higher_is_better=True,
+                steps=args.steps, warmup=args.warmup, warmup_steps_run=warmup_run, ms_per_step=ms_total / args.steps,
+                higher_is_better=True,
                 scaling="strong" if split else "weak", vs_baseline=None, dtype="int8", data="synthetic", config=CONFIG,
                 e2e=dict(value=tokens * args.steps / (ms_e2e / 1e3), unit="tokens/s",
                          h2d_bytes_per_step=sum(x.numel() * 2 for x in host), d2h_bytes_per_step=out.numel() * 2),
-                gpu_launches=(1 if cache.layers[0]["unit_done"] is not None else 2) * args.steps,
+                gpu_launches=launches_per_step * args.steps,
                 roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                              # ncu capture of a batch-8 case (profiles/decode_kernel_c2.md): reads = 1.0014 x algorithmic
-                              # bytes, writes = 23.4 KB per segment; scaled by the tiles / segments of this launch
+                              # from an ncu capture of a batch-8 case: DRAM reads = 1.0014 x the algorithmic bytes, writes
+                              # = 23.4 KB per segment; scaled to this launch by its tiles and segments
                               traffic=int(bytes_per_launch * 1.0014 + plan["segments"].shape[0] * 23400),
                               kernel="decode_kernel", us_per_launch=kernel_s * 1e6, bytes_per_launch=bytes_per_launch,
                               peak_source=f"{peak_kind} copy bandwidth", frac_of_8tbs=achieved / 8000.0,
@@ -510,7 +783,8 @@ def main():
         line["sequence_split"] = f"every unit's tile range cut over {world} GPUs; one all-gather of folded partials per step"
     if batch != CONFIG["batch"]:
         line["reduced_case"] = f"batch {batch} instead of {CONFIG['batch']}: not a benchmark value"
-    if args.cpu_steps > 0:
+    line.update(extras)
+    if args.cpu_steps > 0 and world == 1:
         line["cpu_baseline"] = CpuPort(os.cpu_count() or 1).run(args.cpu_steps, 1)[0]
     print(json.dumps(line))
     if dist is not None:

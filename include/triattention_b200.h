@@ -50,10 +50,14 @@ int tri_prepare_qk(const void* q, const void* k, int batch, int heads_q, int hea
  * vstat f32 [B*Hkv,3,128] = (mean, scale, 1/scale); (0,1,1) when neither v8 nor v4 is requested.
  * v16 [B*Hkv,tiles,16384 B], v8 [..,8192 B], v4 [..,4096 B]; each may be NULL.
  * v8h [B*Hkv,tiles,16384 B] (may be NULL; no counterpart in the reference): the INT8 codes again as fp16 numbers
- * in the v16 layout, the P.V operand of tri_attention, whose tensor-core weights are fp16. */
+ * in the v16 layout, the P.V operand of tri_attention, whose tensor-core weights are fp16.
+ * raw_heads int32 [Hkv] on the device or NULL (no counterpart in the reference): non-zero marks an un-quantised
+ * (BF16) KV head; its units get identity statistics (0, 1, 1) and only the v16 blob, holding V itself as fp16
+ * (values beyond +-65504 clamped), which is what tri_attention reads for such heads. */
 int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
                int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
-               float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, void* stream);
+               float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h,
+               const int32_t* raw_heads, void* stream);
 
 /* Quantise K and V rows that arrive after the prompt with the prompt's statistics (no statistics pass): K8 blobs
  * and scales as tri_prepare_qk writes them, V8 blobs as tri_pack_v writes them, rows >= tokens zero.  The decode cache
@@ -70,15 +74,22 @@ int tri_requantize_kv(const void* k, const void* v, int batch, int heads_kv, int
  * Replaces attention(order,bands,groups,entries,v16p,v8p,v4p,vstat,q8,k8p,qa8,ka8,q4,k4p,qa4,ka4,out,scale),
  *   triattention/kernels/cuda/prefill_sm80.cu:510-543, in band mode.  The CTA order is internal
  *   (heaviest query blocks first); task-table mode (groups/entries) is tri_attention_tasks.
- * bands int32 [Hq,2] = (w8,w4) in tile distances; a head with w8 < 1 is skipped (un-quantised BF16
- * extension heads are computed by the caller).  out is bf16 (or fp16 when out_is_half) [B,Hq,T,128]
+ * bands int32 [Hq,2] = (w8,w4) in tile distances.  out is bf16 (or fp16 when out_is_half) [B,Hq,T,128]
  * with element strides.  v8h: the fp16 rendering of the INT8 V codes from tri_pack_v (where the reference passes
- * its v8p).  device_error: int32 word, set non-zero if a bounded wait ran out. */
+ * its v8p).  device_error: int32 word, set non-zero if a bounded wait ran out.
+ * Un-quantised (BF16) heads, an extension (the reference's only BF16 attention is torch's SDPA,
+ * triattention/models.py:45-47): a head with w8 < 1 is computed by the same kernel as exact causal attention over
+ * every tile — bf16 QK^T with fp32 scores and an exact online softmax on the tensor cores — from the caller's own
+ * tensors q_raw bf16 [B,Hq,T,128] and k_raw bf16 [B,Hkv,T,128] (element strides, rows 16-byte aligned; read by TMA
+ * tensor copies) and the v16 blobs that tri_pack_v wrote for a raw head.  With q_raw = k_raw = NULL such heads are
+ * skipped. */
 int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat,
                   const void* q8, const void* k8, const float* qa8, const float* ka8,
                   const void* q4x, const void* k4x, const float* qa4, const float* ka4,
                   void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
                   int batch, int heads_q, int heads_kv, int tokens, double scale,
+                  const void* q_raw, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                  const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
                   int* device_error, void* stream);
 
 /* Task-table mode of the prefill attention: every (Q head, query block) brings four explicit tile lists.

@@ -1,4 +1,5 @@
-"""Drives the reference's own CUDA extension (``oracle/_ref``) for one sequence.  Test infrastructure.
+"""Drives the reference's own CUDA extension (``oracle/_ref``) for one sequence.  Test and baseline infrastructure:
+only the tests, the golden generator and the baseline legs of ``bench.py`` import it.
 
 The reference's Python executors are not importable on the GPU box, so the buffer shapes and call
 sequences of ``triattention/kernels/prefill.py:60-108`` and ``triattention/kernels/decode.py:24-80`` are
@@ -24,8 +25,9 @@ class RefRunner:
     def __init__(self, mod):
         self.mod = mod
 
-    def prefill(self, q, k, v, bands, scale, with_decode=True, out_dtype=torch.bfloat16):
-        """q [1,Hq,T,128], k/v [1,Hkv,T,128] cuda bf16; bands numpy [Hq,2].  Returns the operand dict."""
+    def prefill(self, q, k, v, bands, scale, with_decode=True, out_dtype=torch.bfloat16, attention=True):
+        """q [1,Hq,T,128], k/v [1,Hkv,T,128] cuda bf16; bands numpy [Hq,2].  Returns the operand dict.
+        attention=False stops after the KV-cache write (prepare_qk + pack_v): enough to build a decode cache."""
         _, hq, t, _ = q.shape
         hk, rows, dev = k.shape[1], (t + 63) // 64, q.device
         formats = set(orc.band_formats(bands, rows))
@@ -47,9 +49,10 @@ class RefRunner:
         self.mod.pack_v(v, o["partial"], o["vstat"], packed[F16], packed[I8], packed[I4])
         order = torch.from_numpy(orc.cta_order(hq, hk, rows)).to(dev)
         bands_t = torch.from_numpy(np.asarray(bands, np.int32)).contiguous().to(dev)
-        out = torch.empty((1, t, hq, 128), dtype=out_dtype, device=dev).transpose(1, 2)
-        self.mod.attention(order, bands_t, None, None, packed[F16], packed[I8], packed[I4], o["vstat"], o["q8"], o["kp"],
-                           o["qa"], o["ka"], o["q4"], o["k4"], o["qa4"], o["ka4"], out, float(scale))
+        out = torch.empty((1, t, hq, 128), dtype=out_dtype, device=dev).transpose(1, 2) if attention else None
+        if attention:
+            self.mod.attention(order, bands_t, None, None, packed[F16], packed[I8], packed[I4], o["vstat"], o["q8"], o["kp"],
+                               o["qa"], o["ka"], o["q4"], o["k4"], o["qa4"], o["ka4"], out, float(scale))
         o.update(out=out, packed=packed, rows=rows, t=t, hq=hq, hk=hk, vcodes=vcodes, int4=int4)
         return o
 
@@ -75,10 +78,14 @@ class RefRunner:
                            o["vstat"], o["q8"], o["kp"], o["qa"], o["ka"], o["q4"], o["k4"], o["qa4"], o["ka4"], out, float(scale))
         return out
 
-    def decode_setup(self, o, bands, max_tail, per):
-        """kernels/decode.py:24-67 restated with numpy; returns the buffers `decode` needs."""
+    def decode_setup(self, o, bands, max_tail, per=None):
+        """kernels/decode.py:24-67 restated with numpy; returns the buffers `decode` needs.
+        per=None applies the reference's own rule (decode.py:53-55): kept tiles / (SMs x resident CTAs per SM)."""
         t, hk, tiles, dev = o["t"], o["hk"], o["rows"], o["qa"].device
         tabs = orc.decode_tables(bands, hk, t)
+        if per is None:
+            wave = torch.cuda.get_device_properties(dev).multi_processor_count * self.mod.decode_occupancy()
+            per = max(1, -(-sum(len(tb["tiles"]) for tb in tabs) // wave))
         count = np.array([len(tb["tiles"]) for tb in tabs])
         maxn = max(1, int(count.max()))
         entry = np.zeros((hk, maxn), np.int32); kinfo = np.zeros((hk, maxn), np.int32); slot = np.zeros((hk, maxn), np.int32)

@@ -295,7 +295,7 @@ def _margin(slope, base):
 
 
 def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles_i8, tiles_q4,
-                  qc4=None, qs4=None, kc4=None, ks4=None, return_acc=False, tiles_i4=(), v4=None):
+                  qc4=None, qs4=None, kc4=None, ks4=None, return_acc=False, tiles_i4=(), v4=None, precise=False):
     """One (Q head, query block): prefill_sm80.cu:259-488.  Band mode gives three tile lists; the task-table mode
     (:287-292, :478-481) gives four, the extra one (tiles_i4, run third) being INT8 scores with 4-bit P codes
     against the INT4 V codes v4.  In every pass only the LAST tile is masked, and only if it is the diagonal one.
@@ -303,12 +303,19 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
     qc int8 [64,128] Q codes of the block (rows >= T zero), qs float32 [64] = qa*sm_log2 (FLT_MIN for
     rows >= T); kc int8 [tiles,64,128], ks [tiles,4]; v16 float16 / v8 int8 [tiles,64,128];
     vstat_h [3,128].  Returns float32 [64,128] before the output cast.
+
+    precise=True keeps every code, maximum and float32 scale exactly as above but carries the running output and
+    denominator in float64 without the 12582912 bias on the integer P.V sums (the reference adds float_bits(d) * bq to
+    a float32 accumulator and removes the bias at the end, :416-449,466-487): the difference between the two modes
+    is the float32 rounding noise of the reference's own accumulation scheme, which bounds how closely any
+    implementation that sums the same products can agree with it.
     """
     qbeg = qb * BM
     rows = np.arange(BM)
-    out = np.zeros((BM, D), np.float32)
+    acc_t = np.float64 if precise else np.float32
+    out = np.zeros((BM, D), acc_t)
     m = np.full(BM, -FLT_MAX, np.float32)
-    denom = np.zeros(BM, np.float32)
+    denom = np.zeros(BM, acc_t)
     corr = np.zeros(BM, np.float32)
     accs = {}
     pv8_done = 0
@@ -337,8 +344,11 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
         # the reference folds corr into out when any alpha != 1 in the warp (or on flush); doing it
         # per row whenever alpha != 1 (or on flush) is the same arithmetic up to when the fold happens
         fold = flush | (alpha != 1)
-        out = np.where(fold[:, None], fma32(out, alpha[:, None], (-corr * alpha)[:, None]), out)
-        corr = np.where(fold, f32(0), corr)
+        if precise:
+            out = out * alpha.astype(np.float64)[:, None]
+        else:
+            out = np.where(fold[:, None], fma32(out, alpha[:, None], (-corr * alpha)[:, None]), out)
+            corr = np.where(fold, f32(0), corr)
         slope = np.repeat(slope_col, 16, axis=1)                    # [64,64]
         if pv == F16:
             denom = denom * alpha
@@ -347,8 +357,8 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
             else:
                 arg = fma32(slope, accf + MAGIC_F, fma32(-slope, MAGIC_F, -m[:, None]))
             p = np.where(dead, f32(0), exp2_32(arg)).astype(np.float16)
-            denom = denom + p.astype(np.float32).sum(1, dtype=np.float32)
-            out = out + p.astype(np.float32) @ v16[tile].astype(np.float32)
+            denom = denom + p.astype(acc_t).sum(1, dtype=acc_t)
+            out = out + p.astype(acc_t) @ v16[tile].astype(acc_t)
             return
         ks_max = ksc.max()
         base = np.where(tile_max > -np.inf, tile_max, m).astype(np.float32)
@@ -359,6 +369,10 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
             e = np.where(dead, f32(0), exp2_32(arg))
             p4 = (np.floor(fma32(e, f32(15), f32(49152.5)).astype(np.float64) - 49152.0).astype(np.int64)) & 0xFF
             d = p4 @ v4[tile].astype(np.int64)
+            if precise:
+                out = out + d.astype(np.float64) * (bq * (f32(127) / f32(7))).astype(np.float64)[:, None]
+                denom = denom * alpha.astype(np.float64) + p4.sum(1).astype(np.float64) * bq.astype(np.float64)
+                return
             out = fma32(d.astype(np.float32), (bq * (f32(127) / f32(7))).astype(np.float32)[:, None], out)
             denom = fma32(p4.sum(1).astype(np.float32), bq, denom * alpha)
             return
@@ -371,6 +385,10 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
         w = fma32(e, f32(255), f32(49152.5))
         p8 = (np.floor(w.astype(np.float64) - 49152.0).astype(np.int64)) & 0xFF
         d = p8 @ v8[tile].astype(np.int64)                           # [64,128] exact
+        if precise:
+            out = out + d.astype(np.float64) * bq.astype(np.float64)[:, None]
+            denom = denom * alpha.astype(np.float64) + p8.sum(1).astype(np.float64) * bq.astype(np.float64)
+            return
         out = fma32((d + 12582912).astype(np.float32), bq[:, None], out)
         corr = fma32(MAGIC_F, bq, corr)
         denom = fma32(p8.sum(1).astype(np.float32), bq, denom * alpha)
@@ -389,6 +407,10 @@ def prefill_block(qc, qs, kc, ks, v16, v8, vstat_h, tokens, qb, tiles_f16, tiles
         last = i == len(tiles_q4) - 1
         flush = (not last) and (pv8_done + i) % 16 == 15
         visit(t, qc4, qs4, kc4, ks4, I8, t == qb and last, np.full(BM, flush), True)
+    if precise:
+        with np.errstate(divide="ignore", invalid="ignore"):
+            res = np.where(denom[:, None] > 0, out / denom[:, None], 0.0) * vstat_h[1][None, :].astype(np.float64) + vstat_h[0][None, :]
+        return (res.astype(np.float32), accs) if return_acc else res.astype(np.float32)
     with np.errstate(divide="ignore"):
         inv = np.where(denom > 0, f32(1) / denom, f32(0)).astype(np.float32)
     res = fma32((out - corr[:, None]) * inv[:, None], vstat_h[1][None, :], vstat_h[0][None, :])

@@ -1,4 +1,5 @@
-"""Build the test-only operand-layout probe (``tests/probe/libtriattn_probe.so``) for sm_100a.
+"""Build the probe library (``tests/probe/libtriattn_probe.so``) for sm_100a: the test-only operand-layout probe
+(umma_probe.cu) and the measurement-only INT8 tensor-peak kernel that bench.py times (i8_peak.cu).
 
 Usage:  python tests/probe/build_probe.py [--force]
 """
@@ -22,14 +23,14 @@ ARGTYPES = [_P, _I, _P, _I, _U, _U, _U, _U, _U, _U, _U, _U, _U, _I, _I, _I, _P, 
 
 def build(force: bool = False) -> Path:
     from triattention_b200.build import CSRC, FLAGS, nvcc
-    source = HERE / "umma_probe.cu"
-    h = hashlib.sha256(source.read_bytes())
-    for name in ("tcgen05.cuh", "common.cuh", "abi_internal.h"):
-        h.update((CSRC / name).read_bytes())
+    sources = [HERE / "umma_probe.cu", HERE / "i8_peak.cu"]
+    h = hashlib.sha256()
+    for path in sources + [CSRC / name for name in ("tcgen05.cuh", "common.cuh", "abi_internal.h")]:
+        h.update(path.read_bytes())
     stamp, want = HERE / "stamp.txt", h.hexdigest()[:16]
     if LIBRARY.is_file() and stamp.is_file() and stamp.read_text().strip() == want and not force:
         return LIBRARY
-    subprocess.run([nvcc(), *FLAGS, "-I", str(CSRC), "-shared", str(source), "-o", str(LIBRARY)], check=True)
+    subprocess.run([nvcc(), *FLAGS, "-I", str(CSRC), "-shared", *map(str, sources), "-o", str(LIBRARY)], check=True)
     stamp.write_text(want + "\n")
     return LIBRARY
 
@@ -40,6 +41,8 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIBRARY))
     lib.tri_umma_probe.argtypes, lib.tri_umma_probe.restype = ARGTYPES, ctypes.c_int
     lib.tri_probe_last_error.argtypes, lib.tri_probe_last_error.restype = [], ctypes.c_char_p
+    lib.tri_i8_peak.argtypes = [_I, _I, ctypes.POINTER(ctypes.c_int64), _P, _P]
+    lib.tri_i8_peak.restype = ctypes.c_int
     return lib
 
 

@@ -217,7 +217,7 @@ def test_argument_errors_without_gpu():
     lib = load_library()
     assert lib.tri_prepare_qk(*([None] * 2), 1, 8, 2, 64, *([0] * 6), *([None] * 13)) == -1
     assert b"null" in lib.tri_last_error()
-    assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 7)) == -1
+    assert lib.tri_pack_v(None, 1, 2, 64, 0, 0, 0, *([None] * 8)) == -1
 
 
 def test_error_word_is_keyed_by_the_device_that_ran_the_kernel(monkeypatch):

@@ -213,3 +213,34 @@ def test_decode_partials_match_reference_golden(name):
             assert abs(m - pm[h, s]) <= 1e-4 * max(1.0, abs(m)), (h, s, m, pm[h, s])
             assert abs(l - pl[h, s]) <= 1e-4 * abs(l), (h, s, l, pl[h, s])
             assert np.abs(o - po[h, s]).max() <= 1e-3 * np.abs(o).max(), (h, s)
+
+
+def test_reference_accumulator_noise_floor():
+    """How reproducible the reference kernel's outputs are at all.  It accumulates every tile's integer P.V sums, biased
+    by 12582912, into a float32 register and removes the bias at the end (prefill_sm80.cu:416-449,466-487): near
+    2^27 that register resolves 16 units while a tile contributes a few thousand.  Here the restatement evaluates one
+    query block twice over the same codes, maxima and float32 scales: once with the reference's float32 accumulation
+    and once in float64 without the bias.  The difference is the reference's own rounding noise.  In a V channel
+    scaled x20 (a benchmark outlier channel) it exceeds the flat 2e-3 of the parity contract, so no implementation that
+    sums the same products can agree with the reference kernel to 2e-3 there; scaled by the channel's range it is
+    small, and in ordinary channels it is far below 2e-3.  This is why the full-size GPU comparisons scale the absolute
+    bound by range / 8 in wide channels (tests/test_gpu_7_full_size.py)."""
+    t, wide = 4096, 93
+    mk = lambda seed, dims: orc.synth((1, t, 128), seed, outlier_dims=dims, outlier_scale=20.0)
+    q, k, v = mk(1, (5,)), mk(2, (77,)), mk(3, (wide,))
+    sl2 = orc.sm_log2(1.0 / np.sqrt(128.0))
+    q8, qa, _, _ = orc.quantize_q(q)
+    kstat = orc.channel_stats(k)
+    k8, ka, _, _ = orc.quantize_k(k, kstat[:, 0])
+    vstat = orc.channel_stats(v)
+    v16, v8, _ = orc.pack_v(v, vstat)
+    qb = t // 64 - 1
+    rows = slice(qb * 64, (qb + 1) * 64)
+    tf, t8, t4 = orc.band_tiles(qb, orc.INF, orc.INF)
+    args = (q8[0, rows], (qa[0, rows] * sl2).astype(np.float32), k8[0], ka[0], v16[0], v8[0], vstat[0], t, qb, tf, t8, t4)
+    noise = np.abs(orc.prefill_block(*args) - orc.prefill_block(*args, precise=True))
+    span = float(v[0, :, wide].max() - v[0, :, wide].min())
+    others = np.delete(noise, wide, axis=1)
+    assert span > 100 and noise[:, wide].max() > 2e-3, (span, noise[:, wide].max())        # the flat bound is out of reach
+    assert noise[:, wide].max() < 2e-3 * span / 8 / 4                                       # a quarter of the scaled bound
+    assert others.max() < 1e-3 and np.sqrt((others ** 2).mean()) < 1e-4                     # ordinary channels: far below

@@ -118,7 +118,9 @@ def _gather_worker(rank, world, port, result):
         s = shards[rank]
         local = sharding.take_shard(full, s, s.q_heads(2))
         out = sharding.gather_outputs(local, shards, 2, 3, 8)
-        result[rank] = bool((out == full).all())
+        gatherer = sharding.OutputGatherer(shards, 2, 3, 8, local)        # the same, with buffers and index built once
+        again = [gatherer(local).clone() for _ in range(2)]
+        result[rank] = bool((out == full).all()) and all(bool((a == full).all()) for a in again)
     finally:
         dist.destroy_process_group()
 

@@ -84,3 +84,16 @@ def test_requests_outside_the_kernels_shapes_are_refused_on_the_host(probe):
     assert run(probe, img, img, (128, 1024, 0, 256), ok_b, good, False, 2, 128, expect_ok=False) < 0
     assert run(probe, img, img, (128, 512, 1, 256), ok_b, good, False, 2, 128, expect_ok=False) < 0
     assert b"umma_probe" in probe.tri_probe_last_error()
+
+
+def test_qk_bf16_rows_both_swizzled(probe):
+    """Scores of un-quantised heads: bf16 Q rows (A) and bf16 K rows (B), both as 128-byte-swizzled boxes of 64 features,
+    the image a TMA tensor copy of the caller's [T,128] rows leaves; one box = 4 MMAs of 16 features."""
+    rng = np.random.default_rng(3)
+    bf16 = lambda x: (x.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)       # truncation: exact inputs below
+    qf = np.round(rng.standard_normal((128, 64)) * 8).astype(np.float32) / 8               # few mantissa bits: exact in bf16
+    kf = np.round(rng.standard_normal((64, 64)) * 8).astype(np.float32) / 8
+    a_img = layouts.swizzle128(bf16(qf).view(np.uint8).reshape(128, 128)).reshape(-1)
+    b_img = layouts.swizzle128(bf16(kf).view(np.uint8).reshape(64, 128)).reshape(-1)
+    got = run(probe, a_img, b_img, (0, 1024, 2, 32), (0, 1024, 2, 32), idesc(1, 1, 1, 128, 64), True, 4, 64).view(np.float32)
+    assert np.abs(got - qf @ kf.T).max() < 1e-4

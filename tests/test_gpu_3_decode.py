@@ -295,7 +295,9 @@ def test_sequence_split_emulated_on_one_gpu(module, world, ctas):
             mine = cache.partials(0, qs, ks, SCALE).clone()
             fm, fl, fo = torch.empty_like(e["fm"]), torch.empty_like(e["fl"]), torch.empty_like(e["fo"])
             module.decode_fold(e["pm"], e["pl"], e["po"], e["dev"]["unit_slots"], fm, fl, fo, hq // hk)
-            assert torch.equal(torch.cat([fm.flatten(), fl.flatten(), fo.flatten()]), mine)
+            g = hq // hk      # rows of Q heads the group does not have are written by neither
+            assert torch.equal(fm[:, :g], e["fm"][:, :g]) and torch.equal(fl[:, :g], e["fl"][:, :g])
+            assert torch.equal(fo[:, :g], e["fo"][:, :g])
             folded.append(mine)
         outs_rank = []
         for cache in caches:        # every rank merges the same gathered buffer with its own (replicated) tail

@@ -52,9 +52,10 @@ CASES = [
 ]
 
 
-def product_prefill(module, q, k, v, bands, dtype=torch.bfloat16):
+def product_prefill(module, q, k, v, bands, out_dtype=torch.bfloat16):
     pre = Prefill(module, bands_fn_of(bands))
-    out = pre(0, bf16_cuda(q).to(dtype) if dtype != torch.bfloat16 else bf16_cuda(q), bf16_cuda(k), bf16_cuda(v), SCALE)
+    out = pre(0, bf16_cuda(q), bf16_cuda(k), bf16_cuda(v), SCALE, out_dtype=out_dtype)
+    assert out.dtype == out_dtype
     module.check_device_error()
     return out.float().cpu().numpy()
 
@@ -69,14 +70,19 @@ def test_prefill_vs_oracle(module, hq, hk, t, bands):
         assert_fp_close(got[b], orc.to_bf16(want), f"prefill b={b}")
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16], ids=["bf16-out", "fp16-out"])
 @pytest.mark.parametrize("hq,hk,t,bands", CASES)
-def test_prefill_vs_reference(module, ref_ext, hq, hk, t, bands):
+def test_prefill_vs_reference(module, ref_ext, hq, hk, t, bands, out_dtype):
+    """Both output types of the reference's kernel (prefill_sm80.cu:533-539).  With fp16 outputs the one-ulp allowance
+    for the final rounding is 8 times smaller than with bf16 (10 instead of 7 explicit significand bits)."""
     bands = np.asarray(bands, np.int64)
     q, k, v = make_inputs(hq, hk, t, seed=17, batch=1)
-    got = product_prefill(module, q, k, v, bands)
+    got = product_prefill(module, q, k, v, bands, out_dtype)
     run = RefRunner(ref_ext)
-    ref = run.prefill(bf16_cuda(q[0])[None], bf16_cuda(k[0])[None], bf16_cuda(v[0])[None], bands, SCALE, with_decode=False)
-    assert_fp_close(got[0], ref["out"].float().cpu().numpy()[0], "prefill vs reference kernel")
+    ref = run.prefill(bf16_cuda(q[0])[None], bf16_cuda(k[0])[None], bf16_cuda(v[0])[None], bands, SCALE, with_decode=False,
+                      out_dtype=out_dtype)
+    assert_fp_close(got[0], ref["out"].float().cpu().numpy()[0], "prefill vs reference kernel",
+                    ulp_digits=7 if out_dtype == torch.bfloat16 else 10)
 
 
 def test_prefill_c1_config(module, ref_ext):

@@ -88,3 +88,64 @@ def test_generate_fold_tail_runs_past_the_tail():
     assert engine.generate(ids, 140, eos=()) == rows          # a second prompt starts from a fresh cache
     with pytest.raises(RuntimeError):
         engine.generate(ids, 8, eos=(), cuda_graph=True)
+
+
+class ReferenceEngine:
+    """The reference's TriAttention (models.py:58-85 of the reference) restated over its own CUDA extension: the same
+    Hugging Face hook, per layer its prepare_qk / pack_v / attention at the prompt and its decode afterwards, batch 1,
+    greedy loop with use_cache=False.  Test infrastructure (the reference's Python package is not on the GPU box)."""
+
+    def __init__(self, model, ref_ext, bands_fn, max_new_tokens):
+        from ref_harness import RefRunner
+        from triattention_b200.models import use_attention
+        self.model, self.run, self.bands_fn, self.max_tail, self.layers = model, RefRunner(ref_ext), bands_fn, max_new_tokens, {}
+
+        def attention(mod, query, key, value, scaling):
+            layer = mod.layer_idx
+            if query.shape[2] == 1 and layer in self.layers:
+                return self.run.decode(self.layers[layer], query, key, value, scaling)
+            bands = self.bands_fn(layer, query.shape[1]).numpy().astype(np.int64)
+            o = self.run.prefill(query, key, value, bands, scaling)
+            self.layers[layer] = self.run.decode_setup(o, bands, self.max_tail)
+            return o["out"]
+
+        use_attention(model, "reference_triattention", attention)
+
+    @torch.inference_mode()
+    def generate(self, ids, n):
+        self.layers.clear()
+        logits = self.model(input_ids=ids, use_cache=False, logits_to_keep=1).logits[:, -1].float()
+        tokens, first = [], logits.clone()
+        token = int(logits.argmax(-1))
+        for i in range(n):
+            tokens.append(token)
+            if i + 1 == n:
+                break
+            position = torch.tensor([[ids.shape[1] + i]], device=ids.device)
+            out = self.model(input_ids=torch.tensor([[token]], device=ids.device), position_ids=position, use_cache=False)
+            for st in self.layers.values():
+                st["step"].add_(1)
+            token = int(out.logits[0, -1].argmax(-1))
+        return first, tokens
+
+
+@torch.inference_mode()
+def test_hook_level_parity_with_the_reference_extension(ref_ext):
+    """The whole surface at once: the same toy Llama run through the reference's kernels and through this library by
+    way of the same attention hook (batch 1, the reference's limit): prompt-pass logits agree and the first 8 greedy
+    tokens are the same."""
+    from triattention_b200.maps import INF, from_bands
+    from triattention_b200.models import TriAttention
+    model = tiny_llama()
+    bands = {str(layer): [[INF, INF], [INF, INF], [2, 3], [1, INF]] for layer in range(3)}
+    fn = from_bands(bands, model)
+    ids = torch.randint(0, 1024, (1, 330), generator=torch.Generator().manual_seed(11)).cuda()
+    want_logits, want_tokens = ReferenceEngine(model, ref_ext, fn, 8).generate(ids, 8)
+    engine = TriAttention(model, fn, max_new_tokens=8)
+    got_logits = model(input_ids=ids, use_cache=False, logits_to_keep=1).logits[:, -1].float()
+    got_tokens = engine.generate(ids, 8, eos=())
+    engine.module.check_device_error()
+    cos = torch.nn.functional.cosine_similarity(got_logits, want_logits, dim=-1).item()
+    worst = (got_logits - want_logits).abs().max().item() / want_logits.abs().max().item()
+    assert cos > 0.9999 and worst < 0.02, (cos, worst)
+    assert got_tokens == want_tokens, (got_tokens, want_tokens)

@@ -50,23 +50,35 @@ def check_convex(out, v, group):
     assert bool(((o >= lo) & (o <= hi)).all())
 
 
-def assert_close_by_channel_range(got, ref, v, group, what):
-    """The FP tolerance of the parity contract with its absolute part scaled per V channel: 2e-3 is meant for
-    unit-variance channels (range about 8 over a long prompt); in a channel whose values span R times that, one
-    quantisation step of the reference itself and every rounding of a weight times a V value are R times larger.
-    With the benchmark's x20 outlier channels (range > 150) a few elements in 10^7 of exactly those channels differ
-    from the reference kernel by up to 0.009 although both kernels hold the same P codes: the reference sums
-    integer code products per tile, this kernel sums fp16-rounded weights on the tensor core."""
+def assert_close_to_reference(got, ref, v, group, what):
+    """The FP tolerance of the parity contract on every element (computed on the GPU: 58.7 M elements at 16,384 tokens):
+    cosine >= 0.9999, mean-abs <= 5e-4, and max-abs 2e-3 plus one ulp of the output type at the reference value (both
+    sides are rounded to it) —
+      * as stated, unscaled, in every V channel of ordinary range (<= 16, i.e. twice that of a unit-variance channel);
+      * scaled by range / 8 in wider channels (the benchmark's x20 outlier channels span > 150).  There the reference
+        kernel itself is not reproducible to 2e-3: it adds every tile's integer P.V sums, biased by 12582912, into a
+        float32 accumulator (prefill_sm80.cu:416-449), and that accumulator's own rounding noise, measured by evaluating
+        the same codes and scales in float64 (tests/test_cpu_oracle.py::test_reference_accumulator_noise_floor), reaches
+        4e-3 in such a channel within 64 rows.  This kernel sums the same products without the bias and lands between
+        the two; what is left against the reference is the reference's noise;
+      * and the unscaled bound still holds for all but 1e-5 of the elements (measured: about 1e-6).
+    Prints the counts for the record."""
+    digits = 7 if got.dtype == torch.bfloat16 else 10
     got, ref = got.float(), ref.float()
-    rng = (v.float().amax(2) - v.float().amin(2)).repeat_interleave(group, 1)            # [B, Hq, 128]
-    scale = (rng / 8.0).clamp_min(1.0)[:, :, None, :]
-    ulp = torch.exp2(torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -120))) - 7)
+    ulp = torch.exp2(torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -120))) - digits)
     err = (got - ref).abs()
+    rng = (v.float().amax(2) - v.float().amin(2)).repeat_interleave(group, 1)[:, :, None, :].expand_as(err)
+    scale = (rng / 8.0).clamp_min(1.0)
     excess = float((err - (2e-3 * scale + ulp)).max())
+    narrow = rng <= 16.0
+    excess_narrow = float((err - (2e-3 + ulp))[narrow].max())
+    over = int((err > 2e-3 + ulp).sum())
     cos = float((got.double() * ref.double()).sum() / (got.double().norm() * ref.double().norm()))
-    plain = int((err > 2e-3 + ulp).sum())
-    assert excess <= 0 and cos >= 0.9999 and float(err.mean()) <= 5e-4, (what, excess, cos, float(err.mean()))
-    assert plain <= 1e-5 * err.numel(), (what, plain)   # and the unscaled bound holds for all but a few in 10^5
+    print(f"{what}: elements over the unscaled 2e-3 + 1 ulp: {over} of {err.numel()} (all in channels of range > 16: "
+          f"{bool(excess_narrow <= 0)}), worst excess over the unscaled bound {float((err - (2e-3 + ulp)).max()):.5f}, "
+          f"mean {float(err.mean()):.2e}, cosine {cos:.7f}")
+    assert excess <= 0 and excess_narrow <= 0 and cos >= 0.9999 and float(err.mean()) <= 5e-4, (what, excess, excess_narrow, cos)
+    assert over <= 1e-5 * err.numel(), (what, over)
 
 
 def check_codes(module, o, q, k, v):
@@ -88,8 +100,13 @@ def test_prefill_config3_size_vs_reference(module, ref_ext):
     o = RefRunner(ref_ext).prefill(q, k, v, bands, SCALE)
     check_codes(module, o, q, k, v)
     ref = o["out"]
-    assert_close_by_channel_range(got, ref, v, hq // hk, "prefill at 16384 tokens")
+    assert_close_to_reference(got, ref, v, hq // hk, "prefill at 16384 tokens")
     check_convex(got, v, hq // hk)
+    # once more with fp16 outputs on both sides: the allowance for the final rounding shrinks from 2^-8 to 2^-11 of the value
+    got16 = Prefill(module, from_bands({"0": bands.tolist()}, None))(0, q, k, v, SCALE, out_dtype=torch.float16)
+    module.check_device_error()
+    ref16 = RefRunner(ref_ext).prefill(q, k, v, bands, SCALE, with_decode=False, out_dtype=torch.float16)["out"]
+    assert_close_to_reference(got16, ref16, v, hq // hk, "prefill at 16384 tokens, fp16 outputs")
 
 
 def run_decode(module, q, k, v, bands, bf16, qd, kd, vd, ctas=None):
@@ -140,7 +157,7 @@ def test_max_length_prefill_and_decode_vs_reference(module, ref_ext):
     check_codes(module, o, q, k, v)
     got = Prefill(module, from_bands({"0": bands.tolist()}, None))(0, q, k, v, SCALE)
     module.check_device_error()
-    assert_close_by_channel_range(got, o["out"], v, hq // hk, "prefill at 131072 tokens")
+    assert_close_to_reference(got, o["out"], v, hq // hk, "prefill at 131072 tokens")
     st = run.decode_setup(o, bands, max_tail=4, per=64)
     ref = run.decode(st, qd, kd, vd, SCALE)
     dec = run_decode(module, q, k, v, bands, (), qd, kd, vd)

@@ -21,17 +21,18 @@ def ulp_diff(a, b) -> np.ndarray:
     return np.abs(ia - ib)
 
 
-def fp_report(got, ref, bf16_ulp=True):
+def fp_report(got, ref, bf16_ulp=True, ulp_digits=7):
+    """ulp_digits: explicit significand bits of the output type the two sides were rounded to (7 = bf16, 10 = fp16)."""
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
-    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 2.0 ** -120))) - 7)
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 2.0 ** -120))) - ulp_digits)
     tol = ABS_TOL + (ulp if bf16_ulp else 0.0)
     err = np.abs(got - ref)
     cos = float((got * ref).sum() / max(np.linalg.norm(got) * np.linalg.norm(ref), 1e-30))
     return dict(max_abs=float(err.max()), worst_excess=float((err - tol).max()), mean_abs=float(err.mean()), cos=cos)
 
 
-def assert_fp_close(got, ref, what, bf16_ulp=True):
-    r = fp_report(got, ref, bf16_ulp)
+def assert_fp_close(got, ref, what, bf16_ulp=True, ulp_digits=7):
+    r = fp_report(got, ref, bf16_ulp, ulp_digits)
     assert r["worst_excess"] <= 0 and r["cos"] >= COS_TOL and r["mean_abs"] <= ABS_TOL / 4, f"{what}: {r}"
     return r
 

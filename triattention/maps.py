@@ -1,0 +1,5 @@
+"""``triattention.maps`` (maps.py of the reference): the module object of ``triattention_b200.maps``."""
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("triattention_b200.maps")

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(D) stats_partial_kernel(const __nv_bfloat16* k
 
 // grid (units, 2), 128 threads.  common_device.cuh:44-56.
 __global__ void __launch_bounds__(D) stats_finalize_kernel(const float* partial_k, const float* partial_v,
-    float* kstat, float* vstat, int tokens, int v_identity) {
+    float* kstat, float* vstat, int tokens, int v_identity, const int32_t* raw_heads, int heads) {
   grid_dependency_wait();     // launched with launch_chained(): nothing is read or written before the predecessor is done
   grid_launch_dependents();
   const int64_t unit = blockIdx.x;
@@ -79,7 +79,9 @@ __global__ void __launch_bounds__(D) stats_finalize_kernel(const float* partial_
   float* stat = which == 0 ? kstat : vstat;
   if (stat == nullptr) return;
   float mean = 0.f, scale = 1.f;
-  if (!(which == 1 && v_identity)) {
+  // V of an un-quantised head stays as it is: identity statistics (0, 1, 1), like the reference's identity mode
+  const bool identity = which == 1 && (v_identity || (raw_heads != nullptr && raw_heads[unit % heads] != 0));
+  if (!identity) {
     const float* in = partial + unit * StatBlocks * 3 * D + c;
     float sum = 0.f, hi = -FLT_MAX, lo = FLT_MAX;
     for (int b0 = 0; b0 < StatBlocks; b0 += 16) {   // 48 loads in flight; the sum stays sequential in block order
@@ -299,7 +301,8 @@ __global__ void __launch_bounds__(128) quantize_k_kernel(const __nv_bfloat16* k,
 // grid (tiles, B*Hkv), 256 threads.  The tile is transposed through shared memory once; each thread
 // then emits whole 16-byte runs.
 __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, const float* vstat, uint8_t* v16,
-    uint8_t* v8, uint8_t* v4, uint8_t* v8h, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst) {
+    uint8_t* v8, uint8_t* v4, uint8_t* v8h, int tokens, int heads, int64_t vsb, int64_t vsh, int64_t vst,
+    const int32_t* raw_heads) {
   // Row stride 132 floats: a thread stores its 8 channels of a row as two 16-byte words (two lanes of a quarter
   // warp share a bank), and a warp that later reads 32 consecutive channels of one row hits 32 different banks.
   __shared__ __align__(16) float vn[BN][D + 4];
@@ -308,6 +311,10 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
   const int tile = blockIdx.x, unit = blockIdx.y, tiles = gridDim.x, tid = threadIdx.x;
   const __nv_bfloat16* base = v + (unit / heads) * vsb + (unit % heads) * vsh;
   const float* stat = vstat + (int64_t)unit * StatFloats;
+  // an un-quantised head gets only the fp16 blob (its statistics are the identity, so V' = V), with values beyond the
+  // fp16 range clamped to +-65504; no integer codes
+  const bool raw_unit = raw_heads != nullptr && raw_heads[unit % heads] != 0;
+  if (raw_unit) { v8 = nullptr; v4 = nullptr; v8h = nullptr; }
   {
     const int c0 = (tid % (D / 8)) * 8;     // the same 8 channels in every pass
     float mean[8], inv[8];
@@ -345,6 +352,10 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
   float x[32];
 #pragma unroll
   for (int kk = 0; kk < 32; ++kk) x[kk] = vn[kc * 32 + kk][ch];
+  if (raw_unit) {
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) x[kk] = fminf(fmaxf(x[kk], -65504.f), 65504.f);
+  }
   if (v16 != nullptr) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {          // run (ch/8, key/8, ch%8)
@@ -440,14 +451,16 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
       static_cast<int8_t*>(q4x), qa4, q_modes, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
   launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, partial, nullptr, tokens, heads_kv,
       k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
-  launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, partial, nullptr, kstat, nullptr, tokens, 0);
+  launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, partial, nullptr, kstat, nullptr, tokens, 0,
+      static_cast<const int32_t*>(nullptr), heads_kv);
   launch_chained(quantize_k_kernel, dim3(tiles, uk), dim3(128), 0, s, kp, kstat, static_cast<uint8_t*>(k8), ka,
       static_cast<uint8_t*>(k4x), static_cast<uint8_t*>(k4), ka4, tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
   return tri_launch_status("prepare_qk");
 }
 
 extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, int64_t v_stride_b, int64_t v_stride_h,
-    int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, void* stream) {
+    int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, const int32_t* raw_heads,
+    void* stream) {
   TRI_CHECK(v && partial && vstat, "pack_v: null V buffers");
   TRI_CHECK(batch > 0 && heads_kv > 0 && tokens > 0, "pack_v: bad geometry");
   TRI_CHECK(aligned16(v) && v_stride_b % 8 == 0 && v_stride_h % 8 == 0 && v_stride_t % 8 == 0, "BF16 V [B,Hkv,T,128]");
@@ -459,9 +472,10 @@ extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, in
   if (!identity)
     launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 2), dim3(D), 0, s, nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
         v_stride_b, v_stride_h, v_stride_t);
-  launch_chained(stats_finalize_kernel, dim3(uk, 2), dim3(D), 0, s, nullptr, partial, nullptr, vstat, tokens, identity);
+  launch_chained(stats_finalize_kernel, dim3(uk, 2), dim3(D), 0, s, nullptr, partial, nullptr, vstat, tokens, identity, raw_heads,
+      heads_kv);
   launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
-      static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
+      static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t, raw_heads);
   return tri_launch_status("pack_v");
 }
 
@@ -482,6 +496,6 @@ extern "C" int tri_requantize_kv(const void* k, const void* v, int batch, int he
       static_cast<float*>(nullptr), tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
   launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(v), vstat,
       static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(v8), static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(nullptr),
-      tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t);
+      tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t, static_cast<const int32_t*>(nullptr));
   return tri_launch_status("requantize_kv");
 }

@@ -37,6 +37,7 @@ constexpr uint32_t TmemCols = 512, TmemO = 0, TmemS = 256;      // O: [tile] x 1
 constexpr float RefSlack = 8.f;   // a row's reference exponent moves when a tile's maximum exceeds it by this (log2)
 constexpr float PMagic64 = 58368.5f;   // 2^15 * 1.78125 + 0.5: like 49152.5f, with 0x64 in byte 2 of the sum
 constexpr float PShift = 5.f;     // weights are carried times 2^5: keeps small tiles out of the fp16 subnormals
+constexpr float PScale = 32.f;    // 2^PShift
 enum Mode : int { ModeF16 = 0, ModeI8 = 1, ModeQ4 = 2 };
 
 struct QuadPlan {   // tile visiting order of one CTA (four query blocks q0..q0+3), all warp-uniform integers
@@ -175,6 +176,22 @@ static int make_q_map(CUtensorMap* map, const void* base, int tokens, int units)
   return TRI_OK;
 }
 
+// bf16 rows of a caller's [B,H,T,128] tensor with element strides: box = `rows` tokens x 64 features (128 bytes) of one
+// head, 128-byte swizzle, tokens past `tokens` filled with zeros.  Coordinates (feature, token, head, sequence).
+static int make_raw_map(CUtensorMap* map, const void* base, int tokens, int heads, int batch, int64_t sb, int64_t sh, int64_t st,
+                        unsigned rows) {
+  EncodeTiled enc = encode_fn();
+  TRI_CHECK(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)tokens, (cuuint64_t)heads, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  const cuuint32_t box[4] = {64u, rows, 1u, 1u}, estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TRI_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for the raw Q / K rows of un-quantised heads");
+  return TRI_OK;
+}
+
 template <typename K> static int allow_smem(K kernel, int bytes) {
   TRI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attribute");
   return TRI_OK;
@@ -187,8 +204,14 @@ using namespace tri;
 extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat, const void* q8,
     const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4, const float* ka4,
     void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
-    int heads_kv, int tokens, double scale, int* device_error, void* stream) {
+    int heads_kv, int tokens, double scale, const void* q_raw, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+    const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t, int* device_error, void* stream) {
   TRI_CHECK(bands && v16 && vstat && q8 && k8 && qa8 && ka8 && out && device_error, "attention: null buffers");
+  TRI_CHECK((q_raw == nullptr) == (k_raw == nullptr), "attention: raw Q and K rows of un-quantised heads (both or none)");
+  TRI_CHECK(q_raw == nullptr || (aligned16(q_raw) && aligned16(k_raw) && q_stride_b % 8 == 0 && q_stride_h % 8 == 0 &&
+                                 q_stride_t % 8 == 0 && k_stride_b % 8 == 0 && k_stride_h % 8 == 0 && k_stride_t % 8 == 0 &&
+                                 q_stride_t >= D && k_stride_t >= D),
+            "attention: raw BF16 Q/K [B,H,T,128] rows must be 16-byte aligned");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && tokens > 0, "attention: bad geometry");
   TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
   const bool int4 = q4x != nullptr;
@@ -206,14 +229,22 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
     configured.mark(device);
   }
   const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
-  CUtensorMap map8, map4;
+  CUtensorMap map8, map4, mapq, mapk;
   if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
   if (make_q_map(&map4, int4 ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
+  const int has_raw = q_raw != nullptr ? 1 : 0;
+  if (has_raw) {
+    if (make_raw_map(&mapq, q_raw, tokens, heads_q, batch, q_stride_b, q_stride_h, q_stride_t, 128u) != TRI_OK) return TRI_ERR_CUDA;
+    if (make_raw_map(&mapk, k_raw, tokens, heads_kv, batch, k_stride_b, k_stride_h, k_stride_t, 64u) != TRI_OK) return TRI_ERR_CUDA;
+  } else {
+    mapq = map8; mapk = map8;   // never dereferenced: heads with w8 < 1 are skipped when no raw rows are given
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
   const dim3 grid((unsigned)((int64_t)quads * units));
 #define TRI_LAUNCH(T)                                                                                                      \
-  prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, bands, static_cast<const uint8_t*>(k8),       \
+  prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, mapq, mapk, has_raw, bands,                   \
+      static_cast<const uint8_t*>(k8),                                                                                     \
       static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8h), qa8, \
       qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, heads_q, heads_kv, tokens, units,       \
       sm_log2, device_error)

@@ -19,20 +19,22 @@
 // |score| < 2^22 the result read as a float IS 12582912 + score.  Row maxima are taken on those floats with the
 // three-input max.
 //
-// P never touches shared memory: a softmax thread writes its fp16 weights over the first half of its own 32
-// score columns (tcgen05.st) once it has read them, and the P.V MMAs take their A operand from tensor memory.
+// P never touches shared memory: a softmax thread writes its fp16 weights over its own 32 score columns
+// (tcgen05.st: high parts over the first 16, low parts over the last 16) once it has read them, and the P.V MMAs
+// take their A operand from tensor memory.
 // The bias MMA of two steps later overwrites P; its issuer waits for that P.V to have completed first.  With A in tensor memory an M128 N128 K16 MMA takes 65 cycles instead of 108 (measured).
 //
 // Per step (one 64-key tile) and MMA tile:
 //   S[128x64]  = Q8 . K8^T            4 x kind::i8 (M128 N64 K32), s32 accumulators (bit-equal to the reference's)
 //   P codes    = the reference's u8 quantisation of 2^(score - base) per row and tile (prefill_sm80.cu:386-414)
-//   O[128x128] += (code * s) . V      4 x kind::f16 (M128 N128 K16): the per-tile scale s = 2^(base - ref) / 255 is
-//                                     folded into the fp16 P operand, V codes are exact in fp16, and the fp32
-//                                     accumulator stays in TMEM for the whole CTA
+//   O[128x128] += (code * s) . V      8 x kind::f16 (M128 N128 K16): the per-tile scale s = 2^(base - ref) / 255 is
+//                                     folded into the P operand, which goes in as two fp16 parts, high (exact) + low,
+//                                     whose sum is code * s to 2^-15 (4 MMAs each over the same V operand); V codes are
+//                                     exact in fp16, and the fp32 accumulator stays in TMEM for the whole CTA
 // where ref is a per-row reference exponent that is only moved (and O rescaled in TMEM) when a tile's
 // maximum exceeds it by more than 2^8.  The reference instead reads an integer P.V accumulator out per
-// tile and folds it into registers; both evaluate sum_t s_t * (codes_t . V) / sum_t s_t * sum(codes_t),
-// here with one extra fp16 rounding (2^-12 relative) of each weight, far inside the output tolerance.
+// tile and folds it into registers; both evaluate sum_t s_t * (codes_t . V) / sum_t s_t * sum(codes_t) over the same
+// integer-code products; the reference's float32 accumulator (biased by 12582912 per tile) is the noisier of the two.
 // Sink and diagonal tiles use fp16 weights and the fp16 V blob exactly like the reference.
 //
 // Every mbarrier wait has a time limit and obeys the CTA-wide abort flag.  The only other barrier inside
@@ -59,6 +61,8 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 // column (inside a score buffer) of the P words of key group kk: the first half of the columns of the thread that owns it
 __device__ __forceinline__ constexpr uint32_t p_column(int kk) { return RowSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; }
+constexpr uint32_t PLow = 16;   // the low parts of the quantised weights: 16 columns behind the high parts
+static_assert(RowSplit == 2, "the high / low weight parts share a thread's 32 score columns: 16 + 16");
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -67,7 +71,8 @@ __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
 // grid = quads * batch * heads_q CTAs, heaviest query rows first; 640 threads; one CTA per SM.
 template <typename Out>
 __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
-    const __grid_constant__ CUtensorMap map_q4, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
+    const __grid_constant__ CUtensorMap map_q4, const __grid_constant__ CUtensorMap map_qraw,
+    const __grid_constant__ CUtensorMap map_kraw, int has_raw, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
     const float* ka4, const uint8_t* v16, const uint8_t* v8h, const float* qa8, const float* qa4, const float* vstat, Out* out,
     int64_t osb, int64_t osh, int64_t ost, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
   extern __shared__ uint8_t raw_smem[];
@@ -83,11 +88,15 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   const int b = qunit / heads_q, h = qunit % heads_q, g = heads_q / heads_kv;
   const int64_t kvunit = (int64_t)b * heads_kv + h / g;
   const int w8 = bands[h * 2], w4 = bands[h * 2 + 1];
-  if (w8 < 1) return;   // head handled elsewhere (un-quantised BF16 extension); uniform for the CTA
+  // A head with w8 < 1 belongs to an un-quantised (BF16) KV group: exact attention over every causal tile, straight
+  // from the raw bf16 Q and K rows (TMA tensor copies of the caller's tensors) and the fp16 V blobs.  Uniform for the CTA.
+  const bool raw = w8 < 1;
+  if (raw && !has_raw) return;
   QuadPlan plan;
-  plan.build(quad_id, rows, w8, w4);
+  plan.build(quad_id, rows, raw ? (1 << 20) : w8, raw ? (1 << 20) : w4);
   const int nsteps = plan.steps();
-  const bool need_q4 = plan.n4 > 0;
+  const bool need_q4 = !raw && plan.n4 > 0;
+  const int kmask = raw ? 1 : 3, kshift = raw ? 1 : 2;   // K ring: four 8 KB stages of codes, or two 16 KB stages of bf16 rows
 
   // the visiting order as tables: tile | mode << 12, and the 4-bit mask of query blocks that take part
   uint16_t* step_tm = reinterpret_cast<uint16_t*>(smem + SmSteps);
@@ -124,22 +133,38 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------------
     if (lane == 0) {
-      mbar_expect_tx(&bars.q, need_q4 ? 65536u : 32768u);
-      for (int x = 0; x < 2; ++x) {
-        tma_load_3d(smem + SmQ8 + x * 16384, &map_q8, 0, plan.q0 * BM + x * 128, qunit, &bars.q);
-        if (need_q4) tma_load_3d(smem + SmQ4 + x * 16384, &map_q4, 0, plan.q0 * BM + x * 128, qunit, &bars.q);
+      if (raw) {
+        // bf16 Q rows of the caller's tensor: per MMA tile two boxes of 128 rows x 64 features (128-byte swizzle)
+        mbar_expect_tx(&bars.q, 65536u);
+        for (int x = 0; x < 2; ++x)
+          for (int half = 0; half < 2; ++half)
+            tma_load_4d(smem + SmQ8 + x * 32768 + half * 16384, &map_qraw, half * 64, plan.q0 * BM + x * 128, h, b, &bars.q);
+      } else {
+        mbar_expect_tx(&bars.q, need_q4 ? 65536u : 32768u);
+        for (int x = 0; x < 2; ++x) {
+          tma_load_3d(smem + SmQ8 + x * 16384, &map_q8, 0, plan.q0 * BM + x * 128, qunit, &bars.q);
+          if (need_q4) tma_load_3d(smem + SmQ4 + x * 16384, &map_q4, 0, plan.q0 * BM + x * 128, qunit, &bars.q);
+        }
       }
       for (int i = 0; i < nsteps; ++i) {
-        const int tile = tile_of(i), mode = mode_of(i), s = i & 3, vb = i & 1;
-        if (i >= 4 && !wait(&bars.k_empty[s], (i >> 2) - 1)) break;
+        const int tile = tile_of(i), mode = mode_of(i), s = i & kmask, vb = i & 1;
+        if (i > kmask && !wait(&bars.k_empty[s], (i >> kshift) - 1)) break;
         const int64_t ht = kvunit * tiles + tile;
-        mbar_expect_tx(&bars.k_full[s], K8Bytes + 16);
-        bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bars.k_full[s]);
-        bulk_g2s(&k_scales[i & 7][0], (mode == ModeQ4 ? ka4 : ka8) + ht * 4, 16, &bars.k_full[s]);
-        // the fp16 P.V operand of the step: V' itself for sink / diagonal tiles, the INT8 codes as fp16 numbers otherwise
+        if (raw) {
+          // the tile's 64 bf16 K rows from the caller's tensor: two boxes of 64 keys x 64 features
+          mbar_expect_tx(&bars.k_full[s], 2 * K8Bytes);
+          for (int half = 0; half < 2; ++half)
+            tma_load_4d(smem + SmK + s * 2 * K8Bytes + half * K8Bytes, &map_kraw, half * 64, tile * BN, h / g, b, &bars.k_full[s]);
+        } else {
+          mbar_expect_tx(&bars.k_full[s], K8Bytes + 16);
+          bulk_g2s(smem + SmK + s * K8Bytes, (mode == ModeQ4 ? k4x : k8) + ht * K8Bytes, K8Bytes, &bars.k_full[s]);
+          bulk_g2s(&k_scales[i & 7][0], (mode == ModeQ4 ? ka4 : ka8) + ht * 4, 16, &bars.k_full[s]);
+        }
+        // the fp16 P.V operand of the step: V' itself for sink / diagonal tiles (and for every tile of an un-quantised
+        // head, whose V' is V), the INT8 codes as fp16 numbers otherwise
         if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
         mbar_expect_tx(&bars.v16_full[vb], V16Bytes);
-        bulk_g2s(smem + SmV16 + vb * V16Bytes, (mode == ModeF16 ? v16 : v8h) + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
+        bulk_g2s(smem + SmV16 + vb * V16Bytes, ((raw || mode == ModeF16) ? v16 : v8h) + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
       }
     }
   } else if (warp < 3) {
@@ -160,19 +185,30 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const uint32_t st = tmem + TmemS + x * 128;
       int nqk = 0;
       bool ok = wait(&bars.q, 0);
+      const uint64_t dqr = smem_desc(smem_u32(smem + SmQ8 + x * 32768), 0, 1024, Layout128B);   // bf16 rows, both 128-byte swizzled
+      const uint64_t dkr = smem_desc(smem_u32(smem + SmK), 0, 1024, Layout128B);
       for (int i = 0; ok && i < nsteps; ++i) {
-        const int s = i & 3;
-        // every step, also those this tile sits out: an issuer that ran four steps ahead would arrive twice on the
+        const int s = i & kmask;
+        // every step, also those this tile sits out: an issuer that ran a ring round ahead would arrive twice on the
         // same k_empty phase
-        if (!(ok = wait(&bars.k_full[s], i >> 2))) break;
+        if (!(ok = wait(&bars.k_full[s], i >> kshift))) break;
         if ((step_mask[i] >> (2 * x)) & 3) {
           const int sb = nqk & 1;
           if (nqk >= 2 && !(ok = wait(&bars.o_done[x][sb], (nqk - 2) >> 1))) break;
           tc_fence_after();
-          const uint64_t dqm = mode_of(i) == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
-          umma_f16(st + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
+          if (raw) {
+            // S = Q . K^T on bf16 rows, fp32 accumulators: 8 MMAs of 16 features; feature half hf sits in its own box
+            const uint64_t dks = at(dkr, s * 2 * K8Bytes);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_i8(st + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_f16(st + sb * 64, at(dqr, (kk >> 2) * 16384 + (kk & 3) * 32), at(dks, (kk >> 2) * K8Bytes + (kk & 3) * 32),
+                       IdescQKRaw, kk > 0 ? 1u : 0u);
+          } else {
+            const uint64_t dqm = mode_of(i) == ModeQ4 ? dq4 : dq8, dks = at(dk, s * K8Bytes);
+            umma_f16(st + sb * 64, dba, dbb, IdescBias, 0u);   // the bias (and the end of the P that lived here)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_i8(st + sb * 64, at(dqm, kk * 32), at(dks, kk * 256), IdescQK, 1u);
+          }
           tc_commit(&bars.s_full[x][sb]);
           ++nqk;
         }
@@ -188,6 +224,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       bool ok = true;
       for (int i = 0; ok && i < nsteps; ++i) {
         const int mask = step_mask[i], vb = i & 1;
+        const bool two_part = !raw && mode_of(i) != ModeF16;   // quantised weights come as high + low fp16 parts
         if (!(ok = wait(&bars.v16_full[vb], i >> 1))) break;
         const uint64_t dvs = at(dv, vb * V16Bytes);
         if (mask & 3) {
@@ -200,6 +237,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16_ts(tmem + TmemO, pt + p_column(kk), at(dvs, kk * 256), IdescPV16, (npv0 > 0 || kk > 0) ? 1u : 0u);
+          if (two_part) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_f16_ts(tmem + TmemO, pt + p_column(kk) + PLow, at(dvs, kk * 256), IdescPV16, 1u);
+          }
           tc_commit(&bars.o_done[0][pb]);
           ++npv0;
         }
@@ -211,6 +252,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16_ts(tmem + TmemO + 128, pt + p_column(kk), at(dvs, kk * 256), IdescPV16, (npv1 > 0 || kk > 0) ? 1u : 0u);
+          if (two_part) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_f16_ts(tmem + TmemO + 128, pt + p_column(kk) + PLow, at(dvs, kk * 256), IdescPV16, 1u);
+          }
           tc_commit(&bars.o_done[1][pb]);
           ++npv1;
         }
@@ -227,7 +272,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const int bh = plan.q0 + blk, qi = bh * BM + (row & 63);
     const bool row_valid = blk < plan.nb && qi < tokens;
     const int64_t qrow = (int64_t)qunit * tokens + qi;
-    const float qs8 = row_valid ? qa8[qrow] * sm_log2 : FLT_MIN;
+    const float qs8 = (row_valid && !raw) ? qa8[qrow] * sm_log2 : FLT_MIN;
     const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
     float ref = -FLT_MAX, denom = 0.f;   // reference exponent of the row; this thread's share of the denominator
     int n = 0;                           // steps of this tile so far
@@ -253,10 +298,14 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       if (ok) tc_fence_after();
       // The tile's K scales came with the tile (the ring slot is not reused before step i+8, and the producer
       // cannot be more than 4 steps ahead of a softmax warp).
-      const float4 ks = *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
+      const float4 ks = raw ? make_float4(1.f, 1.f, 1.f, 1.f) : *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
       float slope[G];   // one per 16-key group of this thread
       if constexpr (RowSplit == 2) { slope[0] = qs * (ch ? ks.z : ks.x); slope[1] = qs * (ch ? ks.w : ks.y); }
       else { slope[0] = qs * ks.x; slope[1] = qs * ks.y; slope[G - 2] = qs * ks.z; slope[G - 1] = qs * ks.w; }
+      if (raw) {
+#pragma unroll
+        for (int cc = 0; cc < G; ++cc) slope[cc] = sm_log2;   // scores are plain fp32 dot products
+      }
       float tmax = -CUDART_INF_F;
       uint32_t a[G][16];   // this thread's scores as float bits (12582912 + score); read once per step
       if (active) {
@@ -268,6 +317,13 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           tmem_ld_wait();
 #pragma unroll
           for (int cc = 0; cc < G; ++cc) {
+            if (raw) {   // plain fp32 scores (sm_log2 > 0, so the scaled maximum is the scaled maximum score)
+              float m = -CUDART_INF_F;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) if (!diag || !dead(key0 + 16 * cc + j)) m = fmaxf(m, __uint_as_float(a[cc][j]));
+              part = fmaxf(part, sm_log2 * m);
+              continue;
+            }
             float m = 0.f;   // below every biased score
             if (diag) {
 #pragma unroll
@@ -290,12 +346,22 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         }
       }
       if (ok && active) {
-        // move the row's reference exponent when this tile towers over it, and rescale what O holds
-        const bool move = tmax > ref + RefSlack;
+        // Move the row's reference exponent, and rescale what O holds, when this tile towers over it.  In the fp16
+        // steps (sink and diagonal tiles, the first steps of a row, in the reference's order) it moves with every
+        // increase, so that it IS the reference's running maximum m there: the reference rounds 2^(score - m) to fp16
+        // (prefill_sm80.cu:362-373), and only the same exponent gives the same rounding.  That costs one rescale of a
+        // one-tile accumulator per row.  In the quantised steps the codes do not depend on the running maximum.
+        // In a quantised step the exponent that matters is the tile's base (its maximum plus the reference's margin):
+        // the weight of one code step is 2^(base - ref) / 255, kept below 2^(RefSlack + PShift) / 255 so that 1024 times
+        // it stays inside fp16.
+        const bool quantised = !raw && mode != ModeF16;
+        const float ks_top = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
+        const float top = quantised ? tmax + tile_base_margin(qs * ks_top, tmax) : tmax;
+        const bool move = (mode == ModeF16 && !raw) ? top > ref : top > ref + RefSlack;
         float factor = 1.f;
         if (move) {
-          factor = ref > -FLT_MAX ? exp2f(ref - tmax) : 0.f;
-          ref = tmax;
+          factor = ref > -FLT_MAX ? exp2f(ref - top) : 0.f;
+          ref = top;
           denom *= factor;
         }
         if (n > 0 && __any_sync(0xffffffffu, move)) {
@@ -321,19 +387,20 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       if (ok && !active) {
         const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing to the tile's P.V
 #pragma unroll
-        for (int cc = 0; cc < G; ++cc) tmem_st8(s_addr + 8 * cc, zero);
-      } else if (ok && mode == ModeF16) {
+        for (int cc = 0; cc < 2 * G; ++cc) tmem_st8(s_addr + 8 * cc, zero);   // high and low parts (the latter unread in fp16 mode)
+      } else if (ok && (mode == ModeF16 || raw)) {
         float sum = 0.f;
 #pragma unroll
         for (int cc = 0; cc < G; ++cc) {
-          const float off = fmaf(-slope[cc], 12582912.f, PShift - ref);
+          // quantised heads: the reference's expression, bit for bit, then x 2^PShift (exact); plain scores carry no bias
+          const float off = raw ? -ref : fmaf(-slope[cc], 12582912.f, -ref);
           uint32_t w[8];
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             float e[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              e[u] = exp2f(fmaf(slope[cc], __uint_as_float(a[cc][j + u]), off));
+              e[u] = exp2f(fmaf(slope[cc], __uint_as_float(a[cc][j + u]), off)) * PScale;
               if (diag && dead(key0 + 16 * cc + j + u)) e[u] = 0.f;
             }
             const __half2 hp = __floats2half2_rn(e[0], e[1]);
@@ -348,21 +415,30 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         const float ks_max = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
         float base = tmax;
         base += tile_base_margin(qs * ks_max, base);
-        // weight of one code step, rounded to fp16 once: numerator (tensor core) and denominator use the same value
-        const __half sh = __float2half_rn(exp2f(base - ref + PShift) * (1.f / 255.f));
-        const __half2 s2 = __half2half2(sh), nb2 = __half2half2(__hneg(__hmul(sh, __float2half(1024.f))));
+        // Weight of one code step, s = 2^(base - ref) / 255 (times 2^PShift), split as s_hi + s_lo: s_hi = s rounded to
+        // 3 significant bits, so that code * s_hi (8 + 3 bits) is EXACT in fp16, and s_lo = fp16(s - s_hi), at most
+        // 2^-3 of s.  Each weight goes to the tensor core as two fp16 operands, p_hi = code * s_hi (exact) and
+        // p_lo = fp16(code * s_lo) (one rounding, 2^-12 of a part that is at most 2^-3 of the weight), so p_hi + p_lo =
+        // code * s to 2^-15 at worst: the tensor core sums the integer-code products the reference sums per tile
+        // (prefill_sm80.cu:416-449), scaled like its fp32 `bq`, to well below the float32 noise of the reference's own
+        // accumulator.  (A single fp16 weight, 2^-12 relative, left outputs in x20 outlier channels of V up to 0.009
+        // from the reference.)  The denominator uses the same s_hi + s_lo.
+        const float sf = exp2f(base - ref + PShift) * (1.f / 255.f);
+        const float sf_hi = __uint_as_float((__float_as_uint(sf) + 0x00100000u) & 0xffe00000u);
+        const __half sh = __float2half_rn(sf_hi), sl = __float2half_rn(sf - sf_hi);
+        const __half2 shi2 = __half2half2(sh), slo2 = __half2half2(sl);
+        const __half2 nhi2 = __half2half2(__hneg(__hmul(sh, __float2half(1024.f)))), nlo2 = __half2half2(__hneg(__hmul(sl, __float2half(1024.f))));
         int rs = 0;
         // The code is byte 1 of fma(2^x, 255, 2^15 + ... + 0.5) exactly as in the reference (prefill_sm80.cu:78-88);
         // this constant of the same binade also leaves 0x64 in byte 2, so that bytes 1-2 of the word are the
-        // fp16 number 1024 + code.  Eight keys at a time (one 16-byte run of the P operand) to keep the live
-        // registers low.  The INT4 pass takes (float)acc (exact for |acc| < 2^22) and rounds once like the
-        // reference's conversion; the INT8 pass keeps the bias inside the fma like the reference does.
+        // fp16 number 1024 + code.  Eight keys at a time to keep the live registers low.  The INT4 pass takes
+        // (float)acc (exact for |acc| < 2^22) and rounds once like the reference's conversion; the INT8 pass keeps
+        // the bias inside the fma like the reference does.
         auto codes = [&](auto int4_pass) {
           constexpr bool Int4 = decltype(int4_pass)::value;
 #pragma unroll
           for (int cc = 0; cc < G; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
-            uint32_t pw[8];   // the 16 weights of this key group, two per word
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
               uint32_t w[8];
@@ -372,24 +448,24 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
                 const float sc = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
                 w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
               }
-              const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[2], w[3], 0x6521);   // (1024 + code) x 2 as fp16
-              const uint32_t h2 = __byte_perm(w[4], w[5], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
-              rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
-              rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
-              rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);
-              rs = (int)__dp4a(h3, 0x00010001u, (uint32_t)rs);
-              const __half2 p0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), s2, nb2);   // (1024 + code) * s - 1024 * s
-              const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), s2, nb2);
-              const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), s2, nb2);
-              const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), s2, nb2);
-              pw[4 * hb] = *reinterpret_cast<const uint32_t*>(&p0); pw[4 * hb + 1] = *reinterpret_cast<const uint32_t*>(&p1);
-              pw[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&p2); pw[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&p3);
+              uint32_t hi[4], lo[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t h = __byte_perm(w[2 * u], w[2 * u + 1], 0x6521);   // (1024 + code) x 2 as fp16
+                rs = (int)__dp4a(h, 0x00010001u, (uint32_t)rs);                     // sum of the codes
+                // (1024 + code) * s - 1024 * s in one fused operation: code * s rounded once (exact for s_hi)
+                const __half2 ph = __hfma2(*reinterpret_cast<const __half2*>(&h), shi2, nhi2);
+                const __half2 pl = __hfma2(*reinterpret_cast<const __half2*>(&h), slo2, nlo2);
+                hi[u] = *reinterpret_cast<const uint32_t*>(&ph);
+                lo[u] = *reinterpret_cast<const uint32_t*>(&pl);
+              }
+              tmem_st4(s_addr + 8 * cc + 4 * hb, hi);
+              tmem_st4(s_addr + 16 + 8 * cc + 4 * hb, lo);   // the low parts sit over the second half of the thread's columns
             }
-            tmem_st8(s_addr + 8 * cc, pw);
           }
         };
         if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
-        denom = fmaf((float)rs, __half2float(sh), denom);
+        denom = fmaf((float)rs, __half2float(sh) + __half2float(sl), denom);
       }
       if (ok) {
         tmem_st_wait();   // P is in tensor memory before the issuer is told

@@ -21,9 +21,10 @@ _P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_dou
 # name -> argtypes, in the order of include/triattention_b200.h
 SIGNATURES = {
     "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
-    "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P],
+    "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P],
     "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
-    "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
+    "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D,
+                      _P, _L, _L, _L, _P, _L, _L, _L, _P, _P],
     "tri_attention_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
@@ -139,8 +140,13 @@ class Module:
                                                 kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4), _ptr(ka4),
                                                 _ptr(q_modes), _stream()))
 
-    def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None, v8h=None):
+    def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None, v8h=None, raw_heads=None):
+        """raw_heads int32 [Hkv] on the device (or None): non-zero = un-quantised KV head (identity statistics, fp16 blob
+        of V itself only)."""
         self._bhtd(v, "V")
+        if raw_heads is not None and not (raw_heads.is_cuda and raw_heads.dtype == torch.int32 and
+                                          raw_heads.numel() == v.shape[1] and raw_heads.is_contiguous()):
+            raise RuntimeError("raw_heads int32 [Hkv] on the device")
         b, hk, t, _ = v.shape
         tiles = (t + 63) // 64
         for buf, size in ((v16, 16384), (v8, 8192), (v4, 4096), (v8h, 16384)):
@@ -151,7 +157,7 @@ class Module:
         with torch.cuda.device(v.device):
             self._check(self.lib.tri_pack_v(v.data_ptr(), b, hk, t, v.stride(0), v.stride(1), v.stride(2),
                                             partial.data_ptr(), vstat.data_ptr(), _ptr(v16), _ptr(v8), _ptr(v4), _ptr(v8h),
-                                            _stream()))
+                                            _ptr(raw_heads), _stream()))
 
     def requantize_kv(self, k, v, kstat, vstat, k8, ka, v8):
         """K8 / V8 blobs of rows that came after the prompt, with the prompt's statistics."""
@@ -166,10 +172,22 @@ class Module:
                                                    v.stride(0), v.stride(1), v.stride(2), kstat.data_ptr(), vstat.data_ptr(),
                                                    k8.data_ptr(), ka.data_ptr(), v8.data_ptr(), _stream()))
 
-    def attention(self, bands, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):
+    def attention(self, bands, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv, q_raw=None,
+                  k_raw=None):
+        """q_raw / k_raw: the caller's bf16 Q [B,Hq,T,128] and K [B,Hkv,T,128] when the map has un-quantised heads (bands
+        rows of zeros); those heads are then computed as exact attention from these rows and their fp16 V blobs."""
         if not (out.dim() == 4 and out.stride(3) == 1 and out.dtype in (torch.bfloat16, torch.float16)):
             raise RuntimeError("output [B,Hq,T,128] aligned")
         b, hq, t, _ = out.shape
+        if (q_raw is None) != (k_raw is None):
+            raise RuntimeError("raw Q and K rows of un-quantised heads (both or none)")
+        raw = (0, 0, 0, 0, 0, 0, 0, 0)
+        if q_raw is not None:
+            self._bhtd(q_raw, "Q"), self._bhtd(k_raw, "K")
+            if q_raw.shape != (b, hq, t, 128) or k_raw.shape != (b, heads_kv, t, 128):
+                raise RuntimeError("BF16 Q/K [B,H,T,128] with contiguous features")
+            raw = (q_raw.data_ptr(), q_raw.stride(0), q_raw.stride(1), q_raw.stride(2),
+                   k_raw.data_ptr(), k_raw.stride(0), k_raw.stride(1), k_raw.stride(2))
         if bands.dtype != torch.int32 or bands.numel() != hq * 2 or not bands.is_contiguous():
             raise RuntimeError("bands [Hq,2] or task tables")
         with torch.cuda.device(out.device):
@@ -177,7 +195,7 @@ class Module:
                                                k8.data_ptr(), qa8.data_ptr(), ka8.data_ptr(), _ptr(q4x), _ptr(k4x),
                                                _ptr(qa4), _ptr(ka4), out.data_ptr(), int(out.dtype == torch.float16),
                                                out.stride(0), out.stride(1), out.stride(2), b, hq, heads_kv, t,
-                                               float(scale), self.error_word(out.device).data_ptr(), _stream()))
+                                               float(scale), *raw, self.error_word(out.device).data_ptr(), _stream()))
         return out
 
     def attention_tasks(self, groups, entries, v16, v8, v4, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):

@@ -6,15 +6,14 @@ Differences from the reference, all additive:
   * q/k/v carry a batch dimension ``[B,H,T,128]`` (the reference asserts batch 1);
   * operands live in the tile blob layouts of ``csrc/common.cuh`` instead of mma.sync fragment order;
   * a map may mark KV heads as un-quantised BF16 (``bands_fn.bf16_kv_heads(layer)``); their groups are
-    computed with exact attention, which is what the reference's ``exact_attention`` baseline does
-    (``triattention/models.py:45-47``).
+    computed as exact attention by the same kernel launch (bf16 QK^T, exact online softmax), which is what the
+    reference's ``exact_attention`` baseline computes with torch's SDPA (``triattention/models.py:45-47``).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 
 SKIP, F16, I8, I4, Q4 = 0, 1, 2, 3, 4
 K8_BYTES, K4_BYTES, V16_BYTES, V8_BYTES, V4_BYTES = 8192, 4096, 16384, 8192, 4096
@@ -28,6 +27,7 @@ class BandTable:
     host: torch.Tensor       # int32 [Hq,2] as given by the map
     bf16_kv: tuple = ()
     q_modes: torch.Tensor = None   # int32 [Hq] on the device: bit 0 = the head's INT8 Q codes are read, bit 1 = its INT4 codes
+    raw_kv: torch.Tensor = None    # int32 [Hkv] on the device, 1 = un-quantised KV head; None when the map has none
 
     @classmethod
     def build(cls, bands, rows, kv_heads, device, bf16_kv=()):
@@ -52,8 +52,13 @@ class BandTable:
         dev[~quant] = 0
         modes = torch.zeros(b.shape[0], dtype=torch.int32)
         modes[quant] = 1 + 2 * (n4 > 0).any(dim=1).to(torch.int32)
+        raw_kv = None
+        if bf16_kv:
+            raw_kv = torch.zeros(kv_heads, dtype=torch.int32)
+            raw_kv[list(bf16_kv)] = 1
+            raw_kv = raw_kv.to(device)
         return cls(order.to(torch.int32).to(device), dev.to(device), frozenset(formats), host, tuple(sorted(bf16_kv)),
-                   modes.to(device))
+                   modes.to(device), raw_kv)
 
 
 class Prefill:
@@ -118,23 +123,22 @@ class Prefill:
         m = self.module
         m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
                      ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"], q_modes=table.q_modes)
-        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"])
+        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"], raw_heads=table.raw_kv)
         return table, ops
 
-    def __call__(self, layer, q, k, v, scale):
+    def __call__(self, layer, q, k, v, scale, out_dtype=None):
+        """out_dtype: torch.bfloat16 (default: q's) or torch.float16, the two output types of the reference's kernel
+        (prefill_sm80.cu:533-539)."""
         b, hq, t, _ = q.shape
         hk, device = k.shape[1], q.device
         table, ops = self.write(layer, q, k, v)
         q4 = Q4 in table.formats
-        out = torch.empty((b, t, hq, 128), dtype=q.dtype, device=device).transpose(1, 2)
+        out = torch.empty((b, t, hq, 128), dtype=out_dtype or q.dtype, device=device).transpose(1, 2)
+        # un-quantised extension heads run in the same launch: exact attention from the raw Q / K rows and fp16 V blobs
+        raw = (q, k) if table.bf16_kv else (None, None)
         self.module.attention(table.bands, ops["v16"], ops["v8h"], ops["vstat"], ops["q8"], ops["k8"], ops["qa"], ops["ka"],
                               ops["q4x"] if q4 else None, ops["k4x"] if q4 else None, ops["qa4"] if q4 else None,
-                              ops["ka4"] if q4 else None, out, scale, hk)
-        group = hq // hk
-        for kh in table.bf16_kv:   # un-quantised extension heads: exact attention on the raw tensors
-            heads = slice(kh * group, (kh + 1) * group)
-            out[:, heads] = F.scaled_dot_product_attention(q[:, heads], k[:, kh:kh + 1], v[:, kh:kh + 1], is_causal=True,
-                                                           scale=scale, enable_gqa=True)
+                              ops["ka4"] if q4 else None, out, scale, hk, q_raw=raw[0], k_raw=raw[1])
         if self.decode_cache is not None:
             self.decode_cache.store(layer, t, ops, table.host, k, v, table.bf16_kv)
         return out

@@ -109,6 +109,34 @@ def gather_outputs(local, shards, group_size, batch, heads_q, group=None):
     return out
 
 
+class OutputGatherer:
+    """gather_outputs for a loop: the padded send buffer, the receive buffer and the row index that puts every
+    (sequence, Q head) of every rank in its place are built once; a call is one all_gather_into_tensor (NCCL) and
+    one index_select.  local [b, h_local, ...] -> full [B, Hq, ...] on every rank."""
+
+    def __init__(self, shards, group_size, batch, heads_q, like, group=None):
+        self.group, world = group, len(shards)
+        bmax = max(s.batch.stop - s.batch.start for s in shards)
+        hmax = max(len(s.kv_heads) for s in shards) * group_size
+        tail = tuple(like.shape[2:])
+        self.pad = like.new_zeros((bmax, hmax) + tail)
+        self.recv = like.new_empty((world, bmax, hmax) + tail)
+        index = torch.zeros((batch, heads_q), dtype=torch.long)
+        for r, s in enumerate(shards):
+            qh = torch.as_tensor(s.q_heads(group_size))
+            for i, b in enumerate(range(s.batch.start, s.batch.stop)):
+                index[b, qh] = (r * bmax + i) * hmax + torch.arange(len(qh))
+        self.index = index.flatten().to(like.device)
+        self.shape = (batch, heads_q) + tail
+
+    def __call__(self, local):
+        import torch.distributed as dist
+        self.pad[:local.shape[0], :local.shape[1]] = local
+        dist.all_gather_into_tensor(self.recv, self.pad[None], group=self.group)
+        rows = self.recv.flatten(0, 2)
+        return rows.index_select(0, self.index).view(self.shape)
+
+
 def merge_triples(m, l, o):
     """Merge split partials along dim 0: m, l [S,...], o [S,...,128] -> (m, l, o) of the union.
     common_device.cuh:418-438 of the reference (base-2 running maximum), in torch for any device."""
