@@ -224,8 +224,10 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   const int device = configured.pending();
   TRI_CHECK(device != -2, "attention: no current CUDA device");
   if (device >= 0) {
-    if (allow_smem(prefill_kernel<__nv_bfloat16>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
-    if (allow_smem(prefill_kernel<__half>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    if (allow_smem(prefill_kernel<__nv_bfloat16, false>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    if (allow_smem(prefill_kernel<__half, false>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    if (allow_smem(prefill_kernel<__nv_bfloat16, true>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
+    if (allow_smem(prefill_kernel<__half, true>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
     configured.mark(device);
   }
   const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
@@ -242,13 +244,17 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
   const dim3 grid((unsigned)((int64_t)quads * units));
-#define TRI_LAUNCH(T)                                                                                                      \
-  prefill_kernel<T><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, mapq, mapk, has_raw, bands,                   \
+#define TRI_LAUNCH(T, R)                                                                                                   \
+  prefill_kernel<T, R><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, mapq, mapk, has_raw, bands,                \
       static_cast<const uint8_t*>(k8),                                                                                     \
       static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8h), qa8, \
       qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, heads_q, heads_kv, tokens, units,       \
       sm_log2, device_error)
-  if (out_is_half) TRI_LAUNCH(__half); else TRI_LAUNCH(__nv_bfloat16);
+  // quantised heads, then (if the map has any) the un-quantised ones: the same kernel, instantiated for each kind
+  if (out_is_half) TRI_LAUNCH(__half, false); else TRI_LAUNCH(__nv_bfloat16, false);
+  if (has_raw) {
+    if (out_is_half) TRI_LAUNCH(__half, true); else TRI_LAUNCH(__nv_bfloat16, true);
+  }
 #undef TRI_LAUNCH
   return tri_launch_status("attention");
 }

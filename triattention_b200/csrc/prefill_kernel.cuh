@@ -69,7 +69,7 @@ __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
 }
 
 // grid = quads * batch * heads_q CTAs, heaviest query rows first; 640 threads; one CTA per SM.
-template <typename Out>
+template <typename Out, bool Raw>
 __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid_constant__ CUtensorMap map_q8,
     const __grid_constant__ CUtensorMap map_q4, const __grid_constant__ CUtensorMap map_qraw,
     const __grid_constant__ CUtensorMap map_kraw, int has_raw, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
@@ -90,8 +90,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   const int w8 = bands[h * 2], w4 = bands[h * 2 + 1];
   // A head with w8 < 1 belongs to an un-quantised (BF16) KV group: exact attention over every causal tile, straight
   // from the raw bf16 Q and K rows (TMA tensor copies of the caller's tensors) and the fp16 V blobs.  Uniform for the CTA.
-  const bool raw = w8 < 1;
-  if (raw && !has_raw) return;
+  // (two instantiations: Raw = false serves the quantised heads, Raw = true the un-quantised ones; a CTA of the other
+  // kind leaves at once, so the arithmetic of one kind costs the other neither registers nor instructions)
+  constexpr bool raw = Raw;
+  if ((w8 < 1) != Raw || (Raw && !has_raw)) return;
   QuadPlan plan;
   plan.build(quad_id, rows, raw ? (1 << 20) : w8, raw ? (1 << 20) : w4);
   const int nsteps = plan.steps();
@@ -439,6 +441,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 #pragma unroll
           for (int cc = 0; cc < G; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
+            uint32_t hi[8], lo[8];   // the 16 weights of this key group, two per word: high and low parts
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
               uint32_t w[8];
@@ -448,20 +451,28 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
                 const float sc = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
                 w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
               }
-              uint32_t hi[4], lo[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const uint32_t h = __byte_perm(w[2 * u], w[2 * u + 1], 0x6521);   // (1024 + code) x 2 as fp16
-                rs = (int)__dp4a(h, 0x00010001u, (uint32_t)rs);                     // sum of the codes
-                // (1024 + code) * s - 1024 * s in one fused operation: code * s rounded once (exact for s_hi)
-                const __half2 ph = __hfma2(*reinterpret_cast<const __half2*>(&h), shi2, nhi2);
-                const __half2 pl = __hfma2(*reinterpret_cast<const __half2*>(&h), slo2, nlo2);
-                hi[u] = *reinterpret_cast<const uint32_t*>(&ph);
-                lo[u] = *reinterpret_cast<const uint32_t*>(&pl);
-              }
-              tmem_st4(s_addr + 8 * cc + 4 * hb, hi);
-              tmem_st4(s_addr + 16 + 8 * cc + 4 * hb, lo);   // the low parts sit over the second half of the thread's columns
+              const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[2], w[3], 0x6521);   // (1024 + code) x 2 as fp16
+              const uint32_t h2 = __byte_perm(w[4], w[5], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
+              rs = (int)__dp4a(h0, 0x00010001u, (uint32_t)rs);   // sum of the codes
+              rs = (int)__dp4a(h1, 0x00010001u, (uint32_t)rs);
+              rs = (int)__dp4a(h2, 0x00010001u, (uint32_t)rs);
+              rs = (int)__dp4a(h3, 0x00010001u, (uint32_t)rs);
+              // (1024 + code) * s - 1024 * s in one fused operation: code * s rounded once (exact for s_hi)
+              const __half2 p0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), shi2, nhi2);
+              const __half2 p1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), shi2, nhi2);
+              const __half2 p2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), shi2, nhi2);
+              const __half2 p3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), shi2, nhi2);
+              hi[4 * hb] = *reinterpret_cast<const uint32_t*>(&p0); hi[4 * hb + 1] = *reinterpret_cast<const uint32_t*>(&p1);
+              hi[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&p2); hi[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&p3);
+              const __half2 l0 = __hfma2(*reinterpret_cast<const __half2*>(&h0), slo2, nlo2);
+              const __half2 l1 = __hfma2(*reinterpret_cast<const __half2*>(&h1), slo2, nlo2);
+              const __half2 l2 = __hfma2(*reinterpret_cast<const __half2*>(&h2), slo2, nlo2);
+              const __half2 l3 = __hfma2(*reinterpret_cast<const __half2*>(&h3), slo2, nlo2);
+              lo[4 * hb] = *reinterpret_cast<const uint32_t*>(&l0); lo[4 * hb + 1] = *reinterpret_cast<const uint32_t*>(&l1);
+              lo[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&l2); lo[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&l3);
             }
+            tmem_st8(s_addr + 8 * cc, hi);
+            tmem_st8(s_addr + 16 + 8 * cc, lo);   // the low parts sit over the second half of the thread's columns
           }
         };
         if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
