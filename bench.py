@@ -135,7 +135,7 @@ class ClockSampler:
 
 
 def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, split_group=None, cfg=None, heads=None,
-                sequences=None):
+                sequences=None, exchange="nccl"):
     """Synthetic prompt K/V -> quantised cache through the product's write kernels.  Returns (module, cache, plan).
     part = sequences written per pass (None = all at once); with it the prompts are generated on the GPU.
     cfg = the configuration (default: the benchmark's); heads / sequences = the KV heads and sequence numbers this
@@ -149,7 +149,7 @@ def build_cache(batch, seed0, tile_costs=None, fused_merge=False, part=None, spl
     hq, hk, t = cfg["heads_q"], cfg["heads_kv"], cfg["cache_tokens"]
     g = hq // hk
     module = load_extension()
-    cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, split_group=split_group,
+    cache = DecodeCache(module, max_tail=256, fused_merge=fused_merge, split_group=split_group, exchange=exchange,
                         **({"tile_costs": tile_costs} if tile_costs else {}))
     fn = per_kv_head(kv_kinds(cfg=cfg), g)
     by_unit = heads is not None
@@ -526,20 +526,36 @@ def measure_split(rank, world, dist, steps):
         del cache, plan
         torch.cuda.empty_cache()
     dist.barrier()
-    module, cache, plan = build_cache(batch, 0, part=2, cfg=cfg, heads=list(range(hk)), split_group=dist.group.WORLD)
-    ms = time_steps(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, dist, warm=50)
-    ms_local = time_steps(lambda i: cache(0, qd, kd, vd, scale, phases=1, out=out), steps, dist, warm=5)
-    cache(0, qd, kd, vd, scale, out=out)
-    module.check_device_error()
+    how = dict(nccl="fold inside the split pass; one all_gather_into_tensor (NCCL) of [units, 8, 130] f32 per rank; the merge "
+                    "reads the gathered buffer by stride",
+               peer="fold inside the split pass writes the triples, then a flag, into every GPU's exchange buffer by peer "
+                    "stores over NVLink; the merge waits per unit for the flags; no collective call in the step")
+    for exchange in ("nccl", "peer"):
+        try:
+            module, cache, plan = build_cache(batch, 0, part=2, cfg=cfg, heads=list(range(hk)), split_group=dist.group.WORLD,
+                                              exchange=exchange)
+        except (RuntimeError, ImportError) as e:       # no symmetric memory on this system: every rank fails alike
+            if rank == 0:
+                record[exchange] = dict(unavailable=str(e)[:200])
+            continue
+        ms = time_steps(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, dist, warm=50)
+        ms_local = time_steps(lambda i: cache(0, qd, kd, vd, scale, phases=1, out=out), steps, dist, warm=5)
+        cache(0, qd, kd, vd, scale, out=out)
+        module.check_device_error()
+        if rank == 0:
+            record[exchange] = dict(ms_per_step=ms, tokens_per_s=batch / (ms / 1e3), speedup_vs_one_gpu=one["ms"] / ms,
+                                    efficiency=one["ms"] / (world * ms), ms_split_pass_alone=ms_local,
+                                    rank0_cache_bytes=int(plan["payload_bytes"]),
+                                    max_abs_diff_vs_one_gpu=float((out.float() - one["out"].float()).abs().max()),
+                                    exchange=how[exchange])
+        del cache, plan
+        torch.cuda.empty_cache()
+        dist.barrier()
     if rank == 0:
-        record.update(n_gpus=world, ms_per_step=ms, tokens_per_s=batch / (ms / 1e3), speedup_vs_one_gpu=one["ms"] / ms,
-                      efficiency=one["ms"] / (world * ms), ms_split_pass_alone=ms_local,
-                      rank0_cache_bytes=int(plan["payload_bytes"]),
-                      max_abs_diff_vs_one_gpu=float((out.float() - one["out"].float()).abs().max()),
-                      exchange="fold inside the split pass; one all_gather_into_tensor (NCCL) of [units, 8, 130] f32 per rank; "
-                               "merge reads the gathered buffer by stride")
-    del cache, plan
-    torch.cuda.empty_cache()
+        best = max((r for r in (record.get("nccl"), record.get("peer")) if r and "ms_per_step" in r),
+                   key=lambda r: r["speedup_vs_one_gpu"])
+        record.update(n_gpus=world, ms_per_step=best["ms_per_step"], speedup_vs_one_gpu=best["speedup_vs_one_gpu"],
+                      efficiency=best["efficiency"])
     return record
 
 

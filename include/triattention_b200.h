@@ -162,24 +162,42 @@ int tri_decode_fold(const float* pm, const float* pl, const float* po, const int
 
 /* Sequence split across GPUs, this GPU's part: the split pass of tri_decode over this rank's tiles, and in
  * the same launch the fold of every unit's segments to one (m, l, o) per Q head (the CTA that finishes a
- * unit's last segment folds it): fold_m, fold_l f32 [U,8], fold_o f32 [U,8,128] — what the ranks exchange.
- * unit_done int32 [U], zero before the first call, left at zero.  A unit without any segment on this rank is
- * not touched: give its fold entries m = -FLT_MAX, l = 0, o = 0 once.  No counterpart in the reference (single GPU). */
+ * unit's last segment folds it).  unit_done int32 [U], zero before the first call, left at zero.  The triples go
+ *   - either into fold_m, fold_l f32 [U,8], fold_o f32 [U,8,128] for the caller to exchange (one NCCL all-gather);
+ *     a unit without any segment on this rank is not touched: give its entries m = -FLT_MAX, l = 0, o = 0 once;
+ *   - or (fold_* NULL, peer_buffers given) straight into the exchange buffer of every GPU of the group by peer stores,
+ *     each followed by a flag: the compute step and the collective are one kernel.  peer_buffers: device array of
+ *     `world` pointers, entry r = rank r's exchange buffer as mapped into THIS process (symmetric / peer memory; this
+ *     rank's own buffer at entry `rank`).  Buffer layout, in 4-byte words: data f32 [2][world][U*8*130] (parity of the
+ *     step's epoch, source rank, then m [U,8] | l [U,8] | o [U,8,128]) followed by flags int32 [world][U].  Before the
+ *     first step every rank fills its own buffer with m = -FLT_MAX, l = 0, o = 0, flags = 0 and the group synchronises
+ *     once.  epoch int32 [U], zero at first: the steps this rank has folded, per unit.  tri_decode_merge with
+ *     `exchange_buffer` is the matching consumer.  Every GPU of the group must run the same sequence of steps.
+ * No counterpart in the reference (single GPU). */
 int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool,
                         const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags,
                         const int32_t* tmeta, const int32_t* segments, const int32_t* cta_segments, int num_ctas,
                         const int32_t* unit_slots, float* pm, float* pl, float* po, int32_t* unit_done,
-                        float* fold_m, float* fold_l, float* fold_o, int batch, int heads_q, int heads_kv,
-                        int prompt, double scale, int* device_error, void* stream);
+                        float* fold_m, float* fold_l, float* fold_o,
+                        void* const* peer_buffers, int world, int rank, int32_t* epoch,
+                        int batch, int heads_q, int heads_kv, int prompt, double scale,
+                        int* device_error, void* stream);
 
 /* The merge of tri_decode alone, over partials that may lie strided: split s of unit u is read at
  * pm[(first*8 + r) + s*split_stride], pl likewise, po[(first*8 + r)*128 + ch + s*split_stride] with
  * (first, count) = unit_slots[u].  split_stride = 0 means the dense buffers of the split pass.  With
  * triples all-gathered as [rank][m | l | o] and unit_slots[u] = (u, world), split_stride = the floats per rank:
- * the gathered buffer is merged in place, no re-layout.  Other arguments as tri_decode.
+ * the gathered buffer is merged in place, no re-layout.
+ * exchange_buffer (or NULL): this rank's exchange buffer of the peer-memory exchange (tri_decode_partials); pm, pl, po
+ * and split_stride are then ignored: the CTA of a unit waits — at most one second, then device error 1 — until every
+ * source rank r with present[r*U + u] != 0 (int32 [world,U]: rank r holds tiles of unit u) has delivered the triple
+ * of the unit's next epoch, and merges that epoch's block.  seen int32 [U], zero at first: the steps merged so far.
+ * Other arguments as tri_decode.
  * Replaces decode_merge_kernel, triattention/kernels/cuda/common_device.cuh:373-469. */
 int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
-                     const float* po, int64_t split_stride, const int32_t* unit_slots, const float* kstat,
+                     const float* po, int64_t split_stride,
+                     const void* exchange_buffer, const int32_t* present, int32_t* seen, int world,
+                     const int32_t* unit_slots, const float* kstat,
                      const float* vstat, void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t,
                      const void* kcur, const void* vcur, int64_t cur_stride_b, int64_t cur_stride_h,
                      const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,

@@ -265,13 +265,17 @@ def test_store_in_parts_equals_store_at_once(module):
         DecodeCache(module, max_tail=4).store(0, t, ops, table.host, kc[3:], vc[3:], table.bf16_kv, first_sequence=3, sequences=batch)
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
 @pytest.mark.parametrize("world,ctas", [(2, None), (3, 5)])
-def test_sequence_split_emulated_on_one_gpu(module, world, ctas):
+def test_sequence_split_emulated_on_one_gpu(module, world, ctas, exchange):
     """The sequence-split path without a process group: `world` caches each hold one part of every unit's tile range
-    (what the ranks of a split group hold), each runs its split pass with the in-kernel fold (tri_decode_partials), the
-    folded triples are stacked [rank][m | l | o] as an all-gather would leave them, and tri_decode_merge reads that
-    buffer in place by stride.  Against the un-split decode over three steps, with a BF16 unit, an INT4 band and a
-    short prompt part so that some ranks hold no tile of some units."""
+    (what the ranks of a split group hold) and each runs its split pass with the in-kernel fold (tri_decode_partials).
+    "nccl": the folded triples are stacked [rank][m | l | o] as an all-gather would leave them, and tri_decode_merge
+    reads that buffer in place by stride.  "peer": every part's fold writes its triples, then a flag, straight into the
+    exchange buffers of all parts (here all on this GPU), and the merge takes them from there; all producers are
+    launched before any consumer, on one stream, so no kernel ever waits for another.
+    Against the un-split decode over three steps, with a BF16 unit, an INT4 band and a prompt short enough that some
+    parts hold no tile of some units."""
     hq, hk, t, batch = 6, 3, 900, 2
     bands = np.asarray([[INF, INF]] * 2 + [[2, 5]] * 2 + [[INF, INF]] * 2, np.int64)
     q, k, v = make_inputs(hq, hk, t, seed=71, batch=batch)
@@ -280,31 +284,64 @@ def test_sequence_split_emulated_on_one_gpu(module, world, ctas):
     kc, vc = bf16_cuda(k), bf16_cuda(v)
     caches = []
     for rank in range(world):
-        cache = DecodeCache(module, max_tail=8, split=(rank, world), ctas=ctas)
+        cache = DecodeCache(module, max_tail=8, split=(rank, world), ctas=ctas, exchange=exchange)
         pre = Prefill(module, bands_fn_of(bands, (2,)), cache)
         table, ops = pre.write(0, bf16_cuda(q), kc, vc)
         cache.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
         caches.append(cache)
-    # the fused fold equals the stand-alone fold kernel bit for bit (same arithmetic, same order)
+    if exchange == "peer":
+        for cache in caches:
+            cache.attach_peers(0, [c.layers[0]["xbuf"] for c in caches])
+    g = hq // hk
     outs = []
     for s in range(3):
         qs, ks, vs = (bf16_cuda(x[:, :, s:s + 1]) for x in (qd, kd, vd))
         folded = []
-        for cache in caches:
+        for cache in caches:            # every producer first
             e = cache.layers[0]
             mine = cache.partials(0, qs, ks, SCALE).clone()
-            fm, fl, fo = torch.empty_like(e["fm"]), torch.empty_like(e["fl"]), torch.empty_like(e["fo"])
-            module.decode_fold(e["pm"], e["pl"], e["po"], e["dev"]["unit_slots"], fm, fl, fo, hq // hk)
-            g = hq // hk      # rows of Q heads the group does not have are written by neither
-            assert torch.equal(fm[:, :g], e["fm"][:, :g]) and torch.equal(fl[:, :g], e["fl"][:, :g])
-            assert torch.equal(fo[:, :g], e["fo"][:, :g])
+            if exchange == "nccl":
+                # the fused fold equals the stand-alone fold kernel bit for bit (same arithmetic, same order); rows of Q heads
+                # the group does not have are written by neither
+                fm, fl, fo = torch.empty_like(e["fm"]), torch.empty_like(e["fl"]), torch.empty_like(e["fo"])
+                module.decode_fold(e["pm"], e["pl"], e["po"], e["dev"]["unit_slots"], fm, fl, fo, g)
+                assert torch.equal(fm[:, :g], e["fm"][:, :g]) and torch.equal(fl[:, :g], e["fl"][:, :g])
+                assert torch.equal(fo[:, :g], e["fo"][:, :g])
             folded.append(mine)
         outs_rank = []
-        for cache in caches:        # every rank merges the same gathered buffer with its own (replicated) tail
-            cache.layers[0]["gathered"].copy_(torch.stack(folded))
+        for cache in caches:        # every rank merges the same triples with its own (replicated) tail
+            if exchange == "nccl":
+                cache.layers[0]["gathered"].copy_(torch.stack(folded))
             outs_rank.append(cache.merge_gathered(0, qs, ks, vs, SCALE).float().cpu().numpy()[:, :, 0])
             cache.advance()
         assert all((o == outs_rank[0]).all() for o in outs_rank)
         outs.append(outs_rank[0])
     module.check_device_error()
+    if exchange == "peer":          # every unit's counters moved once per step, on both sides
+        for cache in caches:
+            e = cache.layers[0]
+            assert (e["seen"] == 3).all() and (e["epoch"][e["present"][cache.split[0]].bool()] == 3).all()
     assert_fp_close(np.stack(outs, 1), whole, f"sequence split over {world} parts vs whole units")
+
+
+def test_exchange_wait_runs_out_without_hanging(module):
+    """The consumer's wait is bounded: a merge whose peers never deliver (nothing sets the flags) gives up after its time
+    limit, reports device error 1 and leaves the context usable."""
+    hq, hk, t, batch = 4, 2, 300, 1
+    bands = np.asarray([[INF, INF]] * 4, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=73, batch=batch)
+    qd, kd, vd = (bf16_cuda(x) for x in make_inputs(hq, hk, 1, seed=74, batch=batch))
+    cache = DecodeCache(module, max_tail=8, split=(0, 2), exchange="peer")
+    pre = Prefill(module, bands_fn_of(bands), cache)
+    kc, vc = bf16_cuda(k), bf16_cuda(v)
+    table, ops = pre.write(0, bf16_cuda(q), kc, vc)
+    cache.store(0, t, ops, table.host, kc, vc, table.bf16_kv)
+    other = torch.zeros_like(cache.layers[0]["xbuf"])      # stands for the absent rank's buffer: written, never read
+    cache.attach_peers(0, [cache.layers[0]["xbuf"], other])
+    cache.partials(0, qd, kd, SCALE)                       # this rank delivers; rank 1 never does
+    cache.merge_gathered(0, qd, kd, vd, SCALE)
+    with pytest.raises(RuntimeError, match="device error 1"):
+        module.check_device_error()
+    assert int(cache.layers[0]["seen"].max()) == 0          # nothing was merged
+    whole, _ = product_decode(module, q, k, v, bands, *make_inputs(hq, hk, 1, seed=74, batch=batch), steps=1)
+    assert np.isfinite(whole).all()                         # and the GPU still computes

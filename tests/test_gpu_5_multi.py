@@ -1,4 +1,5 @@
-"""Two-GPU paths: unit sharding with output gather, and the sequence split with the NCCL (m, l, o) exchange.
+"""Two-GPU paths: unit sharding with output gather, and the sequence split with the (m, l, o) exchange over NCCL and
+over peer memory.
 Skipped on a single-GPU box; the host logic of both is covered on CPU by tests/test_cpu_sharding.py."""
 import os
 import socket
@@ -24,10 +25,10 @@ def _inputs(hq, hk, t, batch, steps):
     return make_inputs(hq, hk, t, seed=3, batch=batch) + make_inputs(hq, hk, steps, seed=4, batch=batch)
 
 
-def _decode_steps(module, bands_fn, q, k, v, qd, kd, vd, steps, group=None):
+def _decode_steps(module, bands_fn, q, k, v, qd, kd, vd, steps, group=None, exchange="nccl"):
     from triattention_b200.kernels.decode import DecodeCache
     from triattention_b200.kernels.prefill import Prefill
-    cache = DecodeCache(module, max_tail=8, split_group=group)
+    cache = DecodeCache(module, max_tail=8, split_group=group, exchange=exchange)
     pre = Prefill(module, bands_fn, cache)
     table, ops = pre.write(0, q, k, v)
     cache.store(0, q.shape[2], ops, table.host, k, v, table.bf16_kv)
@@ -56,6 +57,11 @@ def _worker(rank, world, port, result):
         # 1. sequence split: every unit's tile range cut in two, folded triples all-gathered over NCCL
         split = _decode_steps(module, fn, q, k, v, qd, kd, vd, steps, group=dist.group.WORLD)
         r1 = fp_report(split.cpu().numpy(), whole.cpu().numpy())
+        # 1b. the same with the exchange fused into the kernels: peer stores into every GPU's exchange buffer, no collective
+        # call in the step (plain peer stores and loads; no multicast objects are involved)
+        fused = _decode_steps(module, fn, q, k, v, qd, kd, vd, steps, group=dist.group.WORLD, exchange="peer")
+        dist.barrier()
+        r1b = fp_report(fused.cpu().numpy(), whole.cpu().numpy())
         # 2. unit sharding: this rank's (batch slice, KV-head group), outputs gathered
         costs = sharding.head_costs(fn(0, hq).numpy(), hk, t, fn.bf16_kv_heads(0))
         shards = sharding.shard_grid(batch, costs, world)
@@ -66,7 +72,7 @@ def _worker(rank, world, port, result):
                               take(qd, qh), take(kd, kvh), take(vd, kvh), steps)
         full = sharding.gather_outputs(local.transpose(1, 2).contiguous(), shards, 2, batch, hq).transpose(1, 2)
         r2 = fp_report(full.cpu().numpy(), whole.cpu().numpy())
-        result[rank] = (r1, r2, [list(x.kv_heads) for x in shards])
+        result[rank] = (r1, r2, [list(x.kv_heads) for x in shards], r1b)
     finally:
         dist.destroy_process_group()
 
@@ -79,7 +85,8 @@ def test_two_gpu_split_and_sharding():
         result = manager.dict()
         mp.spawn(_worker, args=(world, port, result), nprocs=world, join=True)
         for rank in range(world):
-            r1, r2, groups = result[rank]
+            r1, r2, groups, r1b = result[rank]
             assert r1["worst_excess"] <= 0 and r1["cos"] >= 0.9999, ("sequence split", r1)
+            assert r1b["worst_excess"] <= 0 and r1b["cos"] >= 0.9999, ("sequence split, peer-memory exchange", r1b)
             # a shard is a smaller problem with its own CTA partition, so only the float summation order differs
             assert r2["worst_excess"] <= 0 and r2["cos"] >= 0.9999, ("unit sharding", r2, groups)

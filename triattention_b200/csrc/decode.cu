@@ -25,8 +25,14 @@ namespace tri {
 // split s of the unit: ml_stride = 8, o_stride = 1024 for the dense [slot][8] buffers of the split pass; other
 // strides let the merge read triples gathered from several GPUs in place ([rank][unit][8]).
 constexpr int MergeThreads = 256, MergeWarps = MergeThreads / 32;
+// Consumer side of the peer-memory exchange of a sequence-split group (decode_kernel.cuh): world > 0 makes the unit's CTA
+// wait until every source rank that holds tiles of the unit (present[rank][unit]) has delivered the triple of this
+// unit's next epoch into the local exchange buffer, and read the partials from that epoch's parity block.
+struct SplitExchange {
+  const float* local; const int32_t* present; int32_t* seen; int world, units; int64_t rank_stride;
+};
 __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float* pm, const float* pl, const float* po,
-    int64_t ml_stride, int64_t o_stride, const int2* unit_slots, int slot_limit, const float* vstat, const float* kstat,
+    int64_t ml_stride, int64_t o_stride, SplitExchange xchg, const int2* unit_slots, int slot_limit, const float* vstat, const float* kstat,
     const __nv_bfloat16* q, int64_t qsb, int64_t qsh, __nv_bfloat16* ktail, __nv_bfloat16* vtail, int64_t tsu, int64_t tst,
     const __nv_bfloat16* kcur, const __nv_bfloat16* vcur, int64_t csb, int64_t csh, const int64_t* step, __nv_bfloat16* out,
     int64_t osb, int64_t osh, int heads_q, int heads_kv, int max_tail, float sm_log2, int* err) {
@@ -39,6 +45,30 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   if (sl.x < 0 || sl.y < 0 || sl.x + sl.y > slot_limit) {   // the unit's slots do not fit the partial buffers
     if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
     return;
+  }
+  __shared__ int exchange_failed;
+  if (xchg.world > 0) {
+    // triples of this unit's next epoch from every rank that has tiles of it; bounded wait (1 s), then an error code
+    const int epoch = xchg.seen[unit] + 1;
+    if (tid == 0) exchange_failed = 0;
+    __syncthreads();
+    if (tid < xchg.world && xchg.present[(int64_t)tid * xchg.units + unit]) {
+      const int32_t* flag = reinterpret_cast<const int32_t*>(xchg.local + exchange_flag_offset(xchg.world, xchg.rank_stride)) +
+                            (int64_t)tid * xchg.units + unit;
+      const uint64_t t0 = globaltimer_ns();
+      while (load_acquire_sys(flag) < epoch) {
+        if (globaltimer_ns() - t0 > 1000000000ull) { exchange_failed = 1; break; }
+      }
+    }
+    __syncthreads();
+    if (exchange_failed) {
+      if (tid == 0) atomicCAS(err, ErrNone, ErrBarrierTimeout);
+      return;
+    }
+    if (tid == 0) xchg.seen[unit] = epoch;
+    const float* block = xchg.local + (int64_t)(epoch & 1) * xchg.world * xchg.rank_stride;
+    const int64_t ug = (int64_t)xchg.units * MaxGroup;
+    pm = block; pl = block + ug; po = block + 2 * ug;
   }
   const int prior = min((int)*step, max_tail - 1), tail = prior + 1;
   const __nv_bfloat16* kc = kcur + b * csb + kh * csh;
@@ -91,11 +121,24 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   for (int t = lane; t < tail; t += 32) ts[r][t] = exp2f(ts[r][t] - m);
   __syncwarp();
   float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < sl.y; ++s) {
-    const float w = exp2f(pm[first + s * ml_stride] - m);
-    total = fmaf(pl[first + s * ml_stride], w, total);
-    const float4 p = *reinterpret_cast<const float4*>(po + first * D + s * o_stride + lane * 4);
-    acc[0] = fmaf(p.x, w, acc[0]); acc[1] = fmaf(p.y, w, acc[1]); acc[2] = fmaf(p.z, w, acc[2]); acc[3] = fmaf(p.w, w, acc[3]);
+  for (int s0 = 0; s0 < sl.y; s0 += 4) {   // four splits' loads in flight at a time; the sums stay in split order
+    float pmv[4], plv[4];
+    float4 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const bool on = s0 + u < sl.y;
+      pmv[u] = on ? pm[first + (s0 + u) * ml_stride] : -FLT_MAX;
+      plv[u] = on ? pl[first + (s0 + u) * ml_stride] : 0.f;
+      p[u] = on ? *reinterpret_cast<const float4*>(po + first * D + (s0 + u) * o_stride + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (s0 + u < sl.y) {
+        const float w = exp2f(pmv[u] - m);
+        total = fmaf(plv[u], w, total);
+        acc[0] = fmaf(p[u].x, w, acc[0]); acc[1] = fmaf(p[u].y, w, acc[1]); acc[2] = fmaf(p[u].z, w, acc[2]); acc[3] = fmaf(p[u].w, w, acc[3]);
+      }
+    }
   }
   const float4 mean = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + lane * 4);
   const float4 scale = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + D + lane * 4);
@@ -232,13 +275,14 @@ static cudaError_t launch_split(const DecodeCall& c, float* pm, float* pl, float
 }
 
 static cudaError_t launch_merge(const DecodeCall& c, const float* pm, const float* pl, const float* po, int64_t ml_stride,
-                                int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained) {
+                                int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained,
+                                SplitExchange xchg = SplitExchange{}) {
   const dim3 grid(c.batch * c.heads_kv);
   if (chained)
-    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, unit_slots,
+    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, unit_slots,
                           slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb,
                           c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
-  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
+  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
       c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
       c.heads_kv, c.max_tail, c.sm_log2, c.err);
   return cudaSuccess;
@@ -304,10 +348,15 @@ extern "C" int tri_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
 extern "C" int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool,
     const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
     const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, float* pm, float* pl, float* po, int32_t* unit_done,
-    float* fold_m, float* fold_l, float* fold_o, int batch, int heads_q, int heads_kv, int prompt, double scale,
-    int* device_error, void* stream) {
+    float* fold_m, float* fold_l, float* fold_o, void* const* peer_buffers, int world, int rank, int32_t* epoch,
+    int batch, int heads_q, int heads_kv, int prompt, double scale, int* device_error, void* stream) {
   TRI_CHECK(q && pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && unit_slots && pm && pl &&
-            po && unit_done && fold_m && fold_l && fold_o && device_error, "decode_partials: null buffers");
+            po && unit_done && device_error, "decode_partials: null buffers");
+  TRI_CHECK((peer_buffers != nullptr) != (fold_m != nullptr) && (fold_m != nullptr) == (fold_l != nullptr) &&
+            (fold_m != nullptr) == (fold_o != nullptr),
+            "decode_partials: either the fold buffers or the peers' exchange buffers");
+  TRI_CHECK(peer_buffers == nullptr || (epoch != nullptr && world >= 1 && world <= 64 && rank >= 0 && rank < world),
+            "decode_partials: exchange group");
   TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0 && heads_q / heads_kv <= MaxGroup && prompt > 0 &&
             num_ctas >= 0, "decode geometry/buffers");
   TRI_CHECK(aligned16(pool) && aligned16(po) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && q_stride_b % 4 == 0 &&
@@ -323,17 +372,30 @@ extern "C" int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_
   call.sm_log2 = (float)(scale * 1.4426950408889634); call.err = device_error;
   MergeArgs margs{};
   margs.unit_slots = call.unit_slots; margs.unit_done = unit_done; margs.fold_m = fold_m; margs.fold_l = fold_l; margs.fold_o = fold_o;
+  if (peer_buffers != nullptr) {
+    margs.peers = reinterpret_cast<float* const*>(peer_buffers); margs.world = world; margs.rank = rank;
+    margs.units = batch * heads_kv; margs.rank_stride = (int64_t)batch * heads_kv * MaxGroup * (D + 2); margs.epoch = epoch;
+  }
   TRI_CUDA(launch_split(call, pm, pl, po, NoSlotLimit, 0, margs, static_cast<cudaStream_t>(stream), true), "decode_partials");
   return tri_launch_status("decode_partials");
 }
 
 extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
-    const float* po, int64_t split_stride, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k,
+    const float* po, int64_t split_stride, const void* exchange_buffer, const int32_t* present, int32_t* seen, int world,
+    const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k,
     void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b,
     int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, int batch, int heads_q,
     int heads_kv, int max_tail, double scale, int* device_error, void* stream) {
   const int prompt = 1;
   TRI_DECODE_COMMON_CHECKS("decode_merge");
+  SplitExchange xchg{};
+  if (exchange_buffer != nullptr) {
+    TRI_CHECK(present && seen && world >= 1 && world <= 64 && aligned16(exchange_buffer), "decode_merge: exchange group");
+    xchg = SplitExchange{static_cast<const float*>(exchange_buffer), present, seen, world, batch * heads_kv,
+                         (int64_t)batch * heads_kv * MaxGroup * (D + 2)};
+    split_stride = xchg.rank_stride;
+    pm = pl = po = static_cast<const float*>(exchange_buffer);   // replaced per unit by the epoch's parity block
+  }
   TRI_CHECK(pm && pl && po && aligned16(po) && split_stride >= 0 && split_stride % 4 == 0, "decode_merge: partials");
   DecodeCall call{};
   call.q = static_cast<const __nv_bfloat16*>(q); call.qsb = q_stride_b; call.qsh = q_stride_h;
@@ -345,7 +407,7 @@ extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_str
   call.err = device_error;
   const int64_t ml = split_stride ? split_stride : MaxGroup, os = split_stride ? split_stride : (int64_t)MaxGroup * D;
   TRI_CUDA(launch_merge(call, pm, pl, po, ml, os, reinterpret_cast<const int2*>(unit_slots), NoSlotLimit,
-                        static_cast<cudaStream_t>(stream), true), "decode_merge");
+                        static_cast<cudaStream_t>(stream), true, xchg), "decode_merge");
   return tri_launch_status("decode_merge");
 }
 

@@ -219,6 +219,9 @@ __device__ __forceinline__ void bf16_chunk(const uint8_t* stage, const uint32_t 
 struct MergeArgs {
   const int2* unit_slots; int32_t* unit_done;      // unit_done == nullptr: no fused merge
   float* fold_m; float* fold_l; float* fold_o;     // fold_m != nullptr: fold the unit's segments to one triple instead of merging
+  // Sequence split with the exchange fused into the fold (peers != nullptr): the folded triple goes straight into the
+  // exchange buffer of every GPU of the group by peer stores, followed by a flag.  See SplitExchange below.
+  float* const* peers; int world, rank, units; int64_t rank_stride; int32_t* epoch;
   const float* vstat; const float* kstat;
   __nv_bfloat16* ktail; __nv_bfloat16* vtail; int64_t tsu, tst;
   const __nv_bfloat16* kcur; const __nv_bfloat16* vcur; int64_t csb, csh;
@@ -311,6 +314,25 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
   }
 }
 
+// ---- exchange of folded triples between the GPUs of a sequence-split group, over peer memory ----------------------
+// Every GPU owns one exchange buffer of the same layout, mapped into all the others (symmetric memory):
+//   float data[2][world][rank_stride]   parity of the step's epoch, source rank, then that rank's [m | l | o] block
+//                                       (m, l: [units][8]; o: [units][8][128]; rank_stride = units * 8 * 130)
+//   int   flag[world][units]            the last epoch for which source rank's triple of the unit is complete
+// A unit's epoch counts the decode steps: the folding CTA keeps it in `epoch[unit]` (local memory), the merging CTA in
+// its own counter; both advance by one per step on every GPU.  The producer writes the triple into block
+// [epoch & 1][its rank] of EVERY GPU's buffer (plain stores through NVLink), fences, and then stores the epoch into
+// flag[its rank][unit] there.  The consumer (the merge kernel's CTA of that unit) waits, with a time limit, until the
+// flags of all source ranks have reached its epoch and reads the parity's blocks from its own buffer.  Two parities
+// are enough: a GPU cannot fold step e+1 before its own merge of step e is done, which needed every other GPU's fold of
+// step e, which came after that GPU's merge of step e-1.
+__device__ __forceinline__ int32_t load_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int64_t exchange_flag_offset(int world, int64_t rank_stride) { return 2 * (int64_t)world * rank_stride; }
+
 // Fold of one unit by the consumer warps of the CTA that finished the unit's last segment: one (m, l, o) per
 // Q head from the unit's segment partials, written at [unit][MaxGroup] of the fold buffers.  Used when a unit's
 // tile range is split across GPUs: the folded triples are what the ranks exchange.  Same arithmetic and order as
@@ -318,20 +340,72 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
 __device__ __forceinline__ void fold_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
     int unit, int g) {
   const int2 sl = a.unit_slots[unit];
-  for (int e = threadIdx.x; e < g * D; e += ConsumerWarps * 32) {
-    const int r = e / D, ch = e % D;
+  // One item = (Q head r, 4 channels).  The partials come from other CTAs (read past L1); a segment's three loads
+  // depend on nothing but the segment number, so they are issued four segments at a time and the latency of the
+  // second-level cache is paid once per batch instead of once per segment.  The sums run in segment order.
+  for (int e = threadIdx.x; e < g * (D / 4); e += ConsumerWarps * 32) {
+    const int r = e / (D / 4), ch = (e % (D / 4)) * 4;
+    const float* m0 = pm + (int64_t)sl.x * MaxGroup + r;
+    const float* l0 = pl + (int64_t)sl.x * MaxGroup + r;
+    const float* o0 = po + ((int64_t)sl.x * MaxGroup + r) * D + ch;
     float big = -FLT_MAX;
-    for (int s = 0; s < sl.y; ++s) big = fmaxf(big, __ldcg(pm + (int64_t)(sl.x + s) * MaxGroup + r));
-    float o = 0.f, l = 0.f;
-    for (int s = 0; s < sl.y; ++s) {
-      const int64_t idx = (int64_t)(sl.x + s) * MaxGroup + r;
-      const float w = exp2f(__ldcg(pm + idx) - big);
-      o = fmaf(__ldcg(po + idx * D + ch), w, o);
-      l = fmaf(__ldcg(pl + idx), w, l);
+    for (int s0 = 0; s0 < sl.y; s0 += 4) {
+      float m[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) m[u] = s0 + u < sl.y ? __ldcg(m0 + (int64_t)(s0 + u) * MaxGroup) : -FLT_MAX;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) big = fmaxf(big, m[u]);
+    }
+    float o[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+    for (int s0 = 0; s0 < sl.y; s0 += 4) {
+      float m[4], pl4[4];
+      float4 p[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool on = s0 + u < sl.y;
+        m[u] = on ? __ldcg(m0 + (int64_t)(s0 + u) * MaxGroup) : -FLT_MAX;
+        pl4[u] = on ? __ldcg(l0 + (int64_t)(s0 + u) * MaxGroup) : 0.f;
+        p[u] = on ? __ldcg(reinterpret_cast<const float4*>(o0 + (int64_t)(s0 + u) * MaxGroup * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < sl.y) {
+          const float w = exp2f(m[u] - big);
+          o[0] = fmaf(p[u].x, w, o[0]); o[1] = fmaf(p[u].y, w, o[1]); o[2] = fmaf(p[u].z, w, o[2]); o[3] = fmaf(p[u].w, w, o[3]);
+          l = fmaf(pl4[u], w, l);
+        }
+      }
     }
     const int64_t dst = (int64_t)unit * MaxGroup + r;
-    a.fold_o[dst * D + ch] = o;
-    if (ch == 0) { a.fold_m[dst] = big; a.fold_l[dst] = l; }
+    if (a.peers == nullptr) {
+      *reinterpret_cast<float4*>(a.fold_o + dst * D + ch) = make_float4(o[0], o[1], o[2], o[3]);
+      if (ch == 0) { a.fold_m[dst] = big; a.fold_l[dst] = l; }
+    } else {
+      // straight into every GPU's exchange buffer: block [parity of this unit's next epoch][this rank]
+      const int parity = (a.epoch[unit] + 1) & 1;
+      const int64_t ug = (int64_t)a.units * MaxGroup;
+      const int64_t block = ((int64_t)parity * a.world + a.rank) * a.rank_stride;
+      for (int p = 0; p < a.world; ++p) {
+        float* base = a.peers[p] + block;
+        *reinterpret_cast<float4*>(base + 2 * ug + dst * D + ch) = make_float4(o[0], o[1], o[2], o[3]);
+        if (ch == 0) { base[dst] = big; base[ug + dst] = l; }
+      }
+    }
+  }
+  if (a.peers != nullptr) {
+    // All threads' peer stores, then the barrier, then ONE system-wide fence by the thread that raises the flags: the
+    // fence is cumulative over what the barrier made visible to that thread (the pattern of a grid-wide barrier), so a
+    // GPU that sees the flag sees the triple; one NVLink round trip instead of one per thread and per flag.
+    consumer_sync();
+    if (threadIdx.x == 0) {
+      const int e = a.epoch[unit] + 1;
+      a.epoch[unit] = e;
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p) {
+        volatile int32_t* flags = reinterpret_cast<volatile int32_t*>(a.peers[p] + exchange_flag_offset(a.world, a.rank_stride));
+        flags[(int64_t)a.rank * a.units + unit] = e;
+      }
+    }
   }
 }
 
@@ -530,7 +604,7 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
           const int2 sl = margs.unit_slots[unit];
           if (sl.x < 0 || sl.y < 0 || sl.x + sl.y > slot_limit) {
             if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
-          } else if (margs.fold_m != nullptr) {
+          } else if (margs.fold_m != nullptr || margs.peers != nullptr) {
             fold_unit_by_consumers(margs, pm, pl, po, unit, g);
           } else {
             merge_unit_by_consumers(margs, pm, pl, po, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);

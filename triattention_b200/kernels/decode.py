@@ -136,7 +136,7 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
 
 class DecodeCache:
     def __init__(self, module, max_tail=256, ctas=None, tile_costs=TILE_COSTS, split_group=None, fused_merge=False,
-                 fold_tail=0, split=None):
+                 fold_tail=0, split=None, exchange="nccl"):
         """fold_tail: 0 keeps the reference's behaviour (generated tokens stay in a BF16 tail of at most max_tail
         <= 1024 rows).  N > 0 lifts that cap: room for N generated tokens is reserved behind every unit's stream, and
         each time 64 tokens have gathered in the tail they are quantised with the prompt's statistics into one more
@@ -151,12 +151,20 @@ class DecodeCache:
         (long-context decode): each rank streams its part, the folded (m, l, o) triples are all-gathered over
         NCCL and every rank runs the final merge.  None = this process holds whole units.
         split = (rank, world) without a process group: this cache holds that part of every unit and the caller moves
-        the folded triples itself (`partials`, `merge_gathered`)."""
+        the folded triples itself (`partials`, `merge_gathered`).
+        exchange: how the ranks of a split group exchange the triples.  "nccl" = one all_gather_into_tensor per step.
+        "peer" = no collective call at all: the split pass writes every folded triple straight into the exchange buffer
+        of every GPU of the group (symmetric memory, plain peer stores over NVLink, then a flag) and each merge CTA
+        waits, with a time limit, for the flags of its unit — compute and collective in one kernel.  Every rank must
+        then make the same sequence of calls."""
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
         self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
         self.split_group, self.split, self.fused_merge = split_group, None if split is None else tuple(split), bool(fused_merge)
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.exchange = exchange
         self.reserve, self.generated, self.fold_buffers = -(-int(fold_tail) // FOLD_KEYS), 0, {}
         if self.reserve and (split_group is not None or split is not None or max_tail < FOLD_KEYS):
             raise ValueError("fold_tail needs max_tail >= 64 and no split_group")
@@ -241,6 +249,8 @@ class DecodeCache:
                              gm=every[0, :ug], gl=every[0, ug:2 * ug], go=every[0, 2 * ug:],
                              rank_slots=torch.stack([torch.arange(units, dtype=torch.int32),
                                                      torch.full((units,), world, dtype=torch.int32)], 1).to(device))
+                if self.exchange == "peer":
+                    self._exchange_setup(entry, bands, heads_kv, prompt, batch, bf16_kv, device)
         lo, n = first_sequence * heads_kv, part * heads_kv        # this call's units
         entry["kstat"][lo:lo + n] = ops["kstat"].view(n, 3, 128)
         entry["vstat"][lo:lo + n] = ops["vstat"].view(n, 3, 128)
@@ -262,6 +272,42 @@ class DecodeCache:
             ident = torch.tensor([0.0, 1.0, 1.0], device=device)[None, :, None]
             entry["kstat"][mine.long()] = ident
             entry["vstat"][mine.long()] = ident
+
+    def _exchange_setup(self, entry, bands, heads_kv, prompt, batch, bf16_kv, device):
+        """Buffers of the peer-memory exchange (layout: csrc/decode_kernel.cuh): this rank's exchange buffer, mapped into
+        every process of the group through torch's symmetric memory, the table of which rank holds tiles of which unit,
+        and the per-unit step counters of the producer (epoch) and the consumer (seen)."""
+        rank, world = self.split
+        units, ug = batch * heads_kv, batch * heads_kv * MAX_GROUP
+        stride, words = ug * 130, 2 * world * ug * 130 + world * units
+        present = np.stack([plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
+                                         tile_costs=self.tile_costs, split=(r, world))["unit_slots"][:, 1] > 0
+                            for r in range(world)]).astype(np.int32)
+        handle = None
+        if self.split_group is not None:
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty(words, dtype=torch.float32, device=device)
+        else:
+            buf = torch.empty(words, dtype=torch.float32, device=device)
+        data = buf[:2 * world * stride].view(2, world, stride)
+        data[:, :, :ug] = torch.finfo(torch.float32).min      # m of every (rank, unit, head): nothing delivered yet
+        data[:, :, ug:] = 0
+        buf[2 * world * stride:] = 0                          # flags
+        peers = None
+        if self.split_group is not None:
+            handle = symm.rendezvous(buf, self.split_group)
+            torch.cuda.synchronize(device)
+            handle.barrier()                                   # every rank's buffer is initialised before anyone writes
+            peers = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=device)
+        entry.update(xbuf=buf, xhandle=handle, peers=peers, present=torch.from_numpy(present).to(device),
+                     seen=torch.zeros(units, dtype=torch.int32, device=device),
+                     epoch=torch.zeros(units, dtype=torch.int32, device=device))
+
+    def attach_peers(self, layer, buffers):
+        """exchange="peer" without a process group (several parts held by one process, e.g. in a test): the exchange
+        buffers of all parts, in rank order."""
+        e = self.layers[layer]
+        e["peers"] = torch.tensor([b.data_ptr() for b in buffers], dtype=torch.int64, device=e["xbuf"].device)
 
     def fold(self, layer):
         """Quantise the first 64 rows of the layer's tail into one more tile of every unit's stream."""
@@ -312,9 +358,10 @@ class DecodeCache:
             return out
         # sequence split: one launch streams this rank's tiles and folds every unit to one triple per Q head, one
         # all-gather moves the triples over NVLink, and the merge reads the gathered [rank][m | l | o] buffer in place
-        import torch.distributed as dist
         self.partials(layer, q, k, scale)
-        dist.all_gather_into_tensor(e["gathered"], e["folded"][None], group=self.split_group)
+        if self.exchange == "nccl":
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(e["gathered"], e["folded"][None], group=self.split_group)
         return self.merge_gathered(layer, q, k, v, scale, out)
 
     def partials(self, layer, q, k, scale):
@@ -322,15 +369,22 @@ class DecodeCache:
         unit and Q head), which the ranks exchange."""
         e = self.layers[layer]
         d = e["dev"]
+        peer = self.exchange == "peer"
         self.module.decode_partials(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
-                                    d["cta_segments"], d["unit_slots"], e["pm"], e["pl"], e["po"], e["unit_done"], e["fm"],
-                                    e["fl"], e["fo"], k.shape[1], e["prompt"], scale)
+                                    d["cta_segments"], d["unit_slots"], e["pm"], e["pl"], e["po"], e["unit_done"],
+                                    None if peer else e["fm"], None if peer else e["fl"], None if peer else e["fo"],
+                                    k.shape[1], e["prompt"], scale, peers=e["peers"] if peer else None, rank=self.split[0],
+                                    epoch=e["epoch"] if peer else None)
         return e["folded"]
 
     def merge_gathered(self, layer, q, k, v, scale, out=None):
         """Sequence split, after the exchange: merges the layer's `gathered` buffer ([rank][m | l | o]) with the tail."""
         e = self.layers[layer]
         out = torch.empty_like(q) if out is None else out
+        if self.exchange == "peer":      # waits per unit for the triples the peers' split passes deliver
+            return self.module.decode_merge(q, None, None, None, 0, e["rank_slots"], e["kstat"], e["vstat"], e["tail_k"],
+                                            e["tail_v"], k, v, self.step, out, scale, exchange=e["xbuf"],
+                                            present=e["present"], seen=e["seen"], world=self.split[1])
         return self.module.decode_merge(q, e["gm"], e["gl"], e["go"], e["rank_stride"], e["rank_slots"], e["kstat"],
                                         e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, scale)
 

@@ -33,9 +33,10 @@ SIGNATURES = {
     "tri_decode_static": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P,
                           _L, _L, _I, _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_fold": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
-    "tri_decode_partials": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D, _P, _P],
-    "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L, _I, _I, _I, _I,
-                         _D, _P, _P],
+    "tri_decode_partials": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P,
+                            _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
+                         _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_abi_version": [],
@@ -292,28 +293,41 @@ class Module:
                                                  _stream()))
 
     def decode_partials(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, pm, pl, po,
-                        unit_done, fm, fl, fo, heads_kv, prompt, scale):
-        """This GPU's part of a sequence-split decode step: split pass + in-kernel fold to one triple per (unit, Q head)."""
+                        unit_done, fm, fl, fo, heads_kv, prompt, scale, peers=None, rank=0, epoch=None):
+        """This GPU's part of a sequence-split decode step: split pass + in-kernel fold to one triple per (unit, Q head),
+        into fm / fl / fo, or (those None; peers = int64 device tensor of every rank's exchange-buffer address as mapped
+        here, epoch = int32 [units]) by peer stores into every GPU's exchange buffer."""
         if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1 and
-                unit_done.dtype == torch.int32 and fm.dtype == torch.float32 and fo.is_contiguous()):
+                unit_done.dtype == torch.int32):
             raise RuntimeError("decode geometry/buffers")
+        if peers is None:
+            if not (fm.dtype == torch.float32 and fo.is_contiguous()):
+                raise RuntimeError("decode geometry/buffers")
+        elif not (peers.dtype == torch.int64 and peers.is_cuda and epoch is not None and epoch.dtype == torch.int32 and
+                  epoch.numel() >= q.shape[0] * heads_kv and fm is None and fl is None and fo is None):
+            raise RuntimeError("decode_partials: exchange group")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_decode_partials(
                 q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
                 unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(), cta_segments.data_ptr(), cta_segments.numel() - 1,
-                unit_slots.data_ptr(), pm.data_ptr(), pl.data_ptr(), po.data_ptr(), unit_done.data_ptr(), fm.data_ptr(),
-                fl.data_ptr(), fo.data_ptr(), q.shape[0], q.shape[1], heads_kv, int(prompt), float(scale),
+                unit_slots.data_ptr(), pm.data_ptr(), pl.data_ptr(), po.data_ptr(), unit_done.data_ptr(), _ptr(fm),
+                _ptr(fl), _ptr(fo), _ptr(peers), 0 if peers is None else peers.numel(), int(rank), _ptr(epoch),
+                q.shape[0], q.shape[1], heads_kv, int(prompt), float(scale),
                 self.error_word(q.device).data_ptr(), _stream()))
 
-    def decode_merge(self, q, pm, pl, po, split_stride, unit_slots, kstat, vstat, tail_k, tail_v, kcur, vcur, step, out, scale):
-        """The merge alone, over partials that may lie strided (triples gathered from several GPUs, merged in place)."""
+    def decode_merge(self, q, pm, pl, po, split_stride, unit_slots, kstat, vstat, tail_k, tail_v, kcur, vcur, step, out, scale,
+                     exchange=None, present=None, seen=None, world=0):
+        """The merge alone, over partials that may lie strided (triples gathered from several GPUs, merged in place), or
+        (exchange = this rank's exchange buffer, present int32 [world, units], seen int32 [units]) over the triples that
+        the peer-memory exchange of decode_partials delivers, waiting for them per unit."""
         if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1 and
                 kcur.stride(3) == 1 and vcur.stride(0) == kcur.stride(0) and vcur.stride(1) == kcur.stride(1) and
                 tail_v.stride() == tail_k.stride() and out.stride(3) == 1 and step.dtype == torch.int64):
             raise RuntimeError("decode geometry/buffers")
         with torch.cuda.device(q.device):
             self._check(self.lib.tri_decode_merge(
-                q.data_ptr(), q.stride(0), q.stride(1), pm.data_ptr(), pl.data_ptr(), po.data_ptr(), int(split_stride),
+                q.data_ptr(), q.stride(0), q.stride(1), _ptr(pm), _ptr(pl), _ptr(po), int(split_stride),
+                _ptr(exchange), _ptr(present), _ptr(seen), int(world),
                 unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(), tail_k.data_ptr(), tail_v.data_ptr(),
                 tail_k.stride(0), tail_k.stride(1), kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
                 step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), q.shape[0], q.shape[1], kcur.shape[1],
