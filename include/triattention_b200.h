@@ -183,6 +183,25 @@ int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_stride_h, c
                         int batch, int heads_q, int heads_kv, int prompt, double scale,
                         int* device_error, void* stream);
 
+/* A whole decode step of a sequence-split group on this GPU as ONE kernel: the split pass over this rank's tiles, the
+ * fold of every unit to one triple, its delivery into every GPU's exchange buffer by peer stores (as
+ * tri_decode_partials with peer_buffers), and — in the CTA that delivered it — the wait for the other ranks' triples
+ * of that unit (at most one second, then device error 1) and the merge with the BF16 tail into `out`.  Compute step and
+ * collective are fused; no NCCL call and no second launch.  present int32 [world,U]: rank r holds tiles of unit u;
+ * every rank must hold tiles of every unit (otherwise use tri_decode_partials + tri_decode_merge, which also merge
+ * units this rank has no tiles of).  Other arguments as tri_decode / tri_decode_partials.
+ * No counterpart in the reference (single GPU). */
+int tri_decode_split(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
+                     const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments,
+                     const int32_t* cta_segments, int num_ctas, const int32_t* unit_slots, const float* kstat,
+                     const float* vstat, void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t,
+                     const void* kcur, const void* vcur, int64_t cur_stride_b, int64_t cur_stride_h,
+                     const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                     float* pm, float* pl, float* po, int32_t* unit_done,
+                     void* const* peer_buffers, int world, int rank, int32_t* epoch, const int32_t* present,
+                     int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale,
+                     int* device_error, void* stream);
+
 /* The merge of tri_decode alone, over partials that may lie strided: split s of unit u is read at
  * pm[(first*8 + r) + s*split_stride], pl likewise, po[(first*8 + r)*128 + ch + s*split_stride] with
  * (first, count) = unit_slots[u].  split_stride = 0 means the dense buffers of the split pass.  With

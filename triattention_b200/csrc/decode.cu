@@ -79,85 +79,13 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     kt[prior * tst + tid] = kc[tid];
     vt[prior * tst + tid] = vc[tid];
   }
-  // ---- tail scores for all heads of the group: one pass over the tail's K rows --------------------------
-  {
-    float qv[MaxGroup][4], kmean[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) kmean[i] = kstat[(int64_t)unit * StatFloats + lane * 4 + i];
-#pragma unroll
-    for (int r = 0; r < MaxGroup; ++r) {
-      const __nv_bfloat16* qrow = q + b * qsb + (int64_t)(kh * g + min(r, g - 1)) * qsh + lane * 4;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) qv[r][i] = __bfloat162float(qrow[i]);
-    }
-    for (int t = warp; t < tail; t += MergeWarps) {
-      const __nv_bfloat16* kv = (t < prior ? kt + t * tst : kc) + lane * 4;
-      float kd[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) kd[i] = __bfloat162float(kv[i]) - kmean[i];
-#pragma unroll
-      for (int r = 0; r < MaxGroup; ++r) {
-        if (r < g) {
-          float part = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) part = fmaf(qv[r][i], kd[i], part);
-#pragma unroll
-          for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-          if (lane == 0) ts[r][t] = part * sm_log2;
-        }
-      }
-    }
-  }
+  // tail scores for all heads of the group in one pass over the tail's K rows, then warp r merges Q head r
+  unit_tail_scores(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
+                   sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
   __syncthreads();
-  // ---- warp r merges Q head r ---------------------------------------------------------------------------
-  const int r = warp;
-  if (r >= g) return;
-  const int64_t first = (int64_t)sl.x * MaxGroup + r;
-  float m = -FLT_MAX;
-  for (int s = lane; s < sl.y; s += 32) m = fmaxf(m, pm[first + s * ml_stride]);
-  for (int t = lane; t < tail; t += 32) m = fmaxf(m, ts[r][t]);
-#pragma unroll
-  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  for (int t = lane; t < tail; t += 32) ts[r][t] = exp2f(ts[r][t] - m);
-  __syncwarp();
-  float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s0 = 0; s0 < sl.y; s0 += 4) {   // four splits' loads in flight at a time; the sums stay in split order
-    float pmv[4], plv[4];
-    float4 p[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const bool on = s0 + u < sl.y;
-      pmv[u] = on ? pm[first + (s0 + u) * ml_stride] : -FLT_MAX;
-      plv[u] = on ? pl[first + (s0 + u) * ml_stride] : 0.f;
-      p[u] = on ? *reinterpret_cast<const float4*>(po + first * D + (s0 + u) * o_stride + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (s0 + u < sl.y) {
-        const float w = exp2f(pmv[u] - m);
-        total = fmaf(plv[u], w, total);
-        acc[0] = fmaf(p[u].x, w, acc[0]); acc[1] = fmaf(p[u].y, w, acc[1]); acc[2] = fmaf(p[u].z, w, acc[2]); acc[3] = fmaf(p[u].w, w, acc[3]);
-      }
-    }
-  }
-  const float4 mean = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + lane * 4);
-  const float4 scale = *reinterpret_cast<const float4*>(vstat + (int64_t)unit * StatFloats + D + lane * 4);
-  acc[0] = acc[0] * scale.x + total * mean.x; acc[1] = acc[1] * scale.y + total * mean.y;
-  acc[2] = acc[2] * scale.z + total * mean.z; acc[3] = acc[3] * scale.w + total * mean.w;
-  for (int t = 0; t < tail; ++t) {
-    const float e = ts[r][t];
-    const uint2 raw = *reinterpret_cast<const uint2*>((t < prior ? vt + (int64_t)t * tst : vc) + lane * 4);
-    const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    total += e;
-    acc[0] = fmaf(e, v01.x, acc[0]); acc[1] = fmaf(e, v01.y, acc[1]); acc[2] = fmaf(e, v23.x, acc[2]); acc[3] = fmaf(e, v23.y, acc[3]);
-  }
-  const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc[0] / total, acc[1] / total);
-  const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc[2] / total, acc[3] / total);
-  uint2 packed;
-  packed.x = *reinterpret_cast<const uint32_t*>(&o01);
-  packed.y = *reinterpret_cast<const uint32_t*>(&o23);
-  *reinterpret_cast<uint2*>(out + b * osb + (int64_t)(kh * g + r) * osh + lane * 4) = packed;
+  if (warp < g)
+    merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
+                       vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
 }
 
 
@@ -378,6 +306,27 @@ extern "C" int tri_decode_partials(const void* q, int64_t q_stride_b, int64_t q_
   }
   TRI_CUDA(launch_split(call, pm, pl, po, NoSlotLimit, 0, margs, static_cast<cudaStream_t>(stream), true), "decode_partials");
   return tri_launch_status("decode_partials");
+}
+
+extern "C" int tri_decode_split(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* pool, const int64_t* unit_base,
+    const int32_t* unit_tab, const int32_t* unit_flags, const int32_t* tmeta, const int32_t* segments, const int32_t* cta_segments,
+    int num_ctas, const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k, void* tail_v,
+    int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b,
+    int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, float* pm, float* pl,
+    float* po, int32_t* unit_done, void* const* peer_buffers, int world, int rank, int32_t* epoch, const int32_t* present,
+    int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale, int* device_error, void* stream) {
+  TRI_DECODE_COMMON_CHECKS("decode_split");
+  TRI_CHECK(pool && unit_base && unit_tab && unit_flags && tmeta && segments && cta_segments && pm && pl && po && unit_done &&
+            peer_buffers && epoch && present && num_ctas > 0, "decode_split: null buffers");
+  TRI_CHECK(aligned16(pool) && aligned16(po) && world >= 1 && world <= 64 && rank >= 0 && rank < world, "decode_split: exchange group");
+  if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
+  const DecodeCall call = TRI_DECODE_CALL();
+  MergeArgs margs = fused_merge_args(call, unit_done);
+  margs.peers = reinterpret_cast<float* const*>(peer_buffers); margs.world = world; margs.rank = rank;
+  margs.units = batch * heads_kv; margs.rank_stride = (int64_t)batch * heads_kv * MaxGroup * (D + 2); margs.epoch = epoch;
+  margs.present = present;
+  TRI_CUDA(launch_split(call, pm, pl, po, NoSlotLimit, 0, margs, static_cast<cudaStream_t>(stream), true), "decode_split");
+  return tri_launch_status("decode_split");
 }
 
 extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,

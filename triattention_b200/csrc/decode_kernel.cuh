@@ -222,6 +222,9 @@ struct MergeArgs {
   // Sequence split with the exchange fused into the fold (peers != nullptr): the folded triple goes straight into the
   // exchange buffer of every GPU of the group by peer stores, followed by a flag.  See SplitExchange below.
   float* const* peers; int world, rank, units; int64_t rank_stride; int32_t* epoch;
+  // present != nullptr: the CTA that delivered a unit's triple also waits for the other ranks' triples of the unit and
+  // merges it (the whole sequence-split step is this one kernel); present[r * units + u] = rank r holds tiles of unit u.
+  const int32_t* present;
   const float* vstat; const float* kstat;
   __nv_bfloat16* ktail; __nv_bfloat16* vtail; int64_t tsu, tst;
   const __nv_bfloat16* kcur; const __nv_bfloat16* vcur; int64_t csb, csh;
@@ -229,24 +232,109 @@ struct MergeArgs {
   int max_tail;
 };
 
-// Merge of one unit by the consumer warps of the CTA that finished the unit's last segment:
-// decode_merge_kernel's arithmetic (common_device.cuh:373-469 of the reference) for the unit's g Q heads,
-// one after the other, with the fold buffer as scratch.  All ConsumerWarps*32 threads call it.
-// The partials come from other CTAs of the same launch, so they are read past L1 (ld.cg).
+// ---- merge of one unit: split partials + BF16 tail -> output rows of its Q heads ------------------------------------
+// Same arithmetic as decode_merge_kernel of the reference (common_device.cuh:373-469): tail scores q.(k - kmean) in fp32 on
+// the un-rotated rows, base-2 maximum over partials and tail, de-normalisation of the cached part (acc * vscale +
+// l * vmean), then the tail's exact P.V.  Shared by the stand-alone merge kernel (one CTA per unit) and by the decode
+// kernel's CTA that finishes a unit (merge fused into the split pass).
+
+// Tail scores of `nh` Q heads (rows qrows + i * qsh, i < nh) against the unit's tail, one pass over the tail's K rows:
+// the `warps` calling warps split the rows, a lane holds 4 features of the row and of each head's q.  ts[i * ts_stride + t].
+__device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int64_t qsh, int nh, const float* kmean_unit,
+    const __nv_bfloat16* kt, int64_t tst, const __nv_bfloat16* kc, int prior, int tail, float sm_log2, float* ts, int ts_stride,
+    int warp, int warps, int lane) {
+  float qv[MaxGroup][4], kmean[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) kmean[i] = kmean_unit[lane * 4 + i];
+#pragma unroll
+  for (int r = 0; r < MaxGroup; ++r) {
+    const __nv_bfloat16* qrow = qrows + (int64_t)min(r, nh - 1) * qsh + lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qv[r][i] = __bfloat162float(qrow[i]);
+  }
+  for (int t = warp; t < tail; t += warps) {
+    const __nv_bfloat16* kv = (t < prior ? kt + t * tst : kc) + lane * 4;
+    float kd[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) kd[i] = __bfloat162float(kv[i]) - kmean[i];
+#pragma unroll
+    for (int r = 0; r < MaxGroup; ++r) {
+      if (r < nh) {
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part = fmaf(qv[r][i], kd[i], part);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) ts[r * ts_stride + t] = part * sm_log2;
+      }
+    }
+  }
+}
+
+// One warp merges one Q head: nsplit partials at pm[first + s * ml_stride], pl likewise, po[first * 128 + s * o_stride + ch]
+// (a lane holds 4 of the 128 channels), the tail scores of the head in ts_row[0 .. tail) (turned into weights in place),
+// the tail's V rows, and writes the head's output row.  Partials are read past L1 (they may come from other CTAs of the
+// same launch or from other GPUs), four splits' loads in flight at a time; the sums run in split order.
+__device__ __forceinline__ void merge_head_by_warp(const float* pm, const float* pl, const float* po, int64_t first,
+    int64_t ml_stride, int64_t o_stride, int nsplit, float* ts_row, int tail, int prior, const __nv_bfloat16* vt, int64_t tst,
+    const __nv_bfloat16* vc, const float* vstat_unit, __nv_bfloat16* out_row, int lane) {
+  float m = -FLT_MAX;
+  for (int s = lane; s < nsplit; s += 32) m = fmaxf(m, __ldcg(pm + first + s * ml_stride));
+  for (int t = lane; t < tail; t += 32) m = fmaxf(m, ts_row[t]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  for (int t = lane; t < tail; t += 32) ts_row[t] = exp2f(ts_row[t] - m);
+  __syncwarp();
+  float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s0 = 0; s0 < nsplit; s0 += 4) {
+    float pmv[4], plv[4];
+    float4 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const bool on = s0 + u < nsplit;
+      pmv[u] = on ? __ldcg(pm + first + (s0 + u) * ml_stride) : -FLT_MAX;
+      plv[u] = on ? __ldcg(pl + first + (s0 + u) * ml_stride) : 0.f;
+      p[u] = on ? __ldcg(reinterpret_cast<const float4*>(po + first * D + (s0 + u) * o_stride + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (s0 + u < nsplit) {
+        const float w = exp2f(pmv[u] - m);
+        total = fmaf(plv[u], w, total);
+        acc[0] = fmaf(p[u].x, w, acc[0]); acc[1] = fmaf(p[u].y, w, acc[1]); acc[2] = fmaf(p[u].z, w, acc[2]); acc[3] = fmaf(p[u].w, w, acc[3]);
+      }
+    }
+  }
+  const float4 mean = *reinterpret_cast<const float4*>(vstat_unit + lane * 4);
+  const float4 scale = *reinterpret_cast<const float4*>(vstat_unit + D + lane * 4);
+  acc[0] = acc[0] * scale.x + total * mean.x; acc[1] = acc[1] * scale.y + total * mean.y;
+  acc[2] = acc[2] * scale.z + total * mean.z; acc[3] = acc[3] * scale.w + total * mean.w;
+  for (int t = 0; t < tail; ++t) {
+    const float e = ts_row[t];
+    const uint2 raw = *reinterpret_cast<const uint2*>((t < prior ? vt + (int64_t)t * tst : vc) + lane * 4);
+    const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    total += e;
+    acc[0] = fmaf(e, v01.x, acc[0]); acc[1] = fmaf(e, v01.y, acc[1]); acc[2] = fmaf(e, v23.x, acc[2]); acc[3] = fmaf(e, v23.y, acc[3]);
+  }
+  const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc[0] / total, acc[1] / total);
+  const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc[2] / total, acc[3] / total);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&o01);
+  packed.y = *reinterpret_cast<const uint32_t*>(&o23);
+  *reinterpret_cast<uint2*>(out_row + lane * 4) = packed;
+}
+
+// Merge of one unit by the consumer warps of the decode kernel's CTA that finished the unit's last segment, with the
+// CTA's fold buffer as scratch for the tail scores: up to ConsumerWarps Q heads per round, one warp per head.
+// All ConsumerWarps*32 threads call it.  Partials: split s of head r at pm[(first*8 + r) + s*ml_stride] (see
+// decode_merge_kernel).
 __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
-    const __nv_bfloat16* q, int64_t qsb, int64_t qsh, int unit, int heads_kv, int g, float sm_log2, float* scratch) {
-  constexpr int NT = ConsumerWarps * 32;
+    int64_t first_slot, int64_t ml_stride, int64_t o_stride, int nsplit, const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
+    int unit, int heads_kv, int g, float sm_log2, float* scratch) {
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   const int b = unit / heads_kv, kh = unit % heads_kv;
-  float* ts = scratch;                 // [1024] tail scores
-  float* ew = scratch + 1024;          // [1024] tail weights
-  float* wred = scratch + 2048;        // [ConsumerWarps] block reductions
-  float* wl = wred + ConsumerWarps;    // [ConsumerWarps]
-  float* wo = wl + ConsumerWarps + (16 - 2 * ConsumerWarps % 16) % 16;   // [ConsumerWarps][128], 16-float aligned
   const int prior = min((int)*a.step, a.max_tail - 1), tail = prior + 1;
-  const int2 sl = a.unit_slots[unit];
-  const float* mean = a.vstat + (int64_t)unit * StatFloats;
-  const float* scale = mean + D;
   const __nv_bfloat16* kc = a.kcur + b * a.csb + kh * a.csh;
   const __nv_bfloat16* vc = a.vcur + b * a.csb + kh * a.csh;
   __nv_bfloat16* kt = a.ktail + unit * a.tsu;
@@ -255,62 +343,18 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
     kt[prior * a.tst + tid] = kc[tid];
     vt[prior * a.tst + tid] = vc[tid];
   }
-  float kmean[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) kmean[i] = a.kstat[(int64_t)unit * StatFloats + lane * 4 + i];
-  for (int r = 0; r < g; ++r) {
-    const int hq = kh * g + r;
-    const __nv_bfloat16* qrow = q + b * qsb + hq * qsh;
-    float qv[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qv[i] = __bfloat162float(qrow[lane * 4 + i]);
-    for (int t = warp; t < tail; t += ConsumerWarps) {
-      const __nv_bfloat16* kv = t < prior ? kt + t * a.tst : kc;
-      float part = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) part = fmaf(qv[i], __bfloat162float(kv[lane * 4 + i]) - kmean[i], part);
-#pragma unroll
-      for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-      if (lane == 0) ts[t] = part * sm_log2;
-    }
+  const int per_round = min(min(g, ConsumerWarps), (ConsumerWarps * CombFloats) / tail);   // >= 6 for tails up to 1024 rows
+  for (int h0 = 0; h0 < g; h0 += per_round) {
+    const int nh = min(per_round, g - h0);
+    const __nv_bfloat16* qrows = q + b * qsb + (int64_t)(kh * g + h0) * qsh;
+    unit_tail_scores(qrows, qsh, nh, a.kstat + (int64_t)unit * StatFloats, kt, a.tst, kc, prior, tail, sm_log2, scratch, tail,
+                     warp, ConsumerWarps, lane);
     consumer_sync();
-    float m = -FLT_MAX;
-    for (int s = tid; s < sl.y; s += NT) m = fmaxf(m, __ldcg(pm + (int64_t)(sl.x + s) * MaxGroup + r));
-    for (int t = tid; t < tail; t += NT) m = fmaxf(m, ts[t]);
-#pragma unroll
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) wred[warp] = m;
-    consumer_sync();
-    m = wred[0];
-#pragma unroll
-    for (int w = 1; w < ConsumerWarps; ++w) m = fmaxf(m, wred[w]);
-    for (int t = tid; t < tail; t += NT) ew[t] = exp2f(ts[t] - m);
-    float l = 0.f, o4[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = warp; s < sl.y; s += ConsumerWarps) {
-      const int64_t idx = (int64_t)(sl.x + s) * MaxGroup + r;
-      const float w = exp2f(__ldcg(pm + idx) - m);
-      l = fmaf(__ldcg(pl + idx), w, l);
-      const float4 p = __ldcg(reinterpret_cast<const float4*>(po + idx * D + lane * 4));
-      o4[0] = fmaf(p.x, w, o4[0]); o4[1] = fmaf(p.y, w, o4[1]); o4[2] = fmaf(p.z, w, o4[2]); o4[3] = fmaf(p.w, w, o4[3]);
-    }
-    if (lane == 0) wl[warp] = l;
-    *reinterpret_cast<float4*>(&wo[warp * D + lane * 4]) = make_float4(o4[0], o4[1], o4[2], o4[3]);
-    consumer_sync();
-    if (tid < D) {
-      float total = 0.f, acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < ConsumerWarps; ++w) { total += wl[w]; acc += wo[w * D + tid]; }
-      acc = acc * scale[tid] + total * mean[tid];
-      for (int t = 0; t < prior; ++t) {
-        const float e = ew[t];
-        total += e;
-        acc = fmaf(e, __bfloat162float(vt[(int64_t)t * a.tst + tid]), acc);
-      }
-      total += ew[prior];
-      acc = fmaf(ew[prior], __bfloat162float(vc[tid]), acc);
-      a.out[b * a.osb + hq * a.osh + tid] = __float2bfloat16(acc / total);
-    }
-    consumer_sync();   // scratch is reused by the next Q head
+    if (warp < nh)
+      merge_head_by_warp(pm, pl, po, first_slot * MaxGroup + h0 + warp, ml_stride, o_stride, nsplit, scratch + warp * tail, tail,
+                         prior, vt, a.tst, vc, a.vstat + (int64_t)unit * StatFloats,
+                         a.out + b * a.osb + (int64_t)(kh * g + h0 + warp) * a.osh, lane);
+    consumer_sync();   // scratch is reused by the next round (and by the next segment's fold)
   }
 }
 
@@ -606,8 +650,35 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
             if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
           } else if (margs.fold_m != nullptr || margs.peers != nullptr) {
             fold_unit_by_consumers(margs, pm, pl, po, unit, g);
+            if (margs.peers != nullptr && margs.present != nullptr) {
+              // This GPU's triple of the unit is on its way to every GPU of the group.  Wait (at most one second) for
+              // theirs, then merge the unit here: the exchange and the merge cost no further launch.  The producer warp
+              // keeps prefetching this CTA's next tiles meanwhile.
+              if (tid == 0) merge_flag = 0;
+              consumer_sync();                      // (also makes epoch[unit], just advanced by thread 0, visible)
+              const int e = margs.epoch[unit];
+              float* local = margs.peers[margs.rank];
+              if (tid < margs.world && tid != margs.rank && margs.present[(int64_t)tid * margs.units + unit]) {
+                const int32_t* flag = reinterpret_cast<const int32_t*>(local + exchange_flag_offset(margs.world, margs.rank_stride)) +
+                                      (int64_t)tid * margs.units + unit;
+                const uint64_t t_wait = globaltimer_ns();
+                while (load_acquire_sys(flag) < e) {
+                  if (globaltimer_ns() - t_wait > 1000000000ull) { merge_flag = 1; break; }
+                }
+              }
+              consumer_sync();
+              if (merge_flag) {
+                if (tid == 0) atomicCAS(err, ErrNone, ErrBarrierTimeout);
+              } else {
+                const float* block = local + (int64_t)(e & 1) * margs.world * margs.rank_stride;
+                const int64_t ug = (int64_t)margs.units * MaxGroup;
+                merge_unit_by_consumers(margs, block, block + ug, block + 2 * ug, unit, margs.rank_stride, margs.rank_stride,
+                                        margs.world, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+              }
+            }
           } else {
-            merge_unit_by_consumers(margs, pm, pl, po, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+            merge_unit_by_consumers(margs, pm, pl, po, sl.x, MaxGroup, (int64_t)MaxGroup * D, sl.y, q, qsb, qsh, unit, heads_kv, g,
+                                    sm_log2, comb);
           }
         }
       }

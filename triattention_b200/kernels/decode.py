@@ -300,6 +300,7 @@ class DecodeCache:
             handle.barrier()                                   # every rank's buffer is initialised before anyone writes
             peers = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=device)
         entry.update(xbuf=buf, xhandle=handle, peers=peers, present=torch.from_numpy(present).to(device),
+                     all_present=bool(present.all()),
                      seen=torch.zeros(units, dtype=torch.int32, device=device),
                      epoch=torch.zeros(units, dtype=torch.int32, device=device))
 
@@ -358,6 +359,12 @@ class DecodeCache:
             return out
         # sequence split: one launch streams this rank's tiles and folds every unit to one triple per Q head, one
         # all-gather moves the triples over NVLink, and the merge reads the gathered [rank][m | l | o] buffer in place
+        if self.exchange == "peer" and e["all_present"] and self.split_group is not None:
+            # compute and collective in one kernel: the CTA that delivers a unit's triple waits for the peers' and merges
+            return self.module.decode_split(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
+                                            d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"],
+                                            k, v, self.step, out, e["pm"], e["pl"], e["po"], e["unit_done"], e["peers"],
+                                            self.split[0], e["epoch"], e["present"], e["prompt"], scale)
         self.partials(layer, q, k, scale)
         if self.exchange == "nccl":
             import torch.distributed as dist

@@ -35,6 +35,8 @@ SIGNATURES = {
     "tri_decode_fold": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     "tri_decode_partials": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P,
                             _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_split": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
+                         _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
                          _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_occupancy": [],
@@ -314,6 +316,28 @@ class Module:
                 _ptr(fl), _ptr(fo), _ptr(peers), 0 if peers is None else peers.numel(), int(rank), _ptr(epoch),
                 q.shape[0], q.shape[1], heads_kv, int(prompt), float(scale),
                 self.error_word(q.device).data_ptr(), _stream()))
+
+    def decode_split(self, q, pool, unit_base, unit_tab, unit_flags, tmeta, segments, cta_segments, unit_slots, kstat, vstat,
+                     tail_k, tail_v, kcur, vcur, step, out, pm, pl, po, unit_done, peers, rank, epoch, present, prompt, scale):
+        """A whole sequence-split decode step on this GPU as one kernel: split pass, fold, delivery of the triples into every
+        GPU's exchange buffer, wait for the others' and merge.  Buffers as decode / decode_partials."""
+        if not (q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[2] == 1 and q.shape[3] == 128 and q.stride(3) == 1 and
+                kcur.stride(3) == 1 and vcur.stride(0) == kcur.stride(0) and vcur.stride(1) == kcur.stride(1) and
+                tail_v.stride() == tail_k.stride() and out.stride(3) == 1 and step.dtype == torch.int64 and
+                peers.dtype == torch.int64 and epoch.dtype == torch.int32 and present.dtype == torch.int32 and
+                present.numel() == peers.numel() * q.shape[0] * kcur.shape[1]):
+            raise RuntimeError("decode geometry/buffers")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_decode_split(
+                q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), unit_base.data_ptr(), unit_tab.data_ptr(),
+                unit_flags.data_ptr(), tmeta.data_ptr(), segments.data_ptr(), cta_segments.data_ptr(), cta_segments.numel() - 1,
+                unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(), tail_k.data_ptr(), tail_v.data_ptr(),
+                tail_k.stride(0), tail_k.stride(1), kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
+                step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), pm.data_ptr(), pl.data_ptr(), po.data_ptr(),
+                unit_done.data_ptr(), peers.data_ptr(), peers.numel(), int(rank), epoch.data_ptr(), present.data_ptr(),
+                q.shape[0], q.shape[1], kcur.shape[1], int(prompt), tail_k.shape[1], float(scale),
+                self.error_word(q.device).data_ptr(), _stream()))
+        return out
 
     def decode_merge(self, q, pm, pl, po, split_stride, unit_slots, kstat, vstat, tail_k, tail_v, kcur, vcur, step, out, scale,
                      exchange=None, present=None, seen=None, world=0):
