@@ -110,25 +110,46 @@ def plan_streams(bands, heads_kv, prompt, batch, bf16_kv=(), ctas=148, tile_cost
     unit_cost = np.array([ccum[kh][-1] for kh in kh_of], np.float64)
     unit_start = np.concatenate([[0.0], np.cumsum(unit_cost)])
     share = max(unit_start[-1] / ctas, 1.0)
-    segments, seg_cta, unit_slots = [], [], []
-    for u in range(units):
-        kh, n, lo = kh_of[u], count[kh_of[u]], unit_start[u]
-        c0, c1 = int(lo // share), int(min(ctas - 1, (unit_start[u + 1] - 1e-6) // share))
-        cuts = np.searchsorted(ccum[kh], (np.arange(c0 + 1, c1 + 1) * share) - lo, side="left") if c1 > c0 else np.zeros(0, np.int64)
-        edges = np.concatenate([[0], np.clip(cuts, 0, n), [n]]).astype(np.int64)
-        first_slot = len(segments)
-        for i, (a, e) in enumerate(zip(edges[:-1], edges[1:])):
-            if e > a:
-                segments.append((u, int(a), int(e - a), len(segments)))
-                seg_cta.append(min(ctas - 1, c0 + i))
-        unit_slots.append((first_slot, len(segments) - first_slot))
+    # All units at once (no Python loop per unit: a per-layer map means one plan per layer, on the path of the first
+    # prompt).  Unit u spans CTAs c0[u] .. c1[u]; its cut before CTA k is where its cumulative cost reaches k * share.
+    # Units of one KV head share the cost prefix sums, so the cuts are one searchsorted per head.
+    n_of = np.asarray(count, np.int64)[kh_of]
+    lo, hi = unit_start[:-1], unit_start[1:]
+    c0 = np.floor_divide(lo, share).astype(np.int64)
+    c1 = np.minimum(ctas - 1, np.floor_divide(hi - 1e-6, share)).astype(np.int64)
+    ncut = np.maximum(c1 - c0, 0)
+    unit_of = np.repeat(np.arange(units), ncut)
+    within = np.arange(int(ncut.sum())) - np.repeat(np.cumsum(ncut) - ncut, ncut)
+    target = (c0[unit_of] + 1 + within) * share - lo[unit_of]
+    cuts = np.zeros(len(unit_of), np.int64)
+    for kh in range(heads_kv):
+        sel = kh_of[unit_of] == kh
+        if sel.any():
+            cuts[sel] = np.searchsorted(ccum[kh], target[sel], side="left")
+    cuts = np.clip(cuts, 0, n_of[unit_of])
+    ecount = ncut + 2                                   # edges of a unit: 0, its cuts, n
+    eoff = np.cumsum(ecount) - ecount
+    edges = np.zeros(int(ecount.sum()), np.int64)
+    edges[eoff + ecount - 1] = n_of
+    edges[eoff[unit_of] + 1 + within] = cuts
+    inner = np.ones(len(edges), bool)
+    inner[eoff + ecount - 1] = False                    # an interval starts at every edge but a unit's last
+    begin, end = edges[inner], edges[1:][inner[:-1]]
+    unit_iv = np.repeat(np.arange(units), ecount - 1)   # unit and number of every interval
+    index_iv = np.arange(len(begin)) - np.repeat(np.cumsum(ecount - 1) - (ecount - 1), ecount - 1)
+    keep = end > begin
+    nseg = int(keep.sum())
+    segments = np.stack([unit_iv[keep], begin[keep], end[keep] - begin[keep], np.arange(nseg)], 1)
+    seg_cta = np.minimum(ctas - 1, c0[unit_iv[keep]] + index_iv[keep])
+    per_unit = np.bincount(unit_iv[keep], minlength=units)
+    unit_slots = np.stack([np.cumsum(per_unit) - per_unit, per_unit], 1)
     seg_cta = np.asarray(seg_cta, np.int64)
     cta_segments = np.searchsorted(seg_cta, np.arange(ctas + 1), side="left").astype(np.int32)
     return dict(tmeta=tmeta, tab_begin=np.asarray(tab_begin, np.int32), count=np.asarray(count, np.int32),
                 head_bytes=np.asarray(head_bytes, np.int64), unit_base=unit_base,
                 unit_tab=np.asarray(tab_begin, np.int32)[kh_of], unit_count=np.asarray(count, np.int32)[kh_of],
                 unit_flags=unit_flags, segments=np.asarray(segments, np.int32).reshape(-1, 4), cta_segments=cta_segments,
-                unit_slots=np.asarray(unit_slots, np.int32).reshape(-1, 2), slots=len(segments),
+                unit_slots=np.asarray(unit_slots, np.int32).reshape(-1, 2), slots=nseg,
                 append_off=np.asarray(append_off, np.int64),
                 pool_bytes=int(batch * seq_bytes), seq_bytes=seq_bytes, tiles=tiles, bf16_range=bf16_range,
                 payload_bytes=int(batch * sum(int(s.sum()) for s in sizes)))
@@ -160,7 +181,8 @@ class DecodeCache:
         if not 1 <= max_tail <= 1024:
             raise ValueError("max_tail must be in 1..1024")
         self.module, self.max_tail, self.ctas, self.tile_costs = module, max_tail, ctas, tuple(tile_costs)
-        self.layers, self.formats, self.plans, self.step = {}, {}, {}, None
+        self.layers, self.formats, self.plans, self.step, self.plan_seconds = {}, {}, {}, None, 0.0
+        self._staging, self._staged = None, 0
         self.split_group, self.split, self.fused_merge = split_group, None if split is None else tuple(split), bool(fused_merge)
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
@@ -196,15 +218,47 @@ class DecodeCache:
     def plan(self, bands, heads_kv, prompt, batch, bf16_kv, device, extra=0):
         key = (np.asarray(bands).tobytes(), heads_kv, prompt, batch, tuple(bf16_kv), str(device), self.split, extra)
         if key not in self.plans:
+            import time
+            t0 = time.perf_counter()
             host = plan_streams(np.asarray(bands), heads_kv, prompt, batch, bf16_kv, ctas=self.wave(device),
                                 tile_costs=self.tile_costs, split=self.split, extra=extra, reserve=self.reserve)
-            dev = {name: torch.from_numpy(host[name]).to(device) for name in
-                   ("tmeta", "unit_base", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
+            # every int32 table in ONE host-to-device copy (a per-layer map makes one plan per layer), 16-byte aligned parts
+            parts = {name: np.ascontiguousarray(host[name], np.int32) for name in
+                     ("tmeta", "unit_tab", "unit_count", "unit_flags", "segments", "cta_segments", "unit_slots")}
             if bf16_kv:
-                units = np.nonzero(host["unit_flags"])[0].astype(np.int32)
-                dev["bf16_units"] = torch.from_numpy(units).to(device)
+                parts["bf16_units"] = np.nonzero(host["unit_flags"])[0].astype(np.int32)
+            offsets, total = {}, 0
+            for name, arr in parts.items():
+                offsets[name] = total
+                total += -(-arr.size // 4) * 4
+            packed = np.zeros(max(total, 4), np.int32)
+            for name, arr in parts.items():
+                packed[offsets[name]:offsets[name] + arr.size] = arr.reshape(-1)
+            on_device = self._upload(packed, device)
+            dev = {name: on_device[offsets[name]:offsets[name] + arr.size].view(arr.shape) for name, arr in parts.items()}
+            dev["unit_base"] = self._upload(np.ascontiguousarray(host["unit_base"], np.int64), device)
             self.plans[key] = host, dev
+            self.plan_seconds += time.perf_counter() - t0      # host time spent planning and uploading (first use of a geometry)
         return self.plans[key]
+
+    def _upload(self, array, device):
+        """Host table -> device without stopping the host: the bytes go through a pinned staging area and an asynchronous
+        copy on the current stream, so planning layer n+1 overlaps the kernels of layer n (a pageable copy would wait for
+        everything queued on the stream).  The area is used front to back; when it is full the host waits once for the
+        copies still reading it and starts over."""
+        nbytes = array.nbytes
+        if self._staging is None or nbytes > self._staging.numel():
+            self._staging, self._staged = torch.empty(max(4 << 20, 2 * nbytes), dtype=torch.uint8, pin_memory=True), 0
+        if self._staged + nbytes > self._staging.numel():
+            torch.cuda.current_stream(device).synchronize()
+            self._staged = 0
+        start = self._staged
+        self._staged = -(-(start + nbytes) // 64) * 64
+        view = self._staging[start:start + nbytes]
+        view.numpy()[:] = array.reshape(-1).view(np.uint8)
+        out = torch.empty(array.shape, dtype=torch.from_numpy(array[:0]).dtype, device=device)
+        out.view(torch.uint8).view(-1).copy_(view, non_blocking=True)
+        return out
 
     def store(self, layer, prompt, ops, bands, k, v, bf16_kv=(), first_sequence=0, sequences=None):
         """Build the layer's cache streams from the prefill operands (one gather launch, plus one for BF16 units).
