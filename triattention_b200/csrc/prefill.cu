@@ -23,7 +23,7 @@
 namespace tri {
 
 // ---- shared-memory / tensor-memory plan of the prefill CTA ------------------------------------
-constexpr int RowSplit = 2;           // softmax threads per query row (1 or 2; measured on config 3: 4.47 ms with 2, 4.60 ms with 1)
+constexpr int RowSplit = 2;           // softmax threads per query row (1 or 2; measured on config 3: 4.84 ms with 2, 5.60 ms with 1)
 constexpr int PrefillThreads = (4 + 8 * RowSplit) * 32;   // producer, 2 QK^T issuers, P.V issuer, 8 * RowSplit softmax warps
 constexpr int ProbeThreads = 128;   // qk_accum_kernel
 constexpr int MaxSteps = 2 * MaxTiles + 8;

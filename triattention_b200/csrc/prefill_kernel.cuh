@@ -61,8 +61,8 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 // column (inside a score buffer) of the P words of key group kk: the first half of the columns of the thread that owns it
 __device__ __forceinline__ constexpr uint32_t p_column(int kk) { return RowSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; }
-constexpr uint32_t PLow = 16;   // the low parts of the quantised weights: 16 columns behind the high parts
-static_assert(RowSplit == 2, "the high / low weight parts share a thread's 32 score columns: 16 + 16");
+constexpr uint32_t PLow = 32 / RowSplit;   // the low parts of the quantised weights sit behind the high parts: a thread's score
+                                           // columns (64 / RowSplit) hold its high parts in their first half, its low parts in the second
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -427,9 +427,12 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         // from the reference.)  The denominator uses the same s_hi + s_lo.
         const float sf = exp2f(base - ref + PShift) * (1.f / 255.f);
         const float sf_hi = __uint_as_float((__float_as_uint(sf) + 0x00100000u) & 0xffe00000u);
-        const __half sh = __float2half_rn(sf_hi), sl = __float2half_rn(sf - sf_hi);
-        const __half2 shi2 = __half2half2(sh), slo2 = __half2half2(sl);
-        const __half2 nhi2 = __half2half2(__hneg(__hmul(sh, __float2half(1024.f)))), nlo2 = __half2half2(__hneg(__hmul(sl, __float2half(1024.f))));
+        // both parts, and -1024 times both, with two packing conversions (the conversion unit is the exponential unit's)
+        const __half2 parts = __floats2half2_rn(sf_hi, sf - sf_hi);
+        const __half2 shi2 = __low2half2(parts), slo2 = __high2half2(parts);
+        const __half2 nparts = __hmul2(parts, __half2half2(__float2half(-1024.f)));   // exact: a power of two
+        const __half2 nhi2 = __low2half2(nparts), nlo2 = __high2half2(nparts);
+        const float s_sum = sf_hi + __high2float(parts);   // what the two operand parts add up to, for the denominator
         int rs = 0;
         // The code is byte 1 of fma(2^x, 255, 2^15 + ... + 0.5) exactly as in the reference (prefill_sm80.cu:78-88);
         // this constant of the same binade also leaves 0x64 in byte 2, so that bytes 1-2 of the word are the
@@ -472,11 +475,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               lo[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&l2); lo[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&l3);
             }
             tmem_st8(s_addr + 8 * cc, hi);
-            tmem_st8(s_addr + 16 + 8 * cc, lo);   // the low parts sit over the second half of the thread's columns
+            tmem_st8(s_addr + PLow + 8 * cc, lo);   // the low parts sit over the second half of the thread's columns
           }
         };
         if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
-        denom = fmaf((float)rs, __half2float(sh) + __half2float(sl), denom);
+        denom = fmaf((float)rs, s_sum, denom);
       }
       if (ok) {
         tmem_st_wait();   // P is in tensor memory before the issuer is told
