@@ -120,7 +120,14 @@ def _gather_worker(rank, world, port, result):
         out = sharding.gather_outputs(local, shards, 2, 3, 8)
         gatherer = sharding.OutputGatherer(shards, 2, 3, 8, local)        # the same, with buffers and index built once
         again = [gatherer(local).clone() for _ in range(2)]
-        result[rank] = bool((out == full).all()) and all(bool((a == full).all()) for a in again)
+        # equal batch slices holding all heads: the gathered blocks are the output as they lie, no index pass
+        even = [sharding.Shard(r, slice(2 * r, 2 * r + 2), (0, 1, 2, 3)) for r in range(world)]
+        full4 = torch.arange(4 * 8 * 2 * 4, dtype=torch.float32).view(4, 8, 2, 4)
+        g2 = sharding.OutputGatherer(even, 2, 4, 8, full4[even[rank].batch])
+        g2.send.copy_(full4[even[rank].batch])                            # a kernel would write here
+        direct = g2(g2.send)
+        result[rank] = (bool((out == full).all()) and all(bool((a == full).all()) for a in again) and g2.in_order
+                        and not gatherer.in_order and bool((direct == full4).all()))
     finally:
         dist.destroy_process_group()
 

@@ -111,30 +111,39 @@ def gather_outputs(local, shards, group_size, batch, heads_q, group=None):
 
 class OutputGatherer:
     """gather_outputs for a loop: the padded send buffer, the receive buffer and the row index that puts every
-    (sequence, Q head) of every rank in its place are built once; a call is one all_gather_into_tensor (NCCL) and
-    one index_select.  local [b, h_local, ...] -> full [B, Hq, ...] on every rank."""
+    (sequence, Q head) of every rank in its place are built once; a call is one all_gather_into_tensor (NCCL) and, unless
+    the ranks' blocks already lie in output order (equal batch slices holding all heads: then the receive buffer IS the
+    output), one index_select.  local [b, h_local, ...] -> full [B, Hq, ...] on every rank.
+    `send` is this rank's slot of the exchange: a kernel that writes its output there (out=gatherer.send) saves the copy."""
 
-    def __init__(self, shards, group_size, batch, heads_q, like, group=None):
+    def __init__(self, shards, group_size, batch, heads_q, like, group=None, rank=None):
+        import torch.distributed as dist
         self.group, world = group, len(shards)
+        rank = dist.get_rank(group) if rank is None else rank
         bmax = max(s.batch.stop - s.batch.start for s in shards)
         hmax = max(len(s.kv_heads) for s in shards) * group_size
         tail = tuple(like.shape[2:])
         self.pad = like.new_zeros((bmax, hmax) + tail)
+        mine = shards[rank]
+        self.send = self.pad[:mine.batch.stop - mine.batch.start, :len(mine.kv_heads) * group_size]
         self.recv = like.new_empty((world, bmax, hmax) + tail)
         index = torch.zeros((batch, heads_q), dtype=torch.long)
         for r, s in enumerate(shards):
             qh = torch.as_tensor(s.q_heads(group_size))
             for i, b in enumerate(range(s.batch.start, s.batch.stop)):
                 index[b, qh] = (r * bmax + i) * hmax + torch.arange(len(qh))
+        self.in_order = bool((index.flatten() == torch.arange(batch * heads_q)).all()) and world * bmax * hmax == batch * heads_q
         self.index = index.flatten().to(like.device)
         self.shape = (batch, heads_q) + tail
 
     def __call__(self, local):
         import torch.distributed as dist
-        self.pad[:local.shape[0], :local.shape[1]] = local
+        if local.data_ptr() != self.send.data_ptr():
+            self.send.copy_(local)
         dist.all_gather_into_tensor(self.recv, self.pad[None], group=self.group)
-        rows = self.recv.flatten(0, 2)
-        return rows.index_select(0, self.index).view(self.shape)
+        if self.in_order:
+            return self.recv.view(self.shape)
+        return self.recv.flatten(0, 2).index_select(0, self.index).view(self.shape)
 
 
 def merge_triples(m, l, o):
