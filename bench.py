@@ -487,9 +487,23 @@ def measure_sharded_c5(rank, world, dist, steps):
         cache(0, ql, kl, vl, scale, out=out_local)
         full[0] = gather(out_local)
 
-    ms = time_steps(step, steps, dist)
+    ms_nccl = time_steps(step, steps, dist)
     ms_local = time_steps(lambda i: cache(0, ql, kl, vl, scale, out=out_local), steps, dist)
     module.check_device_error()
+    # the same step with the gather fused into the merge kernel: output rows stored into every GPU's full tensor by peer
+    # stores, a flag per rank and one bounded wait; no collective call
+    ms_peer, peer_note = None, None
+    try:
+        peer = sharding.PeerOutputGatherer(module, shards, g, batch, hq, ql.device)
+
+        def step_peer(i):
+            full[0] = cache(0, ql, kl, vl, scale, gather=peer)
+
+        ms_peer = time_steps(step_peer, steps, dist)
+        module.check_device_error()
+    except (RuntimeError, ImportError) as e:      # no symmetric memory on this system: every rank fails alike
+        peer_note = str(e)[:200]
+    ms = min(ms_nccl, ms_peer) if ms_peer is not None else ms_nccl
     loads = torch.tensor([float(plan["payload_bytes"])], device="cuda")
     every = [torch.zeros_like(loads) for _ in range(world)]
     dist.all_gather(every, loads)
@@ -497,11 +511,14 @@ def measure_sharded_c5(rank, world, dist, steps):
     if rank == 0:
         diff = float((full[0].float() - one["out"].float()).abs().max())
         record.update(n_gpus=world, tokens_per_s=batch / (ms / 1e3), ms_per_step=ms, ms_per_step_without_the_output_gather=ms_local,
+                      ms_per_step_gather_by_nccl=ms_nccl, ms_per_step_gather_by_peer_stores=ms_peer, peer_gather_unavailable=peer_note,
                       per_gpu_gbs=max(loads) / (ms / 1e3) / 1e9, bytes_per_rank_max=max(loads),
                       bytes_per_rank_mean=sum(loads) / world, balance_mean_over_max=sum(loads) / world / max(loads),
                       efficiency=one["ms"] / (world * ms), max_abs_diff_vs_one_gpu=diff,
-                      output_gather="one all_gather_into_tensor (NCCL) of the bf16 outputs per step; the decode writes into the send "
-                                    "slot, and the gathered blocks are the output when the shards are equal batch slices",
+                      output_gather="nccl: one all_gather_into_tensor of the bf16 outputs per step (the decode writes into the send slot; "
+                                    "the gathered blocks are the output when the shards are equal batch slices); peer stores: the "
+                                    "merge kernel writes every row into every GPU's full output tensor, one flag per rank, one "
+                                    "bounded wait; ms_per_step is the faster of the two",
                       shards=[dict(sequences=[s.batch.start, s.batch.stop], kv_heads=list(s.kv_heads)) for s in shards])
     del cache, plan
     torch.cuda.empty_cache()

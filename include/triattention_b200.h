@@ -211,17 +211,32 @@ int tri_decode_split(const void* q, int64_t q_stride_b, int64_t q_stride_h, cons
  * and split_stride are then ignored: the CTA of a unit waits — at most one second, then device error 1 — until every
  * source rank r with present[r*U + u] != 0 (int32 [world,U]: rank r holds tiles of unit u) has delivered the triple
  * of the unit's next epoch, and merges that epoch's block.  seen int32 [U], zero at first: the steps merged so far.
+ * gather_peers (or NULL): output gather by peer stores, for units sharded across GPUs.  Instead of `out`, every Q-head
+ * row is stored into the full output tensor of EVERY GPU of the group: gather_peers = device array of gather_world
+ * pointers, entry r = rank r's gather buffer as mapped into this process, laid out as bf16 [2][rows_total][128] (parity
+ * of the step, then the rows of the full [B, Hq] output) followed, 64-byte aligned, by int32 flags [gather_world], all
+ * zero at first.  unit_row int64 [U]: row of this rank's unit u's first Q head in the full tensor.  gather_sync int32 [2],
+ * zero at first (finished CTAs, steps done).  The last CTA to finish raises this rank's flag on every GPU;
+ * tri_gather_wait is the consumer.  Every rank must run the same sequence of steps.
  * Other arguments as tri_decode.
  * Replaces decode_merge_kernel, triattention/kernels/cuda/common_device.cuh:373-469. */
 int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
                      const float* po, int64_t split_stride,
                      const void* exchange_buffer, const int32_t* present, int32_t* seen, int world,
+                     void* const* gather_peers, int gather_world, int gather_rank, const int64_t* unit_row,
+                     int64_t rows_total, int32_t* gather_sync,
                      const int32_t* unit_slots, const float* kstat,
                      const float* vstat, void* tail_k, void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t,
                      const void* kcur, const void* vcur, int64_t cur_stride_b, int64_t cur_stride_h,
                      const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h,
                      int batch, int heads_q, int heads_kv, int max_tail, double scale,
                      int* device_error, void* stream);
+
+/* Consumer of the output gather of tri_decode_merge: one small launch that waits (at most one second, then device error
+ * 1) until the flag of every rank in this GPU's gather buffer has reached the next step, so that whatever follows in the
+ * stream reads the complete output of the step from parity block (step & 1), counting steps from 1.  seen int32 [1],
+ * zero at first.  No counterpart in the reference (single GPU). */
+int tri_gather_wait(const void* gather_buffer, int64_t rows_total, int32_t* seen, int world, int* device_error, void* stream);
 
 /* tri_decode for callers that cannot allocate device memory (a runtime that gave all of HBM to its KV
  * pool up front, a binding that can only pass buffers it was handed).  Same arguments as tri_decode

@@ -243,12 +243,13 @@ def test_error_word_is_keyed_by_the_device_that_ran_the_kernel(monkeypatch):
 
 def test_decode_entry_points_validate_before_any_cuda_call():
     lib = load_library()
-    assert lib.tri_decode_merge(None, 0, 0, *([None] * 3), 0, None, None, None, 0, *([None] * 5), 0, 0, None, None, 0, 0,
-                                None, None, 0, 0, 1, 8, 2, 4, 0.088, None, None) == -1
+    assert lib.tri_decode_merge(None, 0, 0, *([None] * 3), 0, None, None, None, 0, None, 0, 0, None, 0, None,
+                                *([None] * 5), 0, 0, None, None, 0, 0, None, None, 0, 0, 1, 8, 2, 4, 0.088, None, None) == -1
     assert b"decode_merge" in lib.tri_last_error()
     assert lib.tri_decode_partials(None, 0, 0, *([None] * 7), 4, *([None] * 8), None, 0, 0, None, 1, 8, 2, 64, 0.088,
                                    None, None) == -1
     assert b"decode_partials" in lib.tri_last_error()
+    assert lib.tri_gather_wait(None, 0, None, 0, None, None) == -1 and b"gather_wait" in lib.tri_last_error()
 
 
 def test_plan_streams_appended_tiles():

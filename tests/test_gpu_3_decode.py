@@ -345,3 +345,50 @@ def test_exchange_wait_runs_out_without_hanging(module):
     assert int(cache.layers[0]["seen"].max()) == 0          # nothing was merged
     whole, _ = product_decode(module, q, k, v, bands, *make_inputs(hq, hk, 1, seed=74, batch=batch), steps=1)
     assert np.isfinite(whole).all()                         # and the GPU still computes
+
+
+def test_output_gather_by_peer_stores_emulated_on_one_gpu(module):
+    """Units sharded over two "ranks" held by this process on one GPU: each part's merge kernel stores its output rows into
+    the full output tensor of both parts (their gather buffers, here ordinary device memory), the last CTA raises the
+    part's flag in both, and the wait kernel of each part then finds both flags set (all producers are launched before any
+    consumer, so nothing ever waits for a later launch).  The full tensor equals the un-sharded decode, bit for bit per
+    row (a shard is the same units with its own CTA partition, so only the float summation order may differ: tolerance),
+    over three steps so that both parity blocks are used."""
+    from triattention_b200 import sharding
+    hq, hk, t, batch, g = 8, 4, 700, 2, 2
+    bands = np.asarray([[INF, INF]] * 4 + [[2, 5]] * 2 + [[1, INF]] * 2, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=81, batch=batch)
+    qd, kd, vd = make_inputs(hq, hk, 3, seed=82, batch=batch)
+    whole, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3)
+    shards = [sharding.Shard(0, slice(0, 2), (0, 3)), sharding.Shard(1, slice(0, 2), (1, 2))]     # head groups, not in order
+    fn = bands_fn_of(bands)
+    nbytes = sharding.PeerOutputGatherer.buffer_bytes(batch, hq, 2)
+    buffers = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in shards]
+    parts = []
+    for s in shards:
+        heads, qh = list(s.kv_heads), list(s.q_heads(g))
+        cache = DecodeCache(module, max_tail=8)
+        pre = Prefill(module, sharding.slice_map(fn, s, g, hq), cache)
+        take = lambda x, hs: bf16_cuda(np.ascontiguousarray(x[:, hs]))
+        table, ops = pre.write(0, take(q, qh), take(k, heads), take(v, heads))
+        cache.store(0, t, ops, table.host, take(k, heads), take(v, heads), table.bf16_kv)
+        gather = sharding.PeerOutputGatherer(module, shards, g, batch, hq, "cuda", rank=s.rank, buffers=buffers)
+        parts.append((cache, gather, heads, qh))
+    outs = []
+    for step in range(3):
+        for cache, gather, heads, qh in parts:          # every producer first: split pass + merge with peer stores
+            e, d = cache.layers[0], cache.layers[0]["dev"]
+            qs, ks, vs = (bf16_cuda(np.ascontiguousarray(x[:, hs, step:step + 1])) for x, hs in ((qd, qh), (kd, heads), (vd, heads)))
+            module.decode(qs, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
+                          d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], ks, vs, cache.step,
+                          qs, e["pm"], e["pl"], e["po"], e["prompt"], SCALE, 1)
+            module.decode_merge(qs, e["pm"], e["pl"], e["po"], 0, d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"],
+                                ks, vs, cache.step, qs, SCALE, gather=gather.arguments())
+        fulls = [gather.wait().float().cpu().numpy()[:, :, 0] for _, gather, _, _ in parts]      # then the consumers
+        for cache, _, _, _ in parts:
+            cache.advance()
+        assert (fulls[0] == fulls[1]).all()
+        outs.append(fulls[0])
+    module.check_device_error()
+    assert all(int(gather.seen.item()) == 3 and gather.sync.tolist() == [0, 3] for _, gather, _, _ in parts)
+    assert_fp_close(np.stack(outs, 1), whole, "units sharded over two parts, outputs gathered by peer stores")

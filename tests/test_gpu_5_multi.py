@@ -72,7 +72,24 @@ def _worker(rank, world, port, result):
                               take(qd, qh), take(kd, kvh), take(vd, kvh), steps)
         full = sharding.gather_outputs(local.transpose(1, 2).contiguous(), shards, 2, batch, hq).transpose(1, 2)
         r2 = fp_report(full.cpu().numpy(), whole.cpu().numpy())
-        result[rank] = (r1, r2, [list(x.kv_heads) for x in shards], r1b)
+        # 2b. the same with the output gather fused into the merge kernel: every rank's rows stored into every GPU's full
+        # output tensor by peer stores, a flag per rank, one bounded wait; no collective call in the step
+        from triattention_b200.kernels.decode import DecodeCache
+        from triattention_b200.kernels.prefill import Prefill
+        cache = DecodeCache(module, max_tail=8)
+        pre = Prefill(module, sharding.slice_map(fn, s, 2, hq), cache)
+        table, ops = pre.write(0, take(q, qh), take(k, kvh), take(v, kvh))
+        cache.store(0, t, ops, table.host, take(k, kvh), take(v, kvh), table.bf16_kv)
+        gatherer = sharding.PeerOutputGatherer(module, shards, 2, batch, hq, q.device)
+        outs = []
+        for st in range(steps):
+            outs.append(cache(0, take(qd, qh)[:, :, st:st + 1], take(kd, kvh)[:, :, st:st + 1], take(vd, kvh)[:, :, st:st + 1],
+                              SCALE, gather=gatherer).float().clone())
+            cache.advance()
+        module.check_device_error()
+        dist.barrier()
+        r2b = fp_report(torch.stack(outs, 1).cpu().numpy(), whole.cpu().numpy())
+        result[rank] = (r1, r2, [list(x.kv_heads) for x in shards], r1b, r2b)
     finally:
         dist.destroy_process_group()
 
@@ -85,7 +102,8 @@ def test_two_gpu_split_and_sharding():
         result = manager.dict()
         mp.spawn(_worker, args=(world, port, result), nprocs=world, join=True)
         for rank in range(world):
-            r1, r2, groups, r1b = result[rank]
+            r1, r2, groups, r1b, r2b = result[rank]
+            assert r2b["worst_excess"] <= 0 and r2b["cos"] >= 0.9999, ("unit sharding, peer-store output gather", r2b, groups)
             assert r1["worst_excess"] <= 0 and r1["cos"] >= 0.9999, ("sequence split", r1)
             assert r1b["worst_excess"] <= 0 and r1b["cos"] >= 0.9999, ("sequence split, peer-memory exchange", r1b)
             # a shard is a smaller problem with its own CTA partition, so only the float summation order differs

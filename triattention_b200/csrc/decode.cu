@@ -31,8 +31,19 @@ constexpr int MergeThreads = 256, MergeWarps = MergeThreads / 32;
 struct SplitExchange {
   const float* local; const int32_t* present; int32_t* seen; int world, units; int64_t rank_stride;
 };
+// Output gather by peer stores (unit sharding across GPUs): world > 0 makes every Q-head row go, instead of into `out`,
+// into the full output tensor of EVERY GPU of the group, at the row the (sequence, head) has there.  peers[r] = rank r's
+// gather buffer as mapped here: bf16 data [2][rows_total][128] (parity of the step, then the full [B, Hq] rows) followed
+// by int32 flags [world] (64-byte aligned).  unit_row[u] = row of the unit's first Q head in the full tensor.
+// sync[0] counts finished CTAs of the launch, sync[1] the steps done (the epoch).  The CTA that finishes last raises
+// flag[rank] = epoch on every GPU; gather_wait_kernel is the consumer.
+struct OutputGather {
+  void* const* peers; const int64_t* unit_row; int32_t* sync; int world, rank; int64_t rows_total;
+};
+__device__ __forceinline__ int64_t gather_flag_offset_bytes(int64_t rows_total) { return (2 * rows_total * D * 2 + 63) / 64 * 64; }
 __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float* pm, const float* pl, const float* po,
-    int64_t ml_stride, int64_t o_stride, SplitExchange xchg, const int2* unit_slots, int slot_limit, const float* vstat, const float* kstat,
+    int64_t ml_stride, int64_t o_stride, SplitExchange xchg, OutputGather gather, const int2* unit_slots, int slot_limit,
+    const float* vstat, const float* kstat,
     const __nv_bfloat16* q, int64_t qsb, int64_t qsh, __nv_bfloat16* ktail, __nv_bfloat16* vtail, int64_t tsu, int64_t tst,
     const __nv_bfloat16* kcur, const __nv_bfloat16* vcur, int64_t csb, int64_t csh, const int64_t* step, __nv_bfloat16* out,
     int64_t osb, int64_t osh, int heads_q, int heads_kv, int max_tail, float sm_log2, int* err) {
@@ -83,9 +94,62 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   unit_tail_scores(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
                    sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
   __syncthreads();
+  if (gather.world == 0) {
+    if (warp < g)
+      merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
+                         vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
+    return;
+  }
+  // unit sharding: the row is computed into shared memory once and stored into every GPU's full output tensor
+  __shared__ __align__(16) __nv_bfloat16 rows[MaxGroup][D];
+  const int epoch = gather.sync[1] + 1;          // read by every CTA before the last one to finish advances it
   if (warp < g)
     merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
-                       vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
+                       vstat + (int64_t)unit * StatFloats, rows[warp], lane);
+  __syncthreads();
+  const int64_t row0 = (int64_t)(epoch & 1) * gather.rows_total + gather.unit_row[unit];
+  for (int i = tid; i < gather.world * g * (D / 8); i += MergeThreads) {   // 16-byte pieces: peer, head row, piece
+    const int p = i / (g * (D / 8)), r = (i / (D / 8)) % g, piece = i % (D / 8);
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(gather.peers[p]) + (row0 + r) * D + piece * 8;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&rows[r][piece * 8]);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();                      // cumulative over the CTA's stores (the barrier made them visible here)
+    const int done = atomicAdd(&gather.sync[0], 1);
+    if (done == (int)gridDim.x - 1) {            // every CTA of the launch has stored and fenced
+      gather.sync[0] = 0;
+      gather.sync[1] = epoch;
+      __threadfence_system();
+      for (int p = 0; p < gather.world; ++p) {
+        volatile int32_t* flags = reinterpret_cast<volatile int32_t*>(static_cast<char*>(gather.peers[p]) +
+                                                                      gather_flag_offset_bytes(gather.rows_total));
+        flags[gather.rank] = epoch;
+      }
+    }
+  }
+}
+
+// Consumer of the output gather: one warp waits (at most one second, then device error 1) until every rank's flag has
+// reached this GPU's next epoch; what follows in the stream sees the complete output of that step.
+__global__ void __launch_bounds__(64) gather_wait_kernel(const void* local, int64_t rows_total, int32_t* seen, int world, int* err) {
+  grid_dependency_wait();
+  const int epoch = *seen + 1;
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const int32_t* flag = reinterpret_cast<const int32_t*>(static_cast<const char*>(local) + gather_flag_offset_bytes(rows_total)) + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    while (load_acquire_sys(flag) < epoch) {
+      if (globaltimer_ns() - t0 > 1000000000ull) { failed = 1; break; }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (failed) atomicCAS(err, ErrNone, ErrBarrierTimeout);
+    else *seen = epoch;
+  }
 }
 
 
@@ -204,13 +268,13 @@ static cudaError_t launch_split(const DecodeCall& c, float* pm, float* pl, float
 
 static cudaError_t launch_merge(const DecodeCall& c, const float* pm, const float* pl, const float* po, int64_t ml_stride,
                                 int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained,
-                                SplitExchange xchg = SplitExchange{}) {
+                                SplitExchange xchg = SplitExchange{}, OutputGather gather = OutputGather{}) {
   const dim3 grid(c.batch * c.heads_kv);
   if (chained)
-    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, unit_slots,
+    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots,
                           slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb,
                           c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
-  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
+  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
       c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
       c.heads_kv, c.max_tail, c.sm_log2, c.err);
   return cudaSuccess;
@@ -331,6 +395,7 @@ extern "C" int tri_decode_split(const void* q, int64_t q_stride_b, int64_t q_str
 
 extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_stride_h, const float* pm, const float* pl,
     const float* po, int64_t split_stride, const void* exchange_buffer, const int32_t* present, int32_t* seen, int world,
+    void* const* gather_peers, int gather_world, int gather_rank, const int64_t* unit_row, int64_t rows_total, int32_t* gather_sync,
     const int32_t* unit_slots, const float* kstat, const float* vstat, void* tail_k,
     void* tail_v, int64_t tail_stride_u, int64_t tail_stride_t, const void* kcur, const void* vcur, int64_t cur_stride_b,
     int64_t cur_stride_h, const int64_t* step, void* out, int64_t out_stride_b, int64_t out_stride_h, int batch, int heads_q,
@@ -354,10 +419,24 @@ extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_str
   call.out = static_cast<__nv_bfloat16*>(out); call.osb = out_stride_b; call.osh = out_stride_h; call.batch = batch;
   call.heads_q = heads_q; call.heads_kv = heads_kv; call.max_tail = max_tail; call.sm_log2 = (float)(scale * 1.4426950408889634);
   call.err = device_error;
+  OutputGather gather{};
+  if (gather_peers != nullptr) {
+    TRI_CHECK(unit_row && gather_sync && gather_world >= 1 && gather_world <= 64 && gather_rank >= 0 && gather_rank < gather_world &&
+              rows_total > 0, "decode_merge: output gather group");
+    gather = OutputGather{gather_peers, unit_row, gather_sync, gather_world, gather_rank, rows_total};
+  }
   const int64_t ml = split_stride ? split_stride : MaxGroup, os = split_stride ? split_stride : (int64_t)MaxGroup * D;
   TRI_CUDA(launch_merge(call, pm, pl, po, ml, os, reinterpret_cast<const int2*>(unit_slots), NoSlotLimit,
-                        static_cast<cudaStream_t>(stream), true, xchg), "decode_merge");
+                        static_cast<cudaStream_t>(stream), true, xchg, gather), "decode_merge");
   return tri_launch_status("decode_merge");
+}
+
+extern "C" int tri_gather_wait(const void* gather_buffer, int64_t rows_total, int32_t* seen, int world, int* device_error,
+                               void* stream) {
+  TRI_CHECK(gather_buffer && seen && device_error && world >= 1 && world <= 64 && rows_total > 0, "gather_wait: arguments");
+  TRI_CUDA(launch_chained(gather_wait_kernel, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream), gather_buffer, rows_total, seen,
+                          world, device_error), "gather_wait");
+  return tri_launch_status("gather_wait");
 }
 
 extern "C" int tri_cache_store(void* pool, const int64_t* unit_base, const int32_t* unit_tab, const int32_t* unit_count,

@@ -396,8 +396,20 @@ class DecodeCache:
         e["extra"] = done + 1
         e["plan"], e["dev"] = self.plan(bands, heads_kv, prompt, batch, bf16_kv, device, extra=done + 1)
 
-    def __call__(self, layer, q, k, v, scale, phases=3, out=None):
+    def __call__(self, layer, q, k, v, scale, phases=3, out=None, gather=None):
+        """gather: a sharding.PeerOutputGatherer (units sharded across GPUs): the merge then stores every output row straight
+        into the full output tensor of every GPU of the group, and the call returns that full tensor [B, Hq, 1, 128]."""
         e = self.layers[layer]
+        if gather is not None:
+            if self.split is not None or phases != 3:
+                raise RuntimeError("the peer-store output gather belongs to whole units (no sequence split), whole steps")
+            d = e["dev"]
+            self.module.decode(q, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
+                               d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], k, v,
+                               self.step, q, e["pm"], e["pl"], e["po"], e["prompt"], scale, 1)
+            self.module.decode_merge(q, e["pm"], e["pl"], e["po"], 0, d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"],
+                                     e["tail_v"], k, v, self.step, q, scale, gather=gather.arguments())
+            return gather.wait()
         if self.reserve and e["extra"] < self.generated // FOLD_KEYS:
             self.fold(layer)
         d = e["dev"]

@@ -37,8 +37,9 @@ SIGNATURES = {
                             _I, _I, _I, _I, _D, _P, _P],
     "tri_decode_split": [_P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
                          _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _D, _P, _P],
-    "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _L, _P, _P, _L, _L, _P, _P, _L, _L,
-                         _I, _I, _I, _I, _D, _P, _P],
+    "tri_decode_merge": [_P, _L, _L, _P, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P,
+                         _L, _L, _P, _P, _L, _L, _I, _I, _I, _I, _D, _P, _P],
+    "tri_gather_wait": [_P, _L, _P, _I, _P, _P],
     "tri_decode_occupancy": [],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_abi_version": [],
@@ -340,7 +341,7 @@ class Module:
         return out
 
     def decode_merge(self, q, pm, pl, po, split_stride, unit_slots, kstat, vstat, tail_k, tail_v, kcur, vcur, step, out, scale,
-                     exchange=None, present=None, seen=None, world=0):
+                     exchange=None, present=None, seen=None, world=0, gather=None):
         """The merge alone, over partials that may lie strided (triples gathered from several GPUs, merged in place), or
         (exchange = this rank's exchange buffer, present int32 [world, units], seen int32 [units]) over the triples that
         the peer-memory exchange of decode_partials delivers, waiting for them per unit."""
@@ -352,11 +353,20 @@ class Module:
             self._check(self.lib.tri_decode_merge(
                 q.data_ptr(), q.stride(0), q.stride(1), _ptr(pm), _ptr(pl), _ptr(po), int(split_stride),
                 _ptr(exchange), _ptr(present), _ptr(seen), int(world),
+                *((None, 0, 0, None, 0, None) if gather is None else
+                  (gather["peers"].data_ptr(), gather["peers"].numel(), int(gather["rank"]), gather["unit_row"].data_ptr(),
+                   int(gather["rows_total"]), gather["sync"].data_ptr())),
                 unit_slots.data_ptr(), kstat.data_ptr(), vstat.data_ptr(), tail_k.data_ptr(), tail_v.data_ptr(),
                 tail_k.stride(0), tail_k.stride(1), kcur.data_ptr(), vcur.data_ptr(), kcur.stride(0), kcur.stride(1),
                 step.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1), q.shape[0], q.shape[1], kcur.shape[1],
                 tail_k.shape[1], float(scale), self.error_word(q.device).data_ptr(), _stream()))
         return out
+
+    def gather_wait(self, buffer, rows_total, seen, world):
+        """Wait (on the device, bounded) until every rank's rows of the next step have arrived in this GPU's gather buffer."""
+        with torch.cuda.device(buffer.device):
+            self._check(self.lib.tri_gather_wait(buffer.data_ptr(), int(rows_total), seen.data_ptr(), int(world),
+                                                 self.error_word(buffer.device).data_ptr(), _stream()))
 
     def decode_occupancy(self):
         return self._check(self.lib.tri_decode_occupancy())

@@ -146,6 +146,54 @@ class OutputGatherer:
         return self.recv.flatten(0, 2).index_select(0, self.index).view(self.shape)
 
 
+class PeerOutputGatherer:
+    """Output gather without a collective call: the merge kernel of every rank stores its output rows straight into the
+    full output tensor of every GPU of the group (symmetric memory, plain peer stores over NVLink, then a flag), and a
+    one-warp kernel waits for all ranks' flags (bounded).  Pass it to DecodeCache.__call__(gather=...); the call returns
+    the full [B, Hq, 1, 128] output of the step (a view of the step's parity block, valid until the step after next).
+    Every rank must make the same sequence of calls."""
+
+    def __init__(self, module, shards, group_size, batch, heads_q, device, group=None, rank=None, buffers=None):
+        import torch.distributed as dist
+        self.module, self.world = module, len(shards)
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.rows, self.shape, self.steps = batch * heads_q, (batch, heads_q, 1, 128), 0
+        mine = shards[self.rank]
+        kv = torch.as_tensor(mine.kv_heads, dtype=torch.int64)
+        rows = (torch.arange(mine.batch.start, mine.batch.stop, dtype=torch.int64)[:, None] * heads_q + kv[None, :] * group_size)
+        self.unit_row = rows.flatten().to(device)           # unit = local sequence * local KV heads + local KV head
+        data_bytes = -(-(2 * self.rows * 128 * 2) // 64) * 64
+        nbytes = data_bytes + 64 * -(-self.world * 4 // 64)
+        self.handle = None
+        if buffers is None:
+            import torch.distributed._symmetric_memory as symm
+            self.buffer = symm.empty(nbytes, dtype=torch.uint8, device=device)
+            self.buffer.zero_()
+            self.handle = symm.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+            torch.cuda.synchronize(device)
+            self.handle.barrier()
+            pointers = [int(p) for p in self.handle.buffer_ptrs]
+        else:                                               # several parts held by one process (tests): all buffers given
+            self.buffer = buffers[self.rank]
+            pointers = [b.data_ptr() for b in buffers]
+        self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.seen = torch.zeros(1, dtype=torch.int32, device=device)
+        self.blocks = self.buffer[:2 * self.rows * 256].view(torch.bfloat16).view(2, *self.shape)
+
+    @staticmethod
+    def buffer_bytes(batch, heads_q, world):
+        return -(-(2 * batch * heads_q * 256) // 64) * 64 + 64 * -(-world * 4 // 64)
+
+    def arguments(self):
+        return dict(peers=self.peers, rank=self.rank, unit_row=self.unit_row, rows_total=self.rows, sync=self.sync)
+
+    def wait(self):
+        self.module.gather_wait(self.buffer, self.rows, self.seen, self.world)
+        self.steps += 1
+        return self.blocks[self.steps & 1]
+
+
 def merge_triples(m, l, o):
     """Merge split partials along dim 0: m, l [S,...], o [S,...,128] -> (m, l, o) of the union.
     common_device.cuh:418-438 of the reference (base-2 running maximum), in torch for any device."""
