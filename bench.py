@@ -16,6 +16,8 @@ against the measured HBM copy peak; cpu_baseline = the CPU oracle port on a boun
 After that timed region, outside it, the same line gets secondary records (each can be skipped with --no-extras):
   prefill     configuration 3 (28 Q / 4 KV heads, batch 2, 16384 tokens): INT8 TOP/s of the prefill kernel against the
               nominal dense INT8 peak and against i8_peak, and the KV-cache write in GB/s            (1 GPU runs)
+  calibration the reference's calibration grid (86 uniform maps) on one layer in one pass (Prefill.sweep) against one full
+              prefill per grid point, the loop of the reference's tool                               (1 GPU runs)
   i8_peak     what back-to-back tcgen05 kind::i8 MMAs (M128 N256 K32, operands in shared memory) sustain on this GPU
   ref_ext     the reference's own CUDA extension (its sm_80 source compiled for sm_100, what a B200 runs today) timed
               on the same inputs: decode as 32 sequential batch-1 calls, prefill as 2 calls           (1 GPU runs)
@@ -366,6 +368,43 @@ def measure_prefill(b, t, steps, warmup, peak=None):
                 kv_write_gbs=write_bytes / (ms_write / 1e3) / 1e9,
                 kv_write_frac_of_measured_hbm=write_bytes / (ms_write / 1e3) / 1e9 / peak_hbm()[0],
                 clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))
+
+
+def measure_calibration(steps, t=8192, rows=1024):
+    """One layer of the calibration grid (86 uniform maps, 32 Q / 8 KV heads, batch 1, the last `rows` of `t` query rows kept):
+    all grid points in one KV-cache write and one attention launch (Prefill.sweep) against the reference tool's loop of one
+    full prefill per grid point (calibrate.py:46-63 of the reference), both on this library's kernels.  One GPU."""
+    from triattention_b200.calibrate import grid
+    from triattention_b200.kernels.extension import load_extension
+    from triattention_b200.kernels.prefill import Prefill
+    from triattention_b200.maps import INF, uniform
+    module, configs, scale = load_extension(), grid(), 128 ** -0.5
+    _, q, k, v = prefill_inputs(1, 32, 8, t)
+    one = Prefill(module, uniform(INF, INF))
+    shared, loop = {}, []
+    for w8, w4 in configs:
+        loop.append(Prefill(module, uniform(w8, w4)))
+        loop[-1].buffers = shared
+    first = t - rows
+
+    def per_point():
+        return [pre(0, q, k, v, scale)[0, :, first:] for pre in loop]
+
+    warm_up(lambda: one.sweep(configs, q, k, v, scale, rows=rows), 3)
+    per_point()
+    module.check_device_error()
+    steps = max(1, min(steps, 10))
+    ms_sweep = timed(lambda i: one.sweep(configs, q, k, v, scale, rows=rows), steps, None) / steps
+    ms_loop = timed(lambda i: per_point(), 2, None) / 2
+    out, row0 = one.sweep(configs, q, k, v, scale, rows=rows)
+    same = sum(bool(torch.equal(out[c, 0, :, first - row0:], ref)) for c, ref in enumerate(per_point()))
+    module.check_device_error()
+    del out
+    one.buffers.clear(), one.views.clear(), shared.clear()
+    return dict(metric="calibration_grid_points_per_s", value=len(configs) / (ms_sweep / 1e3), unit="grid points/s (one layer)",
+                ms_per_layer=ms_sweep, ms_per_layer_one_prefill_per_point=ms_loop, speedup=ms_loop / ms_sweep,
+                grid_points=len(configs), grid_points_bit_equal_to_their_own_run=same, steps=steps,
+                config=dict(workload=f"calibration grid, 32 Q / 8 KV heads, batch 1, {t} tokens, last {rows} rows kept"))
 
 
 def run_prefill(args):
@@ -796,6 +835,7 @@ def main():
             extras["i8_peak"] = measure_i8_peak()
             extras["prefill"] = measure_prefill(2, 16384, extra_steps, 3, extras["i8_peak"])
             extras["ref_ext"] = measure_ref_ext(extra_steps)
+            extras["calibration"] = measure_calibration(extra_steps)
             torch.cuda.empty_cache()
         extras["sharded_c5"] = measure_sharded_c5(rank, world, dist, extra_steps)
         if world > 1:

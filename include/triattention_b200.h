@@ -92,6 +92,20 @@ int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const 
                   const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
                   int* device_error, void* stream);
 
+/* Several band maps over the same operands in ONE launch, and only the query rows that are wanted: what the reference's
+ * calibration tool does with one full prefill per grid point (triattention/calibrate.py:46-63: ~90 (w8, w4)
+ * configurations per layer and sample, each re-quantising Q, K, V and computing every row, of which it keeps the last
+ * 1024).  bands int32 [configs, Hq, 2]; configuration c writes out + c * out_stride_c.  first_block: query blocks (64
+ * rows) before it are not computed; because a CTA owns four query blocks, rows from (first_block / 4) * 256 on are
+ * written, at out + row * out_stride_t as usual (pass the pointer of a row-0 origin; rows before that are never
+ * touched).  Quantised heads only; other arguments as tri_attention. */
+int tri_attention_sweep(const int32_t* bands, int configs, int first_block, const void* v16, const void* v8h,
+                        const float* vstat, const void* q8, const void* k8, const float* qa8, const float* ka8,
+                        const void* q4x, const void* k4x, const float* qa4, const float* ka4,
+                        void* out, int out_is_half, int64_t out_stride_c, int64_t out_stride_b, int64_t out_stride_h,
+                        int64_t out_stride_t, int batch, int heads_q, int heads_kv, int tokens, double scale,
+                        int* device_error, void* stream);
+
 /* Task-table mode of the prefill attention: every (Q head, query block) brings four explicit tile lists.
  * Replaces attention(order,None,groups,entries,...), triattention/kernels/cuda/prefill_sm80.cu:287-292,510-543
  *   (no caller in the reference; kept for interface completeness as a CUDA-core kernel, not a tensor-core one).

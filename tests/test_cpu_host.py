@@ -291,3 +291,52 @@ def test_band_table_q_modes():
     table = BandTable.build(bands, 40, 4, "cpu", bf16_kv=(0,))
     assert table.q_modes.tolist() == [0, 0, 3, 3, 1, 1, 3, 3]
     assert BandTable.build(bands, 3, 4, "cpu").q_modes.tolist() == [1, 1, 3, 3, 1, 1, 1, 1]   # 3 tiles: [3, 9] never gets past w8
+
+
+def test_calibration_grid_and_error_measure():
+    """The grid has the reference's 86 points in its order (calibrate.py:13-18), and the batched error measure equals the
+    definition evaluated one configuration and one head at a time (calibrate.py:53-62)."""
+    from triattention_b200.calibrate import W4, W8, grid, head_errors
+    from triattention_b200.maps import INF
+    points = grid()
+    assert len(points) == 86 and points[0] == (1, 1) and points[-1] == (INF, INF)
+    assert points == sorted(points) and len(set(points)) == 86
+    assert all(w4 >= w8 and w8 in W8 and (w4 in W4 or w4 == w8) for w8, w4 in points)
+    assert [p for p in points if p[0] == INF] == [(INF, INF)]
+    assert {w4 for w8, w4 in points if w8 == 4} == {4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, INF}
+    g = torch.Generator().manual_seed(5)
+    c, h, r, hidden = 11, 3, 7, 40
+    exact = torch.randn(h, r, 128, generator=g)
+    outputs = (exact[None] + 0.01 * torch.randn(c, h, r, 128, generator=g)).to(torch.bfloat16)
+    weight = torch.randn(hidden, h * 128, generator=g).to(torch.bfloat16)
+    got = head_errors(outputs, exact, weight, chunk=4)
+    assert got.shape == (h, c) and got.dtype == torch.float64
+    w = weight.double()
+    energy = (exact.double().transpose(0, 1).reshape(r, h * 128) @ w.T).square().sum()
+    for ci in range(c):
+        for hi in range(h):
+            delta = outputs[ci, hi].double() - exact[hi].double()
+            want = (delta @ w[:, hi * 128:(hi + 1) * 128].T).square().sum() / energy
+            assert abs(got[hi, ci] - want) <= 1e-4 * want
+
+
+def test_calibration_sample_loader(tmp_path):
+    import json
+    from triattention_b200.calibrate import load_samples
+
+    class Tokens:
+        chat_template = None
+
+        def __call__(self, text, add_special_tokens=False):
+            assert add_special_tokens is False
+            return type("Enc", (), {"input_ids": [ord(ch) for ch in text]})()
+
+        def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+            return "<" + messages[0]["content"] + ">"
+
+    path = tmp_path / "samples.jsonl"
+    path.write_text(json.dumps({"prompt": "ab", "response": "wxyz"}) + "\n" + json.dumps({"prompt": "c", "response": "q"}) + "\n")
+    samples = load_samples(path, Tokens(), 3)
+    assert [n for _, n in samples] == [3, 1]
+    assert samples[0][0][-3:] == [ord("w"), ord("x"), ord("y")] and samples[1][0][-1] == ord("q")
+    assert len(samples[0][0]) > 3

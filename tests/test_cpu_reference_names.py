@@ -50,6 +50,16 @@ def test_calibrate_style_callers_on_cpu():
     assert codes.tolist()[:2] == [2, 3] and formats == frozenset({2, 3}) and not cache.stored(0)
 
 
+def test_calibrate_entry_point_flags():
+    """python -m triattention.calibrate takes the reference tool's flags (calibrate.py:33-39)."""
+    from triattention.calibrate import W4, W8, grid
+    assert len(W8) == 11 and len(W4) == 12 and len(grid()) == 86
+    out = subprocess.run([sys.executable, "-m", "triattention.calibrate", "--help"], cwd=ROOT, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    for flag in ("--model", "--samples", "--output", "--rows", "--response-tokens"):
+        assert flag in out.stdout
+
+
 def test_infer_entry_point_flags():
     out = subprocess.run([sys.executable, "-m", "triattention.infer", "--help"], cwd=ROOT, capture_output=True, text=True)
     assert out.returncode == 0

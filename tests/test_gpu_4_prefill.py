@@ -109,3 +109,47 @@ def test_prefill_bf16_heads(module):
     assert_fp_close(got[0, 2:], orc.to_bf16(want[2:]), "bf16 heads vs exact attention")
     quant = orc.prefill(q[0], k[0], v[0], np.asarray([[INF, INF]] * 4), SCALE)
     assert_fp_close(got[0, :2], orc.to_bf16(quant[:2]), "quantised heads beside bf16 heads")
+
+
+SWEEP = [(1, 2), (2, 2), (1, INF), (2, 8), (4, 4), (INF, INF), (8, 2048), (1, 1)]
+
+
+@pytest.mark.parametrize("rows", [None, 300, 64, 5000], ids=["all-rows", "last-300", "last-64", "more-than-T"])
+@pytest.mark.parametrize("batch,hq,hk,t", [(1, 4, 2, 1100), (2, 2, 1, 333)])
+def test_sweep_of_configurations_equals_one_run_per_configuration(module, batch, hq, hk, t, rows):
+    """One launch over a grid of uniform maps (the calibration's inner loop, calibrate.py:46-63 of the reference) gives,
+    for each configuration, bit for bit what a separate prefill with that map gives on the rows it returns."""
+    q, k, v = (bf16_cuda(x) for x in make_inputs(hq, hk, t, seed=21, batch=batch))
+    out, row0 = Prefill(module, bands_fn_of([[INF, INF]] * hq)).sweep(SWEEP, q, k, v, SCALE, rows=rows)
+    module.check_device_error()
+    wanted = t if rows is None else min(t, rows)
+    assert row0 % 256 == 0 and row0 <= t - wanted and t - wanted - row0 < 256
+    assert out.shape == (len(SWEEP), batch, hq, t - row0, 128) and out.dtype == torch.bfloat16
+    for c, (w8, w4) in enumerate(SWEEP):
+        alone = Prefill(module, bands_fn_of([[w8, w4]] * hq))(0, q, k, v, SCALE)[:, :, row0:]
+        module.check_device_error()
+        if (w8, w4) == (1, 1):
+            # no INT8 tile at all: a run of its own keeps V un-normalised (the reference's identity mode), the sweep
+            # normalises V for every configuration; the outputs differ by the fp16 rounding of V' only
+            assert_fp_close(out[c].float().cpu().numpy(), alone.float().cpu().numpy(), 2e-3, 0.9999)
+        else:
+            assert torch.equal(out[c], alone), (w8, w4, (out[c].float() - alone.float()).abs().max().item())
+
+
+def test_sweep_fp16_outputs_and_argument_checks(module):
+    hq, hk, t = 2, 1, 520
+    q, k, v = (bf16_cuda(x) for x in make_inputs(hq, hk, t, seed=22))
+    pre = Prefill(module, bands_fn_of([[INF, INF]] * hq))
+    out, row0 = pre.sweep([(2, 4), (1, INF)], q, k, v, SCALE, rows=100, out_dtype=torch.float16)
+    module.check_device_error()
+    assert row0 == 256 and out.dtype == torch.float16
+    alone = Prefill(module, bands_fn_of([[2, 4]] * hq))(0, q, k, v, SCALE, out_dtype=torch.float16)[:, :, row0:]
+    assert torch.equal(out[0], alone)
+    with pytest.raises(ValueError):
+        pre.sweep([(0, 4)], q, k, v, SCALE)
+    ops = pre.operands(1, hq, hk, t, True, False, frozenset({1, 2, 4}), q.device)
+    bad = torch.empty((1, 1, hq, t, 128), dtype=torch.bfloat16, device=q.device)
+    with pytest.raises(RuntimeError):     # row0 must be the first row of the group of four blocks that holds first_block
+        module.attention_sweep(torch.ones((1, hq, 2), dtype=torch.int32, device=q.device), 5, ops["v16"], ops["v8h"],
+                               ops["vstat"], ops["q8"], ops["k8"], ops["qa"], ops["ka"], ops["q4x"], ops["k4x"], ops["qa4"],
+                               ops["ka4"], bad, 0, SCALE, hk, t)

@@ -201,11 +201,14 @@ template <typename K> static int allow_smem(K kernel, int bytes) {
 
 using namespace tri;
 
-extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat, const void* q8,
-    const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4, const float* ka4,
-    void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
-    int heads_kv, int tokens, double scale, const void* q_raw, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
-    const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t, int* device_error, void* stream) {
+// Shared by tri_attention and tri_attention_sweep: `configs` band tables evaluated in one launch (grid.y), query blocks
+// from `first_block` on (the grid covers the quads that contain them), outputs `out_stride_c` elements apart.
+static int launch_attention(const int32_t* bands, int configs, int first_block, const void* v16, const void* v8h, const float* vstat,
+    const void* q8, const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4,
+    const float* ka4, void* out, int out_is_half, int64_t out_stride_c, int64_t out_stride_b, int64_t out_stride_h,
+    int64_t out_stride_t, int batch, int heads_q, int heads_kv, int tokens, double scale, const void* q_raw, int64_t q_stride_b,
+    int64_t q_stride_h, int64_t q_stride_t, const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+    int* device_error, void* stream) {
   TRI_CHECK(bands && v16 && vstat && q8 && k8 && qa8 && ka8 && out && device_error, "attention: null buffers");
   TRI_CHECK((q_raw == nullptr) == (k_raw == nullptr), "attention: raw Q and K rows of un-quantised heads (both or none)");
   TRI_CHECK(q_raw == nullptr || (aligned16(q_raw) && aligned16(k_raw) && q_stride_b % 8 == 0 && q_stride_h % 8 == 0 &&
@@ -216,10 +219,12 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
   const bool int4 = q4x != nullptr;
   TRI_CHECK(int4 == (k4x != nullptr) && int4 == (qa4 != nullptr) && int4 == (ka4 != nullptr), "INT4 Q/K operands (all or none)");
-  TRI_CHECK(aligned16(out) && out_stride_t % 8 == 0 && out_stride_h % 8 == 0 && out_stride_b % 8 == 0,
+  TRI_CHECK(aligned16(out) && out_stride_t % 8 == 0 && out_stride_h % 8 == 0 && out_stride_b % 8 == 0 && out_stride_c % 8 == 0,
             "output [B,Hq,T,128] aligned");
   TRI_CHECK(aligned16(q8) && aligned16(q4x) && aligned16(k8) && aligned16(k4x) && aligned16(v16) && aligned16(v8h),
             "attention: operands must be 16-byte aligned");
+  const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
+  TRI_CHECK(configs >= 1 && configs <= 65535 && first_block >= 0 && first_block < rows, "attention: configurations / first query block");
   static TriPerDevice configured;
   const int device = configured.pending();
   TRI_CHECK(device != -2, "attention: no current CUDA device");
@@ -230,7 +235,6 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
     if (allow_smem(prefill_kernel<__half, true>, PrefillShared) != TRI_OK) return TRI_ERR_CUDA;
     configured.mark(device);
   }
-  const int units = batch * heads_q, rows = (tokens + BM - 1) / BM, quads = (rows + 3) / 4;
   CUtensorMap map8, map4, mapq, mapk;
   if (make_q_map(&map8, q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
   if (make_q_map(&map4, int4 ? q4x : q8, tokens, units) != TRI_OK) return TRI_ERR_CUDA;
@@ -243,13 +247,15 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sm_log2 = (float)(scale * 1.4426950408889634);
-  const dim3 grid((unsigned)((int64_t)quads * units));
+  // CTA x = (quads - 1 - quad) * units + unit, heaviest quads first: the first (quads - first_quad) * units CTAs are
+  // exactly the quads that hold query blocks >= first_block
+  const dim3 grid((unsigned)((int64_t)(quads - first_block / 4) * units), (unsigned)configs);
 #define TRI_LAUNCH(T, R)                                                                                                   \
   prefill_kernel<T, R><<<grid, PrefillThreads, PrefillShared, s>>>(map8, map4, mapq, mapk, has_raw, bands,                \
       static_cast<const uint8_t*>(k8),                                                                                     \
       static_cast<const uint8_t*>(k4x), ka8, ka4, static_cast<const uint8_t*>(v16), static_cast<const uint8_t*>(v8h), qa8, \
-      qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, heads_q, heads_kv, tokens, units,       \
-      sm_log2, device_error)
+      qa4, vstat, static_cast<T*>(out), out_stride_b, out_stride_h, out_stride_t, out_stride_c, heads_q, heads_kv, tokens, \
+      units, sm_log2, device_error)
   // quantised heads, then (if the map has any) the un-quantised ones: the same kernel, instantiated for each kind
   if (out_is_half) TRI_LAUNCH(__half, false); else TRI_LAUNCH(__nv_bfloat16, false);
   if (has_raw) {
@@ -257,6 +263,26 @@ extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* 
   }
 #undef TRI_LAUNCH
   return tri_launch_status("attention");
+}
+
+extern "C" int tri_attention(const int32_t* bands, const void* v16, const void* v8h, const float* vstat, const void* q8,
+    const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x, const float* qa4, const float* ka4,
+    void* out, int out_is_half, int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q,
+    int heads_kv, int tokens, double scale, const void* q_raw, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+    const void* k_raw, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t, int* device_error, void* stream) {
+  return launch_attention(bands, 1, 0, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, out_is_half, 0, out_stride_b,
+                          out_stride_h, out_stride_t, batch, heads_q, heads_kv, tokens, scale, q_raw, q_stride_b, q_stride_h,
+                          q_stride_t, k_raw, k_stride_b, k_stride_h, k_stride_t, device_error, stream);
+}
+
+extern "C" int tri_attention_sweep(const int32_t* bands, int configs, int first_block, const void* v16, const void* v8h,
+    const float* vstat, const void* q8, const void* k8, const float* qa8, const float* ka8, const void* q4x, const void* k4x,
+    const float* qa4, const float* ka4, void* out, int out_is_half, int64_t out_stride_c, int64_t out_stride_b,
+    int64_t out_stride_h, int64_t out_stride_t, int batch, int heads_q, int heads_kv, int tokens, double scale,
+    int* device_error, void* stream) {
+  return launch_attention(bands, configs, first_block, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, out_is_half,
+                          out_stride_c, out_stride_b, out_stride_h, out_stride_t, batch, heads_q, heads_kv, tokens, scale, nullptr,
+                          0, 0, 0, nullptr, 0, 0, 0, device_error, stream);
 }
 
 extern "C" int tri_qk_accumulators(const int32_t* requests, int num_requests, const void* q8, const void* q4x, const void* k8,

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const __grid_constant__ CUtensorMap map_q4, const __grid_constant__ CUtensorMap map_qraw,
     const __grid_constant__ CUtensorMap map_kraw, int has_raw, const int32_t* bands, const uint8_t* k8, const uint8_t* k4x, const float* ka8,
     const float* ka4, const uint8_t* v16, const uint8_t* v8h, const float* qa8, const float* qa4, const float* vstat, Out* out,
-    int64_t osb, int64_t osh, int64_t ost, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
+    int64_t osb, int64_t osh, int64_t ost, int64_t osc, int heads_q, int heads_kv, int tokens, int units_q, float sm_log2, int* err) {
   extern __shared__ uint8_t raw_smem[];
   __shared__ __align__(8) PrefillBarriers bars;
   __shared__ uint32_t tmem_slot;
@@ -87,6 +87,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   const int quad_id = quads - 1 - blockIdx.x / units_q, qunit = blockIdx.x % units_q;
   const int b = qunit / heads_q, h = qunit % heads_q, g = heads_q / heads_kv;
   const int64_t kvunit = (int64_t)b * heads_kv + h / g;
+  // blockIdx.y = band configuration of a sweep (one launch evaluates several maps over the same operands; 0 otherwise):
+  // its own [Hq,2] band table and its own output tensor.  gridDim.x may cover only the last query rows (heaviest first).
+  bands += (int64_t)blockIdx.y * heads_q * 2;
+  out += (int64_t)blockIdx.y * osc;
   const int w8 = bands[h * 2], w4 = bands[h * 2 + 1];
   // A head with w8 < 1 belongs to an un-quantised (BF16) KV group: exact attention over every causal tile, straight
   // from the raw bf16 Q and K rows (TMA tensor copies of the caller's tensors) and the fp16 V blobs.  Uniform for the CTA.

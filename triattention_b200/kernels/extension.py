@@ -25,6 +25,7 @@ SIGNATURES = {
     "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D,
                       _P, _L, _L, _L, _P, _L, _L, _L, _P, _P],
+    "tri_attention_sweep": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_attention_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_cache_store": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "tri_cache_store_bf16": [_P, _P, _P, _I, _P, _P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _I, _P],
@@ -200,6 +201,26 @@ class Module:
                                                _ptr(qa4), _ptr(ka4), out.data_ptr(), int(out.dtype == torch.float16),
                                                out.stride(0), out.stride(1), out.stride(2), b, hq, heads_kv, t,
                                                float(scale), *raw, self.error_word(out.device).data_ptr(), _stream()))
+        return out
+
+    def attention_sweep(self, bands, first_block, v16, v8h, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, row0, scale, heads_kv,
+                        tokens):
+        """bands int32 [C,Hq,2] on the device; out [C,B,Hq,R,128] holds query rows row0 .. row0+R-1 (row0 = the first row of
+        the four-block group that contains first_block); one launch evaluates every configuration on the same operands."""
+        if not (out.dim() == 5 and out.stride(4) == 1 and out.dtype in (torch.bfloat16, torch.float16)):
+            raise RuntimeError("output [C,B,Hq,R,128] aligned")
+        c, b, hq, r, _ = out.shape
+        if bands.dtype != torch.int32 or tuple(bands.shape) != (c, hq, 2) or not bands.is_contiguous():
+            raise RuntimeError("bands [C,Hq,2]")
+        if row0 != (first_block // 4) * 256 or row0 + r != tokens:
+            raise RuntimeError("the output holds the rows from the first computed group of query blocks to the end")
+        origin = out.data_ptr() - row0 * out.stride(3) * out.element_size()     # where row 0 would lie
+        with torch.cuda.device(out.device):
+            self._check(self.lib.tri_attention_sweep(bands.data_ptr(), c, int(first_block), _ptr(v16), _ptr(v8h), vstat.data_ptr(),
+                                                     q8.data_ptr(), k8.data_ptr(), qa8.data_ptr(), ka8.data_ptr(), _ptr(q4x),
+                                                     _ptr(k4x), _ptr(qa4), _ptr(ka4), origin, int(out.dtype == torch.float16),
+                                                     out.stride(0), out.stride(1), out.stride(2), out.stride(3), b, hq, heads_kv,
+                                                     int(tokens), float(scale), self.error_word(out.device).data_ptr(), _stream()))
         return out
 
     def attention_tasks(self, groups, entries, v16, v8, v4, vstat, q8, k8, qa8, ka8, q4x, k4x, qa4, ka4, out, scale, heads_kv):

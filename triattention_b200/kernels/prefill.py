@@ -142,3 +142,29 @@ class Prefill:
         if self.decode_cache is not None:
             self.decode_cache.store(layer, t, ops, table.host, k, v, table.bf16_kv)
         return out
+
+    def sweep(self, configs, q, k, v, scale, rows=None, out_dtype=None):
+        """Outputs of several uniform band maps over the same Q / K / V in one pass: one KV-cache write (the operands do
+        not depend on the map), one attention launch for all configurations, and only the query rows that are wanted.
+        The reference's calibration runs one full prefill per configuration (calibrate.py:46-63).
+        configs: list of (w8, w4) applied to every Q head; rows: evaluate only the last `rows` query rows (None = all).
+        Returns (out [C,B,Hq,R,128], row0): out[..., i, :] is query row row0 + i, with row0 <= T - rows."""
+        b, hq, t, _ = q.shape
+        hk, device = k.shape[1], q.device
+        bands = torch.tensor([[list(c)] * hq for c in configs], dtype=torch.int32)
+        if bands.dim() != 3 or bool((bands[:, :, 0] < 1).any()):
+            raise ValueError("configs must be (w8, w4) pairs with w8 >= 1")
+        # every operand format once: INT8 and INT4 codes of Q and K, the fp16 V' blob and the fp16 rendering of the V codes.
+        # (V is normalised by its statistics for all configurations; a configuration without any INT8 tile, which alone
+        # would run on un-normalised V like the reference's identity mode, common_host.cuh:39, differs by that rounding.)
+        ops = self.operands(b, hq, hk, t, True, False, frozenset({F16, I8, Q4}), device)
+        m = self.module
+        m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"], ops["qa4"],
+                     ops["k4x"], ops["ka4"], None)
+        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], None, ops["v8h"])
+        first_block = 0 if rows is None else max(0, (t - int(rows)) // 64)
+        row0 = (first_block // 4) * 256
+        out = torch.empty((len(configs), b, hq, t - row0, 128), dtype=out_dtype or q.dtype, device=device)
+        m.attention_sweep(bands.to(device), first_block, ops["v16"], ops["v8h"], ops["vstat"], ops["q8"], ops["k8"], ops["qa"],
+                          ops["ka"], ops["q4x"], ops["k4x"], ops["qa4"], ops["ka4"], out, row0, scale, hk, t)
+        return out, row0
