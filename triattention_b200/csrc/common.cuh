@@ -188,13 +188,17 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
   if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
-    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    // the hardware usually hands the warp back long before the hint runs out: the abort flag and the clock are looked
+    // at once per eight tries, so that a waiting warp costs the working ones few issue slots
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i)
+      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = 1; return false; }
+    if (globaltimer_ns() - t0 > 2000000000ull) { *abort_flag = site; return false; }   // site != 0: tells which wait gave up
   }
 }
 // 1-D bulk copy global -> shared; dst, src and bytes are multiples of 16.

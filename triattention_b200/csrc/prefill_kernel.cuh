@@ -37,7 +37,8 @@
 // integer-code products; the reference's float32 accumulator (biased by 12582912 per tile) is the noisier of the two.
 // Sink and diagonal tiles use fp16 weights and the fp16 V blob exactly like the reference.
 //
-// Every mbarrier wait has a time limit and obeys the CTA-wide abort flag.  The only other barrier inside
+// Every mbarrier wait has a time limit and obeys the CTA-wide abort flag (a wait that runs out leaves its site in the
+// flag, and the kernel reports it with the error word).  The only other barrier inside
 // the main loop is the 64-thread bar.sync of a softmax warp pair; both warps of a pair walk the same step
 // list and reach it the same number of times even after an abort (they then skip everything else).
 #pragma once
@@ -134,7 +135,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   const uint32_t tmem = tmem_slot;
   auto tile_of = [&](int i) { return (int)(step_tm[i] & 0xfffu); };
   auto mode_of = [&](int i) { return (int)(step_tm[i] >> 12); };
-  auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_parked(bar, parity & 1u, abortp); };
+  // site: which wait this is (reported with the error word when it runs out): 1 Q, 2 K stage free, 3 V stage free, 4 K landed,
+  // 5 score buffer free, 6 V landed, 7 / 8 P of tile 0 / 1, 9 scores, 11 O before a rescale, 12 last P.V; the softmax
+  // sites add the tile's step number << 8
+  auto wait = [&](uint64_t* bar, uint32_t parity, int site) { return mbar_wait_parked(bar, parity & 1u, abortp, site); };
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------------
@@ -154,7 +158,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       }
       for (int i = 0; i < nsteps; ++i) {
         const int tile = tile_of(i), mode = mode_of(i), s = i & kmask, vb = i & 1;
-        if (i > kmask && !wait(&bars.k_empty[s], (i >> kshift) - 1)) break;
+        if (i > kmask && !wait(&bars.k_empty[s], (i >> kshift) - 1, 2)) break;
         const int64_t ht = kvunit * tiles + tile;
         if (raw) {
           // the tile's 64 bf16 K rows from the caller's tensor: two boxes of 64 keys x 64 features
@@ -168,7 +172,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         }
         // the fp16 P.V operand of the step: V' itself for sink / diagonal tiles (and for every tile of an un-quantised
         // head, whose V' is V), the INT8 codes as fp16 numbers otherwise
-        if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1)) break;
+        if (i >= 2 && !wait(&bars.v16_empty[vb], (i - 2) >> 1, 3)) break;
         mbar_expect_tx(&bars.v16_full[vb], V16Bytes);
         bulk_g2s(smem + SmV16 + vb * V16Bytes, ((raw || mode == ModeF16) ? v16 : v8h) + ht * V16Bytes, V16Bytes, &bars.v16_full[vb]);
       }
@@ -190,17 +194,17 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const uint64_t dba = smem_desc(smem_u32(smem + SmBiasA), 128, 256, LayoutNone), dbb = smem_desc(smem_u32(smem + SmBiasB), 128, 256, LayoutNone);
       const uint32_t st = tmem + TmemS + x * 128;
       int nqk = 0;
-      bool ok = wait(&bars.q, 0);
+      bool ok = wait(&bars.q, 0, 1);
       const uint64_t dqr = smem_desc(smem_u32(smem + SmQ8 + x * 32768), 0, 1024, Layout128B);   // bf16 rows, both 128-byte swizzled
       const uint64_t dkr = smem_desc(smem_u32(smem + SmK), 0, 1024, Layout128B);
       for (int i = 0; ok && i < nsteps; ++i) {
         const int s = i & kmask;
         // every step, also those this tile sits out: an issuer that ran a ring round ahead would arrive twice on the
         // same k_empty phase
-        if (!(ok = wait(&bars.k_full[s], i >> kshift))) break;
+        if (!(ok = wait(&bars.k_full[s], i >> kshift, 4))) break;
         if ((step_mask[i] >> (2 * x)) & 3) {
           const int sb = nqk & 1;
-          if (nqk >= 2 && !(ok = wait(&bars.o_done[x][sb], (nqk - 2) >> 1))) break;
+          if (nqk >= 2 && !(ok = wait(&bars.o_done[x][sb], (nqk - 2) >> 1, 5))) break;
           tc_fence_after();
           if (raw) {
             // S = Q . K^T on bf16 rows, fp32 accumulators: 8 MMAs of 16 features; feature half hf sits in its own box
@@ -231,11 +235,11 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       for (int i = 0; ok && i < nsteps; ++i) {
         const int mask = step_mask[i], vb = i & 1;
         const bool two_part = !raw && mode_of(i) != ModeF16;   // quantised weights come as high + low fp16 parts
-        if (!(ok = wait(&bars.v16_full[vb], i >> 1))) break;
+        if (!(ok = wait(&bars.v16_full[vb], i >> 1, 6))) break;
         const uint64_t dvs = at(dv, vb * V16Bytes);
         if (mask & 3) {
           const int pb = npv0 & 1;
-          if (!(ok = wait(&bars.p_full[0][pb], npv0 >> 1))) break;
+          if (!(ok = wait(&bars.p_full[0][pb], npv0 >> 1, 7))) break;
           tc_fence_after();
           // P: key group kk (16 keys = 8 columns of fp16 pairs) sits in the first half of the 32 score columns of the
           // thread that computed it: columns 0-15 (keys 0-31) and 32-47 (keys 32-63) of score buffer pb
@@ -252,7 +256,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
         }
         if (mask & 12) {
           const int pb = npv1 & 1;
-          if (!(ok = wait(&bars.p_full[1][pb], npv1 >> 1))) break;
+          if (!(ok = wait(&bars.p_full[1][pb], npv1 >> 1, 8))) break;
           tc_fence_after();
           const uint32_t pt = tmem + TmemS + 128 + pb * 64;
 #pragma unroll
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, keys in natural
       // order like both fp16 V blobs
 
-      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1));
+      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1, 9 | (n << 8)));
       if (ok) tc_fence_after();
       // The tile's K scales came with the tile (the ring slot is not reused before step i+8, and the producer
       // cannot be more than 4 steps ahead of a softmax warp).
@@ -371,7 +375,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           denom *= factor;
         }
         if (n > 0 && __any_sync(0xffffffffu, move)) {
-          ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1));
+          ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 11 | (n << 8)));
           if (ok) {
             tc_fence_after();
 #pragma unroll
@@ -496,7 +500,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 
     // ---- epilogue: O / denominator, de-normalised (prefill_sm80.cu:466-487) ----------------------------
     if (n > 0) {
-      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1));
+      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 12 | (n << 8)));
       if constexpr (RowSplit == 2) {
         xchg[x][n & 1][ch][row] = denom;
         pair_sync(pair_id);
@@ -531,9 +535,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  const bool failed = *abortp != 0;
+  const int failed = *abortp;
   if (failed) {   // a wait ran out: give copies / MMAs that may still be in flight a bounded time before the CTA goes away
-    if (tid == 0) atomicExch(err, ErrBarrierTimeout);
+    if (tid == 0) atomicExch(err, ErrBarrierTimeout | (failed << 8));   // upper bits: which wait (site, and the tile's step)
     const uint64_t t_abort = globaltimer_ns();
     while (globaltimer_ns() - t_abort < 2000000ull) {}
     __syncthreads();

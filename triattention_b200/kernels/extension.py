@@ -110,9 +110,10 @@ class Module:
             word = int(self._errors[key].item())
             if word:
                 self._errors[key].zero_()
-                raise RuntimeError(f"TriAttention kernel reported device error {word} on cuda:{key} (1 = barrier wait ran "
-                                   "out, 3 = tile number outside the prompt in a task table, 4 = partial slot outside the "
-                                   "buffer)")
+                where = f", wait site {(word >> 8) & 0xff} at step {word >> 16} of the prefill kernel" if word >> 8 else ""
+                raise RuntimeError(f"TriAttention kernel reported device error {word & 0xff} on cuda:{key}{where} (1 = "
+                                   "barrier wait ran out, 3 = tile number outside the prompt in a task table, 4 = partial "
+                                   "slot outside the buffer)")
 
     @staticmethod
     def _bhtd(x, name):
