@@ -64,6 +64,13 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 __device__ __forceinline__ constexpr uint32_t p_column(int kk) { return RowSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; }
 constexpr uint32_t PLow = 32 / RowSplit;   // the low parts of the quantised weights sit behind the high parts: a thread's score
                                            // columns (64 / RowSplit) hold its high parts in their first half, its low parts in the second
+// Two fp32 fused multiply-adds in one instruction (fma.rn.ftz.f32x2): each lane rounds exactly like the scalar fma, so the
+// results are bit-identical; it halves the issue slots of the two fmas every score costs.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.ftz.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -457,10 +464,15 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             for (int hb = 0; hb < 2; ++hb) {
               uint32_t w[8];
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
+              for (int u = 0; u < 8; u += 2) {   // two scores per fused multiply-add
                 const int j = 8 * hb + u;
-                const float sc = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
-                w[u] = __float_as_uint(fmaf(exp2f(fmaf(slope[cc], sc, off)), 255.f, PMagic64));
+                const float s0 = Int4 ? __uint_as_float(a[cc][j]) - 12582912.f : __uint_as_float(a[cc][j]);
+                const float s1 = Int4 ? __uint_as_float(a[cc][j + 1]) - 12582912.f : __uint_as_float(a[cc][j + 1]);
+                float x0, x1, y0, y1;
+                ffma2(x0, x1, slope[cc], slope[cc], s0, s1, off, off);
+                ffma2(y0, y1, exp2f(x0), exp2f(x1), 255.f, 255.f, PMagic64, PMagic64);
+                w[u] = __float_as_uint(y0);
+                w[u + 1] = __float_as_uint(y1);
               }
               const uint32_t h0 = __byte_perm(w[0], w[1], 0x6521), h1 = __byte_perm(w[2], w[3], 0x6521);   // (1024 + code) x 2 as fp16
               const uint32_t h2 = __byte_perm(w[4], w[5], 0x6521), h3 = __byte_perm(w[6], w[7], 0x6521);
