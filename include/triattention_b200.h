@@ -59,6 +59,22 @@ int tri_pack_v(const void* v, int batch, int heads_kv, int tokens,
                float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h,
                const int32_t* raw_heads, void* stream);
 
+/* tri_prepare_qk and tri_pack_v as ONE call (no counterpart in the reference, whose executor makes the two calls one
+ * after the other, triattention/kernels/prefill.py:99-101): same arguments, same kernels and bit-identical results, but
+ * the three independent chains — Q (one bandwidth-bound kernel), K (statistics, then codes) and V (statistics, then
+ * blobs) — run side by side: Q on `stream`, K and V on two streams owned by the library that start behind everything
+ * already queued on `stream` and that `stream` waits for before the call's results can be used.  partial_k and partial_v
+ * are two scratch buffers of the size tri_prepare_qk / tri_pack_v document (they must differ).  Safe to call from
+ * several host threads (calls on one device take turns for the time it takes to queue the launches). */
+int tri_write_kv(const void* q, const void* k, const void* v, int batch, int heads_q, int heads_kv, int tokens,
+                 int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                 int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                 int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+                 void* q8, float* qa, void* k8, float* ka, float* partial_k, float* kstat,
+                 void* q4x, float* qa4, void* k4x, void* k4, float* ka4, const int32_t* q_modes,
+                 float* partial_v, float* vstat, void* v16, void* v8, void* v4, void* v8h,
+                 const int32_t* raw_heads, void* stream);
+
 /* Quantise K and V rows that arrive after the prompt with the prompt's statistics (no statistics pass): K8 blobs
  * and scales as tri_prepare_qk writes them, V8 blobs as tri_pack_v writes them, rows >= tokens zero.  The decode cache
  * uses it to turn 64 generated tokens of the BF16 tail into one more cached tile (no counterpart in the reference,

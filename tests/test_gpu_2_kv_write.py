@@ -189,3 +189,48 @@ def test_q_modes_skip_what_the_attention_does_not_read(module):
     assert (q4[:, 2:4] == full["q4"][:, 2:4]).all() and (qa4[:, 2:4] == full["qa4"][:, 2:4]).all()
     assert (q8[:, 4:] == -128).all() and (qa[:, 4:] == -1).all()                    # un-quantised heads: untouched
     assert (q4[:, :2] == -128).all() and (q4[:, 4:] == -128).all() and (qa4[:, :2] == -1).all()
+
+
+@pytest.mark.parametrize("case", ["all-formats", "int8-only", "identity-v", "raw-head-and-modes"])
+def test_fused_write_equals_the_two_calls(module, case):
+    """tri_write_kv (Q, K and V chains side by side on three streams) leaves byte for byte what prepare_qk followed by
+    pack_v leave, and the caller's stream sees the finished buffers: copies queued right behind the call, on a stream of
+    the caller's, are compared."""
+    b, hq, hk, t = 2, 4, 2, 777
+    q, k, v = (bf16_cuda(x) for x in make_inputs(hq, hk, t, seed=31, batch=b))
+    int4 = case in ("all-formats", "raw-head-and-modes")
+    formats = frozenset({F16}) if case == "identity-v" else frozenset({F16, I8, I4} if int4 else {F16, I8})
+    q_modes = raw = None
+    if case == "raw-head-and-modes":
+        q_modes = torch.tensor([1, 3, 0, 2], dtype=torch.int32, device="cuda")
+        raw = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    names = ("q8", "qa", "k8", "ka", "kstat", "vstat", "q4x", "qa4", "k4x", "ka4", "k4", "v16", "v8", "v4", "v8h")
+
+    def fresh():
+        ops = Prefill(module, None).operands(b, hq, hk, t, int4, int4, formats, "cuda")
+        for name in names:
+            if ops[name] is not None:
+                ops[name].view(torch.uint8).fill_(0x5a)     # rows the modes leave untouched stay as they were in both
+        return ops
+
+    two = fresh()
+    module.prepare_qk(q, k, two["q8"], two["qa"], two["k8"], two["ka"], two["partial"], two["kstat"], two["q4x"], two["qa4"],
+                      two["k4x"], two["ka4"], two["k4"], q_modes=q_modes)
+    module.pack_v(v, two["partial"], two["vstat"], two["v16"], two["v8"], two["v4"], two["v8h"], raw_heads=raw)
+    want = {n: two[n].clone() for n in names if two[n] is not None}
+    one = fresh()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):      # repeated calls reuse the library's side streams and events
+            module.write_kv(q, k, v, one["q8"], one["qa"], one["k8"], one["ka"], one["partial"], one["kstat"], one["partial_v"],
+                            one["vstat"], one["q4x"], one["qa4"], one["k4x"], one["ka4"], one["k4"], q_modes=q_modes,
+                            v16=one["v16"], v8=one["v8"], v4=one["v4"], v8h=one["v8h"], raw_heads=raw)
+        got = {n: one[n].clone() for n in want}
+    stream.synchronize()
+    for n in want:
+        assert torch.equal(got[n].view(torch.uint8), want[n].view(torch.uint8)), n
+    with pytest.raises(RuntimeError):       # the two statistics passes run at the same time: one scratch buffer each
+        module.write_kv(q, k, v, one["q8"], one["qa"], one["k8"], one["ka"], one["partial"], one["kstat"], one["partial"],
+                        one["vstat"], one["q4x"], one["qa4"], one["k4x"], one["ka4"], one["k4"], v16=one["v16"], v8=one["v8"],
+                        v4=one["v4"], v8h=one["v8h"])

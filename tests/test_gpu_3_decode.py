@@ -266,7 +266,7 @@ def test_store_in_parts_equals_store_at_once(module):
 
 
 @pytest.mark.parametrize("exchange", ["nccl", "peer"])
-@pytest.mark.parametrize("world,ctas", [(2, None), (3, 5)])
+@pytest.mark.parametrize("world,ctas", [(2, None), (3, 5), (8, None)])
 def test_sequence_split_emulated_on_one_gpu(module, world, ctas, exchange):
     """The sequence-split path without a process group: `world` caches each hold one part of every unit's tile range
     (what the ranks of a split group hold) and each runs its split pass with the in-kernel fold (tri_decode_partials).
@@ -347,8 +347,9 @@ def test_exchange_wait_runs_out_without_hanging(module):
     assert np.isfinite(whole).all()                         # and the GPU still computes
 
 
-def test_output_gather_by_peer_stores_emulated_on_one_gpu(module):
-    """Units sharded over two "ranks" held by this process on one GPU: each part's merge kernel stores its output rows into
+@pytest.mark.parametrize("layout", ["two-parts", "eight-parts"])
+def test_output_gather_by_peer_stores_emulated_on_one_gpu(module, layout):
+    """Units sharded over two (or eight) "ranks" held by this process on one GPU: each part's merge kernel stores its output rows into
     the full output tensor of both parts (their gather buffers, here ordinary device memory), the last CTA raises the
     part's flag in both, and the wait kernel of each part then finds both flags set (all producers are launched before any
     consumer, so nothing ever waits for a later launch).  The full tensor equals the un-sharded decode, bit for bit per
@@ -360,35 +361,38 @@ def test_output_gather_by_peer_stores_emulated_on_one_gpu(module):
     q, k, v = make_inputs(hq, hk, t, seed=81, batch=batch)
     qd, kd, vd = make_inputs(hq, hk, 3, seed=82, batch=batch)
     whole, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=3)
-    shards = [sharding.Shard(0, slice(0, 2), (0, 3)), sharding.Shard(1, slice(0, 2), (1, 2))]     # head groups, not in order
+    if layout == "two-parts":
+        shards = [sharding.Shard(0, slice(0, 2), (0, 3)), sharding.Shard(1, slice(0, 2), (1, 2))]     # head groups, not in order
+    else:       # one (sequence, KV head) unit per part, as an 8-GPU placement of few heavy units gives
+        shards = [sharding.Shard(r, slice(r // 4, r // 4 + 1), ((r * 3) % 4,)) for r in range(8)]
+    nbytes = sharding.PeerOutputGatherer.buffer_bytes(batch, hq, len(shards))
     fn = bands_fn_of(bands)
-    nbytes = sharding.PeerOutputGatherer.buffer_bytes(batch, hq, 2)
     buffers = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in shards]
     parts = []
     for s in shards:
         heads, qh = list(s.kv_heads), list(s.q_heads(g))
         cache = DecodeCache(module, max_tail=8)
         pre = Prefill(module, sharding.slice_map(fn, s, g, hq), cache)
-        take = lambda x, hs: bf16_cuda(np.ascontiguousarray(x[:, hs]))
+        take = lambda x, hs, s=s: bf16_cuda(np.ascontiguousarray(x[s.batch][:, hs]))
         table, ops = pre.write(0, take(q, qh), take(k, heads), take(v, heads))
         cache.store(0, t, ops, table.host, take(k, heads), take(v, heads), table.bf16_kv)
         gather = sharding.PeerOutputGatherer(module, shards, g, batch, hq, "cuda", rank=s.rank, buffers=buffers)
-        parts.append((cache, gather, heads, qh))
+        parts.append((cache, gather, heads, qh, s.batch))
     outs = []
     for step in range(3):
-        for cache, gather, heads, qh in parts:          # every producer first: split pass + merge with peer stores
+        for cache, gather, heads, qh, seqs in parts:          # every producer first: split pass + merge with peer stores
             e, d = cache.layers[0], cache.layers[0]["dev"]
-            qs, ks, vs = (bf16_cuda(np.ascontiguousarray(x[:, hs, step:step + 1])) for x, hs in ((qd, qh), (kd, heads), (vd, heads)))
+            qs, ks, vs = (bf16_cuda(np.ascontiguousarray(x[seqs][:, hs, step:step + 1])) for x, hs in ((qd, qh), (kd, heads), (vd, heads)))
             module.decode(qs, e["pool"], d["unit_base"], d["unit_tab"], d["unit_flags"], d["tmeta"], d["segments"],
                           d["cta_segments"], d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"], ks, vs, cache.step,
                           qs, e["pm"], e["pl"], e["po"], e["prompt"], SCALE, 1)
             module.decode_merge(qs, e["pm"], e["pl"], e["po"], 0, d["unit_slots"], e["kstat"], e["vstat"], e["tail_k"], e["tail_v"],
                                 ks, vs, cache.step, qs, SCALE, gather=gather.arguments())
-        fulls = [gather.wait().float().cpu().numpy()[:, :, 0] for _, gather, _, _ in parts]      # then the consumers
-        for cache, _, _, _ in parts:
+        fulls = [gather.wait().float().cpu().numpy()[:, :, 0] for _, gather, _, _, _ in parts]      # then the consumers
+        for cache, _, _, _, _ in parts:
             cache.advance()
-        assert (fulls[0] == fulls[1]).all()
+        assert all((f == fulls[0]).all() for f in fulls)
         outs.append(fulls[0])
     module.check_device_error()
-    assert all(int(gather.seen.item()) == 3 and gather.sync.tolist() == [0, 3] for _, gather, _, _ in parts)
-    assert_fp_close(np.stack(outs, 1), whole, "units sharded over two parts, outputs gathered by peer stores")
+    assert all(int(gather.seen.item()) == 3 and gather.sync.tolist() == [0, 3] for _, gather, _, _, _ in parts)
+    assert_fp_close(np.stack(outs, 1), whole, f"units sharded over {len(shards)} parts, outputs gathered by peer stores")

@@ -329,9 +329,12 @@ __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float*
 // CTA's fold buffer as scratch for the tail scores: up to ConsumerWarps Q heads per round, one warp per head.
 // All ConsumerWarps*32 threads call it.  Partials: split s of head r at pm[(first*8 + r) + s*ml_stride] (see
 // decode_merge_kernel).
-__device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
+// part = 0: everything; 1: only what does not need the partials (the tail append and, when all Q heads fit one round, their
+// tail scores), returning whether the scores are in `scratch`; 2: the rest, given that part 1 returned true.  Splitting it
+// lets the CTA do part 1 while the other GPUs' triples are still on their way.
+__device__ __forceinline__ bool merge_unit_by_consumers(const MergeArgs& a, const float* pm, const float* pl, const float* po,
     int64_t first_slot, int64_t ml_stride, int64_t o_stride, int nsplit, const __nv_bfloat16* q, int64_t qsb, int64_t qsh,
-    int unit, int heads_kv, int g, float sm_log2, float* scratch) {
+    int unit, int heads_kv, int g, float sm_log2, float* scratch, int part = 0) {
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   const int b = unit / heads_kv, kh = unit % heads_kv;
   const int prior = min((int)*a.step, a.max_tail - 1), tail = prior + 1;
@@ -339,16 +342,19 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
   const __nv_bfloat16* vc = a.vcur + b * a.csb + kh * a.csh;
   __nv_bfloat16* kt = a.ktail + unit * a.tsu;
   __nv_bfloat16* vt = a.vtail + unit * a.tsu;
-  if (tid < D) {   // append the current token to the tail (read back only by later steps)
+  if (part != 2 && tid < D) {   // append the current token to the tail (read back only by later steps)
     kt[prior * a.tst + tid] = kc[tid];
     vt[prior * a.tst + tid] = vc[tid];
   }
   const int per_round = min(min(g, ConsumerWarps), (ConsumerWarps * CombFloats) / tail);   // >= 6 for tails up to 1024 rows
+  if (part == 1 && per_round < g) return false;
   for (int h0 = 0; h0 < g; h0 += per_round) {
     const int nh = min(per_round, g - h0);
     const __nv_bfloat16* qrows = q + b * qsb + (int64_t)(kh * g + h0) * qsh;
-    unit_tail_scores(qrows, qsh, nh, a.kstat + (int64_t)unit * StatFloats, kt, a.tst, kc, prior, tail, sm_log2, scratch, tail,
-                     warp, ConsumerWarps, lane);
+    if (part != 2)
+      unit_tail_scores(qrows, qsh, nh, a.kstat + (int64_t)unit * StatFloats, kt, a.tst, kc, prior, tail, sm_log2, scratch, tail,
+                       warp, ConsumerWarps, lane);
+    if (part == 1) return true;    // (the caller's next barrier orders the scores before part 2 reads them)
     consumer_sync();
     if (warp < nh)
       merge_head_by_warp(pm, pl, po, first_slot * MaxGroup + h0 + warp, ml_stride, o_stride, nsplit, scratch + warp * tail, tail,
@@ -356,6 +362,7 @@ __device__ __forceinline__ void merge_unit_by_consumers(const MergeArgs& a, cons
                          a.out + b * a.osb + (int64_t)(kh * g + h0 + warp) * a.osh, lane);
     consumer_sync();   // scratch is reused by the next round (and by the next segment's fold)
   }
+  return true;
 }
 
 // ---- exchange of folded triples between the GPUs of a sequence-split group, over peer memory ----------------------
@@ -631,12 +638,14 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
           if (ch == 0) { pm[idx] = big; pl[idx] = l; }
         }
       }
-      if (margs.unit_done != nullptr) __threadfence();   // this segment's partial is visible device-wide
-      consumer_sync();   // the fold buffer is free for the next segment
+      consumer_sync();   // the fold buffer is free for the next segment; every consumer thread's stores of the partial are done
       if (margs.unit_done != nullptr) {
         // Fused merge: whoever finishes a unit's last segment merges the unit (its partials, the BF16 tail
         // and the output) right here, while the producer warp keeps prefetching the next segment.
         if (tid == 0) {
+          // One fence for the CTA: the barrier ordered the other threads' stores before it, and a fence is cumulative, so
+          // the partial is visible device-wide before the count moves (192 fences per segment cost microseconds).
+          __threadfence();
           const int done = atomicAdd(&margs.unit_done[unit], 1);
           const int last = done == margs.unit_slots[unit].y - 1;
           if (last) margs.unit_done[unit] = 0;   // ready for the next launch
@@ -658,6 +667,9 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
               consumer_sync();                      // (also makes epoch[unit], just advanced by thread 0, visible)
               const int e = margs.epoch[unit];
               float* local = margs.peers[margs.rank];
+              // what the merge needs besides the triples (tail append, tail scores) is done while they travel
+              const bool scored = merge_unit_by_consumers(margs, nullptr, nullptr, nullptr, 0, 0, 0, 0, q, qsb, qsh, unit, heads_kv, g,
+                                                          sm_log2, comb, 1);
               if (tid < margs.world && tid != margs.rank && margs.present[(int64_t)tid * margs.units + unit]) {
                 const int32_t* flag = reinterpret_cast<const int32_t*>(local + exchange_flag_offset(margs.world, margs.rank_stride)) +
                                       (int64_t)tid * margs.units + unit;
@@ -673,7 +685,7 @@ __global__ void __launch_bounds__(DecodeThreads, 1) decode_kernel(const __nv_bfl
                 const float* block = local + (int64_t)(e & 1) * margs.world * margs.rank_stride;
                 const int64_t ug = (int64_t)margs.units * MaxGroup;
                 merge_unit_by_consumers(margs, block, block + ug, block + 2 * ug, unit, margs.rank_stride, margs.rank_stride,
-                                        margs.world, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb);
+                                        margs.world, q, qsb, qsh, unit, heads_kv, g, sm_log2, comb, scored ? 2 : 0);
               }
             }
           } else {

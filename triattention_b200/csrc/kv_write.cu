@@ -425,6 +425,81 @@ __global__ void __launch_bounds__(256) pack_v_kernel(const __nv_bfloat16* v, con
 
 using namespace tri;
 
+// ---- argument checks and launch chains shared by the entry points --------------------------------------------------
+struct QkArgs {
+  const void *q, *k;
+  int batch, heads_q, heads_kv, tokens;
+  int64_t qsb, qsh, qst, ksb, ksh, kst;
+  void* q8; float* qa; void* k8; float* ka; float* partial; float* kstat;
+  void* q4x; float* qa4; void* k4x; void* k4; float* ka4; const int32_t* q_modes;
+};
+struct VArgs {
+  const void* v;
+  int batch, heads_kv, tokens;
+  int64_t vsb, vsh, vst;
+  float* partial; float* vstat; void *v16, *v8, *v4, *v8h; const int32_t* raw_heads;
+};
+
+static int check_qk(const QkArgs& a) {
+  TRI_CHECK(a.q && a.k && a.q8 && a.qa && a.k8 && a.ka && a.partial && a.kstat, "prepare_qk: null Q/K buffers");
+  TRI_CHECK(a.batch > 0 && a.heads_q > 0 && a.heads_kv > 0 && a.tokens > 0 && a.heads_q % a.heads_kv == 0, "prepare_qk: bad geometry");
+  TRI_CHECK((a.tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
+  const bool int4 = a.q4x != nullptr;
+  TRI_CHECK(int4 == (a.qa4 != nullptr) && int4 == (a.k4x != nullptr) && int4 == (a.ka4 != nullptr) && (int4 || a.k4 == nullptr),
+            "INT4 Q/K buffers (all or none)");
+  TRI_CHECK(aligned16(a.q) && aligned16(a.k) && a.qsb % 8 == 0 && a.qsh % 8 == 0 && a.qst % 8 == 0 && a.ksb % 8 == 0 &&
+            a.ksh % 8 == 0 && a.kst % 8 == 0, "BF16 Q/K [B,H,T,128] with contiguous features, 16-byte aligned rows");
+  TRI_CHECK(aligned16(a.q8) && aligned16(a.k8) && aligned16(a.q4x) && aligned16(a.k4x) && aligned16(a.k4) && aligned16(a.kstat),
+            "prepare_qk: output buffers must be 16-byte aligned");
+  return TRI_OK;
+}
+static int check_v(const VArgs& a) {
+  TRI_CHECK(a.v && a.partial && a.vstat, "pack_v: null V buffers");
+  TRI_CHECK(a.batch > 0 && a.heads_kv > 0 && a.tokens > 0, "pack_v: bad geometry");
+  TRI_CHECK(aligned16(a.v) && a.vsb % 8 == 0 && a.vsh % 8 == 0 && a.vst % 8 == 0, "BF16 V [B,Hkv,T,128]");
+  TRI_CHECK(aligned16(a.v16) && aligned16(a.v8) && aligned16(a.v4) && aligned16(a.v8h) && aligned16(a.vstat), "packed V alignment");
+  return TRI_OK;
+}
+// the three chains are independent of one another: Q (one kernel), K (statistics, then codes), V (statistics, then blobs)
+static void launch_q(const QkArgs& a, cudaStream_t s) {
+  launch_chained(quantize_q_kernel, dim3((a.tokens + 31) / 32, a.batch * a.heads_q), dim3(128), 0, s,
+      static_cast<const __nv_bfloat16*>(a.q), static_cast<int8_t*>(a.q8), a.qa, static_cast<int8_t*>(a.q4x), a.qa4, a.q_modes,
+      a.tokens, a.heads_q, a.qsb, a.qsh, a.qst);
+}
+static void launch_k(const QkArgs& a, cudaStream_t s) {
+  const int tiles = (a.tokens + BN - 1) / BN, uk = a.batch * a.heads_kv;
+  const auto* kp = static_cast<const __nv_bfloat16*>(a.k);
+  launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, a.partial, nullptr, a.tokens, a.heads_kv,
+      a.ksb, a.ksh, a.kst, 0, 0, 0);
+  launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, a.partial, nullptr, a.kstat, nullptr, a.tokens, 0,
+      static_cast<const int32_t*>(nullptr), a.heads_kv);
+  launch_chained(quantize_k_kernel, dim3(tiles, uk), dim3(128), 0, s, kp, a.kstat, static_cast<uint8_t*>(a.k8), a.ka,
+      static_cast<uint8_t*>(a.k4x), static_cast<uint8_t*>(a.k4), a.ka4, a.tokens, a.heads_kv, a.ksb, a.ksh, a.kst);
+}
+static void launch_v(const VArgs& a, cudaStream_t s) {
+  const int tiles = (a.tokens + BN - 1) / BN, uk = a.batch * a.heads_kv;
+  const auto* vp = static_cast<const __nv_bfloat16*>(a.v);
+  const int identity = (a.v8 == nullptr && a.v4 == nullptr && a.v8h == nullptr) ? 1 : 0;  // common_host.cuh:39
+  if (!identity)
+    launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 2), dim3(D), 0, s, nullptr, vp, nullptr, a.partial, a.tokens, a.heads_kv,
+        0, 0, 0, a.vsb, a.vsh, a.vst);
+  launch_chained(stats_finalize_kernel, dim3(uk, 2), dim3(D), 0, s, nullptr, a.partial, nullptr, a.vstat, a.tokens, identity,
+      a.raw_heads, a.heads_kv);
+  launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, vp, a.vstat, static_cast<uint8_t*>(a.v16), static_cast<uint8_t*>(a.v8),
+      static_cast<uint8_t*>(a.v4), static_cast<uint8_t*>(a.v8h), a.tokens, a.heads_kv, a.vsb, a.vsh, a.vst, a.raw_heads);
+}
+
+// Two side streams and three events per device for tri_write_kv, made on first use.  The mutex is held from the fork to
+// the join of one call, so that two host threads never re-record an event the other is still waiting on.
+#include <mutex>
+struct WriteLanes {
+  std::mutex lock;
+  bool ready = false;
+  cudaStream_t side[2];
+  cudaEvent_t fork, join[2];
+};
+static WriteLanes g_lanes[TriPerDevice::MaxDevices];
+
 // ------------------------------------------------------------------------------------------------
 // C ABI
 // ------------------------------------------------------------------------------------------------
@@ -432,51 +507,67 @@ extern "C" int tri_prepare_qk(const void* q, const void* k, int batch, int heads
     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t, int64_t k_stride_b, int64_t k_stride_h,
     int64_t k_stride_t, void* q8, float* qa, void* k8, float* ka, float* partial, float* kstat, void* q4x,
     float* qa4, void* k4x, void* k4, float* ka4, const int32_t* q_modes, void* stream) {
-  TRI_CHECK(q && k && q8 && qa && k8 && ka && partial && kstat, "prepare_qk: null Q/K buffers");
-  TRI_CHECK(batch > 0 && heads_q > 0 && heads_kv > 0 && tokens > 0 && heads_q % heads_kv == 0, "prepare_qk: bad geometry");
-  TRI_CHECK((tokens + BN - 1) / BN <= MaxTiles, "at most 131072 tokens");
-  const bool int4 = q4x != nullptr;
-  TRI_CHECK(int4 == (qa4 != nullptr) && int4 == (k4x != nullptr) && int4 == (ka4 != nullptr) && (int4 || k4 == nullptr),
-            "INT4 Q/K buffers (all or none)");
-  TRI_CHECK(aligned16(q) && aligned16(k) && q_stride_b % 8 == 0 && q_stride_h % 8 == 0 && q_stride_t % 8 == 0 &&
-            k_stride_b % 8 == 0 && k_stride_h % 8 == 0 && k_stride_t % 8 == 0,
-            "BF16 Q/K [B,H,T,128] with contiguous features, 16-byte aligned rows");
-  TRI_CHECK(aligned16(q8) && aligned16(k8) && aligned16(q4x) && aligned16(k4x) && aligned16(k4) && aligned16(kstat),
-            "prepare_qk: output buffers must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int tiles = (tokens + BN - 1) / BN, uq = batch * heads_q, uk = batch * heads_kv;
-  const auto* qp = static_cast<const __nv_bfloat16*>(q);
-  const auto* kp = static_cast<const __nv_bfloat16*>(k);
-  launch_chained(quantize_q_kernel, dim3((tokens + 31) / 32, uq), dim3(128), 0, s, qp, static_cast<int8_t*>(q8), qa,
-      static_cast<int8_t*>(q4x), qa4, q_modes, tokens, heads_q, q_stride_b, q_stride_h, q_stride_t);
-  launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 1), dim3(D), 0, s, kp, nullptr, partial, nullptr, tokens, heads_kv,
-      k_stride_b, k_stride_h, k_stride_t, 0, 0, 0);
-  launch_chained(stats_finalize_kernel, dim3(uk, 1), dim3(D), 0, s, partial, nullptr, kstat, nullptr, tokens, 0,
-      static_cast<const int32_t*>(nullptr), heads_kv);
-  launch_chained(quantize_k_kernel, dim3(tiles, uk), dim3(128), 0, s, kp, kstat, static_cast<uint8_t*>(k8), ka,
-      static_cast<uint8_t*>(k4x), static_cast<uint8_t*>(k4), ka4, tokens, heads_kv, k_stride_b, k_stride_h, k_stride_t);
+  const QkArgs a{q, k, batch, heads_q, heads_kv, tokens, q_stride_b, q_stride_h, q_stride_t, k_stride_b, k_stride_h, k_stride_t,
+                 q8, qa, k8, ka, partial, kstat, q4x, qa4, k4x, k4, ka4, q_modes};
+  if (const int rc = check_qk(a)) return rc;
+  launch_q(a, static_cast<cudaStream_t>(stream));
+  launch_k(a, static_cast<cudaStream_t>(stream));
   return tri_launch_status("prepare_qk");
 }
 
 extern "C" int tri_pack_v(const void* v, int batch, int heads_kv, int tokens, int64_t v_stride_b, int64_t v_stride_h,
     int64_t v_stride_t, float* partial, float* vstat, void* v16, void* v8, void* v4, void* v8h, const int32_t* raw_heads,
     void* stream) {
-  TRI_CHECK(v && partial && vstat, "pack_v: null V buffers");
-  TRI_CHECK(batch > 0 && heads_kv > 0 && tokens > 0, "pack_v: bad geometry");
-  TRI_CHECK(aligned16(v) && v_stride_b % 8 == 0 && v_stride_h % 8 == 0 && v_stride_t % 8 == 0, "BF16 V [B,Hkv,T,128]");
-  TRI_CHECK(aligned16(v16) && aligned16(v8) && aligned16(v4) && aligned16(v8h) && aligned16(vstat), "packed V alignment");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int tiles = (tokens + BN - 1) / BN, uk = batch * heads_kv;
-  const auto* vp = static_cast<const __nv_bfloat16*>(v);
-  const int identity = (v8 == nullptr && v4 == nullptr && v8h == nullptr) ? 1 : 0;  // common_host.cuh:39
-  if (!identity)
-    launch_chained(stats_partial_kernel, dim3(StatBlocks, uk, 2), dim3(D), 0, s, nullptr, vp, nullptr, partial, tokens, heads_kv, 0, 0, 0,
-        v_stride_b, v_stride_h, v_stride_t);
-  launch_chained(stats_finalize_kernel, dim3(uk, 2), dim3(D), 0, s, nullptr, partial, nullptr, vstat, tokens, identity, raw_heads,
-      heads_kv);
-  launch_chained(pack_v_kernel, dim3(tiles, uk), dim3(256), 0, s, vp, vstat, static_cast<uint8_t*>(v16), static_cast<uint8_t*>(v8),
-      static_cast<uint8_t*>(v4), static_cast<uint8_t*>(v8h), tokens, heads_kv, v_stride_b, v_stride_h, v_stride_t, raw_heads);
+  const VArgs a{v, batch, heads_kv, tokens, v_stride_b, v_stride_h, v_stride_t, partial, vstat, v16, v8, v4, v8h, raw_heads};
+  if (const int rc = check_v(a)) return rc;
+  launch_v(a, static_cast<cudaStream_t>(stream));
   return tri_launch_status("pack_v");
+}
+
+// tri_prepare_qk and tri_pack_v as one call whose three chains run side by side: the Q kernel on the caller's stream, the
+// K and V chains on two high-priority streams of the library that start behind everything already in the caller's
+// stream and that the caller's stream waits for before the call's results are used.  The Q kernel is bound by memory
+// bandwidth, the K and V chains by the latency of their small launches, so together they take about as long as the Q
+// kernel alone.  partial_k and partial_v must be different buffers.
+extern "C" int tri_write_kv(const void* q, const void* k, const void* v, int batch, int heads_q, int heads_kv, int tokens,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+    int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t, void* q8, float* qa, void* k8, float* ka, float* partial_k,
+    float* kstat, void* q4x, float* qa4, void* k4x, void* k4, float* ka4, const int32_t* q_modes, float* partial_v, float* vstat,
+    void* v16, void* v8, void* v4, void* v8h, const int32_t* raw_heads, void* stream) {
+  const QkArgs a{q, k, batch, heads_q, heads_kv, tokens, q_stride_b, q_stride_h, q_stride_t, k_stride_b, k_stride_h, k_stride_t,
+                 q8, qa, k8, ka, partial_k, kstat, q4x, qa4, k4x, k4, ka4, q_modes};
+  const VArgs b{v, batch, heads_kv, tokens, v_stride_b, v_stride_h, v_stride_t, partial_v, vstat, v16, v8, v4, v8h, raw_heads};
+  if (const int rc = check_qk(a)) return rc;
+  if (const int rc = check_v(b)) return rc;
+  TRI_CHECK(partial_k != partial_v, "write_kv: the K and V statistics need scratch buffers of their own");
+  int device = -1;
+  TRI_CUDA(cudaGetDevice(&device), "write_kv");
+  TRI_CHECK(device >= 0 && device < TriPerDevice::MaxDevices, "write_kv: device ordinal");
+  WriteLanes& lanes = g_lanes[device];
+  std::lock_guard<std::mutex> guard(lanes.lock);
+  if (!lanes.ready) {
+    int least = 0, greatest = 0;
+    TRI_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest), "write_kv: stream priorities");
+    for (int i = 0; i < 2; ++i) {
+      // highest priority: the small kernels of the K and V chains get the SM slots that the Q kernel's CTAs free first
+      TRI_CUDA(cudaStreamCreateWithPriority(&lanes.side[i], cudaStreamNonBlocking, greatest), "write_kv: side stream");
+      TRI_CUDA(cudaEventCreateWithFlags(&lanes.join[i], cudaEventDisableTiming), "write_kv: event");
+    }
+    TRI_CUDA(cudaEventCreateWithFlags(&lanes.fork, cudaEventDisableTiming), "write_kv: event");
+    lanes.ready = true;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TRI_CUDA(cudaEventRecord(lanes.fork, s), "write_kv: fork");
+  TRI_CUDA(cudaStreamWaitEvent(lanes.side[0], lanes.fork, 0), "write_kv: fork");
+  TRI_CUDA(cudaStreamWaitEvent(lanes.side[1], lanes.fork, 0), "write_kv: fork");
+  launch_k(a, lanes.side[0]);
+  launch_v(b, lanes.side[1]);
+  launch_q(a, s);
+  TRI_CUDA(cudaEventRecord(lanes.join[0], lanes.side[0]), "write_kv: join");
+  TRI_CUDA(cudaEventRecord(lanes.join[1], lanes.side[1]), "write_kv: join");
+  TRI_CUDA(cudaStreamWaitEvent(s, lanes.join[0], 0), "write_kv: join");
+  TRI_CUDA(cudaStreamWaitEvent(s, lanes.join[1], 0), "write_kv: join");
+  return tri_launch_status("write_kv");
 }
 
 // Quantise K and V rows with statistics that already exist (the prompt's): the cache write for keys that arrive

@@ -22,6 +22,8 @@ _P, _I, _L, _D, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_dou
 SIGNATURES = {
     "tri_prepare_qk": [_P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "tri_pack_v": [_P, _I, _I, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P],
+    "tri_write_kv": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                     _P, _P, _P, _P, _P, _P, _P, _P],
     "tri_requantize_kv": [_P, _P, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P],
     "tri_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _L, _I, _I, _I, _I, _D,
                       _P, _L, _L, _L, _P, _L, _L, _L, _P, _P],
@@ -47,7 +49,7 @@ SIGNATURES = {
 }
 
 
-ABI_VERSION = 3      # tri_abi_version() of the library these signatures describe
+ABI_VERSION = 4      # tri_abi_version() of the library these signatures describe
 
 
 def load_library() -> ctypes.CDLL:
@@ -145,6 +147,36 @@ class Module:
                                                 qa.data_ptr(), k8.data_ptr(), ka.data_ptr(), partial.data_ptr(),
                                                 kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4), _ptr(ka4),
                                                 _ptr(q_modes), _stream()))
+
+    def write_kv(self, q, k, v, q8, qa, k8, ka, partial_k, kstat, partial_v, vstat, q4x=None, qa4=None, k4x=None, ka4=None,
+                 k4=None, q_modes=None, v16=None, v8=None, v4=None, v8h=None, raw_heads=None):
+        """prepare_qk and pack_v in one call whose Q, K and V chains run side by side (tri_write_kv); same results."""
+        self._bhtd(q, "Q"), self._bhtd(k, "K"), self._bhtd(v, "V")
+        b, hq, t, _ = q.shape
+        hk, tiles = k.shape[1], (t + 63) // 64
+        if k.shape[0] != b or k.shape[2] != t or hq % hk or tuple(v.shape) != tuple(k.shape):
+            raise RuntimeError("BF16 Q/K/V [B,H,T,128] with contiguous features")
+        if not (q8.numel() == b * hq * t * 128 and qa.numel() == b * hq * t and k8.numel() == b * hk * tiles * 8192 and
+                ka.numel() == b * hk * tiles * 4 and partial_k.numel() >= b * hk * 64 * 3 * 128 and
+                partial_v.numel() >= b * hk * 64 * 3 * 128 and kstat.numel() == b * hk * 3 * 128 and
+                vstat.numel() == b * hk * 3 * 128 and partial_k.data_ptr() != partial_v.data_ptr()):
+            raise RuntimeError("Q/K/V buffers")
+        int4 = q4x is not None
+        if not (int4 == (qa4 is not None) == (k4x is not None) == (ka4 is not None)) or (k4 is not None and not int4):
+            raise RuntimeError("INT4 Q/K buffers (all or none)")
+        for name, buf, size in (("v16", v16, 16384), ("v8", v8, 8192), ("v4", v4, 4096), ("v8h", v8h, 16384)):
+            if buf is not None and buf.numel() * buf.element_size() != b * hk * tiles * size:
+                raise RuntimeError(f"{name} buffer")
+        for name, tab, n in (("q_modes", q_modes, hq), ("raw_heads", raw_heads, hk)):
+            if tab is not None and not (tab.is_cuda and tab.dtype == torch.int32 and tab.numel() == n and tab.is_contiguous()):
+                raise RuntimeError(f"{name} int32 [{n}] on the device")
+        with torch.cuda.device(q.device):
+            self._check(self.lib.tri_write_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), b, hq, hk, t, q.stride(0), q.stride(1),
+                                              q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
+                                              v.stride(2), q8.data_ptr(), qa.data_ptr(), k8.data_ptr(), ka.data_ptr(),
+                                              partial_k.data_ptr(), kstat.data_ptr(), _ptr(q4x), _ptr(qa4), _ptr(k4x), _ptr(k4),
+                                              _ptr(ka4), _ptr(q_modes), partial_v.data_ptr(), vstat.data_ptr(), _ptr(v16),
+                                              _ptr(v8), _ptr(v4), _ptr(v8h), _ptr(raw_heads), _stream()))
 
     def pack_v(self, v, partial, vstat, v16=None, v8=None, v4=None, v8h=None, raw_heads=None):
         """raw_heads int32 [Hkv] on the device (or None): non-zero = un-quantised KV head (identity statistics, fp16 blob

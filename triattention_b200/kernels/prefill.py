@@ -95,6 +95,7 @@ class Prefill:
             k8=raw("k8", b * hk * rows * K8_BYTES),
             ka=f32("ka", b * hk * rows * 4),
             partial=f32("partial", b * hk * 64 * 3 * 128),
+            partial_v=f32("partial_v", b * hk * 64 * 3 * 128),
             kstat=f32("kstat", b * hk * 3 * 128).view(b * hk, 3, 128),
             vstat=f32("vstat", b * hk * 3 * 128).view(b * hk, 3, 128),
             q4x=raw("q4x", b * hq * t * 128).view(torch.int8).view(b * hq, t, 128) if int4 else None,
@@ -121,9 +122,10 @@ class Prefill:
         int4 = Q4 in table.formats or need_k4
         ops = self.operands(b, hq, hk, t, int4, need_k4, formats, device)
         m = self.module
-        m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"],
-                     ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"], q_modes=table.q_modes)
-        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], ops["v4"], ops["v8h"], raw_heads=table.raw_kv)
+        # the reference's two calls (prepare_qk, then pack_v: kernels/prefill.py:99-101) as one, whose chains overlap
+        m.write_kv(q, k, v, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["partial_v"],
+                   ops["vstat"], ops["q4x"], ops["qa4"], ops["k4x"], ops["ka4"], ops["k4"], q_modes=table.q_modes,
+                   v16=ops["v16"], v8=ops["v8"], v4=ops["v4"], v8h=ops["v8h"], raw_heads=table.raw_kv)
         return table, ops
 
     def __call__(self, layer, q, k, v, scale, out_dtype=None):
@@ -159,9 +161,8 @@ class Prefill:
         # would run on un-normalised V like the reference's identity mode, common_host.cuh:39, differs by that rounding.)
         ops = self.operands(b, hq, hk, t, True, False, frozenset({F16, I8, Q4}), device)
         m = self.module
-        m.prepare_qk(q, k, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["q4x"], ops["qa4"],
-                     ops["k4x"], ops["ka4"], None)
-        m.pack_v(v, ops["partial"], ops["vstat"], ops["v16"], ops["v8"], None, ops["v8h"])
+        m.write_kv(q, k, v, ops["q8"], ops["qa"], ops["k8"], ops["ka"], ops["partial"], ops["kstat"], ops["partial_v"],
+                   ops["vstat"], ops["q4x"], ops["qa4"], ops["k4x"], ops["ka4"], v16=ops["v16"], v8=ops["v8"], v8h=ops["v8h"])
         first_block = 0 if rows is None else max(0, (t - int(rows)) // 64)
         row0 = (first_block // 4) * 256
         out = torch.empty((len(configs), b, hq, t - row0, 128), dtype=out_dtype or q.dtype, device=device)
