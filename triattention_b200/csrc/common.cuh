@@ -190,6 +190,7 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
 }
 __device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site = 1) {
   if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+  if (*abort_flag) return false;   // after an abort nothing completes any more: every later wait costs one try
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
     // the hardware usually hands the warp back long before the hint runs out: the abort flag and the clock are looked

@@ -32,7 +32,8 @@ constexpr int SmBiasA = 65536, SmBiasB = SmBiasA + 4096;         // constant fp1
 constexpr int SmK = SmBiasB + 2048 + 2048;                       // four stages of K (1024-byte aligned)
 constexpr int SmV16 = SmK + 4 * K8Bytes, SmEnd = SmV16 + 2 * V16Bytes;   // two fp16 V operands
 constexpr int SmSteps = SmEnd, StepBytes = (3 * MaxSteps + 15) / 16 * 16;  // visiting order: uint16 tile|mode, uint8 mask
-constexpr int PrefillShared = SmSteps + StepBytes + 1024;       // + slack to align the base to 1024 bytes
+constexpr int ListBytes = 2 * 4 * MaxSteps;                     // per MMA tile: one word per step it takes part in
+constexpr int PrefillShared = SmSteps + StepBytes + ListBytes + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t TmemCols = 512, TmemO = 0, TmemS = 256;      // O: [tile] x 128 columns; S: [tile][buffer] x 64
 constexpr float RefSlack = 8.f;   // a row's reference exponent moves when a tile's maximum exceeds it by this (log2)
 constexpr float PMagic64 = 58368.5f;   // 2^15 * 1.78125 + 0.5: like 49152.5f, with 0x64 in byte 2 of the sum

@@ -61,9 +61,11 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 // column (inside a score buffer) of the P words of key group kk: the first half of the columns of the thread that owns it
-__device__ __forceinline__ constexpr uint32_t p_column(int kk) { return RowSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; }
-constexpr uint32_t PLow = 32 / RowSplit;   // the low parts of the quantised weights sit behind the high parts: a thread's score
-                                           // columns (64 / RowSplit) hold its high parts in their first half, its low parts in the second
+// column (inside a score buffer) of the P words of key group kk (16 keys = 8 columns of fp16 pairs): key groups 2c and 2c+1
+// belong to the thread that owns score columns 32c .. 32c+31; a key group's high parts sit over the first 8 of its own 16
+// score columns and its low parts over the last 8, so that the thread stores both with one 16-column tcgen05.st
+__device__ __forceinline__ constexpr uint32_t p_column(int kk) { return (kk >> 1) * 32 + (kk & 1) * 16; }
+constexpr uint32_t PLow = 8;
 // Two fp32 fused multiply-adds in one instruction (fma.rn.ftz.f32x2): each lane rounds exactly like the scalar fma, so the
 // results are bit-identical; it halves the issue slots of the two fmas every score costs.
 __device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ __align__(16) float k_scales[8][4];   // ring: the four K scales of the tiles of the last 8 steps, fetched with the tile
+  __shared__ int steps_of_tile[2];       // number of steps in which MMA tile x takes part
   __shared__ float xchg[2][2][2][128];   // [tile][parity][column half][row]: partial maxima, at the end denominators
   uint8_t* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -120,6 +123,24 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     plan.get(i, tile, mode, mask);
     step_tm[i] = (uint16_t)(tile | (mode << 12));
     step_mask[i] = (uint8_t)mask;
+  }
+  // per MMA tile the steps in which it takes part, in order, one word each: step | tile << 13 | mode << 24 | block mask << 26
+  // (warps 1 and 2 list tile 0 / 1, 32 steps per round)
+  uint32_t* step_list = reinterpret_cast<uint32_t*>(smem + SmSteps + StepBytes);
+  if (warp == 1 || warp == 2) {
+    const int x = warp - 1;
+    int count = 0;
+    for (int c = 0; c < nsteps; c += 32) {
+      int tile = 0, mode = 0, mask = 0;
+      if (c + lane < nsteps) plan.get(c + lane, tile, mode, mask);
+      const int mx = (mask >> (2 * x)) & 3;
+      const uint32_t votes = __ballot_sync(0xffffffffu, mx != 0);
+      if (mx != 0)
+        step_list[x * MaxSteps + count + __popc(votes & ((1u << lane) - 1u))] =
+            (uint32_t)(c + lane) | ((uint32_t)tile << 13) | ((uint32_t)mode << 24) | ((uint32_t)mx << 26);
+      count += __popc(votes);
+    }
+    if (lane == 0) steps_of_tile[x] = count;
   }
   for (int i = tid; i < (4096 + 2048) / 4; i += PrefillThreads)   // 3072.0 (0x6A00) for A, 256.0 (0x5C00) for B
     reinterpret_cast<uint32_t*>(smem + SmBiasA)[i] = i < 1024 ? 0x6A006A00u : 0x5C005C00u;
@@ -292,15 +313,13 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
     const float qs8 = (row_valid && !raw) ? qa8[qrow] * sm_log2 : FLT_MIN;
     const float qs4 = (row_valid && need_q4) ? qa4[qrow] * sm_log2 : FLT_MIN;
     float ref = -FLT_MAX, denom = 0.f;   // reference exponent of the row; this thread's share of the denominator
-    int n = 0;                           // steps of this tile so far
-    int inext = 0;   // next step in which this tile takes part
-    while (inext < nsteps && ((step_mask[inext] >> (2 * x)) & 3) == 0) ++inext;
-    bool ok = true;
-    while (inext < nsteps) {
-      const int i = inext;
-      const int tile = tile_of(i), mode = mode_of(i), mx = (step_mask[i] >> (2 * x)) & 3;
-      ++inext;
-      while (inext < nsteps && ((step_mask[inext] >> (2 * x)) & 3) == 0) ++inext;
+    const int nx = steps_of_tile[x];     // steps of this tile
+    // No result of a wait is looked at here: after an abort (a wait that ran out anywhere in the CTA) every wait returns at
+    // once and the warp runs through its remaining steps on whatever the tensor memory holds (its own columns, so nothing
+    // is touched that is not this CTA's); the kernel reports the error and the host discards the output.
+    for (int n = 0; n < nx; ++n) {
+      const uint32_t entry = step_list[x * MaxSteps + n];
+      const int i = entry & 0x1fff, tile = (entry >> 13) & 0x7ff, mode = (entry >> 24) & 3, mx = entry >> 26;
       const int sb = n & 1;
       const bool active = (mx >> half) & 1;   // uniform for the warp pair
       const bool diag = mode == ModeF16 && tile == bh;
@@ -311,8 +330,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, keys in natural
       // order like both fp16 V blobs
 
-      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.s_full[x][sb], n >> 1, 9 | (n << 8)));
-      if (ok) tc_fence_after();
+      wait(&bars.s_full[x][sb], n >> 1, 9 | (n << 8));
+      tc_fence_after();
       // The tile's K scales came with the tile (the ring slot is not reused before step i+8, and the producer
       // cannot be more than 4 steps ahead of a softmax warp).
       const float4 ks = raw ? make_float4(1.f, 1.f, 1.f, 1.f) : *reinterpret_cast<const float4*>(&k_scales[i & 7][0]);
@@ -328,9 +347,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       if (active) {
         // partial scaled maximum over this thread's 32 columns (prefill_sm80.cu:244-253), then the row's
         float part = -CUDART_INF_F;
-        if (ok) {
-#pragma unroll
-          for (int cc = 0; cc < G; ++cc) tmem_ld16(s_addr + 16 * cc, a[cc]);
+        {
+          tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(a));
           tmem_ld_wait();
 #pragma unroll
           for (int cc = 0; cc < G; ++cc) {
@@ -362,7 +380,7 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           tmax = part;
         }
       }
-      if (ok && active) {
+      if (active) {
         // Move the row's reference exponent, and rescale what O holds, when this tile towers over it.  In the fp16
         // steps (sink and diagonal tiles, the first steps of a row, in the reference's order) it moves with every
         // increase, so that it IS the reference's running maximum m there: the reference rounds 2^(score - m) to fp16
@@ -382,8 +400,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
           denom *= factor;
         }
         if (n > 0 && __any_sync(0xffffffffu, move)) {
-          ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 11 | (n << 8)));
-          if (ok) {
+          wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 11 | (n << 8));
+          {
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < 2 * G; ++c) {
@@ -395,17 +413,16 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
               tmem_st16(o_addr, o);
             }
-#pragma unroll
-            for (int cc = 0; cc < G; ++cc) tmem_ld16(s_addr + 16 * cc, a[cc]);   // read again: the scores need not survive
-            tmem_ld_wait();                                                      // the (rare) rescale in registers
+            tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(a));   // read again: the scores need not survive
+            tmem_ld_wait();                                            // the (rare) rescale in registers
           }
         }
       }
-      if (ok && !active) {
-        const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing to the tile's P.V
+      if (!active) {
+        const uint32_t zero[16] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // this half's rows contribute nothing
 #pragma unroll
-        for (int cc = 0; cc < 2 * G; ++cc) tmem_st8(s_addr + 8 * cc, zero);   // high and low parts (the latter unread in fp16 mode)
-      } else if (ok && (mode == ModeF16 || raw)) {
+        for (int cc = 0; cc < G; ++cc) tmem_st16(s_addr + 16 * cc, zero);   // high and low parts (the latter unread in fp16 mode)
+      } else if (mode == ModeF16 || raw) {
         float sum = 0.f;
 #pragma unroll
         for (int cc = 0; cc < G; ++cc) {
@@ -424,10 +441,10 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
             sum += __low2float(hp) + __high2float(hp);
             w[j / 2] = *reinterpret_cast<const uint32_t*>(&hp);
           }
-          tmem_st8(s_addr + 8 * cc, w);
+          tmem_st8(s_addr + 16 * cc, w);
         }
         denom += sum;
-      } else if (ok) {
+      } else {
         // prefill_sm80.cu:386-414: u8 codes of 2^(score - base); band tiles are never masked
         const float ks_max = fmaxf(fmaxf(ks.x, ks.y), fmaxf(ks.z, ks.w));
         float base = tmax;
@@ -459,7 +476,9 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
 #pragma unroll
           for (int cc = 0; cc < G; ++cc) {
             const float off = Int4 ? -base : fmaf(-slope[cc], 12582912.f, -base);
-            uint32_t hi[8], lo[8];   // the 16 weights of this key group, two per word: high and low parts
+            uint32_t hl[16];   // the 16 weights of this key group, two per word: high parts in words 0-7, low parts in 8-15
+            uint32_t* const hi = hl;
+            uint32_t* const lo = hl + 8;
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
               uint32_t w[8];
@@ -494,30 +513,27 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
               lo[4 * hb] = *reinterpret_cast<const uint32_t*>(&l0); lo[4 * hb + 1] = *reinterpret_cast<const uint32_t*>(&l1);
               lo[4 * hb + 2] = *reinterpret_cast<const uint32_t*>(&l2); lo[4 * hb + 3] = *reinterpret_cast<const uint32_t*>(&l3);
             }
-            tmem_st8(s_addr + 8 * cc, hi);
-            tmem_st8(s_addr + PLow + 8 * cc, lo);   // the low parts sit over the second half of the thread's columns
+            tmem_st16(s_addr + 16 * cc, hl);   // one store per key group: its high parts, then its low parts
           }
         };
         if (mode == ModeQ4) codes(std::true_type{}); else codes(std::false_type{});
         denom = fmaf((float)rs, s_sum, denom);
       }
-      if (ok) {
-        tmem_st_wait();   // P is in tensor memory before the issuer is told
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cta(&bars.p_full[x][sb]);
-      }
-      ++n;
+      tmem_st_wait();   // P is in tensor memory before the issuer is told
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cta(&bars.p_full[x][sb]);
     }
 
     // ---- epilogue: O / denominator, de-normalised (prefill_sm80.cu:466-487) ----------------------------
-    if (n > 0) {
-      if (ok) ok = __all_sync(0xffffffffu, wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 12 | (n << 8)));
+    if (nx > 0) {
+      const int n = nx;
+      wait(&bars.o_done[x][(n - 1) & 1], (n - 1) >> 1, 12 | (n << 8));
       if constexpr (RowSplit == 2) {
         xchg[x][n & 1][ch][row] = denom;
         pair_sync(pair_id);
       }
-      if (ok) {
+      {
         tc_fence_after();
         const float total = RowSplit == 2 ? xchg[x][n & 1][0][row] + xchg[x][n & 1][1][row] : denom;
         const float inv = total > 0.f ? 1.f / total : 0.f;
