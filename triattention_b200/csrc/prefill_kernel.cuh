@@ -20,7 +20,8 @@
 // three-input max.
 //
 // P never touches shared memory: a softmax thread writes its fp16 weights over its own 32 score columns
-// (tcgen05.st: high parts over the first 16, low parts over the last 16) once it has read them, and the P.V MMAs
+// (one tcgen05.st per 16-key group: the group's high parts over the first 8 of its 16 columns, its low parts over
+// the last 8) once it has read them, and the P.V MMAs
 // take their A operand from tensor memory.
 // The bias MMA of two steps later overwrites P; its issuer waits for that P.V to have completed first.  With A in tensor memory an M128 N128 K16 MMA takes 65 cycles instead of 108 (measured).
 //
@@ -327,8 +328,8 @@ __global__ void __launch_bounds__(PrefillThreads, 1) prefill_kernel(const __grid
       const int key0 = tile * BN + 16 * G * ch;
       const uint32_t s_addr = lane_base + TmemS + x * 128 + sb * 64 + 16 * G * ch;
       auto dead = [&](int key) { return key >= tokens || key > qi || qi >= tokens; };   // diagonal tile only
-      // P goes over the first 16 of this thread's 32 score columns: two fp16 weights per column, keys in natural
-      // order like both fp16 V blobs
+      // P goes over this thread's 32 score columns: two fp16 weights per column, keys in natural order like both fp16
+      // V blobs (p_column)
 
       wait(&bars.s_full[x][sb], n >> 1, 9 | (n << 8));
       tc_fence_after();
