@@ -239,6 +239,10 @@ def test_error_word_is_keyed_by_the_device_that_ran_the_kernel(monkeypatch):
     m.check_device_error("cuda:0")              # another device's word is not this call's business
     with pytest.raises(RuntimeError, match="device error 1"):
         m.check_device_error("cuda")            # the current device (3)
+    # a prefill wait that ran out leaves its site (and the tile's step) in the upper bits: 1 | 11 << 8 | 37 << 16
+    m._errors[0].fill_(1 | (11 << 8) | (37 << 16))
+    with pytest.raises(RuntimeError, match="device error 1 on cuda:0, wait site 11 at step 37 of the prefill kernel"):
+        m.check_device_error()
 
 
 def test_decode_entry_points_validate_before_any_cuda_call():
