@@ -51,12 +51,28 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   const int unit = blockIdx.x, b = unit / heads_kv, kh = unit % heads_kv, g = heads_q / heads_kv;
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   grid_launch_dependents();   // the next step's split pass may set up its barriers behind this kernel
-  grid_dependency_wait();     // the split pass has written all partials
   const int2 sl = unit_slots[unit];
   if (sl.x < 0 || sl.y < 0 || sl.x + sl.y > slot_limit) {   // the unit's slots do not fit the partial buffers
     if (tid == 0) atomicCAS(err, ErrNone, ErrBadSlot);
     return;
   }
+  // What does not depend on the split pass comes before the wait for it: the tail append and the tail scores read only
+  // this step's q / k / v, the statistics and the tail rows of earlier steps, all complete before the split pass began
+  // (it waited for its own predecessor before it let this kernel start), so a CTA that becomes resident while other SMs
+  // still stream has only the partials left to read afterwards.
+  const int prior = min((int)*step, max_tail - 1), tail = prior + 1;
+  const __nv_bfloat16* kc = kcur + b * csb + kh * csh;
+  const __nv_bfloat16* vc = vcur + b * csb + kh * csh;
+  __nv_bfloat16* kt = ktail + unit * tsu;
+  __nv_bfloat16* vt = vtail + unit * tsu;
+  if (tid < D) {   // append the current token to the tail (read back only by later steps)
+    kt[prior * tst + tid] = kc[tid];
+    vt[prior * tst + tid] = vc[tid];
+  }
+  // tail scores for all heads of the group in one pass over the tail's K rows
+  unit_tail_scores(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
+                   sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
+  grid_dependency_wait();     // the split pass has written all partials
   __shared__ int exchange_failed;
   if (xchg.world > 0) {
     // triples of this unit's next epoch from every rank that has tiles of it; bounded wait (1 s), then an error code
@@ -81,19 +97,7 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     const int64_t ug = (int64_t)xchg.units * MaxGroup;
     pm = block; pl = block + ug; po = block + 2 * ug;
   }
-  const int prior = min((int)*step, max_tail - 1), tail = prior + 1;
-  const __nv_bfloat16* kc = kcur + b * csb + kh * csh;
-  const __nv_bfloat16* vc = vcur + b * csb + kh * csh;
-  __nv_bfloat16* kt = ktail + unit * tsu;
-  __nv_bfloat16* vt = vtail + unit * tsu;
-  if (tid < D) {   // append the current token to the tail (read back only by later steps)
-    kt[prior * tst + tid] = kc[tid];
-    vt[prior * tst + tid] = vc[tid];
-  }
-  // tail scores for all heads of the group in one pass over the tail's K rows, then warp r merges Q head r
-  unit_tail_scores(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
-                   sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
-  __syncthreads();
+  __syncthreads();            // the tail scores of all warps are in shared memory; then warp r merges Q head r
   if (gather.world == 0) {
     if (warp < g)
       merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
