@@ -694,7 +694,7 @@ def run_model(args):
         setattr(engine.module, name, call)
         return inner
 
-    names = ("prepare_qk", "pack_v", "attention", "cache_store", "cache_store_bf16", "decode")
+    names = ("write_kv", "attention", "cache_store", "cache_store_bf16", "decode")
     originals = {name: watch(name) for name in names}
     few = min(new, 9)
     engine.generate(ids, few, eos=())
