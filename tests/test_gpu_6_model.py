@@ -149,3 +149,55 @@ def test_hook_level_parity_with_the_reference_extension(ref_ext):
     worst = (got_logits - want_logits).abs().max().item() / want_logits.abs().max().item()
     assert cos > 0.9999 and worst < 0.02, (cos, worst)
     assert got_tokens == want_tokens, (got_tokens, want_tokens)
+
+
+@torch.inference_mode()
+def test_calibration_hook_equals_one_prefill_per_grid_point():
+    """The calibration tool's hook (one sweep per layer: triattention_b200/calibrate.py) on the toy model gives, per layer,
+    head and grid point, the error the reference tool's loop computes with one prefill per grid point
+    (calibrate.py:46-63 of the reference), and leaves the model's exact output in place."""
+    from triattention_b200.calibrate import Calibration, grid
+    from triattention_b200.kernels.extension import load_extension
+    from triattention_b200.kernels.prefill import Prefill
+    from triattention_b200.maps import INF, uniform
+    from triattention_b200.models import exact_attention, use_attention
+    model = tiny_llama()
+    module = load_extension()
+    configs, rows = grid()[::7] + [(INF, INF)], 100
+    ids = torch.randint(0, 1024, (1, 333), generator=torch.Generator().manual_seed(9)).cuda()
+    run = Calibration(Prefill(module, uniform(INF, INF)), configs, rows)
+    use_attention(model, "triattention_calibration_test", run.attention)
+    swept = model(input_ids=ids, use_cache=False, logits_to_keep=1).logits.float()
+    module.check_device_error()
+    assert sorted(run.errors) == [0, 1, 2] and all(e.shape == (4, len(configs)) for e in run.errors.values())
+
+    loop = {}
+    executors = [Prefill(module, uniform(w8, w4)) for w8, w4 in configs]
+
+    def reference_style(mod, query, key, value, scaling):
+        heads, t = query.shape[1], query.shape[2]
+        last = slice(max(0, t - rows), t)
+        ref = exact_attention(query, key, value, scaling)
+        w = mod.o_proj.weight.float()
+        wh = w.view(w.shape[0], heads, 128).permute(1, 0, 2)
+        gram = wh.transpose(1, 2) @ wh
+        exact = ref[0, :, last].float()
+        energy = float((exact.transpose(0, 1).reshape(-1, heads * 128) @ w.T).square().sum())
+        total = loop.setdefault(mod.layer_idx, torch.zeros(heads, len(configs), dtype=torch.float64))
+        for i, prefill in enumerate(executors):
+            delta = prefill(mod.layer_idx, query, key, value, scaling)[0, :, last].float() - exact
+            total[:, i] += torch.einsum("htd,hde,hte->h", delta, gram, delta).double().cpu() / energy
+        return ref
+
+    use_attention(model, "triattention_calibration_loop", reference_style)
+    looped = model(input_ids=ids, use_cache=False, logits_to_keep=1).logits.float()
+    module.check_device_error()
+    assert torch.equal(swept, looped)        # both hooks return the exact attention
+    for layer in range(3):
+        a, b = run.errors[layer], loop[layer]
+        assert torch.isfinite(a).all() and (a >= 0).all()
+        # same outputs bit for bit except the grid point without any INT8 tile, summed in another order
+        assert torch.allclose(a, b, rtol=2e-2, atol=1e-9), (layer, (a - b).abs().max().item())
+    record = run.record("llama", 1)
+    assert record["format"] == "triattention-calibration-v1" and record["configs"] == configs and record["rows"] == rows
+    assert sorted(record["errors"]) == [0, 1, 2] and len(record["errors"][0]) == 4
