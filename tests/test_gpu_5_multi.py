@@ -1,6 +1,6 @@
-"""Two-GPU paths: unit sharding with output gather, and the sequence split with the (m, l, o) exchange over NCCL and
-over peer memory.
-Skipped on a single-GPU box; the host logic of both is covered on CPU by tests/test_cpu_sharding.py."""
+"""Multi-GPU paths (2 and 4 ranks, one process per GPU): unit sharding with output gather, and the sequence split with
+the (m, l, o) exchange over NCCL and over peer memory.
+Skipped where the box has fewer GPUs; the host logic of both is covered on CPU by tests/test_cpu_sharding.py."""
 import os
 import socket
 
@@ -94,10 +94,11 @@ def _worker(rank, world, port, result):
         dist.destroy_process_group()
 
 
-def test_two_gpu_split_and_sharding():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world, port = 2, _free_port()
+@pytest.mark.parametrize("world", [2, 4])
+def test_multi_gpu_split_and_sharding(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = _free_port()
     with mp.Manager() as manager:
         result = manager.dict()
         mp.spawn(_worker, args=(world, port, result), nprocs=world, join=True)
