@@ -278,23 +278,36 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
 __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float* pl, const float* po, int64_t first,
     int64_t ml_stride, int64_t o_stride, int nsplit, float* ts_row, int tail, int prior, const __nv_bfloat16* vt, int64_t tst,
     const __nv_bfloat16* vc, const float* vstat_unit, __nv_bfloat16* out_row, int lane) {
+  // The first four splits' (m, l, o) are requested at once, before the maximum is known: their addresses depend on
+  // nothing that is computed here, so the merge pays one trip to the second-level cache instead of two (a unit seldom
+  // has more than four splits).
+  float pmv[4], plv[4];
+  float4 p[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const bool on = u < nsplit;
+    pmv[u] = on ? __ldcg(pm + first + u * ml_stride) : -FLT_MAX;
+    plv[u] = on ? __ldcg(pl + first + u * ml_stride) : 0.f;
+    p[u] = on ? __ldcg(reinterpret_cast<const float4*>(po + first * D + u * o_stride + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   float m = -FLT_MAX;
-  for (int s = lane; s < nsplit; s += 32) m = fmaxf(m, __ldcg(pm + first + s * ml_stride));
+  for (int s = 4 + lane; s < nsplit; s += 32) m = fmaxf(m, __ldcg(pm + first + s * ml_stride));
   for (int t = lane; t < tail; t += 32) m = fmaxf(m, ts_row[t]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  m = fmaxf(fmaxf(m, fmaxf(pmv[0], pmv[1])), fmaxf(pmv[2], pmv[3]));
   for (int t = lane; t < tail; t += 32) ts_row[t] = exp2f(ts_row[t] - m);
   __syncwarp();
   float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int s0 = 0; s0 < nsplit; s0 += 4) {
-    float pmv[4], plv[4];
-    float4 p[4];
+    if (s0 > 0) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const bool on = s0 + u < nsplit;
-      pmv[u] = on ? __ldcg(pm + first + (s0 + u) * ml_stride) : -FLT_MAX;
-      plv[u] = on ? __ldcg(pl + first + (s0 + u) * ml_stride) : 0.f;
-      p[u] = on ? __ldcg(reinterpret_cast<const float4*>(po + first * D + (s0 + u) * o_stride + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = 0; u < 4; ++u) {
+        const bool on = s0 + u < nsplit;
+        pmv[u] = on ? __ldcg(pm + first + (s0 + u) * ml_stride) : -FLT_MAX;
+        plv[u] = on ? __ldcg(pl + first + (s0 + u) * ml_stride) : 0.f;
+        p[u] = on ? __ldcg(reinterpret_cast<const float4*>(po + first * D + (s0 + u) * o_stride + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
