@@ -291,6 +291,15 @@ int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_stride_h, con
                       int batch, int heads_q, int heads_kv, int prompt, int max_tail, double scale,
                       int* device_error, void* stream);
 
+/* How many rows the BF16 tails hold in the decode launches that follow on this host thread (the token being appended
+ * included); negative = not known, the state a thread starts in.  A hint: it picks between two instantiations of the
+ * merge kernel with the same arithmetic in the same order (bit-equal results) for the separate merge launch of tri_decode
+ * (unit_done NULL), tri_decode_static and tri_decode_merge.  Up to 8 rows the one whose row loops are not unrolled runs
+ * (5 us per step less at one row, 100 us more at 256 rows); above 8 rows, or without a hint, the unrolled one.  Under
+ * stream capture the instantiation chosen at capture time is the one replayed.  No counterpart in the reference (one merge
+ * kernel, triattention/kernels/cuda/decode.cu). */
+int tri_decode_tail_hint(int rows);
+
 /* Resident decode CTAs per SM.  Replaces decode_occupancy(), triattention/kernels/cuda/common_host.cuh:89-94. */
 int tri_decode_occupancy(void);
 

@@ -208,7 +208,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
         if name in SIGNATURES:
             assert len(SIGNATURES[name]) == nargs, (name, len(SIGNATURES[name]), nargs)
-    assert lib.tri_abi_version() == 4
+    assert lib.tri_abi_version() == 5
     assert isinstance(lib.tri_last_error(), bytes)
 
 

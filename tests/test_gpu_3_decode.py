@@ -146,6 +146,31 @@ def test_fused_merge_matches_two_launches(module, ctas):
     assert_fp_close(one, two, f"one launch vs two, {ctas} CTAs")
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["one-launch", "two-launches"])
+def test_long_tail_merge_kernel_gives_the_same_bits(module, monkeypatch, fused):
+    """The merge kernel has a second instantiation for long BF16 tails (row loops unrolled), which the host picks from
+    its count of generated tokens (tri_decode_tail_hint).  70 steps with the hint as DecodeCache gives it (plain kernel up
+    to 8 rows, unrolled after), with the plain kernel throughout and with the unrolled one throughout: the same bits,
+    and the oracle's values."""
+    hq, hk, t, steps = 8, 2, 300, 70
+    bands = np.asarray([[INF, INF]] * 4 + [[2, 6]] * 4, np.int64)
+    q, k, v = make_inputs(hq, hk, t, seed=73, batch=2)
+    qd, kd, vd = make_inputs(hq, hk, steps, seed=74, batch=2)
+    hints = []
+    hint = module.decode_tail_hint
+    monkeypatch.setattr(module, "decode_tail_hint", lambda rows: (hints.append(rows), hint(rows))[1])
+    as_counted, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=steps, max_tail=128, fused=fused)
+    assert hints == list(range(1, steps + 1))
+    for rows in (1, 1000):
+        monkeypatch.setattr(DecodeCache, "tail_rows", lambda self: rows)
+        forced, _ = product_decode(module, q, k, v, bands, qd, kd, vd, steps=steps, max_tail=128, fused=fused)
+        assert np.array_equal(as_counted, forced), rows
+    monkeypatch.undo()
+    module.decode_tail_hint(-1)
+    want = oracle_steps(k[0], v[0], bands, qd[0], kd[0], vd[0], steps, max_tail=128)
+    assert_fp_close(as_counted[0], orc.to_bf16(want), "70-row tail")
+
+
 def test_tail_saturates(module):
     """Steps beyond max_tail-1 keep overwriting the last tail slot (common_device.cuh:384)."""
     hq, hk, t = 2, 1, 64

@@ -19,4 +19,4 @@ int tri_launch_status(const char* where) {
 }
 
 extern "C" const char* tri_last_error(void) { return g_error; }
-extern "C" int tri_abi_version(void) { return 4; }   // 4: tri_write_kv, tri_attention_sweep
+extern "C" int tri_abi_version(void) { return 5; }   // 4: tri_write_kv, tri_attention_sweep; 5: tri_decode_tail_hint

@@ -41,6 +41,12 @@ struct OutputGather {
   void* const* peers; const int64_t* unit_row; int32_t* sync; int world, rank; int64_t rows_total;
 };
 __device__ __forceinline__ int64_t gather_flag_offset_bytes(int64_t rows_total) { return (2 * rows_total * D * 2 + 63) / 64 * 64; }
+// Two instantiations, the same arithmetic in the same order: LongTail = false for steps whose BF16 tail has a few rows
+// (row loops not unrolled: 5 us per step less at one row, 100 us more at 256 rows), LongTail = true for the rest (row
+// loops unrolled; 3 us ahead from 16 rows on).  The host picks one per launch from the caller's hint
+// (tri_decode_tail_hint); a separate kernel and not a branch, because any more code inside this kernel made its one-row
+// case slower.
+template <bool LongTail>
 __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float* pm, const float* pl, const float* po,
     int64_t ml_stride, int64_t o_stride, SplitExchange xchg, OutputGather gather, const int2* unit_slots, int slot_limit,
     const float* vstat, const float* kstat,
@@ -70,8 +76,8 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     vt[prior * tst + tid] = vc[tid];
   }
   // tail scores for all heads of the group in one pass over the tail's K rows
-  unit_tail_scores(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
-                   sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
+  unit_tail_scores<LongTail ? RowsLong : RowsShort>(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
+                             sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
   grid_dependency_wait();     // the split pass has written all partials
   __shared__ int exchange_failed;
   if (xchg.world > 0) {
@@ -100,16 +106,16 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   __syncthreads();            // the tail scores of all warps are in shared memory; then warp r merges Q head r
   if (gather.world == 0) {
     if (warp < g)
-      merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
-                         vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
+      merge_head_by_warp<LongTail ? RowsLong : RowsShort>(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
+                                   vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
     return;
   }
   // unit sharding: the row is computed into shared memory once and stored into every GPU's full output tensor
   __shared__ __align__(16) __nv_bfloat16 rows[MaxGroup][D];
   const int epoch = gather.sync[1] + 1;          // read by every CTA before the last one to finish advances it
   if (warp < g)
-    merge_head_by_warp(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
-                       vstat + (int64_t)unit * StatFloats, rows[warp], lane);
+    merge_head_by_warp<LongTail ? RowsLong : RowsShort>(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
+                                 vstat + (int64_t)unit * StatFloats, rows[warp], lane);
   __syncthreads();
   const int64_t row0 = (int64_t)(epoch & 1) * gather.rows_total + gather.unit_row[unit];
   for (int i = tid; i < gather.world * g * (D / 8); i += MergeThreads) {   // 16-byte pieces: peer, head row, piece
@@ -270,18 +276,37 @@ static cudaError_t launch_split(const DecodeCall& c, float* pm, float* pl, float
   return cudaSuccess;
 }
 
+// How many rows the caller expects the BF16 tails to hold in the launches that follow on this host thread (a hint: it
+// picks between two instantiations of the merge kernel that compute the same bits).  Negative = not known: the
+// instantiation that is good at every length.
+static thread_local int g_tail_hint = -1;
+constexpr int LongTailRows = 8;
+
+extern "C" int tri_decode_tail_hint(int rows) {
+  g_tail_hint = rows;
+  return TRI_OK;
+}
+
+template <bool LongTail>
+static cudaError_t launch_merge_as(const DecodeCall& c, const float* pm, const float* pl, const float* po, int64_t ml_stride,
+                                   int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained,
+                                   SplitExchange xchg, OutputGather gather) {
+  const dim3 grid(c.batch * c.heads_kv);
+  if (chained)
+    return launch_chained(decode_merge_kernel<LongTail>, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, gather,
+                          unit_slots, slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur,
+                          c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
+  decode_merge_kernel<LongTail><<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots, slot_limit, c.vstat,
+      c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
+      c.heads_kv, c.max_tail, c.sm_log2, c.err);
+  return cudaSuccess;
+}
 static cudaError_t launch_merge(const DecodeCall& c, const float* pm, const float* pl, const float* po, int64_t ml_stride,
                                 int64_t o_stride, const int2* unit_slots, int slot_limit, cudaStream_t s, bool chained,
                                 SplitExchange xchg = SplitExchange{}, OutputGather gather = OutputGather{}) {
-  const dim3 grid(c.batch * c.heads_kv);
-  if (chained)
-    return launch_chained(decode_merge_kernel, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots,
-                          slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb,
-                          c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
-  decode_merge_kernel<<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots, slot_limit, c.vstat, c.kstat, c.q,
-      c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
-      c.heads_kv, c.max_tail, c.sm_log2, c.err);
-  return cudaSuccess;
+  return g_tail_hint < 0 || g_tail_hint > LongTailRows
+             ? launch_merge_as<true>(c, pm, pl, po, ml_stride, o_stride, unit_slots, slot_limit, s, chained, xchg, gather)
+             : launch_merge_as<false>(c, pm, pl, po, ml_stride, o_stride, unit_slots, slot_limit, s, chained, xchg, gather);
 }
 
 static MergeArgs fused_merge_args(const DecodeCall& c, int32_t* unit_done) {

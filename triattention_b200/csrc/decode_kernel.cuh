@@ -240,6 +240,11 @@ struct MergeArgs {
 
 // Tail scores of `nh` Q heads (rows qrows + i * qsh, i < nh) against the unit's tail, one pass over the tail's K rows:
 // the `warps` calling warps split the rows, a lane holds 4 features of the row and of each head's q.  ts[i * ts_stride + t].
+// Rows picks how the row loop is compiled; the sums run in row order every way, so all give the same bits.  RowsShort: not
+// unrolled, the first row comes back soonest (a step with a tail of a few rows; a long tail is then a chain of trips to
+// memory).  RowsLong: unrolled so that several rows' loads are in flight.  RowsAny: left to the compiler (in between).
+enum { RowsAny = 0, RowsShort = 1, RowsLong = 2 };
+template <int Rows = RowsAny>
 __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int64_t qsh, int nh, const float* kmean_unit,
     const __nv_bfloat16* kt, int64_t tst, const __nv_bfloat16* kc, int prior, int tail, float sm_log2, float* ts, int ts_stride,
     int warp, int warps, int lane) {
@@ -252,7 +257,7 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
 #pragma unroll
     for (int i = 0; i < 4; ++i) qv[r][i] = __bfloat162float(qrow[i]);
   }
-  for (int t = warp; t < tail; t += warps) {
+  const auto row = [&](int t) {
     const __nv_bfloat16* kv = (t < prior ? kt + t * tst : kc) + lane * 4;
     float kd[4];
 #pragma unroll
@@ -268,6 +273,15 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
         if (lane == 0) ts[r * ts_stride + t] = part * sm_log2;
       }
     }
+  };
+  if constexpr (Rows == RowsShort) {
+#pragma unroll 1
+    for (int t = warp; t < tail; t += warps) row(t);
+  } else if constexpr (Rows == RowsLong) {
+#pragma unroll 4
+    for (int t = warp; t < tail; t += warps) row(t);
+  } else {
+    for (int t = warp; t < tail; t += warps) row(t);
   }
 }
 
@@ -275,6 +289,8 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
 // (a lane holds 4 of the 128 channels), the tail scores of the head in ts_row[0 .. tail) (turned into weights in place),
 // the tail's V rows, and writes the head's output row.  Partials are read past L1 (they may come from other CTAs of the
 // same launch or from other GPUs), four splits' loads in flight at a time; the sums run in split order.
+// Rows: as for unit_tail_scores.
+template <int Rows = RowsAny>
 __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float* pl, const float* po, int64_t first,
     int64_t ml_stride, int64_t o_stride, int nsplit, float* ts_row, int tail, int prior, const __nv_bfloat16* vt, int64_t tst,
     const __nv_bfloat16* vc, const float* vstat_unit, __nv_bfloat16* out_row, int lane) {
@@ -322,13 +338,22 @@ __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float*
   const float4 scale = *reinterpret_cast<const float4*>(vstat_unit + D + lane * 4);
   acc[0] = acc[0] * scale.x + total * mean.x; acc[1] = acc[1] * scale.y + total * mean.y;
   acc[2] = acc[2] * scale.z + total * mean.z; acc[3] = acc[3] * scale.w + total * mean.w;
-  for (int t = 0; t < tail; ++t) {
+  const auto row = [&](int t) {
     const float e = ts_row[t];
     const uint2 raw = *reinterpret_cast<const uint2*>((t < prior ? vt + (int64_t)t * tst : vc) + lane * 4);
     const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
     const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
     total += e;
     acc[0] = fmaf(e, v01.x, acc[0]); acc[1] = fmaf(e, v01.y, acc[1]); acc[2] = fmaf(e, v23.x, acc[2]); acc[3] = fmaf(e, v23.y, acc[3]);
+  };
+  if constexpr (Rows == RowsShort) {
+#pragma unroll 1
+    for (int t = 0; t < tail; ++t) row(t);
+  } else if constexpr (Rows == RowsLong) {
+#pragma unroll 16
+    for (int t = 0; t < tail; ++t) row(t);
+  } else {
+    for (int t = 0; t < tail; ++t) row(t);
   }
   const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc[0] / total, acc[1] / total);
   const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc[2] / total, acc[3] / total);

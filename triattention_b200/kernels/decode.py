@@ -400,6 +400,7 @@ class DecodeCache:
         """gather: a sharding.PeerOutputGatherer (units sharded across GPUs): the merge then stores every output row straight
         into the full output tensor of every GPU of the group, and the call returns that full tensor [B, Hq, 1, 128]."""
         e = self.layers[layer]
+        self.module.decode_tail_hint(self.tail_rows())
         if gather is not None:
             if self.split is not None or phases != 3:
                 raise RuntimeError("the peer-store output gather belongs to whole units (no sequence split), whole steps")
@@ -460,6 +461,11 @@ class DecodeCache:
                                             present=e["present"], seen=e["seen"], world=self.split[1])
         return self.module.decode_merge(q, e["gm"], e["gl"], e["go"], e["rank_stride"], e["rank_slots"], e["kstat"],
                                         e["vstat"], e["tail_k"], e["tail_v"], k, v, self.step, out, scale)
+
+    def tail_rows(self):
+        """Rows in the BF16 tails at the next call, the token it appends included (host-side count: the device keeps
+        its own in ``step``)."""
+        return (self.generated % FOLD_KEYS if self.reserve else self.generated) + 1
 
     def advance(self):
         self.generated += 1

@@ -44,12 +44,14 @@ SIGNATURES = {
                          _L, _L, _P, _P, _L, _L, _I, _I, _I, _I, _D, _P, _P],
     "tri_gather_wait": [_P, _L, _P, _I, _P, _P],
     "tri_decode_occupancy": [],
+    "tri_decode_tail_hint": [_I],
     "tri_qk_accumulators": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "tri_abi_version": [],
 }
 
 
-ABI_VERSION = 4      # tri_abi_version() of the library these signatures describe
+ABI_VERSION = 5         # tri_abi_version() of the library these signatures describe
+LONG_TAIL_ROWS = 8      # tri_decode_tail_hint: above this many rows (or without a hint) the unrolled merge kernel runs
 
 
 def load_library() -> ctypes.CDLL:
@@ -421,6 +423,12 @@ class Module:
         with torch.cuda.device(buffer.device):
             self._check(self.lib.tri_gather_wait(buffer.data_ptr(), int(rows_total), seen.data_ptr(), int(world),
                                                  self.error_word(buffer.device).data_ptr(), _stream()))
+
+    def decode_tail_hint(self, rows):
+        """Rows in the BF16 tails for the decode launches that follow on this thread: picks the merge kernel's instantiation
+        (plain or unrolled row loops, bit-equal results; LONG_TAIL_ROWS is where the library switches; negative = not
+        known)."""
+        self._check(self.lib.tri_decode_tail_hint(int(rows)))
 
     def decode_occupancy(self):
         return self._check(self.lib.tri_decode_occupancy())

@@ -14,7 +14,7 @@ from transformers import AutoConfig, AutoTokenizer
 from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
 from triattention_b200.kernels.decode import DecodeCache
-from triattention_b200.kernels.extension import load_extension
+from triattention_b200.kernels.extension import LONG_TAIL_ROWS, load_extension
 from triattention_b200.kernels.prefill import Prefill
 from triattention_b200.maps import load_map, preset
 
@@ -115,10 +115,18 @@ class TriAttention:
                 pos.sub_(1)
                 self.decode_cache.step.sub_(1)
             torch.cuda.current_stream().wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-            replay = graph.replay
+
+            def capture(pool=None):
+                # Capturing runs the host side of step() without its device side: put the host's token count back.
+                made, graph = self.decode_cache.generated, torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=pool):
+                    step()
+                self.decode_cache.generated = made
+                return graph
+
+            self.decode_cache.generated = 0
+            graph = capture()
+            replay, long_graph = graph.replay, None
         for i in range(max_new_tokens):
             if eos_t.numel():
                 alive &= ~torch.isin(token, eos_t)
@@ -128,7 +136,12 @@ class TriAttention:
             if i + 1 == max_new_tokens:
                 break
             if replay is not None:
+                if long_graph is None and self.decode_cache.tail_rows() > LONG_TAIL_ROWS:
+                    # A graph replays the merge kernel chosen at capture: from here on the one for long tails.
+                    long_graph = capture(graph.pool())
+                    replay = long_graph.replay
                 replay()
+                self.decode_cache.generated += 1
                 token = tok[:, 0].clone()
             else:
                 position = torch.full((batch, 1), ids.shape[1] + i, device=device)
