@@ -70,6 +70,9 @@ def test_generate_cuda_graph_matches_eager():
     assert graph == eager
     stop = eager[0][4]
     assert engine.generate(ids, 12, eos={stop}, cuda_graph=True) == engine.generate(ids, 12, eos={stop})
+    # A longer generation is captured with the merge kernel for long tails (the short one above): same tokens again.
+    longer = TriAttention(model, per_kv_head(["int8", "int4"], 2), max_new_tokens=24)
+    assert longer.generate(ids, 24, eos=(), cuda_graph=True) == longer.generate(ids, 24, eos=())
 
 
 @torch.inference_mode()

@@ -188,6 +188,7 @@ class DecodeCache:
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.exchange = exchange
         self.reserve, self.generated, self.fold_buffers = -(-int(fold_tail) // FOLD_KEYS), 0, {}
+        self.hint_rows = None
         if self.reserve and (split_group is not None or split is not None or max_tail < FOLD_KEYS):
             raise ValueError("fold_tail needs max_tail >= 64 and no split_group")
         if split_group is not None:
@@ -465,6 +466,8 @@ class DecodeCache:
     def tail_rows(self):
         """Rows in the BF16 tails at the next call, the token it appends included (host-side count: the device keeps
         its own in ``step``)."""
+        if self.hint_rows is not None:      # set by a caller that captures the step in a CUDA graph
+            return self.hint_rows
         return (self.generated % FOLD_KEYS if self.reserve else self.generated) + 1
 
     def advance(self):

@@ -104,29 +104,27 @@ class TriAttention:
                 pos.add_(1)
                 self.decode_cache.advance()
 
-            # One eager run on a side stream first (library workspaces, lazy initialisation).  It appends this token's
-            # K / V to the tails at the current step index, which the captured step then simply writes again; the
-            # counters it moved are put back.
-            side = torch.cuda.Stream(device)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step()
-                tok.copy_(token[:, None])
-                pos.sub_(1)
-                self.decode_cache.step.sub_(1)
-            torch.cuda.current_stream().wait_stream(side)
-
-            def capture(pool=None):
-                # Capturing runs the host side of step() without its device side: put the host's token count back.
-                made, graph = self.decode_cache.generated, torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, pool=pool):
+            # A graph replays the merge kernel chosen at capture, whatever the tail has grown to: the one for short tails
+            # only where the whole generation is short.
+            # One eager run on a side stream first (library workspaces, lazy initialisation, the kernels loaded).  It
+            # appends this token's K / V to the tails at the current step index, which the captured step then simply
+            # writes again; the counters it moved are put back.
+            self.decode_cache.hint_rows = 1 if max_new_tokens <= 2 * LONG_TAIL_ROWS else -1
+            try:
+                side = torch.cuda.Stream(device)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
                     step()
-                self.decode_cache.generated = made
-                return graph
-
-            self.decode_cache.generated = 0
-            graph = capture()
-            replay, long_graph = graph.replay, None
+                    tok.copy_(token[:, None])
+                    pos.sub_(1)
+                    self.decode_cache.step.sub_(1)
+                torch.cuda.current_stream().wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+            finally:
+                self.decode_cache.hint_rows = None
+            replay = graph.replay
         for i in range(max_new_tokens):
             if eos_t.numel():
                 alive &= ~torch.isin(token, eos_t)
@@ -136,12 +134,7 @@ class TriAttention:
             if i + 1 == max_new_tokens:
                 break
             if replay is not None:
-                if long_graph is None and self.decode_cache.tail_rows() > LONG_TAIL_ROWS:
-                    # A graph replays the merge kernel chosen at capture: from here on the one for long tails.
-                    long_graph = capture(graph.pool())
-                    replay = long_graph.replay
                 replay()
-                self.decode_cache.generated += 1
                 token = tok[:, 0].clone()
             else:
                 position = torch.full((batch, 1), ids.shape[1] + i, device=device)
