@@ -169,6 +169,16 @@ def test_long_tail_merge_kernel_gives_the_same_bits(module, monkeypatch, fused):
     module.decode_tail_hint(-1)
     want = oracle_steps(k[0], v[0], bands, qd[0], kd[0], vd[0], steps, max_tail=128)
     assert_fp_close(as_counted[0], orc.to_bf16(want), "70-row tail")
+    # Past the 256 rows that the unrolled kernel copies into shared memory (the rest it reads where they lie), and into
+    # the saturated tail: 290 steps on a tail of at most 280 rows.
+    qd, kd, vd = make_inputs(hq, hk, 290, seed=75, batch=2)
+    runs = []
+    for rows in (1, 1000):
+        monkeypatch.setattr(DecodeCache, "tail_rows", lambda self: rows)
+        runs.append(product_decode(module, q, k, v, bands, qd, kd, vd, steps=290, max_tail=280, fused=fused)[0])
+    monkeypatch.undo()
+    module.decode_tail_hint(-1)
+    assert np.array_equal(runs[0], runs[1])
 
 
 def test_tail_saturates(module):

@@ -43,9 +43,12 @@ struct OutputGather {
 __device__ __forceinline__ int64_t gather_flag_offset_bytes(int64_t rows_total) { return (2 * rows_total * D * 2 + 63) / 64 * 64; }
 // Two instantiations, the same arithmetic in the same order: LongTail = false for steps whose BF16 tail has a few rows
 // (row loops not unrolled: 5 us per step less at one row, 100 us more at 256 rows), LongTail = true for the rest (row
-// loops unrolled; 3 us ahead from 16 rows on).  The host picks one per launch from the caller's hint
-// (tri_decode_tail_hint); a separate kernel and not a branch, because any more code inside this kernel made its one-row
-// case slower.
+// loops unrolled; 3 us ahead from 16 rows on; the tail's first StagedTailRows V rows copied into dynamic shared memory
+// by the whole CTA while the scores are computed, so that the g warps that walk them in order do not each fetch them
+// row by row).  The host picks one per launch from the caller's hint (tri_decode_tail_hint); a separate kernel and not
+// a branch, because any more code inside this kernel made its one-row case slower.
+constexpr int StagedTailRows = 256;
+constexpr int StagedTailBytes = StagedTailRows * D * 2;
 template <bool LongTail>
 __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float* pm, const float* pl, const float* po,
     int64_t ml_stride, int64_t o_stride, SplitExchange xchg, OutputGather gather, const int2* unit_slots, int slot_limit,
@@ -75,6 +78,10 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     kt[prior * tst + tid] = kc[tid];
     vt[prior * tst + tid] = vc[tid];
   }
+  extern __shared__ __align__(16) uint8_t staged_rows[];
+  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(staged_rows);
+  int staged = 0;
+  if constexpr (LongTail) staged = stage_tail_rows(vs, vt, tst, vc, prior, tail, StagedTailRows, tid, MergeThreads);
   // tail scores for all heads of the group in one pass over the tail's K rows
   unit_tail_scores<LongTail ? RowsLong : RowsShort>(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
                              sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
@@ -96,6 +103,7 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     __syncthreads();
     if (exchange_failed) {
       if (tid == 0) atomicCAS(err, ErrNone, ErrBarrierTimeout);
+      if constexpr (LongTail) stage_tail_wait();   // no copy in flight when the CTA leaves
       return;
     }
     if (tid == 0) xchg.seen[unit] = epoch;
@@ -103,11 +111,12 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     const int64_t ug = (int64_t)xchg.units * MaxGroup;
     pm = block; pl = block + ug; po = block + 2 * ug;
   }
-  __syncthreads();            // the tail scores of all warps are in shared memory; then warp r merges Q head r
+  if constexpr (LongTail) stage_tail_wait();
+  __syncthreads();            // the tail scores of all warps (and the staged rows) are in shared memory; then warp r merges Q head r
   if (gather.world == 0) {
     if (warp < g)
       merge_head_by_warp<LongTail ? RowsLong : RowsShort>(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
-                                   vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane);
+                                   vstat + (int64_t)unit * StatFloats, out + b * osb + (int64_t)(kh * g + warp) * osh, lane, vs, staged);
     return;
   }
   // unit sharding: the row is computed into shared memory once and stored into every GPU's full output tensor
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
   const int epoch = gather.sync[1] + 1;          // read by every CTA before the last one to finish advances it
   if (warp < g)
     merge_head_by_warp<LongTail ? RowsLong : RowsShort>(pm, pl, po, (int64_t)sl.x * MaxGroup + warp, ml_stride, o_stride, sl.y, ts[warp], tail, prior, vt, tst, vc,
-                                 vstat + (int64_t)unit * StatFloats, rows[warp], lane);
+                                 vstat + (int64_t)unit * StatFloats, rows[warp], lane, vs, staged);
   __syncthreads();
   const int64_t row0 = (int64_t)(epoch & 1) * gather.rows_total + gather.unit_row[unit];
   for (int i = tid; i < gather.world * g * (D / 8); i += MergeThreads) {   // 16-byte pieces: peer, head row, piece
@@ -237,6 +246,7 @@ static int configure_decode() {
   TRI_CHECK(device != -2, "decode: no current CUDA device");
   if (device >= 0) {
     TRI_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeShared), "decode");
+    TRI_CUDA(cudaFuncSetAttribute(decode_merge_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, StagedTailBytes), "decode");
     configured.mark(device);
   }
   return TRI_OK;
@@ -293,10 +303,10 @@ static cudaError_t launch_merge_as(const DecodeCall& c, const float* pm, const f
                                    SplitExchange xchg, OutputGather gather) {
   const dim3 grid(c.batch * c.heads_kv);
   if (chained)
-    return launch_chained(decode_merge_kernel<LongTail>, grid, dim3(MergeThreads), 0, s, pm, pl, po, ml_stride, o_stride, xchg, gather,
+    return launch_chained(decode_merge_kernel<LongTail>, grid, dim3(MergeThreads), LongTail ? StagedTailBytes : 0, s, pm, pl, po, ml_stride, o_stride, xchg, gather,
                           unit_slots, slot_limit, c.vstat, c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur,
                           c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q, c.heads_kv, c.max_tail, c.sm_log2, c.err);
-  decode_merge_kernel<LongTail><<<grid, MergeThreads, 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots, slot_limit, c.vstat,
+  decode_merge_kernel<LongTail><<<grid, MergeThreads, LongTail ? StagedTailBytes : 0, s>>>(pm, pl, po, ml_stride, o_stride, xchg, gather, unit_slots, slot_limit, c.vstat,
       c.kstat, c.q, c.qsb, c.qsh, c.tail_k, c.tail_v, c.tsu, c.tst, c.kcur, c.vcur, c.csb, c.csh, c.step, c.out, c.osb, c.osh, c.heads_q,
       c.heads_kv, c.max_tail, c.sm_log2, c.err);
   return cudaSuccess;
@@ -431,6 +441,7 @@ extern "C" int tri_decode_merge(const void* q, int64_t q_stride_b, int64_t q_str
     int heads_kv, int max_tail, double scale, int* device_error, void* stream) {
   const int prompt = 1;
   TRI_DECODE_COMMON_CHECKS("decode_merge");
+  if (configure_decode() != TRI_OK) return TRI_ERR_CUDA;
   SplitExchange xchg{};
   if (exchange_buffer != nullptr) {
     TRI_CHECK(present && seen && world >= 1 && world <= 64 && aligned16(exchange_buffer), "decode_merge: exchange group");

@@ -285,15 +285,34 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
   }
 }
 
+// Copy of the first min(tail, limit) rows of a unit's tail (row t < prior from the tail buffer, row `prior` = this step's
+// row from the caller's tensor) into shared memory, D elements per row, by asynchronous 8-byte copies of all `threads`
+// calling threads (the alignment the row loops assume anyway); returns the number of rows.  The copies are complete for
+// the CTA after stage_tail_wait() and a barrier.
+__device__ __forceinline__ int stage_tail_rows(__nv_bfloat16* dst, const __nv_bfloat16* rows, int64_t tst, const __nv_bfloat16* current,
+                                               int prior, int tail, int limit, int tid, int threads) {
+  const int n = min(tail, limit);
+  for (int i = tid; i < n * (D / 4); i += threads) {
+    const int t = i / (D / 4), piece = i % (D / 4);
+    const __nv_bfloat16* src = (t < prior ? rows + (int64_t)t * tst : current) + piece * 4;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst + t * D + piece * 4)), "l"(src) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  return n;
+}
+__device__ __forceinline__ void stage_tail_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // One warp merges one Q head: nsplit partials at pm[first + s * ml_stride], pl likewise, po[first * 128 + s * o_stride + ch]
 // (a lane holds 4 of the 128 channels), the tail scores of the head in ts_row[0 .. tail) (turned into weights in place),
 // the tail's V rows, and writes the head's output row.  Partials are read past L1 (they may come from other CTAs of the
 // same launch or from other GPUs), four splits' loads in flight at a time; the sums run in split order.
-// Rows: as for unit_tail_scores.
+// Rows: as for unit_tail_scores.  RowsLong also takes the first `staged` V rows of the tail from a copy in shared memory
+// (vs, D elements per row; stage_tail_rows), the rest from where they lie.
 template <int Rows = RowsAny>
 __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float* pl, const float* po, int64_t first,
     int64_t ml_stride, int64_t o_stride, int nsplit, float* ts_row, int tail, int prior, const __nv_bfloat16* vt, int64_t tst,
-    const __nv_bfloat16* vc, const float* vstat_unit, __nv_bfloat16* out_row, int lane) {
+    const __nv_bfloat16* vc, const float* vstat_unit, __nv_bfloat16* out_row, int lane, const __nv_bfloat16* vs = nullptr,
+    int staged = 0) {
   // The first four splits' (m, l, o) are requested at once, before the maximum is known: their addresses depend on
   // nothing that is computed here, so the merge pays one trip to the second-level cache instead of two (a unit seldom
   // has more than four splits).
@@ -338,20 +357,23 @@ __device__ __forceinline__ void merge_head_by_warp(const float* pm, const float*
   const float4 scale = *reinterpret_cast<const float4*>(vstat_unit + D + lane * 4);
   acc[0] = acc[0] * scale.x + total * mean.x; acc[1] = acc[1] * scale.y + total * mean.y;
   acc[2] = acc[2] * scale.z + total * mean.z; acc[3] = acc[3] * scale.w + total * mean.w;
-  const auto row = [&](int t) {
+  const auto add = [&](int t, const __nv_bfloat16* v) {
     const float e = ts_row[t];
-    const uint2 raw = *reinterpret_cast<const uint2*>((t < prior ? vt + (int64_t)t * tst : vc) + lane * 4);
+    const uint2 raw = *reinterpret_cast<const uint2*>(v + lane * 4);
     const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
     const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
     total += e;
     acc[0] = fmaf(e, v01.x, acc[0]); acc[1] = fmaf(e, v01.y, acc[1]); acc[2] = fmaf(e, v23.x, acc[2]); acc[3] = fmaf(e, v23.y, acc[3]);
   };
+  const auto row = [&](int t) { add(t, t < prior ? vt + (int64_t)t * tst : vc); };
   if constexpr (Rows == RowsShort) {
 #pragma unroll 1
     for (int t = 0; t < tail; ++t) row(t);
   } else if constexpr (Rows == RowsLong) {
+#pragma unroll 8
+    for (int t = 0; t < staged; ++t) add(t, vs + t * D);
 #pragma unroll 16
-    for (int t = 0; t < tail; ++t) row(t);
+    for (int t = staged; t < tail; ++t) row(t);
   } else {
     for (int t = 0; t < tail; ++t) row(t);
   }
