@@ -295,7 +295,8 @@ int tri_decode_static(const void* q, int64_t q_stride_b, int64_t q_stride_h, con
  * included); negative = not known, the state a thread starts in.  A hint: it picks between two instantiations of the
  * merge kernel with the same arithmetic in the same order (bit-equal results) for the separate merge launch of tri_decode
  * (unit_done NULL), tri_decode_static and tri_decode_merge.  Up to 8 rows the one whose row loops are not unrolled runs
- * (5 us per step less at one row, 100 us more at 256 rows); above 8 rows, or without a hint, the unrolled one.  Under
+ * (4 us per step less at one row, 120 us more at 256 rows); above 8 rows, or without a hint, the one that unrolls them
+ * and copies the tail rows into 64 KB of dynamic shared memory first.  Under
  * stream capture the instantiation chosen at capture time is the one replayed.  No counterpart in the reference (one merge
  * kernel, triattention/kernels/cuda/decode.cu). */
 int tri_decode_tail_hint(int rows);

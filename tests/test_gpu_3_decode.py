@@ -146,14 +146,16 @@ def test_fused_merge_matches_two_launches(module, ctas):
     assert_fp_close(one, two, f"one launch vs two, {ctas} CTAs")
 
 
-@pytest.mark.parametrize("fused", [True, False], ids=["one-launch", "two-launches"])
-def test_long_tail_merge_kernel_gives_the_same_bits(module, monkeypatch, fused):
+@pytest.mark.parametrize("fused,hq,hk", [(True, 8, 2), (False, 8, 2), (False, 6, 2), (False, 7, 1), (False, 16, 2)],
+                         ids=["one-launch", "two-launches", "group-of-3", "group-of-7", "group-of-8"])
+def test_long_tail_merge_kernel_gives_the_same_bits(module, monkeypatch, fused, hq, hk):
     """The merge kernel has a second instantiation for long BF16 tails (row loops unrolled), which the host picks from
     its count of generated tokens (tri_decode_tail_hint).  70 steps with the hint as DecodeCache gives it (plain kernel up
     to 8 rows, unrolled after), with the plain kernel throughout and with the unrolled one throughout: the same bits,
-    and the oracle's values."""
-    hq, hk, t, steps = 8, 2, 300, 70
-    bands = np.asarray([[INF, INF]] * 4 + [[2, 6]] * 4, np.int64)
+    and the oracle's values.  The unrolled kernel reduces the scores of four Q heads of a group at a time, so groups
+    of 3, 4, 7 and 8 heads are run."""
+    t, steps = 300, 70
+    bands = np.asarray([[INF, INF]] * (hq // 2) + [[2, 6]] * (hq - hq // 2), np.int64)
     q, k, v = make_inputs(hq, hk, t, seed=73, batch=2)
     qd, kd, vd = make_inputs(hq, hk, steps, seed=74, batch=2)
     hints = []

@@ -43,9 +43,9 @@ struct OutputGather {
 __device__ __forceinline__ int64_t gather_flag_offset_bytes(int64_t rows_total) { return (2 * rows_total * D * 2 + 63) / 64 * 64; }
 // Two instantiations, the same arithmetic in the same order: LongTail = false for steps whose BF16 tail has a few rows
 // (row loops not unrolled: 5 us per step less at one row, 100 us more at 256 rows), LongTail = true for the rest (row
-// loops unrolled; 3 us ahead from 16 rows on; the tail's first StagedTailRows V rows copied into dynamic shared memory
-// by the whole CTA while the scores are computed, so that the g warps that walk them in order do not each fetch them
-// row by row).  The host picks one per launch from the caller's hint (tri_decode_tail_hint); a separate kernel and not
+// loops unrolled; 3 us ahead from 16 rows on; the tail's first StagedTailRows K rows, and after the scores its V rows,
+// copied into dynamic shared memory by the whole CTA in one go, so that a row costs no trip to memory of its own and
+// the g warps that walk the V rows in order do not each fetch them).  The host picks one per launch from the caller's hint (tri_decode_tail_hint); a separate kernel and not
 // a branch, because any more code inside this kernel made its one-row case slower.
 constexpr int StagedTailRows = 256;
 constexpr int StagedTailBytes = StagedTailRows * D * 2;
@@ -79,12 +79,20 @@ __global__ void __launch_bounds__(MergeThreads) decode_merge_kernel(const float*
     vt[prior * tst + tid] = vc[tid];
   }
   extern __shared__ __align__(16) uint8_t staged_rows[];
-  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(staged_rows);
+  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(staged_rows);   // the tail's K rows first, then its V rows
   int staged = 0;
-  if constexpr (LongTail) staged = stage_tail_rows(vs, vt, tst, vc, prior, tail, StagedTailRows, tid, MergeThreads);
+  if constexpr (LongTail) {
+    staged = stage_tail_rows(vs, kt, tst, kc, prior, tail, StagedTailRows, tid, MergeThreads);
+    stage_tail_wait();
+    __syncthreads();
+  }
   // tail scores for all heads of the group in one pass over the tail's K rows
   unit_tail_scores<LongTail ? RowsLong : RowsShort>(q + b * qsb + (int64_t)(kh * g) * qsh, qsh, g, kstat + (int64_t)unit * StatFloats, kt, tst, kc, prior, tail,
-                             sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane);
+                             sm_log2, &ts[0][0], 1024, warp, MergeWarps, lane, vs, staged);
+  if constexpr (LongTail) {
+    __syncthreads();          // every warp has read its K rows
+    stage_tail_rows(vs, vt, tst, vc, prior, tail, StagedTailRows, tid, MergeThreads);
+  }
   grid_dependency_wait();     // the split pass has written all partials
   __shared__ int exchange_failed;
   if (xchg.world > 0) {

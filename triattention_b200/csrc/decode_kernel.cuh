@@ -240,14 +240,16 @@ struct MergeArgs {
 
 // Tail scores of `nh` Q heads (rows qrows + i * qsh, i < nh) against the unit's tail, one pass over the tail's K rows:
 // the `warps` calling warps split the rows, a lane holds 4 features of the row and of each head's q.  ts[i * ts_stride + t].
+// (RowsLong also takes the first `staged` K rows from a copy in shared memory, ks, D elements per row: stage_tail_rows.)
 // Rows picks how the row loop is compiled; the sums run in row order every way, so all give the same bits.  RowsShort: not
 // unrolled, the first row comes back soonest (a step with a tail of a few rows; a long tail is then a chain of trips to
 // memory).  RowsLong: unrolled so that several rows' loads are in flight.  RowsAny: left to the compiler (in between).
 enum { RowsAny = 0, RowsShort = 1, RowsLong = 2 };
+template <int V> struct IntConstant { static constexpr int value = V; };
 template <int Rows = RowsAny>
 __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int64_t qsh, int nh, const float* kmean_unit,
     const __nv_bfloat16* kt, int64_t tst, const __nv_bfloat16* kc, int prior, int tail, float sm_log2, float* ts, int ts_stride,
-    int warp, int warps, int lane) {
+    int warp, int warps, int lane, const __nv_bfloat16* ks = nullptr, int staged = 0) {
   float qv[MaxGroup][4], kmean[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) kmean[i] = kmean_unit[lane * 4 + i];
@@ -278,8 +280,37 @@ __device__ __forceinline__ void unit_tail_scores(const __nv_bfloat16* qrows, int
 #pragma unroll 1
     for (int t = warp; t < tail; t += warps) row(t);
   } else if constexpr (Rows == RowsLong) {
+    // Four heads' lane sums reduced together: after the exchange over 16 lanes a lane carries two heads, after the one
+    // over 8 lanes one, so a row costs six shuffles per four heads instead of twenty, in one chain of five, with no
+    // branch between rows.  Every sum adds the same two operands as the butterfly of the plain loop does in lane 0
+    // (addition commutes, so all lanes of a butterfly hold the same bits): the scores are bit-equal.
+    const bool up16 = lane & 16, up8 = lane & 8;
+    const int mine = ((lane >> 3) & 1) + 2 * ((lane >> 4) & 1);
+    const auto quad = [&](int t, const float (&kd)[4], auto first) {
+      constexpr int r0 = decltype(first)::value;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[j] = fmaf(qv[r0 + j][i], kd[i], v[j]);
+      }
+      const float w0 = (up16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, up16 ? v[0] : v[2], 16);
+      const float w1 = (up16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, up16 ? v[1] : v[3], 16);
+      float x = (up8 ? w1 : w0) + __shfl_xor_sync(0xffffffffu, up8 ? w0 : w1, 8);
+#pragma unroll
+      for (int o = 4; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+      if ((lane & 7) == 0 && r0 + mine < nh) ts[(r0 + mine) * ts_stride + t] = x * sm_log2;
+    };
 #pragma unroll 4
-    for (int t = warp; t < tail; t += warps) row(t);
+    for (int t = warp; t < tail; t += warps) {   // the first `staged` rows from their copy in shared memory (ks)
+      const __nv_bfloat16* kv = (t < staged ? ks + t * D : t < prior ? kt + t * tst : kc) + lane * 4;
+      float kd[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kd[i] = __bfloat162float(kv[i]) - kmean[i];
+      quad(t, kd, IntConstant<0>{});
+      if (nh > 4) quad(t, kd, IntConstant<4>{});
+    }
   } else {
     for (int t = warp; t < tail; t += warps) row(t);
   }
