@@ -18,6 +18,8 @@ After that timed region, outside it, the same line gets secondary records (each 
               nominal dense INT8 peak and against i8_peak, and the KV-cache write in GB/s            (1 GPU runs)
   calibration the reference's calibration grid (86 uniform maps) on one layer in one pass (Prefill.sweep) against one full
               prefill per grid point, the loop of the reference's tool                               (1 GPU runs)
+  long_tail   the benchmark's decode step with 16, 64 and 256 rows in the BF16 tail of generated tokens (--tail-rows N
+              measures the whole line at one such length)                                           (1 GPU runs)
   i8_peak     what back-to-back tcgen05 kind::i8 MMAs (M128 N256 K32, operands in shared memory) sustain on this GPU
   ref_ext     the reference's own CUDA extension (its sm_80 source compiled for sm_100, what a B200 runs today) timed
               on the same inputs: decode as 32 sequential batch-1 calls, prefill as 2 calls           (1 GPU runs)
@@ -722,6 +724,25 @@ def run_model(args):
                           time_inside_the_attention_library=library, clocks=clocks.summary())))
 
 
+def grow_tail(cache, rows, qd, kd, vd, scale, out):
+    """Decode steps with advance() until the next step's BF16 tail holds `rows` rows (the token it appends included)."""
+    while cache.generated + 1 < rows:
+        cache(0, qd, kd, vd, scale, out=out)
+        cache.advance()
+
+
+def measure_long_tail(cache, qd, kd, vd, scale, out, ms_one_row, lengths=(16, 64, 256), steps=100):
+    """The benchmark's decode step later in a generation: the same cache, with 16, 64 and 256 rows in the BF16 tail of
+    generated tokens instead of one (the merge kernel reads them exactly; above 8 rows the host picks its long-tail
+    instantiation).  CUDA events over `steps` steps each; the tail is not advanced inside a timed region."""
+    record = {"us_per_step_by_tail_rows": {"1": ms_one_row * 1e3}, "steps": steps, "workload": "decode C2, one layer-step"}
+    for rows in lengths:
+        grow_tail(cache, rows, qd, kd, vd, scale, out)
+        warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), 32, seconds=0.0)
+        record["us_per_step_by_tail_rows"][str(rows)] = timed(lambda i: cache(0, qd, kd, vd, scale, out=out), steps, None) / steps * 1e3
+    return record
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--workload", default="decode", choices=["decode", "decode-long", "prefill", "model"],
@@ -742,6 +763,9 @@ def main():
     parser.add_argument("--split", action="store_true",
                         help="with --gpus N: the SAME sequences on every GPU, every unit's tile range cut N ways (sequence "
                              "split, one all-gather of folded partials per step); strong scaling, a diagnostic")
+    parser.add_argument("--tail-rows", type=int, default=1,
+                        help="decode workloads: rows in the BF16 tail of generated tokens at the measured step (1..256; the "
+                             "benchmark value is quoted at 1, the first generated token)")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary records (prefill, i8_peak, ref_ext, sharded_c5, split) of the default workload")
     parser.add_argument("--batch", type=int, default=None,
@@ -801,6 +825,9 @@ def main():
     # region would leave the GPU idle for the milliseconds a fork takes, and the first timed steps would run on clocks
     # that had begun to drop (measured: 94.4 instead of 90.5 us per kernel launch over 20 timed steps).  Only the
     # samples taken from the start of the timed region on are summarised.
+    if not 1 <= args.tail_rows <= cache.max_tail:
+        raise SystemExit(f"--tail-rows must be in 1..{cache.max_tail}")
+    grow_tail(cache, args.tail_rows, qd, kd, vd, scale, out)
     with ClockSampler(local) as clocks:
         warmup_run = warm_up(lambda: cache(0, qd, kd, vd, scale, out=out), max(3, args.warmup, 300 if split else 0),
                              seconds=0.0 if split else 0.3)
@@ -843,6 +870,8 @@ def main():
     extras = {}
     if not args.no_extras and not long_case and not split and batch == CONFIG["batch"] and not args.fused_merge:
         # secondary records, outside the timed region of the benchmark value; the C2 cache is released first
+        if world == 1 and args.tail_rows == 1:
+            extras["long_tail"] = measure_long_tail(cache, qd, kd, vd, scale, out, ms_total / args.steps)
         del stepper, cache
         torch.cuda.empty_cache()
         extra_steps = max(5, min(args.steps, 20))
@@ -883,6 +912,8 @@ def main():
                 clocks=dict(clocks.summary(), untimed_steps_of_the_same_load_added_for_sampling=extra))
     if split:
         line["sequence_split"] = f"every unit's tile range cut over {world} GPUs; one all-gather of folded partials per step"
+    if args.tail_rows != 1:
+        line["tail_rows"] = f"{args.tail_rows} rows in the BF16 tail instead of 1: not the benchmark value"
     if batch != CONFIG["batch"]:
         line["reduced_case"] = f"batch {batch} instead of {CONFIG['batch']}: not a benchmark value"
     line.update(extras)
