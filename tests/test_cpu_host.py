@@ -344,3 +344,30 @@ def test_calibration_sample_loader(tmp_path):
     assert [n for _, n in samples] == [3, 1]
     assert samples[0][0][-3:] == [ord("w"), ord("x"), ord("y")] and samples[1][0][-1] == ord("q")
     assert len(samples[0][0]) > 3
+
+
+def test_tail_row_count_for_the_merge_kernel_hint():
+    """DecodeCache counts generated tokens on the host for tri_decode_tail_hint: the next call's tail holds one row more
+    than tokens generated so far, at most max_tail (the tail saturates), starts again at every fold of 64 rows, and a
+    caller that captures the step in a CUDA graph can pin the value."""
+    import torch
+    from triattention_b200.kernels.decode import DecodeCache
+    from triattention_b200.kernels.extension import LONG_TAIL_ROWS
+    cache = DecodeCache(None, 8)
+    cache.step = torch.zeros(1, dtype=torch.int64)
+    seen = []
+    for _ in range(12):
+        seen.append(cache.tail_rows())
+        cache.advance()
+    assert seen == [1, 2, 3, 4, 5, 6, 7, 8, 8, 8, 8, 8] and int(cache.step) == 12
+    folding = DecodeCache(None, 64, fold_tail=128)
+    folding.step = torch.zeros(1, dtype=torch.int64)
+    rows = []
+    for _ in range(130):
+        rows.append(folding.tail_rows())
+        folding.advance()
+    assert rows[:64] == list(range(1, 65)) and rows[64:128] == list(range(1, 65)) and rows[128:] == [1, 2]
+    cache.hint_rows = -1
+    assert cache.tail_rows() == -1
+    cache.hint_rows = None
+    assert cache.tail_rows() == 8 and 1 <= LONG_TAIL_ROWS < 64

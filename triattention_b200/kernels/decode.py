@@ -468,7 +468,7 @@ class DecodeCache:
         its own in ``step``)."""
         if self.hint_rows is not None:      # set by a caller that captures the step in a CUDA graph
             return self.hint_rows
-        return (self.generated % FOLD_KEYS if self.reserve else self.generated) + 1
+        return min((self.generated % FOLD_KEYS if self.reserve else self.generated) + 1, self.max_tail)
 
     def advance(self):
         self.generated += 1
