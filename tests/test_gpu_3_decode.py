@@ -302,9 +302,18 @@ def test_store_in_parts_equals_store_at_once(module):
         DecodeCache(module, max_tail=4).store(0, t, ops, table.host, kc[3:], vc[3:], table.bf16_kv, first_sequence=3, sequences=batch)
 
 
+@pytest.fixture(params=["merge-for-short-tails", "merge-for-long-tails"])
+def merge_kernel(request, monkeypatch):
+    """Runs a test once with the merge kernel that DecodeCache's row count picks (a few steps: the one for short tails)
+    and once with the one for long tails (no hint given), which takes its tail rows through shared memory."""
+    if request.param == "merge-for-long-tails":
+        monkeypatch.setattr(DecodeCache, "tail_rows", lambda self: -1)
+    return request.param
+
+
 @pytest.mark.parametrize("exchange", ["nccl", "peer"])
 @pytest.mark.parametrize("world,ctas", [(2, None), (3, 5), (8, None)])
-def test_sequence_split_emulated_on_one_gpu(module, world, ctas, exchange):
+def test_sequence_split_emulated_on_one_gpu(module, world, ctas, exchange, merge_kernel):
     """The sequence-split path without a process group: `world` caches each hold one part of every unit's tile range
     (what the ranks of a split group hold) and each runs its split pass with the in-kernel fold (tri_decode_partials).
     "nccl": the folded triples are stacked [rank][m | l | o] as an all-gather would leave them, and tri_decode_merge
@@ -361,7 +370,7 @@ def test_sequence_split_emulated_on_one_gpu(module, world, ctas, exchange):
     assert_fp_close(np.stack(outs, 1), whole, f"sequence split over {world} parts vs whole units")
 
 
-def test_exchange_wait_runs_out_without_hanging(module):
+def test_exchange_wait_runs_out_without_hanging(module, merge_kernel):
     """The consumer's wait is bounded: a merge whose peers never deliver (nothing sets the flags) gives up after its time
     limit, reports device error 1 and leaves the context usable."""
     hq, hk, t, batch = 4, 2, 300, 1
@@ -385,7 +394,7 @@ def test_exchange_wait_runs_out_without_hanging(module):
 
 
 @pytest.mark.parametrize("layout", ["two-parts", "eight-parts"])
-def test_output_gather_by_peer_stores_emulated_on_one_gpu(module, layout):
+def test_output_gather_by_peer_stores_emulated_on_one_gpu(module, layout, merge_kernel):
     """Units sharded over two (or eight) "ranks" held by this process on one GPU: each part's merge kernel stores its output rows into
     the full output tensor of both parts (their gather buffers, here ordinary device memory), the last CTA raises the
     part's flag in both, and the wait kernel of each part then finds both flags set (all producers are launched before any
